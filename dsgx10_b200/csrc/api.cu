@@ -1,0 +1,176 @@
+// The C ABI (include/dsgx_moe.h): argument checks, workspace carving, kernel launches.  No allocation on the hot
+// calls; every failure is a status code.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dsgx {
+
+static std::atomic<int> g_last_cuda{0};
+static int cuda_fail(cudaError_t e) {
+  g_last_cuda.store((int)e);
+  return DSGX_ERR_CUDA;
+}
+
+int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+  }
+  return n[dev];
+}
+
+static size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t decode_ws_bytes(int H, int I) {
+  const size_t HB = H / 128, IB = I / 128;
+  size_t n = 256;
+  n += al256(HB * kActBlk);
+  n += al256((size_t)kMaxSlots * 8 * I * 2);
+  n += al256((size_t)kMaxSlots * IB * kActBlk);
+  n += al256((size_t)kMaxSlots * (H / 16) * 128 * 4);
+  n += al256((size_t)kMaxSlots * IB * 4);
+  n += al256((size_t)(H / 16) * 4);
+  return n;
+}
+DecodeWs decode_ws_carve(void* ws, int H, int I) {
+  const size_t HB = H / 128, IB = I / 128;
+  char* p = reinterpret_cast<char*>(ws);
+  DecodeWs w;
+  w.status = reinterpret_cast<int*>(p), p += 256;
+  w.xq = reinterpret_cast<uint8_t*>(p), p += al256(HB * kActBlk);
+  w.h = reinterpret_cast<__nv_bfloat16*>(p), p += al256((size_t)kMaxSlots * 8 * I * 2);
+  w.hq = reinterpret_cast<uint8_t*>(p), p += al256((size_t)kMaxSlots * IB * kActBlk);
+  w.ypick = reinterpret_cast<float*>(p), p += al256((size_t)kMaxSlots * (H / 16) * 128 * 4);
+  w.cnt_h = reinterpret_cast<int*>(p), p += al256((size_t)kMaxSlots * IB * 4);
+  w.cnt_y = reinterpret_cast<int*>(p);
+  return w;
+}
+
+static int check_shape(const dsgx_moe_shape* s) {
+  if (!s) return DSGX_ERR_ARG;
+  if (s->fmt == DSGX_FMT_NVFP4 || s->fmt == DSGX_FMT_RETIRED) return DSGX_ERR_FORMAT;
+  if (s->fmt != DSGX_FMT_FP8 && s->fmt != DSGX_FMT_INT4) return DSGX_ERR_FORMAT;
+  if (s->E < 1 || s->E > 512 || s->topk < 1 || s->topk > kMaxTopK || s->topk > s->E) return DSGX_ERR_SHAPE;
+  if (s->H < 128 || s->I < 128 || s->H % 128 || s->I % 128) return DSGX_ERR_SHAPE;
+  if (s->n_group < 1 || s->n_group > 32 || s->E % s->n_group || s->topk_group < 1 || s->topk_group > s->n_group)
+    return DSGX_ERR_SHAPE;
+  if (s->n_group > 1 && (s->E / s->n_group < 2 || s->topk > s->topk_group * (s->E / s->n_group))) return DSGX_ERR_SHAPE;
+  if (s->score_fn != DSGX_SCORE_SIGMOID && s->score_fn != DSGX_SCORE_SOFTMAX) return DSGX_ERR_SHAPE;
+  if (s->e_lo < 0 || s->e_hi > s->E || s->e_lo > s->e_hi) return DSGX_ERR_SHAPE;
+  if (s->fmt == DSGX_FMT_FP8 && (s->H > 4096 || s->I > 4096 || s->H % 256 || s->I % 256)) return DSGX_ERR_SHAPE;
+  if (s->fmt == DSGX_FMT_INT4 && (s->H % 512 || s->I % 512)) return DSGX_ERR_SHAPE;
+  return DSGX_OK;
+}
+
+}  // namespace dsgx
+
+using namespace dsgx;
+
+extern "C" {
+
+int dsgx_last_cuda_error(void) { return g_last_cuda.load(); }
+
+const char* dsgx_status_name(int s) {
+  switch (s) {
+    case DSGX_OK: return "ok";
+    case DSGX_ERR_ARG: return "bad argument";
+    case DSGX_ERR_FORMAT: return "unknown or refused expert format";
+    case DSGX_ERR_SHAPE: return "unsupported shape";
+    case DSGX_ERR_CUDA: return "CUDA error";
+    case DSGX_ERR_DEVICE_WAIT: return "a bounded device wait ran out";
+    case DSGX_ERR_UNSUPPORTED: return "unsupported";
+  }
+  return "unknown status";
+}
+
+int dsgx_router_logits(const void* x, const float* wr, int M, int H, int E, float* logits, void* stream) {
+  if (!x || !wr || !logits || M < 1) return DSGX_ERR_ARG;
+  if (H < 128 || H % 128 || E < 1) return DSGX_ERR_SHAPE;
+  if (((uintptr_t)x & 7) || ((uintptr_t)wr & 15)) return DSGX_ERR_ARG;
+  cudaError_t e = launch_router_logits(reinterpret_cast<const __nv_bfloat16*>(x), wr, M, H, E, logits,
+                                       (cudaStream_t)stream, true);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+int dsgx_route(const dsgx_moe_shape* s, const float* logits, const float* bias, int M, int32_t* idx, float* w,
+               void* stream) {
+  const int rc = check_shape(s);
+  if (rc) return rc;
+  if (!logits || !idx || !w || M < 1) return DSGX_ERR_ARG;
+  RouteParams p{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
+  cudaError_t e = launch_route(p, logits, bias, M, idx, w, (cudaStream_t)stream, true);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+size_t dsgx_sort_ws_bytes(int T, int topk, int E) { return sort_ws_bytes(T, topk, E); }
+
+int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
+                   int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* ws, void* stream) {
+  if (!idx || !counts || !offsets || !perm_tok || !perm_slot || !pos_of || !row_order || !ws) return DSGX_ERR_ARG;
+  if (T < 0 || topk < 1 || topk > kMaxTopK || E < 1 || E > 512) return DSGX_ERR_SHAPE;
+  if (T == 0) {
+    cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * E, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(offsets, 0, sizeof(int) * (E + 1), (cudaStream_t)stream);
+    return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+  }
+  cudaError_t e = launch_sort_pack(idx, T, topk, E, counts, offsets, perm_tok, perm_slot, pos_of, row_order, ws,
+                                   (cudaStream_t)stream);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+size_t dsgx_decode_ws_bytes(const dsgx_moe_shape* s) {
+  if (check_shape(s)) return 0;
+  return decode_ws_bytes(s->H, s->I);
+}
+
+int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* x, const int32_t* idx, const float* w,
+                    int M, void* ws, float* yr, float* ys, void* stream, const dsgx_decode_cfg* cfg) {
+  const int rc = check_shape(s);
+  if (rc) return rc;
+  if (!L || !x || !idx || !w || !ws || !yr) return DSGX_ERR_ARG;
+  if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
+  if (L->fmt != s->fmt) return DSGX_ERR_FORMAT;
+  if (!L->pool || !L->desc) return DSGX_ERR_ARG;
+  if (((uintptr_t)L->pool & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
+  const bool sh8 = L->sh.g != nullptr;
+  if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds)) return DSGX_ERR_ARG;
+  const dsgx_decode_cfg dflt = {0, 1, {0, 0, 0, 0, 0, 0}};
+  if (!cfg) cfg = &dflt;
+  if (s->fmt == DSGX_FMT_FP8) {
+    if (L->sh.bg || L->sh.bu || L->sh.bd) return DSGX_ERR_FORMAT;  // an FP8 layer's shared expert is FP8
+    if (sh8 && !ys && !cfg->ysum) return DSGX_ERR_ARG;
+    DecodeParams p;
+    p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
+    p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
+    p.idx = idx, p.w = w;
+    p.ws = decode_ws_carve(ws, s->H, s->I);
+    p.yr = yr, p.ys = ys, p.ysum = cfg->ysum;
+    cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0);
+    return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+  }
+  return DSGX_ERR_UNSUPPORTED;
+}
+
+int dsgx_finalize(const float* R, const float* S, int M, int H, void* out, int mode, void* stream) {
+  if (!R || !out || M < 1 || H < 1 || (mode != 0 && mode != 1)) return DSGX_ERR_ARG;
+  cudaError_t e = launch_finalize(R, S, M, H, reinterpret_cast<__nv_bfloat16*>(out), mode, (cudaStream_t)stream, true);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+int dsgx_ws_status(const void* ws) {
+  if (!ws) return DSGX_ERR_ARG;
+  int v = 0;
+  cudaError_t e = cudaMemcpy(&v, ws, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,387 @@
+// FP8 (e4m3, 128x128 block-scaled, W8A8-g128) expert step for 1..8 rows: an HBM-bound weight stream.
+//
+// Two persistent kernels, one CTA a SM, eight warps a CTA.  Every warp is its own producer and consumer: lane 0 issues
+// bulk async copies (the untiled TMA path) of the next chunks of its unit's two weight strips into the warp's private
+// ring in shared memory, an mbarrier per stage counts the bytes in, and the whole warp then feeds the chunk to
+// m16n8k32 e4m3 MMAs with the weights as the A operand (16 output channels x 32 k) and the quantised activations as B
+// (32 k x 8 rows).  One 128-k block is four MMAs into a fresh accumulator, promoted into the f32 sums with the
+// product of the block's weight scale and the row's activation scale.
+//
+//   k_up:   unit = (slot, 8 intermediate channels): A rows 0-7 = gate, rows 8-15 = up, so a lane ends with gate and up
+//           of the same (channel, row) and applies SwiGLU in place.  The 16th unit to finish a 128-group of h
+//           quantises the group for the down kernel (a ticket, no waiting).
+//   k_down: unit = (slot, 16 output channels); every pick's output is rounded to bf16, parked, and the last slot to
+//           finish an output tile adds the tile's picks in ascending expert id (a ticket again) and writes yr / ys.
+//
+// Slots: the sorted union of the rows' picked experts that this GPU owns, then the shared expert.  A row that did not
+// pick a slot's expert runs with routing weight 0: its h, and so its output, is exactly 0.
+//
+// Weight layout consumed as is: the reference's tile_fp8 ([N/8][K/128][32 lanes][32 B]; altar1
+// engine/experts/layout.h:108-119), so an 8-row strip of a matrix is one contiguous run of 8 K bytes.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dsgx {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kKCH = 2;  // 128-k blocks a stage and strip
+constexpr int kNST = 3;  // stages a warp
+constexpr int kUpStage = 2 * kKCH * 1024;
+constexpr int kDownStage = 2 * kKCH * 1024 + kKCH * kActBlk;
+
+struct SlotTab {
+  int nslots;  // routed slots
+  int ntot;    // + the shared expert's
+  int bad;
+  uint32_t bm[16];
+  int e[kMaxSlots];
+  float w[kMaxSlots][8];
+  const uint8_t* a[kMaxSlots];  // k_up: gate, k_down: down
+  const uint8_t* b[kMaxSlots];  // k_up: up
+  const float* sa[kMaxSlots];
+  const float* sb[kMaxSlots];
+};
+
+DSGX_DEV const float* desc_scales(const uint8_t* pool, const dsgx_mat_desc& d) {
+  return reinterpret_cast<const float*>(pool + ((uint64_t)d.rsv[0] | (uint64_t)d.rsv[1] << 32));
+}
+
+// The sorted union of the picks in [e_lo, e_hi) and every slot's pointers; DOWN selects the matrices.
+template <bool DOWN>
+DSGX_DEV void build_union(const DecodeParams& p, SlotTab& tab) {
+  const int tid = threadIdx.x;
+  if (tid < 16) tab.bm[tid] = 0;
+  if (tid == 0) tab.bad = 0;
+  for (int i = tid; i < kMaxSlots * 8; i += kThreads) (&tab.w[0][0])[i] = 0.f;
+  __syncthreads();
+  const int np = p.M * p.topk;
+  for (int i = tid; i < np; i += kThreads) {
+    const int e = p.idx[i];
+    if (e < 0 || e >= p.E) tab.bad = DSGX_ERR_ARG;
+    else if (e >= p.e_lo && e < p.e_hi) atomicOr(&tab.bm[e >> 5], 1u << (e & 31));
+  }
+  __syncthreads();
+  auto rank_of = [&](int e) {
+    int r = __popc(tab.bm[e >> 5] & ((1u << (e & 31)) - 1u));
+    for (int w = 0; w < (e >> 5); ++w) r += __popc(tab.bm[w]);
+    return r;
+  };
+  for (int e = tid; e < p.E; e += kThreads)
+    if ((tab.bm[e >> 5] >> (e & 31)) & 1) {
+      const int s = rank_of(e);
+      tab.e[s] = e;
+      const dsgx_mat_desc* d = p.desc + (size_t)e * 3;
+      if (DOWN) {
+        if (d[2].fmt != DSGX_FMT_FP8) tab.bad = DSGX_ERR_FORMAT;
+        tab.a[s] = p.pool + d[2].off, tab.sa[s] = desc_scales(p.pool, d[2]);
+        tab.b[s] = nullptr, tab.sb[s] = nullptr;
+      } else {
+        if (d[0].fmt != DSGX_FMT_FP8 || d[1].fmt != DSGX_FMT_FP8) tab.bad = DSGX_ERR_FORMAT;
+        tab.a[s] = p.pool + d[0].off, tab.sa[s] = desc_scales(p.pool, d[0]);
+        tab.b[s] = p.pool + d[1].off, tab.sb[s] = desc_scales(p.pool, d[1]);
+      }
+    }
+  if (tid == 0) {
+    int n = 0;
+    for (int w = 0; w < 16; ++w) n += __popc(tab.bm[w]);
+    tab.nslots = n;
+    const bool sh = p.sh.g != nullptr;
+    tab.ntot = n + (sh ? 1 : 0);
+    if (sh) {
+      tab.e[n] = -1;
+      if (DOWN) tab.a[n] = p.sh.d, tab.sa[n] = p.sh.ds, tab.b[n] = nullptr, tab.sb[n] = nullptr;
+      else tab.a[n] = p.sh.g, tab.sa[n] = p.sh.gs, tab.b[n] = p.sh.u, tab.sb[n] = p.sh.us;
+    }
+  }
+  for (int i = tid; i < np; i += kThreads) {
+    const int e = p.idx[i];
+    if (e >= p.e_lo && e < p.e_hi && e >= 0 && e < p.E) tab.w[rank_of(e)][i / p.topk] = p.w[i];
+  }
+  __syncthreads();
+  if (tab.bad) {  // refuse the routed work, keep the kernel well-defined
+    if (tid == 0) {
+      atomicCAS(p.ws.status, 0, tab.bad);
+      tab.ntot -= tab.nslots, tab.nslots = 0;
+      if (p.sh.g != nullptr) {
+        tab.e[0] = -1;
+        if (DOWN) tab.a[0] = p.sh.d, tab.sa[0] = p.sh.ds;
+        else tab.a[0] = p.sh.g, tab.sa[0] = p.sh.gs, tab.b[0] = p.sh.u, tab.sb[0] = p.sh.us;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// order position -> slot: the shared expert's units come first (they are the same every step)
+DSGX_DEV int ord_slot(const SlotTab& tab, int ord) {
+  return tab.ntot > tab.nslots ? (ord == 0 ? tab.nslots : ord - 1) : ord;
+}
+
+DSGX_DEV uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// One 128-k block: A rows 0-7 from strip a, rows 8-15 from strip b, B from the activation block.
+DSGX_DEV void block_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int lane) {
+  const uint4 a0 = lds128(a + 32 * lane), a1 = lds128(a + 32 * lane + 16);
+  const uint4 b0 = lds128(b + 32 * lane), b1 = lds128(b + 32 * lane + 16);
+  const uint4 x0 = lds128(act + 16 * lane), x1 = lds128(act + 512 + 16 * lane);
+  d[0] = d[1] = d[2] = d[3] = 0.f;
+  mma_e4m3(d, a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
+  mma_e4m3(d, a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
+  mma_e4m3(d, a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
+  mma_e4m3(d, a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+}
+
+// -------------------------------------------------------------------------------------------------------------- k_up
+__global__ void __launch_bounds__(kThreads, 1) k_up_fp8(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int HB = p.H / 128, IB = p.I / 128;
+  const int xq_bytes = (HB * kActBlk + 127) & ~127;
+  uint8_t* xq = smem;
+  uint8_t* ring = smem + xq_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kWarps * kNST * kUpStage);
+  SlotTab& tab = *reinterpret_cast<SlotTab*>(bars + kWarps * kNST);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* myring = ring + warp * kNST * kUpStage;
+  uint64_t* mybar = bars + warp * kNST;
+
+  pdl_launch_dependents();
+  if (lane == 0)
+    for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
+  mbar_fence_init();
+  pdl_wait();
+  build_union<false>(p, tab);
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(p.ws.xq);
+    uint4* dst = reinterpret_cast<uint4*>(xq);
+    for (int i = threadIdx.x; i < HB * kActBlk / 16; i += kThreads) dst[i] = src[i];
+  }
+  __syncthreads();
+
+  const int upp = p.I / 8;  // units a slot
+  const int total = tab.ntot * upp;
+  const int GW = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
+  const int cpu = HB / kKCH;  // chunks a unit
+  const size_t strip = (size_t)8 * p.H;
+  int pu = gw, pc = 0;  // lane 0's producer cursor
+  uint32_t issued = 0, consumed = 0;
+  auto issue = [&]() {
+    const int slot = ord_slot(tab, pu / upp), i8 = pu % upp;
+    const size_t off = (size_t)i8 * strip + (size_t)pc * kKCH * 1024;
+    uint8_t* st = myring + (issued % kNST) * kUpStage;
+    uint64_t* bar = mybar + issued % kNST;
+    mbar_expect_tx(bar, kUpStage);
+    bulk_g2s(st, tab.a[slot] + off, kKCH * 1024, bar);
+    bulk_g2s(st + kKCH * 1024, tab.b[slot] + off, kKCH * 1024, bar);
+    ++issued;
+    if (++pc == cpu) pc = 0, pu += GW;
+  };
+  if (lane == 0)
+    for (int s = 0; s < kNST && pu < total; ++s) issue();
+
+  const int g = lane >> 2, t = lane & 3;
+  bool dead = false;
+  for (int unit = gw; unit < total && !dead; unit += GW) {
+    const int slot = ord_slot(tab, unit / upp), i8 = unit % upp;
+    const int srow = (i8 * 8) / 128;
+    const float sgl = lane < HB ? __ldg(tab.sa[slot] + (size_t)srow * HB + lane) : 0.f;
+    const float sul = lane < HB ? __ldg(tab.sb[slot] + (size_t)srow * HB + lane) : 0.f;
+    float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
+    for (int c = 0; c < cpu; ++c) {
+      const uint32_t sidx = consumed % kNST;
+      if (!mbar_wait(mybar + sidx, (consumed / kNST) & 1)) {
+        dead = true;
+        break;
+      }
+      const uint8_t* st = myring + sidx * kUpStage;
+#pragma unroll
+      for (int b = 0; b < kKCH; ++b) {
+        const int kb = c * kKCH + b;
+        const uint8_t* act = xq + kb * kActBlk;
+        float d[4];
+        block_mma(d, st + b * 1024, st + kKCH * 1024 + b * 1024, act, lane);
+        const float2 xs = *reinterpret_cast<const float2*>(act + 1024 + 8 * t);
+        const float sg = __shfl_sync(0xffffffffu, sgl, kb), su = __shfl_sync(0xffffffffu, sul, kb);
+        ag0 = fmaf(d[0], sg * xs.x, ag0), ag1 = fmaf(d[1], sg * xs.y, ag1);
+        au0 = fmaf(d[2], su * xs.x, au0), au1 = fmaf(d[3], su * xs.y, au1);
+      }
+      ++consumed;
+      __syncwarp();
+      if (lane == 0 && pu < total) issue();
+    }
+    if (dead) break;
+    // SwiGLU: g, u rounded to bf16; h = bf16(w_route * silu(g) * u) (no weight for the shared expert)
+    const bool routed = slot < tab.nslots;
+    const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
+    float h0 = __fmul_rn(silu(bf16_round(ag0)), bf16_round(au0));
+    float h1 = __fmul_rn(silu(bf16_round(ag1)), bf16_round(au1));
+    if (routed) h0 = __fmul_rn(tab.w[slot][r0], h0), h1 = __fmul_rn(tab.w[slot][r1], h1);
+    __nv_bfloat16* hrow = p.ws.h + (size_t)slot * 8 * p.I;
+    if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
+    if (r1 < p.M) hrow[(size_t)r1 * p.I + ch] = __float2bfloat16_rn(h1);
+    // the 16th unit of a 128-group of h quantises it
+    const int gi = i8 / 16;
+    __threadfence();
+    __syncwarp();
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(p.ws.cnt_h + slot * IB + gi, 1);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket == 15) {
+      __threadfence();
+      uint8_t* blk = p.ws.hq + ((size_t)slot * IB + gi) * kActBlk;
+      const int kl = 4 * lane, q = kl >> 6, tt = (kl >> 4) & 3, ii = kl & 15;
+      for (int r = 0; r < 8; ++r) {
+        uint32_t packed = 0;
+        float sc = 0.f;
+        if (r < p.M) {
+          const uint2 hv = __ldcg(reinterpret_cast<const uint2*>(hrow + (size_t)r * p.I + 128 * gi + kl));
+          const float v0 = bf16_bits_to_f(hv.x & 0xffffu), v1 = bf16_bits_to_f(hv.x >> 16);
+          const float v2 = bf16_bits_to_f(hv.y & 0xffffu), v3 = bf16_bits_to_f(hv.y >> 16);
+          sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
+          packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+        }
+        *reinterpret_cast<uint32_t*>(blk + (q * 32 + 4 * r + tt) * 16 + ii) = packed;
+        if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
+      }
+      if (lane == 0) p.ws.cnt_h[slot * IB + gi] = 0;
+    }
+  }
+  if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+}
+
+// ------------------------------------------------------------------------------------------------------------ k_down
+__global__ void __launch_bounds__(kThreads, 1) k_down_fp8(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int IB = p.I / 128, NT = p.H / 16;
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kWarps * kNST * kDownStage);
+  SlotTab& tab = *reinterpret_cast<SlotTab*>(bars + kWarps * kNST);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* myring = ring + warp * kNST * kDownStage;
+  uint64_t* mybar = bars + warp * kNST;
+
+  pdl_launch_dependents();
+  if (lane == 0)
+    for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
+  mbar_fence_init();
+  pdl_wait();
+  build_union<true>(p, tab);
+
+  const int GW = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
+  if (tab.ntot == 0) {  // nothing to add on this GPU: the partial sum is zero
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kThreads)
+      p.yr[i] = 0.f;
+    return;
+  }
+  const int total = tab.ntot * NT;
+  const int cpu = IB / kKCH;
+  const size_t strip = (size_t)8 * p.I;
+  int pu = gw, pc = 0;
+  uint32_t issued = 0, consumed = 0;
+  auto issue = [&]() {
+    const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
+    const size_t off = (size_t)(2 * n16) * strip + (size_t)pc * kKCH * 1024;
+    uint8_t* st = myring + (issued % kNST) * kDownStage;
+    uint64_t* bar = mybar + issued % kNST;
+    mbar_expect_tx(bar, kDownStage);
+    bulk_g2s(st, tab.a[slot] + off, kKCH * 1024, bar);
+    bulk_g2s(st + kKCH * 1024, tab.a[slot] + off + strip, kKCH * 1024, bar);
+    bulk_g2s(st + 2 * kKCH * 1024, p.ws.hq + ((size_t)slot * IB + (size_t)pc * kKCH) * kActBlk, kKCH * kActBlk, bar);
+    ++issued;
+    if (++pc == cpu) pc = 0, pu += GW;
+  };
+  if (lane == 0)
+    for (int s = 0; s < kNST && pu < total; ++s) issue();
+
+  const int g = lane >> 2, t = lane & 3;
+  bool dead = false;
+  for (int unit = gw; unit < total && !dead; unit += GW) {
+    const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
+    const int srow = (n16 * 16) / 128;
+    const float sdl = lane < IB ? __ldg(tab.sa[slot] + (size_t)srow * IB + lane) : 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < cpu; ++c) {
+      const uint32_t sidx = consumed % kNST;
+      if (!mbar_wait(mybar + sidx, (consumed / kNST) & 1)) {
+        dead = true;
+        break;
+      }
+      const uint8_t* st = myring + sidx * kDownStage;
+#pragma unroll
+      for (int b = 0; b < kKCH; ++b) {
+        const int kb = c * kKCH + b;
+        const uint8_t* act = st + 2 * kKCH * 1024 + b * kActBlk;
+        float d[4];
+        block_mma(d, st + b * 1024, st + kKCH * 1024 + b * 1024, act, lane);
+        const float2 hs = *reinterpret_cast<const float2*>(act + 1024 + 8 * t);
+        const float sd = __shfl_sync(0xffffffffu, sdl, kb);
+        acc[0] = fmaf(d[0], sd * hs.x, acc[0]), acc[1] = fmaf(d[1], sd * hs.y, acc[1]);
+        acc[2] = fmaf(d[2], sd * hs.x, acc[2]), acc[3] = fmaf(d[3], sd * hs.y, acc[3]);
+      }
+      ++consumed;
+      __syncwarp();
+      if (lane == 0 && pu < total) issue();
+    }
+    if (dead) break;
+    // every pick's output is rounded to bf16 before the f32 adds
+    float* yt = p.ws.ypick + ((size_t)slot * NT + n16) * 128;
+    *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
+    *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
+    __threadfence();
+    __syncwarp();
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(p.ws.cnt_y + n16, 1);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket == tab.ntot - 1) {  // the tile's last slot: add its picks in ascending expert id, the shared expert last
+      __threadfence();
+      const int ch = lane >> 1, r0 = 4 * (lane & 1);
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < tab.nslots; ++s) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws.ypick + ((size_t)s * NT + n16) * 128 + ch * 8 + r0));
+        a.x = __fadd_rn(a.x, v.x), a.y = __fadd_rn(a.y, v.y), a.z = __fadd_rn(a.z, v.z), a.w = __fadd_rn(a.w, v.w);
+      }
+      const bool sh = tab.ntot > tab.nslots;
+      float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (sh) sv = __ldcg(reinterpret_cast<const float4*>(p.ws.ypick + ((size_t)tab.nslots * NT + n16) * 128 + ch * 8 + r0));
+      const float av[4] = {a.x, a.y, a.z, a.w}, svv[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (r0 + c < p.M) {
+          const size_t o = (size_t)(r0 + c) * p.H + n16 * 16 + ch;
+          p.yr[o] = p.ysum && sh ? __fadd_rn(av[c], svv[c]) : av[c];
+          if (sh && p.ys) p.ys[o] = svv[c];
+        }
+      if (lane == 0) p.ws.cnt_y[n16] = 0;
+    }
+  }
+  if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+}
+
+}  // namespace
+
+static size_t up_smem(int H) {
+  return (size_t)(((H / 128) * kActBlk + 127) & ~127) + (size_t)kWarps * kNST * kUpStage + kWarps * kNST * 8 + sizeof(SlotTab) + 16;
+}
+static size_t down_smem() { return (size_t)kWarps * kNST * kDownStage + kWarps * kNST * 8 + sizeof(SlotTab) + 16; }
+
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl) {
+  static bool attr_done = false;
+  const size_t su = up_smem(4096), sd = down_smem();
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(k_up_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)su);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_down_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sd);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  cudaError_t e = launch_act_quant_tiled(x, p.M, p.H, p.ws.xq, st, pdl);
+  if (e != cudaSuccess) return e;
+  const int ctas = sm_count();
+  e = launch_k(k_up_fp8, dim3(ctas), dim3(kThreads), up_smem(p.H), st, pdl, p);
+  if (e != cudaSuccess) return e;
+  return launch_k(k_down_fp8, dim3(ctas), dim3(kThreads), sd, st, pdl, p);
+}
+
+}  // namespace dsgx

@@ -1,0 +1,65 @@
+// Internal interface between the C-ABI layer (api.cu) and the kernel files.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "dsgx_moe.h"
+
+namespace dsgx {
+
+// A quantised activation block: 128 k of up to 8 rows as e4m3 in MMA operand order (1024 B) + the rows' f32 scales.
+constexpr int kActBlk = 1024 + 32;
+constexpr int kMaxRows = DSGX_MAX_ROWS;
+constexpr int kMaxTopK = 8;
+constexpr int kMaxSlots = kMaxRows * kMaxTopK + 1;  // the union of a step's picks + the shared expert
+
+struct RouteParams {
+  int E, topk, n_group, topk_group, score_fn, norm_topk;
+  float route_scale;
+};
+
+cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* wr, int M, int H, int E, float* logits,
+                                 cudaStream_t st, bool pdl);
+cudaError_t launch_route(const RouteParams& p, const float* logits, const float* bias, int M, int* idx, float* w,
+                         cudaStream_t st, bool pdl);
+size_t sort_ws_bytes(int T, int topk, int E);
+cudaError_t launch_sort_pack(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
+                             int* perm_slot, int* pos_of, int* row_order, void* ws, cudaStream_t st);
+cudaError_t launch_act_quant_tiled(const __nv_bfloat16* x, int M, int K, uint8_t* out, cudaStream_t st, bool pdl);
+cudaError_t launch_finalize(const float* R, const float* S, int M, int H, __nv_bfloat16* out, int mode, cudaStream_t st,
+                            bool pdl);
+
+// ---- decode ---------------------------------------------------------------------------------------------------------
+// Workspace of a decode step (all offsets multiples of 256; the first 256 bytes hold the status word and the counters'
+// base).  Zeroed once by the caller; the kernels leave every counter at zero.
+struct DecodeWs {
+  int* status;      // [0]: a dsgx_status recorded by a kernel, 0 if none
+  uint8_t* xq;      // [H/128] activation blocks of x (FP8)
+  __nv_bfloat16* h; // [kMaxSlots][8][I] bf16 h before quantisation
+  uint8_t* hq;      // [kMaxSlots][I/128] activation blocks of h
+  float* ypick;     // [kMaxSlots][H/16][16][8] every pick's down output (bf16-rounded values kept as f32)
+  int* cnt_h;       // [kMaxSlots][I/128] arrivals of the 16 gate/up units of a 128-group of h
+  int* cnt_y;       // [H/16] arrivals of the slots of an output tile
+};
+size_t decode_ws_bytes(int H, int I);
+DecodeWs decode_ws_carve(void* ws, int H, int I);
+
+struct DecodeParams {
+  int H, I, E, topk, M, e_lo, e_hi;
+  const uint8_t* pool;
+  const dsgx_mat_desc* desc;
+  dsgx_shared_w sh;
+  const int* idx;
+  const float* w;
+  DecodeWs ws;
+  float* yr;
+  float* ys;
+  int ysum;
+};
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl);
+
+int sm_count();
+
+}  // namespace dsgx

@@ -1,0 +1,420 @@
+// Router and token-order kernels: logits GEMV with a fixed summation order, score + top-k selection (sigmoid or
+// softmax, optional group-limited selection), the stable token -> expert sort, activation quantisation and the final
+// rounding.  Integer / f32 CUDA-core work, bound by latency (decode) or by HBM and issue rate (prefill); no tensor
+// cores on purpose: the selection must be reproducible bit for bit on a CPU.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dsgx {
+
+// ---------------------------------------------------------------------------------------------------- router logits
+// One warp computes rows [r0, r0 + 8) x experts [e0, e0 + ET).  Order of every sum (what the CPU oracle restates): K in
+// slices of 1024; in a slice lane j accumulates k = base + 128 i + 4 j + c (i ascending, c = 0..3) by fma from zero;
+// the 32 lane sums are combined by the xor butterfly; slice sums are added in ascending order.
+template <int ET>
+__global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr,
+                                                       int M, int H, int E, float* __restrict__ logits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int ntE = (E + ET - 1) / ET;
+  const int rt = gw / ntE, et = gw % ntE;
+  const int r0 = rt * 8, e0 = et * ET;
+  if (r0 >= M) return;
+  const int nr = min(8, M - r0);
+  float total[8][ET];
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+#pragma unroll
+    for (int j = 0; j < ET; ++j) total[r][j] = 0.f;
+  for (int base = 0; base < H; base += 1024) {
+    const int nit = min(1024, H - base) / 128;
+    float acc[8][ET];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int j = 0; j < ET; ++j) acc[r][j] = 0.f;
+#pragma unroll 2
+    for (int i = 0; i < nit; ++i) {
+      const int k = base + 128 * i + 4 * lane;
+      float4 wv[ET];
+#pragma unroll
+      for (int j = 0; j < ET; ++j)
+        wv[j] = e0 + j < E ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)(e0 + j) * H + k)) : make_float4(0, 0, 0, 0);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < nr) {
+          const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)(r0 + r) * H + k));
+          const float x0 = bf16_bits_to_f(xv.x & 0xffffu), x1 = bf16_bits_to_f(xv.x >> 16);
+          const float x2 = bf16_bits_to_f(xv.y & 0xffffu), x3 = bf16_bits_to_f(xv.y >> 16);
+#pragma unroll
+          for (int j = 0; j < ET; ++j) {
+            float a = acc[r][j];
+            a = fmaf(x0, wv[j].x, a);
+            a = fmaf(x1, wv[j].y, a);
+            a = fmaf(x2, wv[j].z, a);
+            a = fmaf(x3, wv[j].w, a);
+            acc[r][j] = a;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int j = 0; j < ET; ++j) {
+        const float s = warp_sum(acc[r][j]);
+        total[r][j] = base ? __fadd_rn(total[r][j], s) : s;
+      }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int j = 0; j < ET; ++j)
+        if (r < nr && e0 + j < E) logits[(size_t)(r0 + r) * E + e0 + j] = total[r][j];
+  }
+}
+
+cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* wr, int M, int H, int E, float* logits,
+                                 cudaStream_t st, bool pdl) {
+  const int rts = (M + 7) / 8;
+  if (M <= 64) {  // decode widths: one expert a warp, as many warps as possible
+    const int warps = rts * E;
+    return launch_k(k_router_logits<1>, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, wr, M, H, E, logits);
+  }
+  const int warps = rts * ((E + 3) / 4);
+  return launch_k(k_router_logits<4>, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, wr, M, H, E, logits);
+}
+
+// ------------------------------------------------------------------------------------------------------------ route
+// e^x from IEEE operations only (the CPU oracle runs the same steps and gets the same bits): n = rint(x log2 e),
+// r = x - n ln 2 in two fused steps, a degree-7 Taylor polynomial in Horner form, an exact scaling by 2^n.
+DSGX_DEV float exp_ieee(float x) {
+  const float n = rintf(__fmul_rn(x, 1.44269504f));
+  float r = fmaf(-n, 0.693145751953125f, x);
+  r = fmaf(-n, 1.428606765330187e-06f, r);
+  float p = 1.f / 5040;
+  p = fmaf(p, r, 1.f / 720);
+  p = fmaf(p, r, 1.f / 120);
+  p = fmaf(p, r, 1.f / 24);
+  p = fmaf(p, r, 1.f / 6);
+  p = fmaf(p, r, 0.5f);
+  p = fmaf(p, r, 1.f);
+  p = fmaf(p, r, 1.f);
+  return __fmul_rn(p, __int_as_float(((int)n + 127) << 23));  // n in [-126, 127] for the callers' ranges
+}
+DSGX_DEV float route_sigmoid(float l) {
+  const float x = -l;
+  if (x > 88.f) return 0.f;
+  if (x < -87.f) return 1.f;
+  return __fdiv_rn(1.f, __fadd_rn(1.f, exp_ieee(x)));
+}
+
+constexpr int kRJ = 16;  // experts a lane: E <= 512
+
+// One row by one warp.  Expert e = lane + 32 j.
+__global__ void __launch_bounds__(128) k_route(RouteParams p, const float* __restrict__ logits,
+                                               const float* __restrict__ bias, int M, int* __restrict__ idx,
+                                               float* __restrict__ wout) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (row >= M) return;
+  const float* l = logits + (size_t)row * p.E;
+  float s[kRJ], key[kRJ];
+  // every load before any math: one round trip
+#pragma unroll
+  for (int j = 0; j < kRJ; ++j) {
+    const int e = lane + 32 * j;
+    s[j] = e < p.E ? __ldcg(l + e) : -INFINITY;
+    key[j] = e < p.E && bias ? __ldg(bias + e) : 0.f;
+  }
+  if (p.score_fn == DSGX_SCORE_SIGMOID) {
+#pragma unroll
+    for (int j = 0; j < kRJ; ++j) s[j] = lane + 32 * j < p.E ? route_sigmoid(s[j]) : 0.f;
+  } else {  // softmax: t = exp(l - max), lane sums over j ascending, butterfly, one division each
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kRJ; ++j) m = fmaxf(m, s[j]);
+    m = warp_max(m);
+    float ps = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRJ; ++j) {
+      if (lane + 32 * j < p.E) {
+        const float d = __fsub_rn(s[j], m);
+        s[j] = d < -87.f ? 0.f : exp_ieee(d);
+        ps = __fadd_rn(ps, s[j]);
+      } else {
+        s[j] = 0.f;
+      }
+    }
+    const float S = warp_sum(ps);
+#pragma unroll
+    for (int j = 0; j < kRJ; ++j) s[j] = __fdiv_rn(s[j], S);
+  }
+#pragma unroll
+  for (int j = 0; j < kRJ; ++j) key[j] = lane + 32 * j < p.E ? __fadd_rn(s[j], key[j]) : -INFINITY;
+
+  if (p.n_group > 1) {
+    // group score = the sum of the group's two largest keys; keep the topk_group best groups (ties: lower id)
+    const int gs = p.E / p.n_group;
+    float mine = -INFINITY;  // lane g < n_group holds group g's score
+    for (int g = 0; g < p.n_group; ++g) {
+      float a = -INFINITY, b = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kRJ; ++j) {
+        const int e = lane + 32 * j;
+        if (e < p.E && e / gs == g) {
+          const float v = key[j];
+          if (v > a) b = a, a = v;
+          else if (v > b) b = v;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+        const float na = fmaxf(a, oa), nb = fmaxf(fminf(a, oa), fmaxf(b, ob));
+        a = na, b = nb;
+      }
+      if (lane == g) mine = __fadd_rn(a, b);
+    }
+    uint32_t keep = 0;
+    for (int t = 0; t < p.topk_group; ++t) {
+      float bv = lane < p.n_group && !((keep >> lane) & 1) ? mine : -INFINITY;
+      int bg = lane < p.n_group && !((keep >> lane) & 1) ? lane : 1 << 30;
+      if (bv != bv) bv = -INFINITY;  // a NaN score never wins
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (og < (1 << 30) && (bg == (1 << 30) || ov > bv || (ov == bv && og < bg))) bv = ov, bg = og;
+      }
+      if (bg < 32) keep |= 1u << bg;
+    }
+#pragma unroll
+    for (int j = 0; j < kRJ; ++j) {
+      const int e = lane + 32 * j;
+      if (e < p.E && !((keep >> (e / gs)) & 1)) key[j] = -INFINITY;
+    }
+  }
+
+  float picked[8];
+  int ids[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    picked[k] = 0.f, ids[k] = 0;
+    if (k < p.topk) {
+      float bv = -INFINITY;
+      int bj = 0;
+#pragma unroll
+      for (int j = 0; j < kRJ; ++j)
+        if (key[j] > bv) bv = key[j], bj = j;
+      int be = bv == -INFINITY ? 1 << 30 : lane + 32 * bj;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
+      }
+      if (be == 1 << 30) be = 0;
+      ids[k] = be;
+      float sv = 0.f;
+#pragma unroll
+      for (int j = 0; j < kRJ; ++j)
+        if (lane + 32 * j == be) sv = s[j], key[j] = -INFINITY;
+      picked[k] = __shfl_sync(0xffffffffu, sv, be & 31);
+    }
+  }
+  // the sum of the picked scores: four running sums at stride 4, then (t0 + t2) + (t1 + t3)
+  float t[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) t[j] = j < p.topk ? picked[j] : 0.f;
+#pragma unroll
+  for (int i = 4; i < 8; ++i)
+    if (i < p.topk) t[i & 3] = __fadd_rn(t[i & 3], picked[i]);
+  float sum;
+  if (p.topk <= 1) sum = t[0];
+  else if (p.topk == 2) sum = __fadd_rn(t[0], t[1]);
+  else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
+  else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
+  sum = __fadd_rn(sum, 1e-20f);
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (k < p.topk && lane == k) {
+      idx[(size_t)row * p.topk + k] = ids[k];
+      wout[(size_t)row * p.topk + k] =
+          p.norm_topk ? __fmul_rn(__fdiv_rn(picked[k], sum), p.route_scale) : __fmul_rn(picked[k], p.route_scale);
+    }
+}
+
+cudaError_t launch_route(const RouteParams& p, const float* logits, const float* bias, int M, int* idx, float* w,
+                         cudaStream_t st, bool pdl) {
+  return launch_k(k_route, dim3((M + 3) / 4), dim3(128), 0, st, pdl, p, logits, bias, M, idx, w);
+}
+
+// ------------------------------------------------------------------------------------------------------- sort / pack
+// Stable order of the picks by (expert id, token): chunks of kSortTok tokens; per-chunk histograms, an exclusive scan
+// expert-major / chunk-minor, then each chunk ranks its own picks with per-expert token bitmaps.  Counts and bitmaps are
+// built with shared-memory atomics whose results do not depend on their order, so every output is deterministic.
+constexpr int kSortTok = 256;
+
+__global__ void __launch_bounds__(kSortTok) k_sort_count(const int* __restrict__ idx, int T, int topk, int E,
+                                                         int* __restrict__ hist, int* __restrict__ err) {
+  extern __shared__ int sh[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
+  __syncthreads();
+  const int t = blockIdx.x * kSortTok + threadIdx.x;
+  if (t < T)
+    for (int j = 0; j < topk; ++j) {
+      const int e = idx[(size_t)t * topk + j];
+      if (e < 0 || e >= E) atomicOr(err, 1);
+      else atomicAdd(&sh[e], 1);
+    }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[(size_t)blockIdx.x * E + e] = sh[e];
+}
+
+// one block: counts, offsets and every (expert, chunk) base
+__global__ void __launch_bounds__(512) k_sort_scan(const int* __restrict__ hist, int nchunk, int E, int* __restrict__ counts,
+                                                   int* __restrict__ offsets, int* __restrict__ base) {
+  __shared__ int tot[512];
+  __shared__ int off[513];
+  const int e = threadIdx.x;
+  int c = 0;
+  if (e < E)
+    for (int k = 0; k < nchunk; ++k) c += hist[(size_t)k * E + e];
+  tot[e] = e < E ? c : 0;
+  __syncthreads();
+  if (e == 0) {
+    int a = 0;
+    for (int i = 0; i < E; ++i) off[i] = a, a += tot[i];
+    off[E] = a;
+  }
+  __syncthreads();
+  if (e < E) {
+    counts[e] = tot[e], offsets[e] = off[e];
+    int a = off[e];
+    for (int k = 0; k < nchunk; ++k) base[(size_t)k * E + e] = a, a += hist[(size_t)k * E + e];
+  }
+  if (e == 0) offsets[E] = off[E];
+}
+
+__global__ void __launch_bounds__(kSortTok) k_sort_scatter(const int* __restrict__ idx, int T, int topk, int E,
+                                                           const int* __restrict__ base, int* __restrict__ perm_tok,
+                                                           int* __restrict__ perm_slot, int* __restrict__ pos_of,
+                                                           int* __restrict__ row_order) {
+  extern __shared__ int sh[];  // [E][kSortTok / 32] token bitmaps
+  constexpr int W = kSortTok / 32;
+  uint32_t* mask = reinterpret_cast<uint32_t*>(sh);
+  for (int i = threadIdx.x; i < E * W; i += blockDim.x) mask[i] = 0;
+  __syncthreads();
+  const int lt = threadIdx.x, t = blockIdx.x * kSortTok + lt;
+  int ex[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    ex[j] = -1;
+    if (t < T && j < topk) {
+      const int e = idx[(size_t)t * topk + j];
+      if (e >= 0 && e < E) ex[j] = e, atomicOr(&mask[e * W + (lt >> 5)], 1u << (lt & 31));
+    }
+  }
+  __syncthreads();
+  if (t >= T) return;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (ex[j] >= 0) {
+      const uint32_t* m = mask + ex[j] * W;
+      int rank = __popc(m[lt >> 5] & ((1u << (lt & 31)) - 1u));
+      for (int w = 0; w < (lt >> 5); ++w) rank += __popc(m[w]);
+      const int pos = base[(size_t)blockIdx.x * E + ex[j]] + rank;
+      perm_tok[pos] = t, perm_slot[pos] = j, pos_of[(size_t)t * topk + j] = pos;
+    }
+  // the row's picks in ascending expert id (insertion sort of at most 8)
+  int o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = j;
+#pragma unroll
+  for (int a = 1; a < 8; ++a)
+    if (a < topk) {
+      const int v = o[a], ev = ex[v];
+      int b = a - 1;
+      while (b >= 0 && ex[o[b]] > ev) o[b + 1] = o[b], --b;
+      o[b + 1] = v;
+    }
+  for (int j = 0; j < topk; ++j) row_order[(size_t)t * topk + j] = o[j];
+}
+
+size_t sort_ws_bytes(int T, int topk, int E) {
+  (void)topk;
+  const size_t nchunk = (size_t)(T + kSortTok - 1) / kSortTok;
+  return 256 + 2 * nchunk * E * sizeof(int);
+}
+
+cudaError_t launch_sort_pack(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
+                             int* perm_slot, int* pos_of, int* row_order, void* ws, cudaStream_t st) {
+  const int nchunk = (T + kSortTok - 1) / kSortTok;
+  int* err = reinterpret_cast<int*>(ws);
+  int* hist = reinterpret_cast<int*>(reinterpret_cast<char*>(ws) + 256);
+  int* base = hist + (size_t)nchunk * E;
+  cudaError_t e = cudaMemsetAsync(err, 0, 4, st);
+  if (e != cudaSuccess) return e;
+  k_sort_count<<<nchunk, kSortTok, E * sizeof(int), st>>>(idx, T, topk, E, hist, err);
+  k_sort_scan<<<1, 512, 0, st>>>(hist, nchunk, E, counts, offsets, base);
+  k_sort_scatter<<<nchunk, kSortTok, (size_t)E * (kSortTok / 32) * sizeof(int), st>>>(idx, T, topk, E, base, perm_tok,
+                                                                                      perm_slot, pos_of, row_order);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------ activation quantisation
+// x bf16 [M][K] -> blocks of 1056 B, one per 128 k: [2 halves q][32 lanes][16 B] e4m3 codes in the operand order of the
+// decode MMAs (lane 4 r + t of half q holds row r, k = 128 j + 64 q + 16 t + 0..15) followed by the 8 rows' f32 scales.
+// Rows M..7 are zero.  One warp a (block, row).
+__global__ void __launch_bounds__(256) k_act_quant_tiled(const __nv_bfloat16* __restrict__ x, int M, int K,
+                                                         uint8_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int j = gw >> 3, r = gw & 7;
+  if (j >= K / 128) return;
+  uint8_t* blk = out + (size_t)j * kActBlk;
+  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
+  uint32_t packed = 0;
+  float sc = 0.f;
+  if (r < M) {
+    const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * K + 128 * j + kl));
+    const float v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
+    const float v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+    const float amax = warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+    sc = act_scale(amax);
+    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  }
+  *reinterpret_cast<uint32_t*>(blk + (q * 32 + 4 * r + t) * 16 + i) = packed;
+  if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
+}
+
+cudaError_t launch_act_quant_tiled(const __nv_bfloat16* x, int M, int K, uint8_t* out, cudaStream_t st, bool pdl) {
+  const int warps = (K / 128) * 8;
+  return launch_k(k_act_quant_tiled, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, M, K, out);
+}
+
+// ----------------------------------------------------------------------------------------------------------- finalize
+__global__ void __launch_bounds__(256) k_finalize(const float* __restrict__ R, const float* __restrict__ S, size_t n,
+                                                  __nv_bfloat16* __restrict__ out, int mode) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float r = R[i], s = S ? S[i] : 0.f;
+  out[i] = mode == 1 ? __float2bfloat16_rn(__fadd_rn(bf16_round(r), bf16_round(s))) : __float2bfloat16_rn(__fadd_rn(r, s));
+}
+cudaError_t launch_finalize(const float* R, const float* S, int M, int H, __nv_bfloat16* out, int mode, cudaStream_t st,
+                            bool pdl) {
+  const size_t n = (size_t)M * H;
+  return launch_k(k_finalize, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl, R, S, n, out, mode);
+}
+
+}  // namespace dsgx

@@ -1,0 +1,94 @@
+"""Host-side mirror of the engine's MoE operator interface over the C ABI, with torch tensors as device memory.
+
+Names and argument meaning follow the reference's `gx::` functions (altar1 engine/experts/experts.h:99-193): `route`,
+`moe_decode`, `finalize`, `decode_ws_bytes`; `router_logits` stands in for the runner's router GEMV
+(altar1 engine/model/model.cu:309-311).  torch is plumbing here (allocation, streams); every computation is a kernel of
+the CUDA library.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import MoeShape, check, lib
+
+
+def shape(H, I, E, topk, fmt=_lib.FMT_FP8, n_group=1, topk_group=1, score_fn=_lib.SCORE_SIGMOID, norm_topk=True,
+          route_scale=1.0, e_lo=0, e_hi=None):
+    return MoeShape(H, I, E, topk, n_group, topk_group, score_fn, int(norm_topk), route_scale, fmt, e_lo,
+                    E if e_hi is None else e_hi)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def router_logits(x, wr):
+    """x bf16 [M][H], wr f32 [E][H] -> logits f32 [M][E]."""
+    M, H = x.shape
+    E = wr.shape[0]
+    out = torch.empty(M, E, dtype=torch.float32, device=x.device)
+    check(lib().dsgx_router_logits(_ptr(x), _ptr(wr), M, H, E, _ptr(out), _stream()), "dsgx_router_logits")
+    return out
+
+
+def route(shp, logits, bias=None):
+    """logits f32 [M][E] -> (idx int32 [M][topk], w f32 [M][topk])."""
+    M = logits.shape[0]
+    idx = torch.empty(M, shp.topk, dtype=torch.int32, device=logits.device)
+    w = torch.empty(M, shp.topk, dtype=torch.float32, device=logits.device)
+    check(lib().dsgx_route(C.byref(shp), _ptr(logits), _ptr(bias), M, _ptr(idx), _ptr(w), _stream()), "dsgx_route")
+    return idx, w
+
+
+def sort_pack(idx, E):
+    T, k = idx.shape
+    dev = idx.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    out = dict(counts=torch.empty(E, **i32), offsets=torch.empty(E + 1, **i32), perm_tok=torch.empty(T * k, **i32),
+               perm_slot=torch.empty(T * k, **i32), pos_of=torch.empty(T, k, **i32), row_order=torch.empty(T, k, **i32))
+    ws = torch.empty(max(lib().dsgx_sort_ws_bytes(T, k, E), 256), dtype=torch.uint8, device=dev)
+    check(lib().dsgx_sort_pack(_ptr(idx), T, k, E, _ptr(out["counts"]), _ptr(out["offsets"]), _ptr(out["perm_tok"]),
+                               _ptr(out["perm_slot"]), _ptr(out["pos_of"]), _ptr(out["row_order"]), _ptr(ws), _stream()),
+          "dsgx_sort_pack")
+    return out
+
+
+def decode_ws_bytes(shp):
+    n = lib().dsgx_decode_ws_bytes(C.byref(shp))
+    if n == 0:
+        raise _lib.DsgxError(_lib.ERR_SHAPE, "dsgx_decode_ws_bytes")
+    return n
+
+
+def decode_ws(shp, device="cuda"):
+    """A zeroed decode workspace (zeroed once; the kernels leave its counters at zero)."""
+    return torch.zeros(decode_ws_bytes(shp), dtype=torch.uint8, device=device)
+
+
+def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True):
+    """x bf16 [M][H]; idx, w from route(); returns (yr, ys) f32 [M][H]: this GPU's partial sums."""
+    M, H = x.shape
+    if yr is None:
+        yr = torch.empty(M, H, dtype=torch.float32, device=x.device)
+    if ys is None:
+        ys = torch.empty(M, H, dtype=torch.float32, device=x.device)
+    cfg = _lib.DecodeCfg(int(ysum), int(pdl))
+    check(lib().dsgx_moe_decode(C.byref(shp), C.byref(layer_w), _ptr(x), _ptr(idx), _ptr(w), M, _ptr(ws), _ptr(yr),
+                                _ptr(ys), _stream(), C.byref(cfg)), "dsgx_moe_decode")
+    return yr, ys
+
+
+def finalize(R, S=None, mode=0):
+    M, H = R.shape
+    out = torch.empty(M, H, dtype=torch.bfloat16, device=R.device)
+    check(lib().dsgx_finalize(_ptr(R), _ptr(S), M, H, _ptr(out), mode, _stream()), "dsgx_finalize")
+    return out
+
+
+def ws_status(ws):
+    return lib().dsgx_ws_status(_ptr(ws))

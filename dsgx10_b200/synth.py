@@ -1,0 +1,123 @@
+"""Seeded synthetic MoE layers in the engine's weight layouts (pool + descriptors), for the tests and the bench.
+
+The reference benches and tests its expert kernels on hashed synthetic layers too (altar1
+engine/experts/tests/testdata.h:52-198); the distributions here are the ones the benchmark configurations name:
+FP8 weights quantised from N(0, 0.02) per 128x128 block (scale = amax / 448), INT4 nibbles uniform in [-8, 7] with bf16
+group scales in [2^-9, 2^-7), router weights f32 N(0, 0.02), activations bf16 N(0, 1).
+"""
+import numpy as np
+import torch
+
+from . import _lib
+
+F8 = torch.float8_e4m3fn
+
+
+def _gen(device, seed):
+    g = torch.Generator(device=device)
+    g.manual_seed(int(seed))
+    return g
+
+
+def al256(n):
+    return (n + 255) & ~255
+
+
+# ------------------------------------------------------------------------------------------------------ FP8 tensors
+
+def quant_fp8_128(w):
+    """f32 [N][K] -> (e4m3 codes uint8 [N][K], f32 scales [N/128][K/128]); scale = amax / 448 per 128x128 block."""
+    N, K = w.shape
+    blk = w.view(N // 128, 128, K // 128, 128)
+    amax = blk.abs().amax(dim=(1, 3)).clamp_min(1e-12)
+    s = amax * (1.0 / 448.0)
+    q = (blk / s[:, None, :, None]).clamp(-448.0, 448.0).to(F8)
+    return q.view(N, K).view(torch.uint8), s.float().contiguous()
+
+
+def tile_fp8(q):
+    """canonical e4m3 codes [N][K] -> the tile_fp8 byte stream [N/8][K/128][32 lanes][32 B]
+    (lane 4 g + t: row 8 n8 + g, k = 128 j + 64 q + 16 t + i at byte 16 q + i; altar1 engine/experts/layout.h:108-119)."""
+    N, K = q.shape
+    v = q.view(N // 8, 8, K // 128, 2, 4, 16)          # n8, g, j, q, t, i
+    return v.permute(0, 2, 1, 4, 3, 5).contiguous().view(-1)   # n8, j, g, t, q, i
+
+
+def untile_fp8(m, N, K):
+    v = m.view(N // 8, K // 128, 8, 4, 2, 16)           # n8, j, g, t, q, i
+    return v.permute(0, 2, 1, 4, 3, 5).contiguous().view(N, K)
+
+
+class Fp8Layer:
+    """One FP8 layer: `E` routed experts + (optionally) a shared expert, all in one device pool."""
+
+    def __init__(self, H, I, E, seed, device="cpu", shared=True, std=0.02):
+        self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_FP8
+        self.device = torch.device(device)
+        mat_b = I * H
+        sc_b = al256((I // 128) * (H // 128) * 4)
+        per_expert = 3 * mat_b + 3 * sc_b
+        n_exp = E + (1 if shared else 0)
+        self.pool = torch.empty(n_exp * per_expert, dtype=torch.uint8, device=self.device)
+        self.desc_host = (_lib.MatDesc * (E * 3))()
+        self._off = {}
+        for e in range(n_exp):
+            base = e * per_expert
+            for m in range(3):
+                N, K = (H, I) if m == 2 else (I, H)
+                g = _gen(self.device, seed * 1000003 + e * 3 + m)
+                w = torch.randn(N, K, generator=g, device=self.device, dtype=torch.float32) * std
+                q, s = quant_fp8_128(w)
+                off = base + m * mat_b
+                soff = base + 3 * mat_b + m * sc_b
+                self.pool[off:off + mat_b] = tile_fp8(q)
+                self.pool[soff:soff + s.numel() * 4] = s.view(-1).view(torch.uint8)
+                self._off[(e, m)] = (off, soff)
+                if e < E:
+                    d = self.desc_host[e * 3 + m]
+                    d.off, d.s2, d.fmt = off, 1.0, _lib.FMT_FP8
+                    d.rsv[0], d.rsv[1] = soff & 0xFFFFFFFF, soff >> 32
+        self.desc = torch.frombuffer(bytearray(bytes(self.desc_host)), dtype=torch.uint8).to(self.device)
+        self.shared = shared
+
+    def layer_w(self):
+        L = _lib.LayerW()
+        L.pool, L.desc, L.fmt = self.pool.data_ptr(), self.desc.data_ptr(), _lib.FMT_FP8
+        if self.shared:
+            p = self.pool.data_ptr()
+            (g, gs), (u, us), (d, ds) = (self._off[(self.E, m)] for m in range(3))
+            L.sh.g, L.sh.u, L.sh.d, L.sh.gs, L.sh.us, L.sh.ds = p + g, p + u, p + d, p + gs, p + us, p + ds
+        return L
+
+    def canonical(self, e):
+        """(wg, sg, wu, su, wd, sd) of expert e (e == E: the shared expert) as numpy arrays, un-tiled from the pool."""
+        out = []
+        for m in range(3):
+            N, K = (self.H, self.I) if m == 2 else (self.I, self.H)
+            off, soff = self._off[(e, m)]
+            q = untile_fp8(self.pool[off:off + N * K], N, K).cpu().numpy()
+            ns = (N // 128) * (K // 128)
+            s = self.pool[soff:soff + ns * 4].cpu().view(torch.float32).view(N // 128, K // 128).numpy().copy()
+            out += [q, s]
+        return tuple(out)
+
+    def expert_bytes(self):
+        """Algorithmic bytes of one expert: three matrices and their block scales."""
+        return 3 * self.I * self.H + 3 * (self.I // 128) * (self.H // 128) * 4
+
+
+# ---------------------------------------------------------------------------------------------- router / activations
+
+def router_weights(E, H, seed, device="cpu", std=0.02):
+    g = _gen(device, seed)
+    return torch.randn(E, H, generator=g, device=device, dtype=torch.float32) * std
+
+
+def activations(M, H, seed, device="cpu"):
+    g = _gen(device, seed)
+    return torch.randn(M, H, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+
+
+def bf16_bits(t):
+    """torch bf16 tensor -> numpy uint16 bit patterns."""
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)

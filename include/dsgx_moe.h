@@ -1,0 +1,141 @@
+/*
+ * dsgx_moe.h - C ABI of the B200 (sm_100a) quantised mixture-of-experts FFN operator.
+ *
+ * A drop-in for the MoE operator of dsgx10's engines: every entry point names the reference interface it stands in
+ * for (paths inside the reference project).  Plain pointers and sizes only; every pointer is caller-owned DEVICE memory
+ * unless a comment says "host".  `stream` is a cudaStream_t passed as void*.  Every call is asynchronous on `stream`
+ * and returns a dsgx_status; nothing aborts the process and no kernel traps (the reference's die()/__trap() become
+ * status codes: altar1 engine/experts/decode.cu:708-730, prefill.cu:784-794).
+ *
+ * Numerics contracts (selected by dsgx_moe_shape.fmt):
+ *   DSGX_FMT_FP8  "W8A8-g128": activations quantised per 128 values to e4m3 with an f32 scale amax/448, weights e4m3
+ *                 with one f32 scale per 128x128 block, gate/up rounded to bf16, h = bf16(w_route * silu(g) * u),
+ *                 h quantised again per 128, every pick's down output rounded to bf16 and added in f32 in ascending
+ *                 expert id (ds41f ref/inference/model.py:841-851, 889-904; ref/torchref/kernel.py:56-132).
+ *   DSGX_FMT_INT4 bf16 activations, W = bf16((u - u_z) * s) per group of 32 along K, gate/up rounded to bf16,
+ *                 h = bf16(bf16(silu(g)) * u), f32 down, yr += w_route * y in ascending expert id
+ *                 (altar1 ref/glmref.py:108-121, 581-643; engine/experts/formats.cuh:102-119).
+ */
+#ifndef DSGX_MOE_H_
+#define DSGX_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dsgx_status {
+  DSGX_OK = 0,
+  DSGX_ERR_ARG = 1,         /* null pointer, row count out of range, misaligned pointer */
+  DSGX_ERR_FORMAT = 2,      /* unknown or refused format tag (0 = NVFP4 and the retired tag 1 are refused) */
+  DSGX_ERR_SHAPE = 3,       /* H, I, E, topk, groups not supported by the kernels */
+  DSGX_ERR_CUDA = 4,        /* a CUDA runtime call failed; dsgx_last_cuda_error() has the code */
+  DSGX_ERR_DEVICE_WAIT = 5, /* a bounded device-side wait ran out (read from the workspace's status word) */
+  DSGX_ERR_UNSUPPORTED = 6
+} dsgx_status;
+
+/* Expert formats.  Tags 2 and 3 are the reference's (altar1 engine/experts/experts.h:39); tag 4 is this library's
+ * routed FP8 format: the reference's "tile_fp8" lane order (experts.h:66-70, layout.h:108-119) for the e4m3 values and
+ * f32 scales [N/128][K/128] row-major. */
+enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF16 = 3, DSGX_FMT_FP8 = 4 };
+enum { DSGX_SCORE_SIGMOID = 0, DSGX_SCORE_SOFTMAX = 1 };
+
+enum { DSGX_MAX_ROWS = 8 };  /* decode rows a step */
+
+/* One routed matrix of one expert: stands in for gx::MatDesc (altar1 engine/experts/experts.h:58-64), 64 bytes.
+ *   off: byte offset of the matrix's blocks in the layer's pool, a multiple of 256
+ *   s2:  per-tensor scale, exactly 1.0 for INT4, BF16 and FP8
+ *   fmt: the layer's format tag
+ *   rsv: zero, except for DSGX_FMT_FP8 where rsv[0] | rsv[1] << 32 is the byte offset in the pool of the matrix's f32
+ *        block scales [N/128][K/128] (a multiple of 16) */
+typedef struct dsgx_mat_desc {
+  uint64_t off;
+  float s2;
+  uint32_t fmt;
+  uint32_t rsv[12];
+} dsgx_mat_desc;
+
+/* The shared expert: stands in for gx::SharedW (experts.h:66-87).  FP8: g, u [I][H] and d [H][I] in the tile_fp8
+ * layout with f32 block scales gs, us, ds.  BF16 (INT4 layers): bg, bu [I][H] and bd [H][I] in the bf16 tile layout
+ * (layout.h:96-107).  All null: the layer has no fused shared expert. */
+typedef struct dsgx_shared_w {
+  const uint8_t *g, *u, *d;
+  const float *gs, *us, *ds;
+  const uint8_t *bg, *bu, *bd;
+} dsgx_shared_w;
+
+/* One layer's weights on one GPU: stands in for gx::LayerW (experts.h:92-97).  desc is [E][3] (gate, up, down) in
+ * device memory; descriptors of experts outside [e_lo, e_hi) are never read. */
+typedef struct dsgx_layer_w {
+  const uint8_t* pool;
+  const dsgx_mat_desc* desc;
+  dsgx_shared_w sh;
+  uint32_t fmt;
+} dsgx_layer_w;
+
+/* The reference fixes its shapes at compile time (experts.h:18-26); here they are run-time parameters. */
+typedef struct dsgx_moe_shape {
+  int32_t H;            /* hidden: K of gate/up, N of down; a multiple of 128 (INT4: of 512) */
+  int32_t I;            /* intermediate: N of gate/up, K of down; a multiple of 128 (INT4: of 512) */
+  int32_t E;            /* routed experts of the layer, <= 512 */
+  int32_t topk;         /* picks a row, <= 8 */
+  int32_t n_group;      /* expert groups for group-limited selection (1: none) */
+  int32_t topk_group;   /* groups kept */
+  int32_t score_fn;     /* DSGX_SCORE_* */
+  int32_t norm_topk;    /* 1: weights = s / (sum + 1e-20) * route_scale; 0: s * route_scale */
+  float route_scale;
+  uint32_t fmt;         /* DSGX_FMT_FP8 or DSGX_FMT_INT4 */
+  int32_t e_lo, e_hi;   /* this GPU's experts [e_lo, e_hi) (expert parallelism: ds41f ref/inference/model.py:863-870) */
+} dsgx_moe_shape;
+
+int dsgx_last_cuda_error(void);
+const char* dsgx_status_name(int status);
+
+/* ---- router ---------------------------------------------------------------------------------------------------
+ * logits[r][e] = sum_k f32(x[r][k]) * wr[e][k] in f32 with a fixed summation order, the same for every M, so that the
+ * selection is reproducible bit for bit on a CPU: stands in for the engines' router GEMV
+ * (altar1 engine/model/model.cu:309-311; ds41f engine/model/model.cu:607).  x bf16 [M][H], wr f32 [E][H]. */
+int dsgx_router_logits(const void* x_bf16, const float* wr, int M, int H, int E, float* logits, void* stream);
+
+/* idx [M][topk] (descending selection key, ties to the lower expert id) and w [M][topk]: stands in for gx::route
+ * (altar1 engine/experts/experts.h:99-102) and dsk::router_topk (ds41f engine/kernels/dsk.h:164-175).  bias may be null. */
+int dsgx_route(const dsgx_moe_shape* shape, const float* logits, const float* bias, int M, int32_t* idx, float* w,
+               void* stream);
+
+/* ---- token -> expert sort / pack ---------------------------------------------------------------------------------
+ * The stable (expert id, token) order of the T * topk picks: stands in for the bucket kernels of the prefill path
+ * (altar1 engine/experts/prefill.cu:94-150; ds41f engine/kernels/prefill.cu:673-781), but deterministic.
+ * counts [E], offsets [E+1], perm_tok [T*topk], perm_slot [T*topk], pos_of [T][topk], row_order [T][topk];
+ * ws: dsgx_sort_ws_bytes(T, topk, E) bytes of scratch. */
+size_t dsgx_sort_ws_bytes(int T, int topk, int E);
+int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
+                   int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* ws, void* stream);
+
+/* ---- decode (1..DSGX_MAX_ROWS rows) ------------------------------------------------------------------------------
+ * Stands in for gx::decode_ws_bytes / gx::moe_decode (altar1 engine/experts/experts.h:104-141) and dsk::moe_routed
+ * (ds41f engine/kernels/dsk.h:212-236).  x bf16 [M][H]; idx, w from dsgx_route; ws: dsgx_decode_ws_bytes(shape) bytes,
+ * zeroed once before the first call (its counters reset themselves).  Writes this GPU's f32 partial sums
+ * yr [M][H] (the routed experts in [e_lo, e_hi), added in ascending expert id) and ys [M][H] (the shared expert, when the
+ * layer has one; ys may be null when it has none).  Calls that share a workspace must not overlap on the device. */
+typedef struct dsgx_decode_cfg {
+  int32_t ysum;        /* 1: ys is added into yr after the routed experts and yr is the only output (experts.h:132-137) */
+  int32_t pdl;         /* 1: launch with programmatic dependent launch (experts.h:120) */
+  int32_t reserved[6];
+} dsgx_decode_cfg;
+size_t dsgx_decode_ws_bytes(const dsgx_moe_shape* shape);
+int dsgx_moe_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, const int32_t* idx,
+                    const float* w, int M, void* ws, float* yr, float* ys, void* stream, const dsgx_decode_cfg* cfg);
+
+/* out = bf16(R + S) (S may be null): the single rounding after the partial sums are reduced; stands in for
+ * gx::finalize (experts.h:146-147), whose bf16(bf16(R) + bf16(S)) order is mode 1. */
+int dsgx_finalize(const float* R, const float* S, int M, int H, void* out_bf16, int mode, void* stream);
+
+/* Reads (synchronously) the device status word of a workspace: DSGX_OK or DSGX_ERR_DEVICE_WAIT. */
+int dsgx_ws_status(const void* ws);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,89 @@
+"""GPU parity of the router front and the token sort: bit-exact against the oracle (ids, weight bits, permutation)."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def _mods():
+    from dsgx10_b200 import _lib, moe, synth
+    return _lib, moe, synth
+
+
+CASES = [
+    # H, E, topk, n_group, topk_group, score, scale, M
+    (2048, 64, 6, 1, 1, 0, 1.0, 1),
+    (2048, 64, 6, 1, 1, 0, 1.5, 8),
+    (4096, 256, 8, 8, 4, 0, 1.0, 8),
+    (4096, 256, 8, 8, 4, 0, 2.5, 5),
+    (6144, 168, 8, 1, 1, 1, 1.0, 4),
+    (6144, 168, 8, 1, 1, 0, 2.5, 8),
+    (256, 8, 2, 1, 1, 0, 1.0, 3),
+    (1280, 40, 3, 4, 2, 1, 1.0, 7),
+]
+
+
+@pytest.mark.parametrize("H,E,topk,ng,tg,score,scale,M", CASES)
+def test_router_logits_and_route_bit_exact(orc, H, E, topk, ng, tg, score, scale, M):
+    _lib, moe, synth = _mods()
+    shp = moe.shape(H, 256, E, topk, n_group=ng, topk_group=tg, score_fn=score, route_scale=scale)
+    x = synth.activations(M, H, 1000 + H + M).cuda()
+    wr = synth.router_weights(E, H, 2000 + E).cuda()
+    bias = (torch.randn(E, generator=torch.Generator().manual_seed(5)) * 0.01).float().cuda()
+    logits = moe.router_logits(x, wr)
+    idx, w = moe.route(shp, logits, bias)
+    torch.cuda.synchronize()
+    from tests.util import oracle_route
+    ol, oi, ow = oracle_route(orc, synth.bf16_bits(x), wr.cpu().numpy(), bias.cpu().numpy(), shp)
+    assert (logits.cpu().numpy().view(np.uint32) == ol.view(np.uint32)).all()
+    assert (idx.cpu().numpy() == oi).all()
+    assert (w.cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("T", [1, 255, 1024, 4099])
+def test_router_prefill_widths_bit_exact(orc, T):
+    _lib, moe, synth = _mods()
+    H, E, topk = 2048, 64, 6
+    shp = moe.shape(H, 1024, E, topk)
+    x = synth.activations(T, H, 77 + T).cuda()
+    wr = synth.router_weights(E, H, 78).cuda()
+    logits = moe.router_logits(x, wr)
+    idx, w = moe.route(shp, logits, None)
+    torch.cuda.synchronize()
+    from tests.util import oracle_route
+    ol, oi, ow = oracle_route(orc, synth.bf16_bits(x), wr.cpu().numpy(), None, shp)
+    assert (logits.cpu().numpy().view(np.uint32) == ol.view(np.uint32)).all()
+    assert (idx.cpu().numpy() == oi).all()
+    assert (w.cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+
+
+def test_route_engineered_ties(orc):
+    """Many equal logits and a 3-way tie at the last place: ties go to the lower expert id, on the GPU as in the oracle."""
+    _lib, moe, synth = _mods()
+    E, topk, M = 168, 8, 19
+    rng = np.random.default_rng(4)
+    l = (rng.integers(0, 8, (M, E)) * 0.5).astype(np.float32)      # heavy ties
+    for m in range(M):
+        l[m, [(m * 13) % E, (m * 13 + 50) % E, (m * 13 + 101) % E]] = 2.25
+    bias = np.full(E, 28.25, np.float32)
+    shp = moe.shape(6144, 2048, E, topk, route_scale=2.5)
+    idx, w = moe.route(shp, torch.from_numpy(l).cuda(), torch.from_numpy(bias).cuda())
+    oi, ow = orc.route(l, bias, topk, route_scale=2.5)
+    assert (idx.cpu().numpy() == oi).all()
+    assert (w.cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("T,E,topk", [(1, 64, 6), (7, 8, 2), (256, 64, 6), (257, 64, 6), (16384, 64, 6), (5000, 256, 8)])
+def test_sort_pack_bit_exact(orc, T, E, topk):
+    _lib, moe, synth = _mods()
+    rng = np.random.default_rng(T + E)
+    # Zipf-like popularity so some experts get thousands of rows and some none
+    p = 1.0 / np.arange(1, E + 1) ** 1.1
+    p /= p.sum()
+    idx = np.stack([rng.choice(E, topk, replace=False, p=p) for _ in range(T)]).astype(np.int32)
+    got = moe.sort_pack(torch.from_numpy(idx).cuda(), E)
+    torch.cuda.synchronize()
+    want = orc.sort_pack(idx, E)
+    for k in want:
+        assert (got[k].cpu().numpy().reshape(want[k].shape) == want[k]).all(), k
