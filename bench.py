@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE decode layer-step (the headline metric): DeepSeek-style FP8 layer, hidden 4096, 256 routed
+experts of intermediate 2048, top-8 sigmoid routing with group-limited selection (8 groups, 4 kept), one shared expert,
+one row by default (`--rows` 1..8).
+
+  python bench.py --gpus N --steps K --warmup W          this library on N GPUs (torchrun for N > 1)
+  python bench.py --impl reference ...                   the CPU path (the oracle port) on the host cores
+
+A step = router logits + top-k + activation quantisation + expert gate/up (SwiGLU) + expert down + combine + rounding of
+one batch of rows through one layer.  Weights are cold: steps cycle through `--layers` distinct layers and distinct
+activations, so that no step finds its experts in L2 (each step streams ~231 MB, the L2 holds 126 MB).
+One JSON line on stdout (rank 0).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4)
+SEED = 20261102
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower() == "active"})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def step_bytes(rows_union, rows):
+    """Algorithmic bytes of one step: each distinct picked expert and the shared expert once (three matrices and
+    their block scales), the router weights, the activations in and out."""
+    H, I, E = CFG["H"], CFG["I"], CFG["E"]
+    expert = 3 * I * H + 3 * (I // 128) * (H // 128) * 4
+    return (rows_union + 1) * expert + E * H * 4 + rows * H * 2 * 2
+
+
+def up_bytes(rows_union):
+    H, I = CFG["H"], CFG["I"]
+    return (rows_union + 1) * (2 * I * H + 2 * (I // 128) * (H // 128) * 4)
+
+
+# --------------------------------------------------------------------------------------------------------- CPU arm
+
+def run_reference(args):
+    """Times the CPU path (the oracle port of the reference's Python/C++ CPU references) on the host cores."""
+    import numpy as np
+    import torch
+    from dsgx10_b200 import moe, synth
+    from oracle import oracle as orc
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    orc.build(with_ref=False) if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")) else None
+    H, I, E, topk = CFG["H"], CFG["I"], CFG["E"], CFG["topk"]
+    rows = args.rows
+    shp = moe.shape(H, I, E, topk, n_group=CFG["n_group"], topk_group=CFG["topk_group"])
+    x = synth.activations(rows, H, SEED + 1000)
+    wr = synth.router_weights(E, H, SEED + 2000).numpy()
+    xb = synth.bf16_bits(x)
+    logits = orc.router_logits(xb, wr)
+    idx, w = orc.route(logits, None, topk, 0, CFG["n_group"], CFG["topk_group"], True, 1.0)
+    picked = sorted(set(int(e) for e in idx.ravel()))
+    # canonical weights of the picked experts only (the other 247 are never read by a step)
+    experts = {}
+    for e in picked + [E]:
+        t = []
+        for m in range(3):
+            N, K = (H, I) if m == 2 else (I, H)
+            g = torch.Generator().manual_seed(SEED * 1000003 + e * 3 + m)
+            q, s = synth.quant_fp8_128(torch.randn(N, K, generator=g) * 0.02)
+            t += [q.numpy(), s.numpy()]
+        experts[e] = tuple(t)
+    shared = experts.pop(E)
+
+    def one():
+        lg = orc.router_logits(xb, wr)
+        ii, ww = orc.route(lg, None, topk, 0, CFG["n_group"], CFG["topk_group"], True, 1.0)
+        return orc.moe_fp8_layer(xb, ii, ww, experts, shared)
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        one()
+    steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    dt = (time.perf_counter() - t0) / steps
+    us = dt * 1e6
+    cores = orc.num_threads()
+    line = {
+        "impl": "reference", "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
+                               f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows},
+        "cpu_baseline": {"value": us, "unit": "us", "cores": cores, "kind": "port",
+                         "sample": f"{steps} whole layer-steps ({rows} row(s), {len(picked)} experts + shared) through "
+                                   "the C oracle (OpenMP)"},
+        "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": rows / dt,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------------- GPU arm
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from dsgx10_b200 import _lib, moe, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this library has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+
+    H, I, E, topk = CFG["H"], CFG["I"], CFG["E"], CFG["topk"]
+    rows = args.rows
+    e_lo, e_hi = rank * E // world, (rank + 1) * E // world
+    shp = moe.shape(H, I, E, topk, n_group=CFG["n_group"], topk_group=CFG["topk_group"], e_lo=e_lo, e_hi=e_hi)
+    NL, NX = args.layers, 16
+    layers, steps_buf = [], []
+    for l in range(NL):
+        lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+        wr = synth.router_weights(E, H, SEED + 2000 + l, device="cpu").to(dev)
+        layers.append((lay, lay.layer_w()))
+        steps_buf.append(moe.LayerStep(shp, wr, None, device=dev))
+    xs = [synth.activations(rows, H, SEED + 1000 + i, device="cpu").to(dev) for i in range(NX)]
+    xs_host = [x.cpu().pin_memory() for x in xs]
+    out_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
+    red = torch.zeros(2, _lib.MAX_ROWS, H, dtype=torch.float32, device=dev) if world > 1 else None
+
+    def step(i, host=False):
+        lay, lw = layers[i % NL]
+        sb = steps_buf[i % NL]
+        if world == 1:
+            if host:
+                sb.run_host(lw, xs_host[i % NX], out_host)
+            else:
+                sb.run(lw, xs[i % NX])
+            return
+        x = xs[i % NX]
+        if host:
+            sb.x_stage[:rows].copy_(xs_host[i % NX], non_blocking=True)
+            x = sb.x_stage[:rows]
+        sb.run(lw, x, finalize=False)
+        red[0].copy_(sb.yr)
+        if rank == 0:
+            red[1].copy_(sb.ys)
+        else:
+            red[1].zero_()
+        dist.all_reduce(red)
+        out = moe.finalize(red[0, :rows], red[1, :rows])
+        if host:
+            out_host.copy_(out, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda i: step(i), args.steps)
+    # end to end: host buffers in, host buffer out, copies inside the timed region
+    for i in range(3):
+        step(i, host=True)
+    ms_e2e = timed(lambda i: step(i, host=True), args.steps)
+
+    # the dominant kernel (gate/up stream) alone, for the roofline: same cold-weight rotation
+    union = []
+    for i in range(NL):
+        sb = steps_buf[i]
+        union.append(len(set(sb.idx[:rows].flatten().tolist()) & set(range(e_lo, e_hi))))
+
+    def up_only(i):
+        lay, lw = layers[i % NL]
+        sb = steps_buf[i % NL]
+        moe.moe_decode(shp, lw, xs[i % NX], sb.idx, sb.w, sb.ws, sb.yr, sb.ys, parts=1)
+    for i in range(3):
+        up_only(i)
+    ms_up = timed(up_only, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    status = max(moe.ws_status(sb.ws) for sb in steps_buf)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks, peak_kind = measured_peaks()
+    us = ms * 1e3 / args.steps
+    us_e2e = ms_e2e * 1e3 / args.steps
+    us_up = ms_up * 1e3 / args.steps
+    # distinct experts a step touches (all ranks): from the routed ids of the last steps (all ranks route identically)
+    tot_union = sum(len(set(sb.idx[:rows].flatten().tolist())) for sb in steps_buf) / NL
+    sb_bytes = step_bytes(tot_union, rows)
+    upb = sum(up_bytes(u - (0 if rank == 0 else 1)) for u in union) / NL  # rank 0 also streams the shared expert
+    ach = upb / (us_up * 1e-6) / 1e9
+    line = {
+        "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
+                               f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows,
+                   "parallelism": f"ep{world}", "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2"},
+        "tokens_per_s": rows / (us * 1e-6),
+        "step_hbm_gbs": sb_bytes / (us * 1e-6) / 1e9,
+        "step_frac_of_measured_hbm": sb_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
+        "step_frac_of_8tbs": sb_bytes / (us * 1e-6) / 1e9 / 8000.0,
+        "step_algorithmic_bytes": sb_bytes,
+        "roofline": {"bound": "hbm", "kernel": "k_up_fp8 (+ activation quantisation launch)", "achieved": ach,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
+                     "us_per_launch": us_up, "algorithmic_bytes": upb, "traffic": None},
+        "e2e": {"value": us_e2e, "unit": "us", "h2d_bytes_per_step": rows * H * 2, "d2h_bytes_per_step": rows * H * 2},
+        "gpu_launches": args.steps * 6,
+        "clocks": clocks,
+        "device_status": status,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(rows)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(rows):
+    """The oracle port on the host cores, a bounded sample: three whole layer-steps of the same workload."""
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "3", "--warmup", "1",
+                        "--rows", str(rows)], capture_output=True, text=True, timeout=600)
+    try:
+        d = json.loads(r.stdout.strip().splitlines()[-1])
+        return d["cpu_baseline"]
+    except Exception as ex:  # report, do not hide
+        return {"value": None, "unit": "us", "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {ex}: {r.stderr[-300:]}"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -31,7 +31,11 @@ class MoeShape(C.Structure):
 
 
 class DecodeCfg(C.Structure):
-    _fields_ = [("ysum", C.c_int32), ("pdl", C.c_int32), ("reserved", C.c_int32 * 6)]
+    _fields_ = [("ysum", C.c_int32), ("pdl", C.c_int32), ("parts", C.c_int32), ("reserved", C.c_int32 * 5)]
+
+
+class LayerStep(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("wr", "bias", "logits", "idx", "w", "ws", "yr", "ys", "out_bf16", "x_stage")]
 
 
 # every symbol include/dsgx_moe.h declares: name -> (restype, argtypes)
@@ -47,6 +51,8 @@ SYMBOLS = {
     "dsgx_moe_decode": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _I, _V, _V, _V, _V,
                              C.POINTER(DecodeCfg)]),
     "dsgx_finalize": (_I, [_V, _V, _I, _I, _V, _I, _V]),
+    "dsgx_moe_layer_decode": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _I, C.POINTER(LayerStep), _I, _V]),
+    "dsgx_moe_layer_decode_host": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _I, C.POINTER(LayerStep), _V, _V]),
     "dsgx_ws_status": (_I, [_V]),
 }
 

@@ -54,16 +54,23 @@ DecodeWs decode_ws_carve(void* ws, int H, int I) {
   return w;
 }
 
-static int check_shape(const dsgx_moe_shape* s) {
+// the routing fields only (dsgx_route reads nothing else)
+static int check_route_shape(const dsgx_moe_shape* s) {
   if (!s) return DSGX_ERR_ARG;
-  if (s->fmt == DSGX_FMT_NVFP4 || s->fmt == DSGX_FMT_RETIRED) return DSGX_ERR_FORMAT;
-  if (s->fmt != DSGX_FMT_FP8 && s->fmt != DSGX_FMT_INT4) return DSGX_ERR_FORMAT;
   if (s->E < 1 || s->E > 512 || s->topk < 1 || s->topk > kMaxTopK || s->topk > s->E) return DSGX_ERR_SHAPE;
-  if (s->H < 128 || s->I < 128 || s->H % 128 || s->I % 128) return DSGX_ERR_SHAPE;
   if (s->n_group < 1 || s->n_group > 32 || s->E % s->n_group || s->topk_group < 1 || s->topk_group > s->n_group)
     return DSGX_ERR_SHAPE;
   if (s->n_group > 1 && (s->E / s->n_group < 2 || s->topk > s->topk_group * (s->E / s->n_group))) return DSGX_ERR_SHAPE;
   if (s->score_fn != DSGX_SCORE_SIGMOID && s->score_fn != DSGX_SCORE_SOFTMAX) return DSGX_ERR_SHAPE;
+  return DSGX_OK;
+}
+static int check_shape(const dsgx_moe_shape* s) {
+  if (!s) return DSGX_ERR_ARG;
+  if (s->fmt == DSGX_FMT_NVFP4 || s->fmt == DSGX_FMT_RETIRED) return DSGX_ERR_FORMAT;
+  if (s->fmt != DSGX_FMT_FP8 && s->fmt != DSGX_FMT_INT4) return DSGX_ERR_FORMAT;
+  const int rc = check_route_shape(s);
+  if (rc) return rc;
+  if (s->H < 128 || s->I < 128 || s->H % 128 || s->I % 128) return DSGX_ERR_SHAPE;
   if (s->e_lo < 0 || s->e_hi > s->E || s->e_lo > s->e_hi) return DSGX_ERR_SHAPE;
   if (s->fmt == DSGX_FMT_FP8 && (s->H > 4096 || s->I > 4096 || s->H % 256 || s->I % 256)) return DSGX_ERR_SHAPE;
   if (s->fmt == DSGX_FMT_INT4 && (s->H % 512 || s->I % 512)) return DSGX_ERR_SHAPE;
@@ -102,7 +109,7 @@ int dsgx_router_logits(const void* x, const float* wr, int M, int H, int E, floa
 
 int dsgx_route(const dsgx_moe_shape* s, const float* logits, const float* bias, int M, int32_t* idx, float* w,
                void* stream) {
-  const int rc = check_shape(s);
+  const int rc = check_route_shape(s);
   if (rc) return rc;
   if (!logits || !idx || !w || M < 1) return DSGX_ERR_ARG;
   RouteParams p{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
@@ -142,7 +149,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
   if (((uintptr_t)L->pool & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh8 = L->sh.g != nullptr;
   if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds)) return DSGX_ERR_ARG;
-  const dsgx_decode_cfg dflt = {0, 1, {0, 0, 0, 0, 0, 0}};
+  const dsgx_decode_cfg dflt = {0, 1, 0, {0, 0, 0, 0, 0}};
   if (!cfg) cfg = &dflt;
   if (s->fmt == DSGX_FMT_FP8) {
     if (L->sh.bg || L->sh.bu || L->sh.bd) return DSGX_ERR_FORMAT;  // an FP8 layer's shared expert is FP8
@@ -153,7 +160,8 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum;
-    cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0);
+    cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
+                                      cfg->parts == 0 ? 3 : cfg->parts);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
   }
   return DSGX_ERR_UNSUPPORTED;
@@ -162,6 +170,36 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
 int dsgx_finalize(const float* R, const float* S, int M, int H, void* out, int mode, void* stream) {
   if (!R || !out || M < 1 || H < 1 || (mode != 0 && mode != 1)) return DSGX_ERR_ARG;
   cudaError_t e = launch_finalize(R, S, M, H, reinterpret_cast<__nv_bfloat16*>(out), mode, (cudaStream_t)stream, true);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* x, int M,
+                          const dsgx_layer_step* st, int finalize, void* stream) {
+  if (!st || !st->wr || !st->logits || !st->idx || !st->w || !st->ws || !st->yr) return DSGX_ERR_ARG;
+  if (finalize && !st->out_bf16) return DSGX_ERR_ARG;
+  int rc = check_shape(s);
+  if (rc) return rc;
+  rc = dsgx_router_logits(x, st->wr, M, s->H, s->E, st->logits, stream);
+  if (rc) return rc;
+  rc = dsgx_route(s, st->logits, st->bias, M, st->idx, st->w, stream);
+  if (rc) return rc;
+  rc = dsgx_moe_decode(s, L, x, st->idx, st->w, M, st->ws, st->yr, st->ys, stream, nullptr);
+  if (rc) return rc;
+  if (!finalize) return DSGX_OK;
+  const bool shared = L->sh.g != nullptr || L->sh.bg != nullptr;
+  return dsgx_finalize(st->yr, shared ? st->ys : nullptr, M, s->H, st->out_bf16, 0, stream);
+}
+
+int dsgx_moe_layer_decode_host(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* x_host, int M,
+                               const dsgx_layer_step* st, void* out_host, void* stream) {
+  if (!st || !st->x_stage || !st->out_bf16 || !x_host || !out_host || !s) return DSGX_ERR_ARG;
+  if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
+  const size_t bytes = (size_t)M * s->H * 2;
+  cudaError_t e = cudaMemcpyAsync(st->x_stage, x_host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const int rc = dsgx_moe_layer_decode(s, L, st->x_stage, M, st, 1, stream);
+  if (rc) return rc;
+  e = cudaMemcpyAsync(out_host, st->out_bf16, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
   return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
 }
 

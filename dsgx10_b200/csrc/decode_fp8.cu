@@ -366,7 +366,7 @@ static size_t up_smem(int H) {
 }
 static size_t down_smem() { return (size_t)kWarps * kNST * kDownStage + kWarps * kNST * 8 + sizeof(SlotTab) + 16; }
 
-cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl) {
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
   static bool attr_done = false;
   const size_t su = up_smem(4096), sd = down_smem();
   if (!attr_done) {
@@ -376,12 +376,16 @@ cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cud
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  cudaError_t e = launch_act_quant_tiled(x, p.M, p.H, p.ws.xq, st, pdl);
-  if (e != cudaSuccess) return e;
   const int ctas = sm_count();
-  e = launch_k(k_up_fp8, dim3(ctas), dim3(kThreads), up_smem(p.H), st, pdl, p);
-  if (e != cudaSuccess) return e;
-  return launch_k(k_down_fp8, dim3(ctas), dim3(kThreads), sd, st, pdl, p);
+  cudaError_t e = cudaSuccess;
+  if (parts & 1) {
+    e = launch_act_quant_tiled(x, p.M, p.H, p.ws.xq, st, pdl);
+    if (e != cudaSuccess) return e;
+    e = launch_k(k_up_fp8, dim3(ctas), dim3(kThreads), up_smem(p.H), st, pdl, p);
+    if (e != cudaSuccess) return e;
+  }
+  if (parts & 2) e = launch_k(k_down_fp8, dim3(ctas), dim3(kThreads), sd, st, pdl, p);
+  return e;
 }
 
 }  // namespace dsgx

@@ -58,7 +58,8 @@ struct DecodeParams {
   float* ys;
   int ysum;
 };
-cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl);
+// parts: 1 = activation quantisation + gate/up, 2 = down + combine, 3 = both
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
 
 int sm_count();
 

@@ -70,14 +70,14 @@ def decode_ws(shp, device="cuda"):
     return torch.zeros(decode_ws_bytes(shp), dtype=torch.uint8, device=device)
 
 
-def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True):
+def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True, parts=0):
     """x bf16 [M][H]; idx, w from route(); returns (yr, ys) f32 [M][H]: this GPU's partial sums."""
     M, H = x.shape
     if yr is None:
         yr = torch.empty(M, H, dtype=torch.float32, device=x.device)
     if ys is None:
         ys = torch.empty(M, H, dtype=torch.float32, device=x.device)
-    cfg = _lib.DecodeCfg(int(ysum), int(pdl))
+    cfg = _lib.DecodeCfg(int(ysum), int(pdl), int(parts))
     check(lib().dsgx_moe_decode(C.byref(shp), C.byref(layer_w), _ptr(x), _ptr(idx), _ptr(w), M, _ptr(ws), _ptr(yr),
                                 _ptr(ys), _stream(), C.byref(cfg)), "dsgx_moe_decode")
     return yr, ys
@@ -92,3 +92,35 @@ def finalize(R, S=None, mode=0):
 
 def ws_status(ws):
     return lib().dsgx_ws_status(_ptr(ws))
+
+
+class LayerStep:
+    """The buffers of one layer step (router to rounded output) and the two step calls."""
+
+    def __init__(self, shp, wr, bias=None, device="cuda"):
+        f32 = dict(dtype=torch.float32, device=device)
+        self.shp, self.wr, self.bias = shp, wr, bias
+        self.logits = torch.empty(_lib.MAX_ROWS, shp.E, **f32)
+        self.idx = torch.empty(_lib.MAX_ROWS, shp.topk, dtype=torch.int32, device=device)
+        self.w = torch.empty(_lib.MAX_ROWS, shp.topk, **f32)
+        self.ws = decode_ws(shp, device)
+        self.yr = torch.zeros(_lib.MAX_ROWS, shp.H, **f32)
+        self.ys = torch.zeros(_lib.MAX_ROWS, shp.H, **f32)
+        self.out = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
+        self.x_stage = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
+        self.c = _lib.LayerStep(_ptr(wr), _ptr(bias), _ptr(self.logits), _ptr(self.idx), _ptr(self.w), _ptr(self.ws),
+                                _ptr(self.yr), _ptr(self.ys), _ptr(self.out), _ptr(self.x_stage))
+
+    def run(self, layer_w, x, finalize=True):
+        """x bf16 [M][H] on the device -> self.out[:M] (bf16) when finalize, else self.yr / self.ys partial sums."""
+        M = x.shape[0]
+        check(lib().dsgx_moe_layer_decode(C.byref(self.shp), C.byref(layer_w), _ptr(x), M, C.byref(self.c),
+                                          int(finalize), _stream()), "dsgx_moe_layer_decode")
+        return self.out[:M]
+
+    def run_host(self, layer_w, x_host, out_host):
+        """x_host, out_host: pinned bf16 host tensors [M][H]; copies, the step and the read-back in stream order."""
+        M = x_host.shape[0]
+        check(lib().dsgx_moe_layer_decode_host(C.byref(self.shp), C.byref(layer_w), _ptr(x_host), M, C.byref(self.c),
+                                               _ptr(out_host), _stream()), "dsgx_moe_layer_decode_host")
+        return out_host

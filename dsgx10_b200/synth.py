@@ -51,18 +51,21 @@ def untile_fp8(m, N, K):
 class Fp8Layer:
     """One FP8 layer: `E` routed experts + (optionally) a shared expert, all in one device pool."""
 
-    def __init__(self, H, I, E, seed, device="cpu", shared=True, std=0.02):
+    def __init__(self, H, I, E, seed, device="cpu", shared=True, std=0.02, e_range=None):
+        """e_range = (lo, hi): only these experts are generated and stored (an expert-parallel rank's share); an
+        expert's weights depend on (seed, expert id) alone, whatever the range."""
         self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_FP8
         self.device = torch.device(device)
         mat_b = I * H
         sc_b = al256((I // 128) * (H // 128) * 4)
         per_expert = 3 * mat_b + 3 * sc_b
-        n_exp = E + (1 if shared else 0)
-        self.pool = torch.empty(n_exp * per_expert, dtype=torch.uint8, device=self.device)
+        lo, hi = e_range if e_range is not None else (0, E)
+        ids = list(range(lo, hi)) + ([E] if shared else [])
+        self.pool = torch.empty(max(len(ids), 1) * per_expert, dtype=torch.uint8, device=self.device)
         self.desc_host = (_lib.MatDesc * (E * 3))()
         self._off = {}
-        for e in range(n_exp):
-            base = e * per_expert
+        for n, e in enumerate(ids):
+            base = n * per_expert
             for m in range(3):
                 N, K = (H, I) if m == 2 else (I, H)
                 g = _gen(self.device, seed * 1000003 + e * 3 + m)

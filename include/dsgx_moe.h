@@ -122,7 +122,8 @@ int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, 
 typedef struct dsgx_decode_cfg {
   int32_t ysum;        /* 1: ys is added into yr after the routed experts and yr is the only output (experts.h:132-137) */
   int32_t pdl;         /* 1: launch with programmatic dependent launch (experts.h:120) */
-  int32_t reserved[6];
+  int32_t parts;       /* bench hook (experts.h:121): 0 or 3 the whole step, 1 gate/up only, 2 down only */
+  int32_t reserved[5];
 } dsgx_decode_cfg;
 size_t dsgx_decode_ws_bytes(const dsgx_moe_shape* shape);
 int dsgx_moe_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, const int32_t* idx,
@@ -131,6 +132,31 @@ int dsgx_moe_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const vo
 /* out = bf16(R + S) (S may be null): the single rounding after the partial sums are reduced; stands in for
  * gx::finalize (experts.h:146-147), whose bf16(bf16(R) + bf16(S)) order is mode 1. */
 int dsgx_finalize(const float* R, const float* S, int M, int H, void* out_bf16, int mode, void* stream);
+
+/* ---- one layer step, router to rounded output --------------------------------------------------------------------
+ * The sequence the engines' layer runners issue around the operator (altar1 engine/model/model.cu:308-352: router
+ * GEMV, route, moe_decode, then the reduction and the rounding): logits = x wr^T, route, the expert step, and
+ * out = bf16(yr + ys).  Every buffer is caller-owned device memory sized for DSGX_MAX_ROWS rows:
+ * logits [8][E] f32, idx [8][topk] i32, w [8][topk] f32, yr, ys [8][H] f32, out [8][H] bf16, x_stage [8][H] bf16.
+ * With n_ranks > 1 the caller reduces yr across GPUs between dsgx_moe_layer_decode(..., finalize = 0) and dsgx_finalize. */
+typedef struct dsgx_layer_step {
+  const float* wr;    /* router weights f32 [E][H] */
+  const float* bias;  /* selection bias f32 [E] or null */
+  float* logits;
+  int32_t* idx;
+  float* w;
+  void* ws;           /* dsgx_decode_ws_bytes(shape), zeroed once */
+  float* yr;
+  float* ys;
+  void* out_bf16;
+  void* x_stage;      /* device staging for dsgx_moe_layer_decode_host */
+} dsgx_layer_step;
+int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, int M,
+                          const dsgx_layer_step* step, int finalize, void* stream);
+/* The same with HOST buffers: x_host bf16 [M][H] (pinned memory for an asynchronous copy) is copied to the device,
+ * the step runs, and out_host bf16 [M][H] receives the result; all in stream order, the caller synchronises. */
+int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_host, int M,
+                               const dsgx_layer_step* step, void* out_host, void* stream);
 
 /* Reads (synchronously) the device status word of a workspace: DSGX_OK or DSGX_ERR_DEVICE_WAIT. */
 int dsgx_ws_status(const void* ws);
