@@ -212,11 +212,25 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     def timed(fn, n):
+        """Device time of exactly n steps.  One GPU: the n steps are captured in one CUDA graph (as a serving engine
+        replays its step graph; the reference benches a graph of 64 steps, altar1
+        engine/experts/tests/bench_experts.cu:46-82) and the replay is timed.  Several GPUs: eager launches."""
+        graph = None
+        if world == 1 and not args.eager:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(n):
+                    fn(i)
+            graph.replay()  # one untimed replay
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(n):
-            fn(i)
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(n):
+                fn(i)
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -272,7 +286,8 @@ def run_gpu(args):
         "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
         "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
                                f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows,
-                   "parallelism": f"ep{world}", "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2"},
+                   "parallelism": f"ep{world}", "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
+                   "launch": "eager" if (world > 1 or args.eager) else "one CUDA graph of the timed steps"},
         "tokens_per_s": rows / (us * 1e-6),
         "step_hbm_gbs": sb_bytes / (us * 1e-6) / 1e9,
         "step_frac_of_measured_hbm": sb_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
@@ -313,6 +328,7 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

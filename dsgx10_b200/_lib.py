@@ -31,7 +31,8 @@ class MoeShape(C.Structure):
 
 
 class DecodeCfg(C.Structure):
-    _fields_ = [("ysum", C.c_int32), ("pdl", C.c_int32), ("parts", C.c_int32), ("reserved", C.c_int32 * 5)]
+    _fields_ = [("ysum", C.c_int32), ("pdl", C.c_int32), ("parts", C.c_int32), ("up", C.c_int32),
+                ("down", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 class LayerStep(C.Structure):

@@ -149,7 +149,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
   if (((uintptr_t)L->pool & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh8 = L->sh.g != nullptr;
   if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds)) return DSGX_ERR_ARG;
-  const dsgx_decode_cfg dflt = {0, 1, 0, {0, 0, 0, 0, 0}};
+  const dsgx_decode_cfg dflt = {0, 1, 0, 0, 0, {0, 0, 0}};
   if (!cfg) cfg = &dflt;
   if (s->fmt == DSGX_FMT_FP8) {
     if (L->sh.bg || L->sh.bu || L->sh.bd) return DSGX_ERR_FORMAT;  // an FP8 layer's shared expert is FP8
@@ -160,6 +160,8 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum;
+    p.up = cfg->up, p.down = cfg->down;
+    if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                       cfg->parts == 0 ? 3 : cfg->parts);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);

@@ -25,12 +25,14 @@ namespace dsgx {
 
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kKCH = 2;  // 128-k blocks a stage and strip
-constexpr int kNST = 3;  // stages a warp
-constexpr int kUpStage = 2 * kKCH * 1024;
-constexpr int kDownStage = 2 * kKCH * 1024 + kKCH * kActBlk;
+// A kernel variant: warps a CTA, 128-k blocks a stage and strip, stages a warp.  Every variant computes the same bits
+// (a unit's sums run over k in the same order whatever the chunking).
+template <int W, int KCH, int NST>
+struct Var {
+  static constexpr int kWarps = W, kThreads = W * 32, kKCH = KCH, kNST = NST;
+  static constexpr int kUpStage = 2 * KCH * 1024;
+  static constexpr int kDownStage = 2 * KCH * 1024 + KCH * kActBlk;
+};
 
 struct SlotTab {
   int nslots;  // routed slots
@@ -52,7 +54,7 @@ DSGX_DEV const float* desc_scales(const uint8_t* pool, const dsgx_mat_desc& d) {
 // The sorted union of the picks in [e_lo, e_hi) and every slot's pointers; DOWN selects the matrices.
 template <bool DOWN>
 DSGX_DEV void build_union(const DecodeParams& p, SlotTab& tab) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, kThreads = blockDim.x;
   if (tid < 16) tab.bm[tid] = 0;
   if (tid == 0) tab.bad = 0;
   for (int i = tid; i < kMaxSlots * 8; i += kThreads) (&tab.w[0][0])[i] = 0.f;
@@ -135,7 +137,9 @@ DSGX_DEV void block_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const
 }
 
 // -------------------------------------------------------------------------------------------------------------- k_up
-__global__ void __launch_bounds__(kThreads, 1) k_up_fp8(const DecodeParams p) {
+template <class V>
+__global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p) {
+  constexpr int kWarps = V::kWarps, kThreads = V::kThreads, kKCH = V::kKCH, kNST = V::kNST, kUpStage = V::kUpStage;
   extern __shared__ __align__(128) uint8_t smem[];
   const int HB = p.H / 128, IB = p.I / 128;
   const int xq_bytes = (HB * kActBlk + 127) & ~127;
@@ -167,14 +171,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_up_fp8(const DecodeParams p) {
   const size_t strip = (size_t)8 * p.H;
   int pu = gw, pc = 0;  // lane 0's producer cursor
   uint32_t issued = 0, consumed = 0;
+  const uint64_t pol = policy_evict_first();  // the weights are read once
   auto issue = [&]() {
     const int slot = ord_slot(tab, pu / upp), i8 = pu % upp;
     const size_t off = (size_t)i8 * strip + (size_t)pc * kKCH * 1024;
     uint8_t* st = myring + (issued % kNST) * kUpStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, kUpStage);
-    bulk_g2s(st, tab.a[slot] + off, kKCH * 1024, bar);
-    bulk_g2s(st + kKCH * 1024, tab.b[slot] + off, kKCH * 1024, bar);
+    bulk_g2s_hint(st, tab.a[slot] + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st + kKCH * 1024, tab.b[slot] + off, kKCH * 1024, bar, pol);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
@@ -252,7 +257,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_up_fp8(const DecodeParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------------------ k_down
-__global__ void __launch_bounds__(kThreads, 1) k_down_fp8(const DecodeParams p) {
+template <class V>
+__global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams p) {
+  constexpr int kWarps = V::kWarps, kThreads = V::kThreads, kKCH = V::kKCH, kNST = V::kNST, kDownStage = V::kDownStage;
   extern __shared__ __align__(128) uint8_t smem[];
   const int IB = p.I / 128, NT = p.H / 16;
   uint8_t* ring = smem;
@@ -280,14 +287,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_down_fp8(const DecodeParams p) 
   const size_t strip = (size_t)8 * p.I;
   int pu = gw, pc = 0;
   uint32_t issued = 0, consumed = 0;
+  const uint64_t pol = policy_evict_first();
   auto issue = [&]() {
     const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
     const size_t off = (size_t)(2 * n16) * strip + (size_t)pc * kKCH * 1024;
     uint8_t* st = myring + (issued % kNST) * kDownStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, kDownStage);
-    bulk_g2s(st, tab.a[slot] + off, kKCH * 1024, bar);
-    bulk_g2s(st + kKCH * 1024, tab.a[slot] + off + strip, kKCH * 1024, bar);
+    bulk_g2s_hint(st, tab.a[slot] + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st + kKCH * 1024, tab.a[slot] + off + strip, kKCH * 1024, bar, pol);
     bulk_g2s(st + 2 * kKCH * 1024, p.ws.hq + ((size_t)slot * IB + (size_t)pc * kKCH) * kActBlk, kKCH * kActBlk, bar);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
@@ -359,32 +367,71 @@ __global__ void __launch_bounds__(kThreads, 1) k_down_fp8(const DecodeParams p) 
   if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
 }
 
+template <class V>
+size_t up_smem(int H) {
+  return (size_t)(((H / 128) * kActBlk + 127) & ~127) + (size_t)V::kWarps * V::kNST * V::kUpStage + V::kWarps * V::kNST * 8 +
+         sizeof(SlotTab) + 16;
+}
+template <class V>
+size_t down_smem() {
+  return (size_t)V::kWarps * V::kNST * V::kDownStage + V::kWarps * V::kNST * 8 + sizeof(SlotTab) + 16;
+}
+
+template <class V>
+cudaError_t launch_up(const DecodeParams& p, cudaStream_t st, bool pdl) {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(k_up_fp8<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)up_smem<V>(4096));
+    if (e != cudaSuccess) return e;
+    done[dev & 63] = true;
+  }
+  return launch_k(k_up_fp8<V>, dim3(sm_count()), dim3(V::kThreads), up_smem<V>(p.H), st, pdl, p);
+}
+template <class V>
+cudaError_t launch_down(const DecodeParams& p, cudaStream_t st, bool pdl) {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(k_down_fp8<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)down_smem<V>());
+    if (e != cudaSuccess) return e;
+    done[dev & 63] = true;
+  }
+  return launch_k(k_down_fp8<V>, dim3(sm_count()), dim3(V::kThreads), down_smem<V>(), st, pdl, p);
+}
+
 }  // namespace
 
-static size_t up_smem(int H) {
-  return (size_t)(((H / 128) * kActBlk + 127) & ~127) + (size_t)kWarps * kNST * kUpStage + kWarps * kNST * 8 + sizeof(SlotTab) + 16;
-}
-static size_t down_smem() { return (size_t)kWarps * kNST * kDownStage + kWarps * kNST * 8 + sizeof(SlotTab) + 16; }
+int decode_fp8_up_variants() { return 7; }
+int decode_fp8_down_variants() { return 5; }
 
 cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
-  static bool attr_done = false;
-  const size_t su = up_smem(4096), sd = down_smem();
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(k_up_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)su);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k_down_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sd);
-    if (e != cudaSuccess) return e;
-    attr_done = true;
-  }
-  const int ctas = sm_count();
   cudaError_t e = cudaSuccess;
   if (parts & 1) {
     e = launch_act_quant_tiled(x, p.M, p.H, p.ws.xq, st, pdl);
     if (e != cudaSuccess) return e;
-    e = launch_k(k_up_fp8, dim3(ctas), dim3(kThreads), up_smem(p.H), st, pdl, p);
+    switch (p.up) {
+      case 1: e = launch_up<Var<8, 4, 2>>(p, st, pdl); break;
+      case 2: e = launch_up<Var<8, 2, 5>>(p, st, pdl); break;
+      case 3: e = launch_up<Var<4, 8, 2>>(p, st, pdl); break;
+      case 4: e = launch_up<Var<16, 2, 2>>(p, st, pdl); break;
+      case 5: e = launch_up<Var<16, 1, 5>>(p, st, pdl); break;
+      case 6: e = launch_up<Var<12, 2, 3>>(p, st, pdl); break;
+      default: e = launch_up<Var<8, 2, 3>>(p, st, pdl); break;
+    }
     if (e != cudaSuccess) return e;
   }
-  if (parts & 2) e = launch_k(k_down_fp8, dim3(ctas), dim3(kThreads), sd, st, pdl, p);
+  if (parts & 2) {
+    switch (p.down) {
+      case 1: e = launch_down<Var<8, 4, 2>>(p, st, pdl); break;
+      case 2: e = launch_down<Var<4, 8, 2>>(p, st, pdl); break;
+      case 3: e = launch_down<Var<16, 1, 4>>(p, st, pdl); break;
+      case 4: e = launch_down<Var<16, 2, 2>>(p, st, pdl); break;
+      default: e = launch_down<Var<8, 2, 3>>(p, st, pdl); break;
+    }
+  }
   return e;
 }
 

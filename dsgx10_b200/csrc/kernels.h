@@ -57,7 +57,10 @@ struct DecodeParams {
   float* yr;
   float* ys;
   int ysum;
+  int up, down;  // kernel variants (same bits)
 };
+int decode_fp8_up_variants();
+int decode_fp8_down_variants();
 // parts: 1 = activation quantisation + gate/up, 2 = down + combine, 3 = both
 cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
 

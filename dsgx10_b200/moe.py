@@ -70,14 +70,14 @@ def decode_ws(shp, device="cuda"):
     return torch.zeros(decode_ws_bytes(shp), dtype=torch.uint8, device=device)
 
 
-def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True, parts=0):
+def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True, parts=0, up=0, down=0):
     """x bf16 [M][H]; idx, w from route(); returns (yr, ys) f32 [M][H]: this GPU's partial sums."""
     M, H = x.shape
     if yr is None:
         yr = torch.empty(M, H, dtype=torch.float32, device=x.device)
     if ys is None:
         ys = torch.empty(M, H, dtype=torch.float32, device=x.device)
-    cfg = _lib.DecodeCfg(int(ysum), int(pdl), int(parts))
+    cfg = _lib.DecodeCfg(int(ysum), int(pdl), int(parts), int(up), int(down))
     check(lib().dsgx_moe_decode(C.byref(shp), C.byref(layer_w), _ptr(x), _ptr(idx), _ptr(w), M, _ptr(ws), _ptr(yr),
                                 _ptr(ys), _stream(), C.byref(cfg)), "dsgx_moe_decode")
     return yr, ys

@@ -123,7 +123,8 @@ typedef struct dsgx_decode_cfg {
   int32_t ysum;        /* 1: ys is added into yr after the routed experts and yr is the only output (experts.h:132-137) */
   int32_t pdl;         /* 1: launch with programmatic dependent launch (experts.h:120) */
   int32_t parts;       /* bench hook (experts.h:121): 0 or 3 the whole step, 1 gate/up only, 2 down only */
-  int32_t reserved[5];
+  int32_t up, down;    /* kernel variants (experts.h:114-118): 0 the default; every variant gives the same bits */
+  int32_t reserved[3];
 } dsgx_decode_cfg;
 size_t dsgx_decode_ws_bytes(const dsgx_moe_shape* shape);
 int dsgx_moe_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, const int32_t* idx,
