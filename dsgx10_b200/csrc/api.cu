@@ -38,6 +38,8 @@ size_t decode_ws_bytes(int H, int I) {
   n += al256((size_t)kMaxSlots * (H / 16) * 128 * 4);
   n += al256((size_t)kMaxSlots * IB * 4);
   n += al256((size_t)(H / 16) * 4);
+  n += kSlotTabBytes;
+  n += al256((size_t)((H + 1023) / 1024) * kMaxRows * 512 * 4);
   return n;
 }
 DecodeWs decode_ws_carve(void* ws, int H, int I) {
@@ -50,7 +52,9 @@ DecodeWs decode_ws_carve(void* ws, int H, int I) {
   w.hq = reinterpret_cast<uint8_t*>(p), p += al256((size_t)kMaxSlots * IB * kActBlk);
   w.ypick = reinterpret_cast<float*>(p), p += al256((size_t)kMaxSlots * (H / 16) * 128 * 4);
   w.cnt_h = reinterpret_cast<int*>(p), p += al256((size_t)kMaxSlots * IB * 4);
-  w.cnt_y = reinterpret_cast<int*>(p);
+  w.cnt_y = reinterpret_cast<int*>(p), p += al256((size_t)(H / 16) * 4);
+  w.tab = reinterpret_cast<SlotTab*>(p), p += kSlotTabBytes;
+  w.lpart = reinterpret_cast<float*>(p);
   return w;
 }
 
@@ -159,7 +163,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
     p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
-    p.yr = yr, p.ys = ys, p.ysum = cfg->ysum;
+    p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr;
     p.up = cfg->up, p.down = cfg->down;
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
@@ -181,6 +185,25 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
   if (finalize && !st->out_bf16) return DSGX_ERR_ARG;
   int rc = check_shape(s);
   if (rc) return rc;
+  if (s->fmt == DSGX_FMT_FP8) {
+    if (!L || !x || !L->pool || !L->desc || L->fmt != s->fmt) return DSGX_ERR_ARG;
+    if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
+    if (((uintptr_t)L->pool & 255) || ((uintptr_t)st->ws & 255) || ((uintptr_t)x & 15) || ((uintptr_t)st->wr & 15))
+      return DSGX_ERR_ARG;
+    const bool sh8 = L->sh.g != nullptr;
+    if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds || !st->ys)) return DSGX_ERR_ARG;
+    DecodeParams p;
+    p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
+    p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
+    p.idx = st->idx, p.w = st->w;
+    p.ws = decode_ws_carve(st->ws, s->H, s->I);
+    p.yr = st->yr, p.ys = st->ys, p.ysum = 0, p.up = 0, p.down = 0;
+    p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
+    RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
+    cudaError_t e = launch_layer_fp8(p, rp, reinterpret_cast<const __nv_bfloat16*>(x), st->wr, st->bias, st->logits,
+                                     st->idx, st->w, (cudaStream_t)stream, true);
+    return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+  }
   rc = dsgx_router_logits(x, st->wr, M, s->H, s->E, st->logits, stream);
   if (rc) return rc;
   rc = dsgx_route(s, st->logits, st->bias, M, st->idx, st->w, stream);

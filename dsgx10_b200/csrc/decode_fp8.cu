@@ -1,25 +1,31 @@
 // FP8 (e4m3, 128x128 block-scaled, W8A8-g128) expert step for 1..8 rows: an HBM-bound weight stream.
 //
-// Two persistent kernels, one CTA a SM, eight warps a CTA.  Every warp is its own producer and consumer: lane 0 issues
-// bulk async copies (the untiled TMA path) of the next chunks of its unit's two weight strips into the warp's private
-// ring in shared memory, an mbarrier per stage counts the bytes in, and the whole warp then feeds the chunk to
-// m16n8k32 e4m3 MMAs with the weights as the A operand (16 output channels x 32 k) and the quantised activations as B
-// (32 k x 8 rows).  One 128-k block is four MMAs into a fresh accumulator, promoted into the f32 sums with the
-// product of the block's weight scale and the row's activation scale.
+// Persistent kernels, one CTA a SM.  Every warp is its own producer and consumer: lane 0 issues bulk async copies
+// (the untiled TMA path) of the next chunks of its unit's two weight strips into the warp's private ring in shared
+// memory, an mbarrier per stage counts the bytes in, and the whole warp then feeds the chunk to m16n8k32 e4m3 MMAs with
+// the weights as the A operand (16 output channels x 32 k) and the quantised activations as B (32 k x 8 rows).  One
+// 128-k block is four MMAs into a fresh accumulator, promoted into the f32 sums with the product of the block's
+// weight scale and the row's activation scale.
 //
-//   k_up:   unit = (slot, 8 intermediate channels): A rows 0-7 = gate, rows 8-15 = up, so a lane ends with gate and up
-//           of the same (channel, row) and applies SwiGLU in place.  The 16th unit to finish a 128-group of h
-//           quantises the group for the down kernel (a ticket, no waiting).
-//   k_down: unit = (slot, 16 output channels); every pick's output is rounded to bf16, parked, and the last slot to
-//           finish an output tile adds the tile's picks in ascending expert id (a ticket again) and writes yr / ys.
-//
-// Slots: the sorted union of the rows' picked experts that this GPU owns, then the shared expert.  A row that did not
-// pick a slot's expert runs with routing weight 0: its h, and so its output, is exactly 0.
+//   k_front:       (layer step) router logit partial sums, one warp per (expert, 1024-k slice), all loads in one
+//                  round trip; the other CTAs quantise x per 128 values.
+//   k_route_union: (layer step) one CTA: sums the slices, routes the rows (route.cuh), builds the slot table.
+//   k_prep:        (moe_decode with the caller's idx / w) the slot table + the quantisation of x.
+//   k_up:          unit = (slot, 8 intermediate channels): A rows 0-7 = gate, rows 8-15 = up, so a lane ends with gate
+//                  and up of the same (channel, row) and applies SwiGLU in place.  The 16th unit to finish a
+//                  128-group of h quantises the group for the down kernel (a ticket, no waiting).
+//   k_down:        unit = (slot, 16 output channels); every pick's output is rounded to bf16, parked, and the last slot
+//                  to finish an output tile adds the tile's picks in ascending expert id (a ticket again) and writes
+//                  yr / ys (and, when asked, the rounded sum).
+// The ticket of a finished unit is taken while the next unit already streams (fence and atomic are issued one chunk
+// later, the answer is read another chunk later), so the stream never waits for a round trip to L2.
 //
 // Weight layout consumed as is: the reference's tile_fp8 ([N/8][K/128][32 lanes][32 B]; altar1
 // engine/experts/layout.h:108-119), so an 8-row strip of a matrix is one contiguous run of 8 K bytes.
 #include "common.cuh"
+#include "decode_common.cuh"
 #include "kernels.h"
+#include "route.cuh"
 
 namespace dsgx {
 
@@ -34,119 +40,165 @@ struct Var {
   static constexpr int kDownStage = 2 * KCH * 1024 + KCH * kActBlk;
 };
 
-struct SlotTab {
-  int nslots;  // routed slots
-  int ntot;    // + the shared expert's
-  int bad;
-  uint32_t bm[16];
-  int e[kMaxSlots];
-  float w[kMaxSlots][8];
-  const uint8_t* a[kMaxSlots];  // k_up: gate, k_down: down
-  const uint8_t* b[kMaxSlots];  // k_up: up
-  const float* sa[kMaxSlots];
-  const float* sb[kMaxSlots];
-};
-
-DSGX_DEV const float* desc_scales(const uint8_t* pool, const dsgx_mat_desc& d) {
-  return reinterpret_cast<const float*>(pool + ((uint64_t)d.rsv[0] | (uint64_t)d.rsv[1] << 32));
-}
-
-// The sorted union of the picks in [e_lo, e_hi) and every slot's pointers; DOWN selects the matrices.
-template <bool DOWN>
-DSGX_DEV void build_union(const DecodeParams& p, SlotTab& tab) {
-  const int tid = threadIdx.x, kThreads = blockDim.x;
-  if (tid < 16) tab.bm[tid] = 0;
-  if (tid == 0) tab.bad = 0;
-  for (int i = tid; i < kMaxSlots * 8; i += kThreads) (&tab.w[0][0])[i] = 0.f;
-  __syncthreads();
-  const int np = p.M * p.topk;
-  for (int i = tid; i < np; i += kThreads) {
-    const int e = p.idx[i];
-    if (e < 0 || e >= p.E) tab.bad = DSGX_ERR_ARG;
-    else if (e >= p.e_lo && e < p.e_hi) atomicOr(&tab.bm[e >> 5], 1u << (e & 31));
-  }
-  __syncthreads();
-  auto rank_of = [&](int e) {
-    int r = __popc(tab.bm[e >> 5] & ((1u << (e & 31)) - 1u));
-    for (int w = 0; w < (e >> 5); ++w) r += __popc(tab.bm[w]);
-    return r;
-  };
-  for (int e = tid; e < p.E; e += kThreads)
-    if ((tab.bm[e >> 5] >> (e & 31)) & 1) {
-      const int s = rank_of(e);
-      tab.e[s] = e;
-      const dsgx_mat_desc* d = p.desc + (size_t)e * 3;
-      if (DOWN) {
-        if (d[2].fmt != DSGX_FMT_FP8) tab.bad = DSGX_ERR_FORMAT;
-        tab.a[s] = p.pool + d[2].off, tab.sa[s] = desc_scales(p.pool, d[2]);
-        tab.b[s] = nullptr, tab.sb[s] = nullptr;
-      } else {
-        if (d[0].fmt != DSGX_FMT_FP8 || d[1].fmt != DSGX_FMT_FP8) tab.bad = DSGX_ERR_FORMAT;
-        tab.a[s] = p.pool + d[0].off, tab.sa[s] = desc_scales(p.pool, d[0]);
-        tab.b[s] = p.pool + d[1].off, tab.sb[s] = desc_scales(p.pool, d[1]);
-      }
-    }
-  if (tid == 0) {
-    int n = 0;
-    for (int w = 0; w < 16; ++w) n += __popc(tab.bm[w]);
-    tab.nslots = n;
-    const bool sh = p.sh.g != nullptr;
-    tab.ntot = n + (sh ? 1 : 0);
-    if (sh) {
-      tab.e[n] = -1;
-      if (DOWN) tab.a[n] = p.sh.d, tab.sa[n] = p.sh.ds, tab.b[n] = nullptr, tab.sb[n] = nullptr;
-      else tab.a[n] = p.sh.g, tab.sa[n] = p.sh.gs, tab.b[n] = p.sh.u, tab.sb[n] = p.sh.us;
-    }
-  }
-  for (int i = tid; i < np; i += kThreads) {
-    const int e = p.idx[i];
-    if (e >= p.e_lo && e < p.e_hi && e >= 0 && e < p.E) tab.w[rank_of(e)][i / p.topk] = p.w[i];
-  }
-  __syncthreads();
-  if (tab.bad) {  // refuse the routed work, keep the kernel well-defined
-    if (tid == 0) {
-      atomicCAS(p.ws.status, 0, tab.bad);
-      tab.ntot -= tab.nslots, tab.nslots = 0;
-      if (p.sh.g != nullptr) {
-        tab.e[0] = -1;
-        if (DOWN) tab.a[0] = p.sh.d, tab.sa[0] = p.sh.ds;
-        else tab.a[0] = p.sh.g, tab.sa[0] = p.sh.gs, tab.b[0] = p.sh.u, tab.sb[0] = p.sh.us;
-      }
-    }
-    __syncthreads();
-  }
-}
-
-// order position -> slot: the shared expert's units come first (they are the same every step)
-DSGX_DEV int ord_slot(const SlotTab& tab, int ord) {
-  return tab.ntot > tab.nslots ? (ord == 0 ? tab.nslots : ord - 1) : ord;
-}
-
-DSGX_DEV uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+constexpr int kTabSmem = (sizeof(SlotTab) + 127) & ~127;
+static_assert(sizeof(SlotTab) <= kSlotTabBytes, "workspace room for the slot table");
 
 // One 128-k block: A rows 0-7 from strip a, rows 8-15 from strip b, B from the activation block.
 DSGX_DEV void block_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int lane) {
   const uint4 a0 = lds128(a + 32 * lane), a1 = lds128(a + 32 * lane + 16);
   const uint4 b0 = lds128(b + 32 * lane), b1 = lds128(b + 32 * lane + 16);
   const uint4 x0 = lds128(act + 16 * lane), x1 = lds128(act + 512 + 16 * lane);
+  float e[4] = {0.f, 0.f, 0.f, 0.f};
   d[0] = d[1] = d[2] = d[3] = 0.f;
   mma_e4m3(d, a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
+  mma_e4m3(e, a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
   mma_e4m3(d, a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
-  mma_e4m3(d, a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
-  mma_e4m3(d, a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+  mma_e4m3(e, a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+  d[0] += e[0], d[1] += e[1], d[2] += e[2], d[3] += e[3];
+}
+
+// quantises one row's 128 values (4 per lane, k = 4 lane ..) into an activation block
+DSGX_DEV void quant_row_to_block(uint8_t* blk, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {
+  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
+  uint32_t packed = 0;
+  float sc = 0.f;
+  if (valid) {
+    sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
+    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  }
+  *reinterpret_cast<uint32_t*>(blk + (q * 32 + 4 * r + t) * 16 + i) = packed;
+  if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
+}
+
+DSGX_DEV void quant_x_block(const __nv_bfloat16* __restrict__ x, int M, int K, uint8_t* out, int j, int r, int lane) {
+  float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+  if (r < M) {
+    const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * K + 128 * j + 4 * lane));
+    v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
+    v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+  }
+  quant_row_to_block(out + (size_t)j * kActBlk, r, lane, r < M, v0, v1, v2, v3);
+}
+
+// ----------------------------------------------------------------------------------------------------------- k_front
+// CTAs [0, nlog): one warp per (expert, slice of 1024 k): the slice's partial logit of every row, in the router's
+// summation order (lane j: k = base + 128 i + 4 j + c by fma, then the butterfly).  CTAs [nlog, ..): x -> blocks.
+__global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M,
+                                               int H, int E, int nlog, float* __restrict__ lpart, uint8_t* __restrict__ xq) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if ((int)blockIdx.x >= nlog) {
+    if (!xq) return;
+    const int gw = ((int)blockIdx.x - nlog) * 8 + warp;
+    const int j = gw >> 3, r = gw & 7;
+    if (j < H / 128) quant_x_block(x, M, H, xq, j, r, lane);
+    return;
+  }
+  const int KS = (H + 1023) / 1024;
+  const int gw = blockIdx.x * 8 + warp;
+  const int e = gw / KS, sl = gw % KS;
+  if (e >= E) return;
+  const int base = sl * 1024, nit = min(1024, H - base) / 128;
+  float4 wv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    wv[i] = i < nit ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)e * H + base + 128 * i + 4 * lane))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < M; ++r) {
+    uint2 xv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      xv[i] = i < nit ? __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * H + base + 128 * i + 4 * lane)) : make_uint2(0, 0);
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nit) {
+        a = fmaf(bf16_bits_to_f(xv[i].x & 0xffffu), wv[i].x, a);
+        a = fmaf(bf16_bits_to_f(xv[i].x >> 16), wv[i].y, a);
+        a = fmaf(bf16_bits_to_f(xv[i].y & 0xffffu), wv[i].z, a);
+        a = fmaf(bf16_bits_to_f(xv[i].y >> 16), wv[i].w, a);
+      }
+    a = warp_sum(a);
+    if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------- k_route_union
+struct TabArgs {
+  int M, topk, E, e_lo, e_hi;
+  const uint8_t* pool;
+  const dsgx_mat_desc* desc;
+  dsgx_shared_w sh;
+  uint32_t fmt;
+};
+
+DSGX_DEV void store_tab(const SlotTab& tab, SlotTab* out) {
+  const uint4* s = reinterpret_cast<const uint4*>(&tab);
+  uint4* d = reinterpret_cast<uint4*>(out);
+  for (int i = threadIdx.x; i < (int)(sizeof(SlotTab) / 16); i += blockDim.x) d[i] = s[i];
+}
+
+// One CTA of 8 warps: warp r routes row r from the logit slices, then the CTA builds the slot table.
+__global__ void __launch_bounds__(256) k_route_union(RouteParams rp, TabArgs ta, const float* __restrict__ lpart, int nsplit,
+                                                     const float* __restrict__ bias, float* __restrict__ logits,
+                                                     int* __restrict__ idx, float* __restrict__ w, SlotTab* __restrict__ out,
+                                                     int* __restrict__ status) {
+  __shared__ SlotTab tab;
+  __shared__ uint32_t bm[16];
+  __shared__ int s_idx[kMaxRows * kMaxTopK];
+  __shared__ float s_w[kMaxRows * kMaxTopK];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp < ta.M) {
+    int id;
+    float wt;
+    route_row(rp, lpart + (size_t)warp * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, lane, id, wt,
+              logits ? logits + (size_t)warp * rp.E : nullptr);
+    if (lane < rp.topk) {
+      s_idx[warp * rp.topk + lane] = id, s_w[warp * rp.topk + lane] = wt;
+      idx[warp * rp.topk + lane] = id, w[warp * rp.topk + lane] = wt;
+    }
+  }
+  __syncthreads();
+  build_slot_tab(tab, bm, s_idx, s_w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
+  if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
+  store_tab(tab, out);
+}
+
+// ------------------------------------------------------------------------------------------------------------ k_prep
+// CTA 0: the slot table from the caller's idx / w.  CTAs 1..: x -> blocks.
+__global__ void __launch_bounds__(256) k_prep(TabArgs ta, const int* __restrict__ idx, const float* __restrict__ w,
+                                              const __nv_bfloat16* __restrict__ x, int H, uint8_t* __restrict__ xq,
+                                              SlotTab* __restrict__ out, int* __restrict__ status) {
+  __shared__ SlotTab tab;
+  __shared__ uint32_t bm[16];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (blockIdx.x == 0) {
+    build_slot_tab(tab, bm, idx, w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
+    if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
+    store_tab(tab, out);
+    return;
+  }
+  const int lane = threadIdx.x & 31, gw = ((int)blockIdx.x - 1) * 8 + (threadIdx.x >> 5);
+  const int j = gw >> 3, r = gw & 7;
+  if (j < H / 128) quant_x_block(x, ta.M, H, xq, j, r, lane);
 }
 
 // -------------------------------------------------------------------------------------------------------------- k_up
 template <class V>
 __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p) {
-  constexpr int kWarps = V::kWarps, kThreads = V::kThreads, kKCH = V::kKCH, kNST = V::kNST, kUpStage = V::kUpStage;
+  constexpr int kWarps = V::kWarps, kKCH = V::kKCH, kNST = V::kNST, kUpStage = V::kUpStage;
   extern __shared__ __align__(128) uint8_t smem[];
   const int HB = p.H / 128, IB = p.I / 128;
   const int xq_bytes = (HB * kActBlk + 127) & ~127;
   uint8_t* xq = smem;
-  uint8_t* ring = smem + xq_bytes;
+  SlotTab& tab = *reinterpret_cast<SlotTab*>(smem + xq_bytes);
+  uint8_t* ring = smem + xq_bytes + kTabSmem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kWarps * kNST * kUpStage);
-  SlotTab& tab = *reinterpret_cast<SlotTab*>(bars + kWarps * kNST);
+  uint64_t* cbar = bars + kWarps * kNST;  // the CTA's barrier for the table and x
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* myring = ring + warp * kNST * kUpStage;
   uint64_t* mybar = bars + warp * kNST;
@@ -154,18 +206,19 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   pdl_launch_dependents();
   if (lane == 0)
     for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
+  if (threadIdx.x == 0) mbar_init(cbar, 1);
   mbar_fence_init();
-  pdl_wait();
-  build_union<false>(p, tab);
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(p.ws.xq);
-    uint4* dst = reinterpret_cast<uint4*>(xq);
-    for (int i = threadIdx.x; i < HB * kActBlk / 16; i += kThreads) dst[i] = src[i];
-  }
   __syncthreads();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(cbar, (uint32_t)(sizeof(SlotTab) + HB * kActBlk));
+    bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), cbar);
+    bulk_g2s(xq, p.ws.xq, HB * kActBlk, cbar);
+  }
+  bool dead = !mbar_wait(cbar, 0);
 
   const int upp = p.I / 8;  // units a slot
-  const int total = tab.ntot * upp;
+  const int total = dead ? 0 : tab.ntot * upp;
   const int GW = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
   const int cpu = HB / kKCH;  // chunks a unit
   const size_t strip = (size_t)8 * p.H;
@@ -178,8 +231,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
     uint8_t* st = myring + (issued % kNST) * kUpStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, kUpStage);
-    bulk_g2s_hint(st, tab.a[slot] + off, kKCH * 1024, bar, pol);
-    bulk_g2s_hint(st + kKCH * 1024, tab.b[slot] + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st, tab.g[slot] + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st + kKCH * 1024, tab.u[slot] + off, kKCH * 1024, bar, pol);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
@@ -187,12 +240,39 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
     for (int s = 0; s < kNST && pu < total; ++s) issue();
 
   const int g = lane >> 2, t = lane & 3;
-  bool dead = false;
+  // the finished unit whose ticket is still to be taken (1), or whose ticket is in flight (2)
+  int pend = 0, pend_slot = 0, pend_gi = 0, pend_ticket = 0;
+  auto advance = [&]() {
+    if (pend == 1) {
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) pend_ticket = atomicAdd(p.ws.cnt_h + pend_slot * IB + pend_gi, 1);
+      pend = 2;
+    } else if (pend == 2) {
+      const int ticket = __shfl_sync(0xffffffffu, pend_ticket, 0);
+      if (ticket == 15) {  // the 16th unit of a 128-group of h quantises it
+        __threadfence();
+        const __nv_bfloat16* hrow = p.ws.h + (size_t)pend_slot * 8 * p.I + 128 * pend_gi + 4 * lane;
+        uint8_t* blk = p.ws.hq + ((size_t)pend_slot * IB + pend_gi) * kActBlk;
+        uint2 hv[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          hv[r] = r < p.M ? __ldcg(reinterpret_cast<const uint2*>(hrow + (size_t)r * p.I)) : make_uint2(0, 0);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          quant_row_to_block(blk, r, lane, r < p.M, bf16_bits_to_f(hv[r].x & 0xffffu), bf16_bits_to_f(hv[r].x >> 16),
+                             bf16_bits_to_f(hv[r].y & 0xffffu), bf16_bits_to_f(hv[r].y >> 16));
+        if (lane == 0) p.ws.cnt_h[pend_slot * IB + pend_gi] = 0;
+      }
+      pend = 0;
+    }
+  };
+
   for (int unit = gw; unit < total && !dead; unit += GW) {
     const int slot = ord_slot(tab, unit / upp), i8 = unit % upp;
     const int srow = (i8 * 8) / 128;
-    const float sgl = lane < HB ? __ldg(tab.sa[slot] + (size_t)srow * HB + lane) : 0.f;
-    const float sul = lane < HB ? __ldg(tab.sb[slot] + (size_t)srow * HB + lane) : 0.f;
+    const float sgl = lane < HB ? __ldg(tab.sg[slot] + (size_t)srow * HB + lane) : 0.f;
+    const float sul = lane < HB ? __ldg(tab.su[slot] + (size_t)srow * HB + lane) : 0.f;
     float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
     for (int c = 0; c < cpu; ++c) {
       const uint32_t sidx = consumed % kNST;
@@ -215,8 +295,10 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
       ++consumed;
       __syncwarp();
       if (lane == 0 && pu < total) issue();
+      advance();
     }
     if (dead) break;
+    while (pend) advance();
     // SwiGLU: g, u rounded to bf16; h = bf16(w_route * silu(g) * u) (no weight for the shared expert)
     const bool routed = slot < tab.nslots;
     const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
@@ -226,33 +308,10 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
     __nv_bfloat16* hrow = p.ws.h + (size_t)slot * 8 * p.I;
     if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
     if (r1 < p.M) hrow[(size_t)r1 * p.I + ch] = __float2bfloat16_rn(h1);
-    // the 16th unit of a 128-group of h quantises it
-    const int gi = i8 / 16;
-    __threadfence();
-    __syncwarp();
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(p.ws.cnt_h + slot * IB + gi, 1);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket == 15) {
-      __threadfence();
-      uint8_t* blk = p.ws.hq + ((size_t)slot * IB + gi) * kActBlk;
-      const int kl = 4 * lane, q = kl >> 6, tt = (kl >> 4) & 3, ii = kl & 15;
-      for (int r = 0; r < 8; ++r) {
-        uint32_t packed = 0;
-        float sc = 0.f;
-        if (r < p.M) {
-          const uint2 hv = __ldcg(reinterpret_cast<const uint2*>(hrow + (size_t)r * p.I + 128 * gi + kl));
-          const float v0 = bf16_bits_to_f(hv.x & 0xffffu), v1 = bf16_bits_to_f(hv.x >> 16);
-          const float v2 = bf16_bits_to_f(hv.y & 0xffffu), v3 = bf16_bits_to_f(hv.y >> 16);
-          sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
-          packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
-        }
-        *reinterpret_cast<uint32_t*>(blk + (q * 32 + 4 * r + tt) * 16 + ii) = packed;
-        if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
-      }
-      if (lane == 0) p.ws.cnt_h[slot * IB + gi] = 0;
-    }
+    pend = 1, pend_slot = slot, pend_gi = i8 / 16;
   }
+  if (!dead)
+    while (pend) advance();
   if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
 }
 
@@ -262,9 +321,10 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   constexpr int kWarps = V::kWarps, kThreads = V::kThreads, kKCH = V::kKCH, kNST = V::kNST, kDownStage = V::kDownStage;
   extern __shared__ __align__(128) uint8_t smem[];
   const int IB = p.I / 128, NT = p.H / 16;
-  uint8_t* ring = smem;
+  SlotTab& tab = *reinterpret_cast<SlotTab*>(smem);
+  uint8_t* ring = smem + kTabSmem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kWarps * kNST * kDownStage);
-  SlotTab& tab = *reinterpret_cast<SlotTab*>(bars + kWarps * kNST);
+  uint64_t* cbar = bars + kWarps * kNST;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* myring = ring + warp * kNST * kDownStage;
   uint64_t* mybar = bars + warp * kNST;
@@ -272,17 +332,25 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   pdl_launch_dependents();
   if (lane == 0)
     for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
+  if (threadIdx.x == 0) mbar_init(cbar, 1);
   mbar_fence_init();
+  __syncthreads();
   pdl_wait();
-  build_union<true>(p, tab);
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(cbar, (uint32_t)sizeof(SlotTab));
+    bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), cbar);
+  }
+  bool dead = !mbar_wait(cbar, 0);
 
   const int GW = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
-  if (tab.ntot == 0) {  // nothing to add on this GPU: the partial sum is zero
-    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kThreads)
+  if (!dead && tab.ntot == 0) {  // nothing to add on this GPU: the partial sum is zero
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kThreads) {
       p.yr[i] = 0.f;
+      if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
+    }
     return;
   }
-  const int total = tab.ntot * NT;
+  const int total = dead ? 0 : tab.ntot * NT;
   const int cpu = IB / kKCH;
   const size_t strip = (size_t)8 * p.I;
   int pu = gw, pc = 0;
@@ -294,8 +362,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
     uint8_t* st = myring + (issued % kNST) * kDownStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, kDownStage);
-    bulk_g2s_hint(st, tab.a[slot] + off, kKCH * 1024, bar, pol);
-    bulk_g2s_hint(st + kKCH * 1024, tab.a[slot] + off + strip, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st, tab.d[slot] + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st + kKCH * 1024, tab.d[slot] + off + strip, kKCH * 1024, bar, pol);
     bulk_g2s(st + 2 * kKCH * 1024, p.ws.hq + ((size_t)slot * IB + (size_t)pc * kKCH) * kActBlk, kKCH * kActBlk, bar);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
@@ -304,11 +372,56 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
     for (int s = 0; s < kNST && pu < total; ++s) issue();
 
   const int g = lane >> 2, t = lane & 3;
-  bool dead = false;
+  int pend = 0, pend_n16 = 0, pend_ticket = 0;
+  auto advance = [&]() {
+    if (pend == 1) {
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) pend_ticket = atomicAdd(p.ws.cnt_y + pend_n16, 1);
+      pend = 2;
+    } else if (pend == 2) {
+      const int ticket = __shfl_sync(0xffffffffu, pend_ticket, 0);
+      if (ticket == tab.ntot - 1) {  // the tile's last slot: add its picks in ascending expert id, the shared expert last
+        __threadfence();
+        const int n16 = pend_n16, ch = lane >> 1, r0 = 4 * (lane & 1);
+        const float* yt = p.ws.ypick + (size_t)n16 * 128 + ch * 8 + r0;
+        const bool sh = tab.ntot > tab.nslots;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        int s = 0;
+        for (; s + 4 <= tab.nslots; s += 4) {  // four loads in flight, added in order
+          float4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)(s + j) * NT * 128));
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            a.x = __fadd_rn(a.x, v[j].x), a.y = __fadd_rn(a.y, v[j].y), a.z = __fadd_rn(a.z, v[j].z), a.w = __fadd_rn(a.w, v[j].w);
+        }
+        for (; s < tab.nslots; ++s) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)s * NT * 128));
+          a.x = __fadd_rn(a.x, v.x), a.y = __fadd_rn(a.y, v.y), a.z = __fadd_rn(a.z, v.z), a.w = __fadd_rn(a.w, v.w);
+        }
+        float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sh) sv = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)tab.nslots * NT * 128));
+        const float av[4] = {a.x, a.y, a.z, a.w}, svv[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (r0 + c < p.M) {
+            const size_t o = (size_t)(r0 + c) * p.H + n16 * 16 + ch;
+            const float both = __fadd_rn(av[c], svv[c]);
+            p.yr[o] = p.ysum && sh ? both : av[c];
+            if (sh && p.ys) p.ys[o] = svv[c];
+            if (p.out) p.out[o] = __float2bfloat16_rn(both);
+          }
+        if (lane == 0) p.ws.cnt_y[n16] = 0;
+      }
+      pend = 0;
+    }
+  };
+
   for (int unit = gw; unit < total && !dead; unit += GW) {
     const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
     const int srow = (n16 * 16) / 128;
-    const float sdl = lane < IB ? __ldg(tab.sa[slot] + (size_t)srow * IB + lane) : 0.f;
+    const float sdl = lane < IB ? __ldg(tab.sd[slot] + (size_t)srow * IB + lane) : 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 0; c < cpu; ++c) {
       const uint32_t sidx = consumed % kNST;
@@ -331,50 +444,29 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
       ++consumed;
       __syncwarp();
       if (lane == 0 && pu < total) issue();
+      advance();
     }
     if (dead) break;
+    while (pend) advance();
     // every pick's output is rounded to bf16 before the f32 adds
     float* yt = p.ws.ypick + ((size_t)slot * NT + n16) * 128;
     *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
     *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
-    __threadfence();
-    __syncwarp();
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(p.ws.cnt_y + n16, 1);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket == tab.ntot - 1) {  // the tile's last slot: add its picks in ascending expert id, the shared expert last
-      __threadfence();
-      const int ch = lane >> 1, r0 = 4 * (lane & 1);
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int s = 0; s < tab.nslots; ++s) {
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws.ypick + ((size_t)s * NT + n16) * 128 + ch * 8 + r0));
-        a.x = __fadd_rn(a.x, v.x), a.y = __fadd_rn(a.y, v.y), a.z = __fadd_rn(a.z, v.z), a.w = __fadd_rn(a.w, v.w);
-      }
-      const bool sh = tab.ntot > tab.nslots;
-      float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (sh) sv = __ldcg(reinterpret_cast<const float4*>(p.ws.ypick + ((size_t)tab.nslots * NT + n16) * 128 + ch * 8 + r0));
-      const float av[4] = {a.x, a.y, a.z, a.w}, svv[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        if (r0 + c < p.M) {
-          const size_t o = (size_t)(r0 + c) * p.H + n16 * 16 + ch;
-          p.yr[o] = p.ysum && sh ? __fadd_rn(av[c], svv[c]) : av[c];
-          if (sh && p.ys) p.ys[o] = svv[c];
-        }
-      if (lane == 0) p.ws.cnt_y[n16] = 0;
-    }
+    pend = 1, pend_n16 = n16;
   }
+  if (!dead)
+    while (pend) advance();
   if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
 }
 
 template <class V>
 size_t up_smem(int H) {
-  return (size_t)(((H / 128) * kActBlk + 127) & ~127) + (size_t)V::kWarps * V::kNST * V::kUpStage + V::kWarps * V::kNST * 8 +
-         sizeof(SlotTab) + 16;
+  return (size_t)(((H / 128) * kActBlk + 127) & ~127) + kTabSmem + (size_t)V::kWarps * V::kNST * V::kUpStage +
+         (V::kWarps * V::kNST + 1) * 8 + 16;
 }
 template <class V>
 size_t down_smem() {
-  return (size_t)V::kWarps * V::kNST * V::kDownStage + V::kWarps * V::kNST * 8 + sizeof(SlotTab) + 16;
+  return kTabSmem + (size_t)V::kWarps * V::kNST * V::kDownStage + (V::kWarps * V::kNST + 1) * 8 + 16;
 }
 
 template <class V>
@@ -402,24 +494,29 @@ cudaError_t launch_down(const DecodeParams& p, cudaStream_t st, bool pdl) {
   return launch_k(k_down_fp8<V>, dim3(sm_count()), dim3(V::kThreads), down_smem<V>(), st, pdl, p);
 }
 
+TabArgs tab_args(const DecodeParams& p) {
+  TabArgs ta;
+  ta.M = p.M, ta.topk = p.topk, ta.E = p.E, ta.e_lo = p.e_lo, ta.e_hi = p.e_hi;
+  ta.pool = p.pool, ta.desc = p.desc, ta.sh = p.sh, ta.fmt = DSGX_FMT_FP8;
+  return ta;
+}
+
 }  // namespace
 
 int decode_fp8_up_variants() { return 7; }
 int decode_fp8_down_variants() { return 5; }
 
-cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
+static cudaError_t launch_up_down(const DecodeParams& p, cudaStream_t st, bool pdl, int parts) {
   cudaError_t e = cudaSuccess;
   if (parts & 1) {
-    e = launch_act_quant_tiled(x, p.M, p.H, p.ws.xq, st, pdl);
-    if (e != cudaSuccess) return e;
     switch (p.up) {
       case 1: e = launch_up<Var<8, 4, 2>>(p, st, pdl); break;
       case 2: e = launch_up<Var<8, 2, 5>>(p, st, pdl); break;
       case 3: e = launch_up<Var<4, 8, 2>>(p, st, pdl); break;
-      case 4: e = launch_up<Var<16, 2, 2>>(p, st, pdl); break;
+      case 4: e = launch_up<Var<8, 2, 3>>(p, st, pdl); break;
       case 5: e = launch_up<Var<16, 1, 5>>(p, st, pdl); break;
       case 6: e = launch_up<Var<12, 2, 3>>(p, st, pdl); break;
-      default: e = launch_up<Var<8, 2, 3>>(p, st, pdl); break;
+      default: e = launch_up<Var<16, 2, 2>>(p, st, pdl); break;
     }
     if (e != cudaSuccess) return e;
   }
@@ -428,11 +525,35 @@ cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cud
       case 1: e = launch_down<Var<8, 4, 2>>(p, st, pdl); break;
       case 2: e = launch_down<Var<4, 8, 2>>(p, st, pdl); break;
       case 3: e = launch_down<Var<16, 1, 4>>(p, st, pdl); break;
-      case 4: e = launch_down<Var<16, 2, 2>>(p, st, pdl); break;
-      default: e = launch_down<Var<8, 2, 3>>(p, st, pdl); break;
+      case 4: e = launch_down<Var<8, 2, 3>>(p, st, pdl); break;
+      default: e = launch_down<Var<16, 2, 2>>(p, st, pdl); break;
     }
   }
   return e;
+}
+
+// The expert step on the caller's idx / w: k_prep, k_up, k_down.
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
+  if (parts & 1) {
+    const int qctas = (p.H / 128 * 8 + 7) / 8;
+    cudaError_t e = launch_k(k_prep, dim3(1 + qctas), dim3(256), 0, st, pdl, tab_args(p), p.idx, p.w, x, p.H, p.ws.xq,
+                             p.ws.tab, p.ws.status);
+    if (e != cudaSuccess) return e;
+  }
+  return launch_up_down(p, st, pdl, parts);
+}
+
+// The whole layer step: k_front, k_route_union, k_up, k_down (p.idx / p.w / logits are outputs of the routing).
+cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
+                             const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl) {
+  const int KS = (p.H + 1023) / 1024;
+  const int nlog = (p.E * KS + 7) / 8, qctas = (p.H / 128 * 8 + 7) / 8;
+  cudaError_t e = launch_k(k_front, dim3(nlog + qctas), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq);
+  if (e != cudaSuccess) return e;
+  e = launch_k(k_route_union, dim3(1), dim3(256), 0, st, pdl, rp, tab_args(p), (const float*)p.ws.lpart, KS, bias, logits, idx,
+               w, p.ws.tab, p.ws.status);
+  if (e != cudaSuccess) return e;
+  return launch_up_down(p, st, pdl, 3);
 }
 
 }  // namespace dsgx

@@ -42,7 +42,10 @@ struct DecodeWs {
   float* ypick;     // [kMaxSlots][H/16][16][8] every pick's down output (bf16-rounded values kept as f32)
   int* cnt_h;       // [kMaxSlots][I/128] arrivals of the 16 gate/up units of a 128-group of h
   int* cnt_y;       // [H/16] arrivals of the slots of an output tile
+  struct SlotTab* tab;  // the step's slot table (decode_common.cuh)
+  float* lpart;     // [H/1024 slices][8][E] partial router logits of the layer step
 };
+constexpr size_t kSlotTabBytes = 8192;  // room reserved for a SlotTab
 size_t decode_ws_bytes(int H, int I);
 DecodeWs decode_ws_carve(void* ws, int H, int I);
 
@@ -56,9 +59,12 @@ struct DecodeParams {
   DecodeWs ws;
   float* yr;
   float* ys;
+  __nv_bfloat16* out;  // when set, k_down also writes bf16(yr + ys)
   int ysum;
   int up, down;  // kernel variants (same bits)
 };
+cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
+                             const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
 int decode_fp8_up_variants();
 int decode_fp8_down_variants();
 // parts: 1 = activation quantisation + gate/up, 2 = down + combine, 3 = both

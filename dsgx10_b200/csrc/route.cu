@@ -4,6 +4,7 @@
 // cores on purpose: the selection must be reproducible bit for bit on a CPU.
 #include "common.cuh"
 #include "kernels.h"
+#include "route.cuh"
 
 namespace dsgx {
 
@@ -89,32 +90,7 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* wr, int M,
 }
 
 // ------------------------------------------------------------------------------------------------------------ route
-// e^x from IEEE operations only (the CPU oracle runs the same steps and gets the same bits): n = rint(x log2 e),
-// r = x - n ln 2 in two fused steps, a degree-7 Taylor polynomial in Horner form, an exact scaling by 2^n.
-DSGX_DEV float exp_ieee(float x) {
-  const float n = rintf(__fmul_rn(x, 1.44269504f));
-  float r = fmaf(-n, 0.693145751953125f, x);
-  r = fmaf(-n, 1.428606765330187e-06f, r);
-  float p = 1.f / 5040;
-  p = fmaf(p, r, 1.f / 720);
-  p = fmaf(p, r, 1.f / 120);
-  p = fmaf(p, r, 1.f / 24);
-  p = fmaf(p, r, 1.f / 6);
-  p = fmaf(p, r, 0.5f);
-  p = fmaf(p, r, 1.f);
-  p = fmaf(p, r, 1.f);
-  return __fmul_rn(p, __int_as_float(((int)n + 127) << 23));  // n in [-126, 127] for the callers' ranges
-}
-DSGX_DEV float route_sigmoid(float l) {
-  const float x = -l;
-  if (x > 88.f) return 0.f;
-  if (x < -87.f) return 1.f;
-  return __fdiv_rn(1.f, __fadd_rn(1.f, exp_ieee(x)));
-}
-
-constexpr int kRJ = 16;  // experts a lane: E <= 512
-
-// One row by one warp.  Expert e = lane + 32 j.
+// One row by one warp (route.cuh).
 __global__ void __launch_bounds__(128) k_route(RouteParams p, const float* __restrict__ logits,
                                                const float* __restrict__ bias, int M, int* __restrict__ idx,
                                                float* __restrict__ wout) {
@@ -123,131 +99,10 @@ __global__ void __launch_bounds__(128) k_route(RouteParams p, const float* __res
   const int lane = threadIdx.x & 31;
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (row >= M) return;
-  const float* l = logits + (size_t)row * p.E;
-  float s[kRJ], key[kRJ];
-  // every load before any math: one round trip
-#pragma unroll
-  for (int j = 0; j < kRJ; ++j) {
-    const int e = lane + 32 * j;
-    s[j] = e < p.E ? __ldcg(l + e) : -INFINITY;
-    key[j] = e < p.E && bias ? __ldg(bias + e) : 0.f;
-  }
-  if (p.score_fn == DSGX_SCORE_SIGMOID) {
-#pragma unroll
-    for (int j = 0; j < kRJ; ++j) s[j] = lane + 32 * j < p.E ? route_sigmoid(s[j]) : 0.f;
-  } else {  // softmax: t = exp(l - max), lane sums over j ascending, butterfly, one division each
-    float m = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kRJ; ++j) m = fmaxf(m, s[j]);
-    m = warp_max(m);
-    float ps = 0.f;
-#pragma unroll
-    for (int j = 0; j < kRJ; ++j) {
-      if (lane + 32 * j < p.E) {
-        const float d = __fsub_rn(s[j], m);
-        s[j] = d < -87.f ? 0.f : exp_ieee(d);
-        ps = __fadd_rn(ps, s[j]);
-      } else {
-        s[j] = 0.f;
-      }
-    }
-    const float S = warp_sum(ps);
-#pragma unroll
-    for (int j = 0; j < kRJ; ++j) s[j] = __fdiv_rn(s[j], S);
-  }
-#pragma unroll
-  for (int j = 0; j < kRJ; ++j) key[j] = lane + 32 * j < p.E ? __fadd_rn(s[j], key[j]) : -INFINITY;
-
-  if (p.n_group > 1) {
-    // group score = the sum of the group's two largest keys; keep the topk_group best groups (ties: lower id)
-    const int gs = p.E / p.n_group;
-    float mine = -INFINITY;  // lane g < n_group holds group g's score
-    for (int g = 0; g < p.n_group; ++g) {
-      float a = -INFINITY, b = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < kRJ; ++j) {
-        const int e = lane + 32 * j;
-        if (e < p.E && e / gs == g) {
-          const float v = key[j];
-          if (v > a) b = a, a = v;
-          else if (v > b) b = v;
-        }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
-        const float na = fmaxf(a, oa), nb = fmaxf(fminf(a, oa), fmaxf(b, ob));
-        a = na, b = nb;
-      }
-      if (lane == g) mine = __fadd_rn(a, b);
-    }
-    uint32_t keep = 0;
-    for (int t = 0; t < p.topk_group; ++t) {
-      float bv = lane < p.n_group && !((keep >> lane) & 1) ? mine : -INFINITY;
-      int bg = lane < p.n_group && !((keep >> lane) & 1) ? lane : 1 << 30;
-      if (bv != bv) bv = -INFINITY;  // a NaN score never wins
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
-        if (og < (1 << 30) && (bg == (1 << 30) || ov > bv || (ov == bv && og < bg))) bv = ov, bg = og;
-      }
-      if (bg < 32) keep |= 1u << bg;
-    }
-#pragma unroll
-    for (int j = 0; j < kRJ; ++j) {
-      const int e = lane + 32 * j;
-      if (e < p.E && !((keep >> (e / gs)) & 1)) key[j] = -INFINITY;
-    }
-  }
-
-  float picked[8];
-  int ids[8];
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    picked[k] = 0.f, ids[k] = 0;
-    if (k < p.topk) {
-      float bv = -INFINITY;
-      int bj = 0;
-#pragma unroll
-      for (int j = 0; j < kRJ; ++j)
-        if (key[j] > bv) bv = key[j], bj = j;
-      int be = bv == -INFINITY ? 1 << 30 : lane + 32 * bj;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-        if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
-      }
-      if (be == 1 << 30) be = 0;
-      ids[k] = be;
-      float sv = 0.f;
-#pragma unroll
-      for (int j = 0; j < kRJ; ++j)
-        if (lane + 32 * j == be) sv = s[j], key[j] = -INFINITY;
-      picked[k] = __shfl_sync(0xffffffffu, sv, be & 31);
-    }
-  }
-  // the sum of the picked scores: four running sums at stride 4, then (t0 + t2) + (t1 + t3)
-  float t[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) t[j] = j < p.topk ? picked[j] : 0.f;
-#pragma unroll
-  for (int i = 4; i < 8; ++i)
-    if (i < p.topk) t[i & 3] = __fadd_rn(t[i & 3], picked[i]);
-  float sum;
-  if (p.topk <= 1) sum = t[0];
-  else if (p.topk == 2) sum = __fadd_rn(t[0], t[1]);
-  else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
-  else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
-  sum = __fadd_rn(sum, 1e-20f);
-#pragma unroll
-  for (int k = 0; k < 8; ++k)
-    if (k < p.topk && lane == k) {
-      idx[(size_t)row * p.topk + k] = ids[k];
-      wout[(size_t)row * p.topk + k] =
-          p.norm_topk ? __fmul_rn(__fdiv_rn(picked[k], sum), p.route_scale) : __fmul_rn(picked[k], p.route_scale);
-    }
+  int id;
+  float w;
+  route_row(p, logits + (size_t)row * p.E, 1, 0, bias, lane, id, w, nullptr);
+  if (lane < p.topk) idx[(size_t)row * p.topk + lane] = id, wout[(size_t)row * p.topk + lane] = w;
 }
 
 cudaError_t launch_route(const RouteParams& p, const float* logits, const float* bias, int M, int* idx, float* w,

@@ -114,3 +114,59 @@ def test_refusals():
     with pytest.raises(_lib.DsgxError) as e:
         moe.decode_ws(moe.shape(500, 256, 16, 4))
     assert e.value.status == _lib.ERR_SHAPE
+
+
+@pytest.mark.parametrize("H,I,E,topk,M,ng,tg", [(2048, 1024, 64, 6, 1, 1, 1), (4096, 2048, 32, 8, 7, 8, 4), (1280, 512, 16, 4, 8, 1, 1)])
+def test_layer_step_equals_separate_calls(orc, H, I, E, topk, M, ng, tg):
+    """The fused layer step (logit slices + route + slot table + experts + rounding) gives the bits of the separate
+    calls: same logits, ids, weights, partial sums and rounded output; and the host-buffer entry point the same again."""
+    from dsgx10_b200 import moe, synth
+    if H % 256:
+        pytest.skip("FP8 kernels need H % 256 == 0")
+    shp = moe.shape(H, I, E, topk, n_group=ng, topk_group=tg)
+    layer = synth.Fp8Layer(H, I, E, 77, device="cuda")
+    x = synth.activations(M, H, 78).cuda()
+    wr = synth.router_weights(E, H, 79).cuda()
+    bias = (torch.randn(E, generator=torch.Generator().manual_seed(5)) * 0.01).float().cuda()
+    logits = moe.router_logits(x, wr)
+    idx, w = moe.route(shp, logits, bias)
+    ws = moe.decode_ws(shp)
+    yr, ys = moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws)
+    out = moe.finalize(yr, ys)
+    step = moe.LayerStep(shp, wr, bias)
+    out2 = step.run(layer.layer_w(), x)
+    torch.cuda.synchronize()
+    assert moe.ws_status(step.ws) == 0
+    assert torch.equal(step.logits[:M], logits)
+    assert torch.equal(step.idx[:M], idx) and torch.equal(step.w[:M], w)
+    assert torch.equal(step.yr[:M], yr) and torch.equal(step.ys[:M], ys)
+    assert torch.equal(out2, out)
+    xh = x.cpu().pin_memory()
+    oh = torch.empty(M, H, dtype=torch.bfloat16).pin_memory()
+    step.run_host(layer.layer_w(), xh, oh)
+    torch.cuda.synchronize()
+    assert torch.equal(oh, out.cpu())
+
+
+def test_kernel_variants_same_bits(orc):
+    """Every up / down kernel variant (warps, chunking, ring depth) gives the same bits (cf. altar1
+    engine/experts/tests/test_experts.cu:557-575)."""
+    from dsgx10_b200 import moe, synth
+    H, I, E, topk, M = 2048, 1024, 16, 4, 5
+    shp = moe.shape(H, I, E, topk)
+    layer = synth.Fp8Layer(H, I, E, 91, device="cuda")
+    x = synth.activations(M, H, 92).cuda()
+    wr = synth.router_weights(E, H, 93).cuda()
+    idx, w = moe.route(shp, moe.router_logits(x, wr), None)
+    ws = moe.decode_ws(shp)
+    base = None
+    for up in range(7):
+        for down in range(5):
+            if up and down:
+                continue
+            yr, ys = moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws, up=up, down=down)
+            torch.cuda.synchronize()
+            if base is None:
+                base = (yr.clone(), ys.clone())
+            assert torch.equal(yr, base[0]) and torch.equal(ys, base[1]), (up, down)
+    assert moe.ws_status(ws) == 0
