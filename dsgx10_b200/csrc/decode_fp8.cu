@@ -139,28 +139,31 @@ DSGX_DEV void store_tab(const SlotTab& tab, SlotTab* out) {
   for (int i = threadIdx.x; i < (int)(sizeof(SlotTab) / 16); i += blockDim.x) d[i] = s[i];
 }
 
-// One CTA of 8 warps: warp r routes row r from the logit slices, then the CTA builds the slot table.
-__global__ void __launch_bounds__(256) k_route_union(RouteParams rp, TabArgs ta, const float* __restrict__ lpart, int nsplit,
+// One CTA a row, one thread an expert (route.cuh: route_row_cta); the last CTA to finish builds the slot table (a ticket).
+__global__ void __launch_bounds__(512) k_route_union(RouteParams rp, TabArgs ta, const float* __restrict__ lpart, int nsplit,
                                                      const float* __restrict__ bias, float* __restrict__ logits,
                                                      int* __restrict__ idx, float* __restrict__ w, SlotTab* __restrict__ out,
-                                                     int* __restrict__ status) {
+                                                     int* __restrict__ status, int* __restrict__ cnt) {
   __shared__ SlotTab tab;
+  __shared__ RouteSmem rs;
   __shared__ uint32_t bm[16];
   __shared__ int s_idx[kMaxRows * kMaxTopK];
   __shared__ float s_w[kMaxRows * kMaxTopK];
+  __shared__ int s_ticket;
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (warp < ta.M) {
-    int id;
-    float wt;
-    route_row(rp, lpart + (size_t)warp * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, lane, id, wt,
-              logits ? logits + (size_t)warp * rp.E : nullptr);
-    if (lane < rp.topk) {
-      s_idx[warp * rp.topk + lane] = id, s_w[warp * rp.topk + lane] = wt;
-      idx[warp * rp.topk + lane] = id, w[warp * rp.topk + lane] = wt;
-    }
-  }
+  const int row = blockIdx.x;
+  route_row_cta(rp, lpart + (size_t)row * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, rs,
+                logits ? logits + (size_t)row * rp.E : nullptr, idx + row * rp.topk, w + row * rp.topk);
+  // the last row to finish builds the slot table of the step
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = ta.M > 1 ? atomicAdd(cnt, 1) : 0;
+  __syncthreads();
+  if (s_ticket != ta.M - 1) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < ta.M * ta.topk; i += blockDim.x) s_idx[i] = __ldcg(idx + i), s_w[i] = __ldcg(w + i);
+  if (threadIdx.x == 0 && ta.M > 1) *cnt = 0;
   __syncthreads();
   build_slot_tab(tab, bm, s_idx, s_w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
   if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
@@ -550,8 +553,8 @@ cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const
   const int nlog = (p.E * KS + 7) / 8, qctas = (p.H / 128 * 8 + 7) / 8;
   cudaError_t e = launch_k(k_front, dim3(nlog + qctas), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq);
   if (e != cudaSuccess) return e;
-  e = launch_k(k_route_union, dim3(1), dim3(256), 0, st, pdl, rp, tab_args(p), (const float*)p.ws.lpart, KS, bias, logits, idx,
-               w, p.ws.tab, p.ws.status);
+  e = launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p), (const float*)p.ws.lpart, KS,
+               bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
   if (e != cudaSuccess) return e;
   return launch_up_down(p, st, pdl, 3);
 }

@@ -105,8 +105,20 @@ __global__ void __launch_bounds__(128) k_route(RouteParams p, const float* __res
   if (lane < p.topk) idx[(size_t)row * p.topk + lane] = id, wout[(size_t)row * p.topk + lane] = w;
 }
 
+// decode widths: one CTA a row, one thread an expert
+__global__ void __launch_bounds__(512) k_route_cta(RouteParams p, const float* __restrict__ logits,
+                                                   const float* __restrict__ bias, int* __restrict__ idx,
+                                                   float* __restrict__ wout) {
+  __shared__ RouteSmem rs;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  route_row_cta(p, logits + (size_t)row * p.E, 1, 0, bias, rs, nullptr, idx + (size_t)row * p.topk, wout + (size_t)row * p.topk);
+}
+
 cudaError_t launch_route(const RouteParams& p, const float* logits, const float* bias, int M, int* idx, float* w,
                          cudaStream_t st, bool pdl) {
+  if (M <= 16) return launch_k(k_route_cta, dim3(M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, p, logits, bias, idx, w);
   return launch_k(k_route, dim3((M + 3) / 4), dim3(128), 0, st, pdl, p, logits, bias, M, idx, w);
 }
 

@@ -176,3 +176,133 @@ DSGX_DEV void route_row(const RouteParams& p, const float* __restrict__ l, int n
 }
 
 }  // namespace dsgx
+
+namespace dsgx {
+
+// ---- the same routing function by one whole CTA, one thread per expert (blockDim.x = E rounded up to 32) ----------
+// For decode widths the routing is a chain of dependent steps, so a row is spread over the CTA: scores in parallel,
+// each pick a block-wide arg-max.  Comparisons are exact and every sum keeps the order of route_row, so the bits
+// are the same.
+struct RouteSmem {
+  float key[512];
+  float wv[16];
+  int wi[16];
+  float red[16];
+  float picked[8];
+  int ids[8];
+  float gsc[32];
+  float S;
+  uint32_t keep;
+};
+
+DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
+                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out) {
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5, nW = blockDim.x >> 5;
+  const bool valid = e < p.E;
+  float lg = -INFINITY, b = 0.f;
+  if (valid) {
+    lg = __ldcg(l + e);
+    if (bias) b = __ldg(bias + e);
+    for (int sp = 1; sp < nsplit; ++sp) lg = __fadd_rn(lg, __ldcg(l + sp * split_stride + e));
+    if (logits_out) logits_out[e] = lg;
+  }
+  float s;
+  if (p.score_fn == DSGX_SCORE_SIGMOID) {
+    s = valid ? route_sigmoid(lg) : 0.f;
+  } else {
+    float m = warp_max(lg);
+    if (lane == 0) sm.red[warp] = m;
+    __syncthreads();
+    m = sm.red[0];
+    for (int w = 1; w < nW; ++w) m = fmaxf(m, sm.red[w]);
+    float t = 0.f;
+    if (valid) {
+      const float d = __fsub_rn(lg, m);
+      t = d < -87.f ? 0.f : exp_ieee(d);
+    }
+    sm.key[e] = t;
+    __syncthreads();
+    if (warp == 0) {  // lane sums over j ascending, then the butterfly
+      float ps = 0.f;
+      for (int ee = lane; ee < p.E; ee += 32) ps = __fadd_rn(ps, sm.key[ee]);
+      ps = warp_sum(ps);
+      if (lane == 0) sm.S = ps;
+    }
+    __syncthreads();
+    s = __fdiv_rn(t, sm.S);
+    __syncthreads();
+  }
+  float key = valid ? __fadd_rn(s, b) : -INFINITY;
+  if (p.n_group > 1) {
+    const int gs = p.E / p.n_group;
+    sm.key[e] = key;
+    __syncthreads();
+    if (e < p.n_group) {
+      float a = -INFINITY, c = -INFINITY;
+      for (int i = e * gs; i < (e + 1) * gs; ++i) {
+        const float v = sm.key[i];
+        if (v > a) c = a, a = v;
+        else if (v > c) c = v;
+      }
+      sm.gsc[e] = __fadd_rn(a, c);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const float mine = lane < p.n_group ? sm.gsc[lane] : -INFINITY;
+      uint32_t keep = 0;
+      for (int t = 0; t < p.topk_group; ++t) {
+        float bv = lane < p.n_group && !((keep >> lane) & 1) ? mine : -INFINITY;
+        int bg = lane < p.n_group && !((keep >> lane) & 1) ? lane : 1 << 30;
+        if (bv != bv) bv = -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+          if (og < (1 << 30) && (bg == (1 << 30) || ov > bv || (ov == bv && og < bg))) bv = ov, bg = og;
+        }
+        if (bg < 32) keep |= 1u << bg;
+      }
+      if (lane == 0) sm.keep = keep;
+    }
+    __syncthreads();
+    if (valid && !((sm.keep >> (e / gs)) & 1)) key = -INFINITY;
+  }
+  for (int k = 0; k < p.topk; ++k) {
+    float bv = key;
+    int be = key == -INFINITY ? 1 << 30 : e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
+    }
+    if (lane == 0) sm.wv[warp] = bv, sm.wi[warp] = be;
+    __syncthreads();
+    bv = sm.wv[0], be = sm.wi[0];
+    for (int w = 1; w < nW; ++w) {
+      const float ov = sm.wv[w];
+      const int oe = sm.wi[w];
+      if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
+    }
+    if (be == 1 << 30) be = 0;
+    if (e == be) sm.picked[k] = s, sm.ids[k] = be, key = -INFINITY;
+    __syncthreads();
+  }
+  if (e < p.topk) {
+    float t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = j < p.topk ? sm.picked[j] : 0.f;
+    for (int i = 4; i < p.topk; ++i) t[i & 3] = __fadd_rn(t[i & 3], sm.picked[i]);
+    float sum;
+    if (p.topk <= 1) sum = t[0];
+    else if (p.topk == 2) sum = __fadd_rn(t[0], t[1]);
+    else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
+    else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
+    sum = __fadd_rn(sum, 1e-20f);
+    const float pk = sm.picked[e];
+    idx_out[e] = sm.ids[e];
+    w_out[e] = p.norm_topk ? __fmul_rn(__fdiv_rn(pk, sum), p.route_scale) : __fmul_rn(pk, p.route_scale);
+  }
+}
+
+}  // namespace dsgx
