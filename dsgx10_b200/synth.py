@@ -124,3 +124,16 @@ def activations(M, H, seed, device="cpu"):
 def bf16_bits(t):
     """torch bf16 tensor -> numpy uint16 bit patterns."""
     return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+# ----------------------------------------------------------------------------------------------------- INT4 tensors
+
+def int4_tensors(N, K, seed):
+    """Canonical symmetric INT4-g32 tensor (compressed-tensors pack-quantized order; altar1 engine/experts/layout.h:24-31):
+    wp uint8 [N][K/2] (value k in byte k/2, low nibble = even k, stored nibble u = q + 8, q uniform in [-8, 7]) and
+    bf16 scale bits [N][K/32] in [2^-9, 2^-7) with a random mantissa (the range of the reference's generator,
+    tests/testdata.h:45-48); the zero point is 8 everywhere."""
+    rng = np.random.default_rng(seed)
+    wp = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    s = (((118 + rng.integers(0, 2, (N, K // 32))) << 7) | rng.integers(0, 128, (N, K // 32))).astype(np.uint16)
+    return wp, s

@@ -1,0 +1,138 @@
+#!/usr/bin/env python
+"""Generates tests/golden/*.npz by running the reference's own Python CPU modules on small seeded layers.
+
+Run in a container that has the reference tree (default /root/reference); the fixtures it writes are committed, this
+script is how they were made.  Nothing of the reference is copied: its modules are imported from where they lie.
+
+  FP8:  ds41f ref/inference/model.py (Gate, Expert, MoE) over ref/torchref/kernel.py, switched to the "g128" recipe the
+        benchmark configurations name: fp8_block_size 128, f32 scales (scale_fmt None), default dtype bf16.
+  INT4: altar1 ref/glmref.py (int4_dequant, moe) with its module constants set to the small shape.
+
+Weights are not stored: the tests rebuild them from the same seeds (dsgx10_b200.synth, CPU generator) and check a
+checksum kept in the fixture, so a fixture only holds activations, routing and outputs (a few KB).
+"""
+import os
+import sys
+import zlib
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+REF = os.environ.get("DSGX_REFERENCE", "/root/reference")
+
+from dsgx10_b200 import synth  # noqa: E402
+
+
+def crc(*arrays):
+    c = 0
+    for a in arrays:
+        c = zlib.crc32(np.ascontiguousarray(a).tobytes(), c)
+    return np.uint32(c)
+
+
+# ------------------------------------------------------------------------------------------------------------- FP8
+
+def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0):
+    sys.path[:0] = [os.path.join(REF, "ds41f-4xgx10-switchless/ref/torchref"),
+                    os.path.join(REF, "ds41f-4xgx10-switchless/ref/inference")]
+    import model as M  # the reference's model.py; `kernel` resolves to torchref/kernel.py
+    M.fp8_block_size, M.scale_fmt, M.scale_dtype = 128, None, torch.float32
+    M.default_dtype = torch.float8_e4m3fn
+    M.world_size, M.rank = 1, 0
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        args = M.ModelArgs(dim=H, moe_inter_dim=I, n_routed_experts=E, n_activated_experts=topk, score_func=score,
+                           route_scale=route_scale, expert_dtype=None, n_layers=1)
+        moe = M.MoE(0, args)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    layer = synth.Fp8Layer(H, I, E, seed, device="cpu")
+    wr = synth.router_weights(E, H, seed + 2000)
+    x = synth.activations(T, H, seed + 1000)
+    sums = []
+    with torch.no_grad():
+        moe.gate.weight = torch.nn.Parameter(wr.clone(), requires_grad=False)
+        moe.gate.bias = torch.nn.Parameter(torch.zeros(E), requires_grad=False)
+        for e in range(E + 1):
+            ex = moe.experts[e] if e < E else moe.shared_experts
+            wg, sg, wu, su, wd, sd = layer.canonical(e)
+            sums.append(crc(wg, sg, wu, su, wd, sd))
+            for lin, q, s in ((ex.w1, wg, sg), (ex.w3, wu, su), (ex.w2, wd, sd)):
+                lin.weight = torch.nn.Parameter(torch.from_numpy(q.copy()).view(torch.float8_e4m3fn), requires_grad=False)
+                lin.weight.scale = lin.scale = torch.nn.Parameter(torch.from_numpy(s.copy()), requires_grad=False)
+        torch.set_default_dtype(torch.bfloat16)
+        try:
+            weights, indices = moe.gate(x)
+            out = moe(x)
+            # one expert on one row, for the oracle's per-expert pin
+            e0 = int(indices[0, 0])
+            y0 = moe.experts[e0](x[:1], weights[:1, :1].float())
+            ysh = moe.shared_experts(x[:1])
+            logits = M.linear(x.float(), moe.gate.weight.float())
+        finally:
+            torch.set_default_dtype(torch.float32)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"),
+                        meta=np.array([H, I, E, topk, T, {"sigmoid": 0, "softmax": 1}[score], seed], np.int64),
+                        route_scale=np.float32(route_scale), weights_crc=np.array(sums, np.uint32),
+                        x=synth.bf16_bits(x), logits=logits.float().numpy(), idx=indices.numpy().astype(np.int32),
+                        w=weights.float().numpy(), out=synth.bf16_bits(out), e0=np.int32(e0), y0=synth.bf16_bits(y0),
+                        ysh=synth.bf16_bits(ysh))
+    print(name, "ok", out.shape)
+
+
+# ------------------------------------------------------------------------------------------------------------ INT4
+
+int4_tensors = synth.int4_tensors
+
+
+def int4_case(name, H, I, E, topk, T, seed, route_scale=2.5):
+    sys.path.insert(0, os.path.join(REF, "altar1-4xgx10-switchless/ref"))
+    import glmref as G
+    G.D, G.NE, G.K8, G.DFF, G.ROUTE_SCALE, G.COMBINE = H, E, topk, I, route_scale, "f32"
+    rng = np.random.default_rng(seed + 5)
+    x = synth.activations(T, H, seed + 1000)
+    wr = synth.router_weights(E, H, seed + 2000).to(torch.bfloat16)   # altar-1's gate weight is bf16
+    bias = torch.from_numpy((rng.standard_normal(E) * 0.01).astype(np.float32))
+    sh = [(torch.randn(n, k, generator=torch.Generator().manual_seed(seed + 9 + i)) * 0.02).to(torch.bfloat16)
+          for i, (n, k) in enumerate(((I, H), (I, H), (H, I)))]
+    ex = {e: [int4_tensors(n, k, seed * 1000 + e * 3 + m) for m, (n, k) in enumerate(((I, H), (I, H), (H, I)))]
+          for e in range(E)}
+    sums = [crc(*[a for t in ex[e] for a in t]) for e in range(E)] + [crc(*[synth.bf16_bits(t) for t in sh])]
+
+    def W(nm):
+        return {"mlp.gate.weight": wr, "mlp.gate.e_score_correction_bias": bias,
+                "mlp.shared_experts.gate_proj.weight": sh[0], "mlp.shared_experts.up_proj.weight": sh[1],
+                "mlp.shared_experts.down_proj.weight": sh[2]}[nm]
+
+    class Src:
+        def load(self, e):
+            return e
+
+        def prepare(self, e):
+            out = []
+            for (wp, s), (n, k) in zip(ex[e], ((I, H), (I, H), (H, I))):
+                packed = torch.from_numpy(wp.view(np.int32).reshape(n, k // 8).copy())
+                zp = torch.full((n // 8, k // 32), -2004318072, dtype=torch.int32)      # 0x88888888: zero point 8
+                out.append(G.int4_dequant(packed, torch.from_numpy(s.view(np.int16).copy()).view(torch.bfloat16), zp))
+            return ("bf16", *out)
+
+    with ThreadPoolExecutor(2) as pool, torch.no_grad():
+        out, route, _ = G.moe(x, W, 0, pool, Src())
+    deq = Src().prepare(0)[1]
+    np.savez_compressed(os.path.join(HERE, name + ".npz"),
+                        meta=np.array([H, I, E, topk, T, 0, seed], np.int64), route_scale=np.float32(route_scale),
+                        weights_crc=np.array(sums, np.uint32), x=synth.bf16_bits(x), bias=bias.numpy(),
+                        idx=route["route_idx"].astype(np.int32), w=route["route_w"], margin=route["route_margin"],
+                        out=out.float().numpy(), deq0=synth.bf16_bits(deq)[:16])
+    print(name, "ok", out.shape)
+
+
+if __name__ == "__main__":
+    fp8_case("fp8_sigmoid_small", 512, 256, 8, 2, 6, "sigmoid", 3101)
+    fp8_case("fp8_sigmoid_top6", 1024, 512, 32, 6, 5, "sigmoid", 3102, route_scale=1.5)
+    fp8_case("fp8_softmax", 512, 512, 16, 4, 4, "softmax", 3103)
+    int4_case("int4_sigmoid", 1024, 512, 16, 8, 5, 3201)

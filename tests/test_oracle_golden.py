@@ -1,0 +1,79 @@
+"""Pins the CPU oracle against outputs of the reference's own Python CPU modules (tests/golden/*.npz, made by
+tests/golden/make_golden.py from ds41f ref/inference/model.py + ref/torchref/kernel.py and altar1 ref/glmref.py)."""
+import os
+import zlib
+
+import numpy as np
+import pytest
+
+from tests.util import rowmax_err
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _crc(*arrays):
+    c = 0
+    for a in arrays:
+        c = zlib.crc32(np.ascontiguousarray(a).tobytes(), c)
+    return np.uint32(c)
+
+
+@pytest.mark.parametrize("name", ["fp8_sigmoid_small", "fp8_sigmoid_top6", "fp8_softmax"])
+def test_fp8_layer_matches_reference_model_py(orc, name):
+    from dsgx10_b200 import synth
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    H, I, E, topk, T, score, seed = (int(v) for v in g["meta"])
+    layer = synth.Fp8Layer(H, I, E, seed, device="cpu")
+    experts = {e: layer.canonical(e) for e in range(E + 1)}
+    if not all(_crc(*experts[e]) == g["weights_crc"][e] for e in range(E + 1)):
+        pytest.skip("this torch build's CPU generator gives other weights than the fixture's (checksum)")
+    wr = synth.router_weights(E, H, seed + 2000).numpy()
+    x = g["x"]
+    # logits: same sums in another order
+    logits = orc.router_logits(x, wr)
+    assert np.abs(logits - g["logits"]).max() <= 2e-5
+    # the selection on the reference's logits: same experts in the same order, same weights (its sum order may differ)
+    idx, w = orc.route(g["logits"], None, topk, score, norm=True, route_scale=float(g["route_scale"]))
+    assert (idx == g["idx"]).all()
+    assert np.abs(w - g["w"]).max() <= 4e-7 * float(g["route_scale"])
+    # and on the oracle's own logits too (no near-ties in these fixtures)
+    idx2, _ = orc.route(logits, None, topk, score, norm=True, route_scale=float(g["route_scale"]))
+    assert (idx2 == g["idx"]).all()
+    # one routed expert and the shared expert on row 0 (bf16 outputs): a rounding flip at most
+    e0 = int(g["e0"])
+    y0, _ = orc.fp8_expert_row(x[0], *experts[e0], wroute=float(g["w"][0, 0]))
+    ysh, _ = orc.fp8_expert_row(x[0], *experts[E])
+    for mine, theirs in ((y0, g["y0"]), (ysh, g["ysh"])):
+        theirs = orc.bf16_to_f32(theirs).reshape(-1)
+        assert rowmax_err(mine, theirs) <= 2e-3
+        assert (orc.f32_to_bf16(mine) == orc.f32_to_bf16(theirs)).mean() > 0.98
+    # the whole layer with the reference's routing
+    shared = experts.pop(E)
+    acc, out = orc.moe_fp8_layer(x, g["idx"], g["w"], experts, shared)
+    want = orc.bf16_to_f32(g["out"])
+    assert rowmax_err(orc.bf16_to_f32(out), want) <= 2e-3 + 2 ** -8
+    assert (out == g["out"]).mean() > 0.97
+
+
+def test_int4_layer_matches_reference_glmref(orc):
+    from dsgx10_b200 import synth
+    import torch
+    g = np.load(os.path.join(GOLD, "int4_sigmoid.npz"))
+    H, I, E, topk, T, _, seed = (int(v) for v in g["meta"])
+    shapes = ((I, H), (I, H), (H, I))
+    raw = {e: [synth.int4_tensors(n, k, seed * 1000 + e * 3 + m) for m, (n, k) in enumerate(shapes)] for e in range(E)}
+    sh = [synth.bf16_bits((torch.randn(n, k, generator=torch.Generator().manual_seed(seed + 9 + i)) * 0.02).to(torch.bfloat16))
+          for i, (n, k) in enumerate(shapes)]
+    crcs = [_crc(*[a for t in raw[e] for a in t]) for e in range(E)] + [_crc(*sh)]
+    if not (np.array(crcs, np.uint32) == g["weights_crc"]).all():
+        pytest.skip("this numpy / torch build's generators give other weights than the fixture's (checksum)")
+    deq = {e: tuple(orc.int4_dequant(wp, s, None) for wp, s in raw[e]) for e in range(E)}
+    assert (deq[0][0][:16] == g["deq0"]).all()          # the dequant contract, bit for bit
+    wr = synth.bf16_bits(synth.router_weights(E, H, seed + 2000).to(torch.bfloat16))
+    logits = orc.router_logits(g["x"], orc.bf16_to_f32(wr))
+    idx, w = orc.route(logits, g["bias"], topk, orc.SCORE_SIGMOID, norm=True, route_scale=float(g["route_scale"]))
+    safe = g["margin"] > 1e-5
+    assert (idx[safe] == g["idx"][safe]).all()
+    assert np.abs(w[safe] - g["w"][safe]).max() <= 1e-6
+    acc, _ = orc.moe_bf16w_layer(g["x"], g["idx"], g["w"], deq, tuple(sh))
+    assert rowmax_err(acc, g["out"]) <= 2e-3
