@@ -32,7 +32,7 @@ static size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
 size_t decode_ws_bytes(int H, int I) {
   const size_t HB = H / 128, IB = I / 128;
   size_t n = 256;
-  n += al256(HB * kActBlk);
+  n += al256(HB * kActBlk > (size_t)H * 16 ? HB * kActBlk : (size_t)H * 16);
   n += al256((size_t)kMaxSlots * 8 * I * 2);
   n += al256((size_t)kMaxSlots * IB * kActBlk);
   n += al256((size_t)kMaxSlots * (H / 16) * 128 * 4);
@@ -47,7 +47,7 @@ DecodeWs decode_ws_carve(void* ws, int H, int I) {
   char* p = reinterpret_cast<char*>(ws);
   DecodeWs w;
   w.status = reinterpret_cast<int*>(p), p += 256;
-  w.xq = reinterpret_cast<uint8_t*>(p), p += al256(HB * kActBlk);
+  w.xq = reinterpret_cast<uint8_t*>(p), p += al256(HB * kActBlk > (size_t)H * 16 ? HB * kActBlk : (size_t)H * 16);
   w.h = reinterpret_cast<__nv_bfloat16*>(p), p += al256((size_t)kMaxSlots * 8 * I * 2);
   w.hq = reinterpret_cast<uint8_t*>(p), p += al256((size_t)kMaxSlots * IB * kActBlk);
   w.ypick = reinterpret_cast<float*>(p), p += al256((size_t)kMaxSlots * (H / 16) * 128 * 4);
@@ -170,6 +170,22 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
                                       cfg->parts == 0 ? 3 : cfg->parts);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
   }
+  if (s->fmt == DSGX_FMT_INT4) {
+    if (L->sh.g || L->sh.u || L->sh.d) return DSGX_ERR_FORMAT;  // an INT4 layer's shared expert is bf16
+    const bool shb = L->sh.bg != nullptr;
+    if (shb && (!L->sh.bu || !L->sh.bd)) return DSGX_ERR_ARG;
+    if (shb && !ys && !cfg->ysum) return DSGX_ERR_ARG;
+    if (!decode_int4_fits(s->H, M)) return DSGX_ERR_SHAPE;
+    DecodeParams p;
+    p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
+    p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
+    p.idx = idx, p.w = w;
+    p.ws = decode_ws_carve(ws, s->H, s->I);
+    p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
+    cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
+                                       cfg->parts == 0 ? 3 : cfg->parts);
+    return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+  }
   return DSGX_ERR_UNSUPPORTED;
 }
 
@@ -185,13 +201,17 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
   if (finalize && !st->out_bf16) return DSGX_ERR_ARG;
   int rc = check_shape(s);
   if (rc) return rc;
-  if (s->fmt == DSGX_FMT_FP8) {
+  {
     if (!L || !x || !L->pool || !L->desc || L->fmt != s->fmt) return DSGX_ERR_ARG;
     if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
     if (((uintptr_t)L->pool & 255) || ((uintptr_t)st->ws & 255) || ((uintptr_t)x & 15) || ((uintptr_t)st->wr & 15))
       return DSGX_ERR_ARG;
-    const bool sh8 = L->sh.g != nullptr;
+    const bool fp8 = s->fmt == DSGX_FMT_FP8;
+    const bool sh8 = L->sh.g != nullptr, shb = L->sh.bg != nullptr;
+    if (fp8 ? shb : sh8) return DSGX_ERR_FORMAT;
     if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds || !st->ys)) return DSGX_ERR_ARG;
+    if (shb && (!L->sh.bu || !L->sh.bd || !st->ys)) return DSGX_ERR_ARG;
+    if (!fp8 && !decode_int4_fits(s->H, M)) return DSGX_ERR_SHAPE;
     DecodeParams p;
     p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
     p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
@@ -200,19 +220,11 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     p.yr = st->yr, p.ys = st->ys, p.ysum = 0, p.up = 0, p.down = 0;
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
-    cudaError_t e = launch_layer_fp8(p, rp, reinterpret_cast<const __nv_bfloat16*>(x), st->wr, st->bias, st->logits,
-                                     st->idx, st->w, (cudaStream_t)stream, true);
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    cudaError_t e = fp8 ? launch_layer_fp8(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true)
+                        : launch_layer_int4(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
   }
-  rc = dsgx_router_logits(x, st->wr, M, s->H, s->E, st->logits, stream);
-  if (rc) return rc;
-  rc = dsgx_route(s, st->logits, st->bias, M, st->idx, st->w, stream);
-  if (rc) return rc;
-  rc = dsgx_moe_decode(s, L, x, st->idx, st->w, M, st->ws, st->yr, st->ys, stream, nullptr);
-  if (rc) return rc;
-  if (!finalize) return DSGX_OK;
-  const bool shared = L->sh.g != nullptr || L->sh.bg != nullptr;
-  return dsgx_finalize(st->yr, shared ? st->ys : nullptr, M, s->H, st->out_bf16, 0, stream);
 }
 
 int dsgx_moe_layer_decode_host(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* x_host, int M,

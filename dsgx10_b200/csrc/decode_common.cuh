@@ -92,4 +92,67 @@ DSGX_DEV int ord_slot(const SlotTab& tab, int ord) {
 
 DSGX_DEV uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
+// quantises one row's 128 values (4 per lane, k = 4 lane ..) into an activation block
+DSGX_DEV void quant_row_to_block(uint8_t* blk, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {
+  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
+  uint32_t packed = 0;
+  float sc = 0.f;
+  if (valid) {
+    sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
+    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  }
+  *reinterpret_cast<uint32_t*>(blk + (q * 32 + 4 * r + t) * 16 + i) = packed;
+  if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
+}
+
+DSGX_DEV void quant_x_block(const __nv_bfloat16* __restrict__ x, int M, int K, uint8_t* out, int j, int r, int lane) {
+  float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+  if (r < M) {
+    const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * K + 128 * j + 4 * lane));
+    v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
+    v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+  }
+  quant_row_to_block(out + (size_t)j * kActBlk, r, lane, r < M, v0, v1, v2, v3);
+}
+
+
+// rows of a bf16 activation tile: M rounded up to 1, 2, 4 or 8
+inline __host__ __device__ int rows_pow2(int M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
+
+// Position of value v (0..15) inside a 16-value group of a bf16 activation tile.  The INT4 kernels pair nibbles i and
+// i + 4 of a 32-bit word into one bf16x2 register (one shift and one logic op per pair), so the activations of a group
+// are stored in the order 0,4,1,5,2,6,3,7, 8,12,9,13,10,14,11,15.
+DSGX_DEV int tile_pos(int v) { return (v & 8) | ((v & 3) << 1) | ((v >> 2) & 1); }
+
+// x bf16 [M][K] -> tile [K/16 groups][R rows][16 values in tile_pos order]; rows M..R-1 are zero.  One thread a (group, row).
+DSGX_DEV void tile_x_group(const __nv_bfloat16* __restrict__ x, int M, int K, int R, uint8_t* out, int kg, int r) {
+  uint16_t v[16], o[16];
+  if (r < M) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * K + 16 * kg));
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * K + 16 * kg + 8));
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[2 * i] = (uint16_t)(w[i] & 0xffffu), v[2 * i + 1] = (uint16_t)(w[i] >> 16);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[(i & 8) | ((i & 3) << 1) | ((i >> 2) & 1)] = v[i];
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = o[2 * i] | (uint32_t)o[2 * i + 1] << 16;
+  uint4* d = reinterpret_cast<uint4*>(out + ((size_t)kg * R + r) * 32);
+  d[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+struct TabArgs {
+  int M, topk, E, e_lo, e_hi;
+  const uint8_t* pool;
+  const dsgx_mat_desc* desc;
+  dsgx_shared_w sh;
+  uint32_t fmt;
+};
+
 }  // namespace dsgx

@@ -25,7 +25,6 @@
 #include "common.cuh"
 #include "decode_common.cuh"
 #include "kernels.h"
-#include "route.cuh"
 
 namespace dsgx {
 
@@ -57,140 +56,6 @@ DSGX_DEV void block_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const
   d[0] += e[0], d[1] += e[1], d[2] += e[2], d[3] += e[3];
 }
 
-// quantises one row's 128 values (4 per lane, k = 4 lane ..) into an activation block
-DSGX_DEV void quant_row_to_block(uint8_t* blk, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {
-  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
-  uint32_t packed = 0;
-  float sc = 0.f;
-  if (valid) {
-    sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
-    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
-  }
-  *reinterpret_cast<uint32_t*>(blk + (q * 32 + 4 * r + t) * 16 + i) = packed;
-  if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
-}
-
-DSGX_DEV void quant_x_block(const __nv_bfloat16* __restrict__ x, int M, int K, uint8_t* out, int j, int r, int lane) {
-  float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
-  if (r < M) {
-    const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * K + 128 * j + 4 * lane));
-    v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
-    v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
-  }
-  quant_row_to_block(out + (size_t)j * kActBlk, r, lane, r < M, v0, v1, v2, v3);
-}
-
-// ----------------------------------------------------------------------------------------------------------- k_front
-// CTAs [0, nlog): one warp per (expert, slice of 1024 k): the slice's partial logit of every row, in the router's
-// summation order (lane j: k = base + 128 i + 4 j + c by fma, then the butterfly).  CTAs [nlog, ..): x -> blocks.
-__global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M,
-                                               int H, int E, int nlog, float* __restrict__ lpart, uint8_t* __restrict__ xq) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if ((int)blockIdx.x >= nlog) {
-    if (!xq) return;
-    const int gw = ((int)blockIdx.x - nlog) * 8 + warp;
-    const int j = gw >> 3, r = gw & 7;
-    if (j < H / 128) quant_x_block(x, M, H, xq, j, r, lane);
-    return;
-  }
-  const int KS = (H + 1023) / 1024;
-  const int gw = blockIdx.x * 8 + warp;
-  const int e = gw / KS, sl = gw % KS;
-  if (e >= E) return;
-  const int base = sl * 1024, nit = min(1024, H - base) / 128;
-  float4 wv[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    wv[i] = i < nit ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)e * H + base + 128 * i + 4 * lane))
-                    : make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int r = 0; r < M; ++r) {
-    uint2 xv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      xv[i] = i < nit ? __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * H + base + 128 * i + 4 * lane)) : make_uint2(0, 0);
-    float a = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (i < nit) {
-        a = fmaf(bf16_bits_to_f(xv[i].x & 0xffffu), wv[i].x, a);
-        a = fmaf(bf16_bits_to_f(xv[i].x >> 16), wv[i].y, a);
-        a = fmaf(bf16_bits_to_f(xv[i].y & 0xffffu), wv[i].z, a);
-        a = fmaf(bf16_bits_to_f(xv[i].y >> 16), wv[i].w, a);
-      }
-    a = warp_sum(a);
-    if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
-  }
-}
-
-// ----------------------------------------------------------------------------------------------------- k_route_union
-struct TabArgs {
-  int M, topk, E, e_lo, e_hi;
-  const uint8_t* pool;
-  const dsgx_mat_desc* desc;
-  dsgx_shared_w sh;
-  uint32_t fmt;
-};
-
-DSGX_DEV void store_tab(const SlotTab& tab, SlotTab* out) {
-  const uint4* s = reinterpret_cast<const uint4*>(&tab);
-  uint4* d = reinterpret_cast<uint4*>(out);
-  for (int i = threadIdx.x; i < (int)(sizeof(SlotTab) / 16); i += blockDim.x) d[i] = s[i];
-}
-
-// One CTA a row, one thread an expert (route.cuh: route_row_cta); the last CTA to finish builds the slot table (a ticket).
-__global__ void __launch_bounds__(512) k_route_union(RouteParams rp, TabArgs ta, const float* __restrict__ lpart, int nsplit,
-                                                     const float* __restrict__ bias, float* __restrict__ logits,
-                                                     int* __restrict__ idx, float* __restrict__ w, SlotTab* __restrict__ out,
-                                                     int* __restrict__ status, int* __restrict__ cnt) {
-  __shared__ SlotTab tab;
-  __shared__ RouteSmem rs;
-  __shared__ uint32_t bm[16];
-  __shared__ int s_idx[kMaxRows * kMaxTopK];
-  __shared__ float s_w[kMaxRows * kMaxTopK];
-  __shared__ int s_ticket;
-  pdl_launch_dependents();
-  pdl_wait();
-  const int row = blockIdx.x;
-  route_row_cta(rp, lpart + (size_t)row * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, rs,
-                logits ? logits + (size_t)row * rp.E : nullptr, idx + row * rp.topk, w + row * rp.topk);
-  // the last row to finish builds the slot table of the step
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_ticket = ta.M > 1 ? atomicAdd(cnt, 1) : 0;
-  __syncthreads();
-  if (s_ticket != ta.M - 1) return;
-  __threadfence();
-  for (int i = threadIdx.x; i < ta.M * ta.topk; i += blockDim.x) s_idx[i] = __ldcg(idx + i), s_w[i] = __ldcg(w + i);
-  if (threadIdx.x == 0 && ta.M > 1) *cnt = 0;
-  __syncthreads();
-  build_slot_tab(tab, bm, s_idx, s_w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
-  if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
-  store_tab(tab, out);
-}
-
-// ------------------------------------------------------------------------------------------------------------ k_prep
-// CTA 0: the slot table from the caller's idx / w.  CTAs 1..: x -> blocks.
-__global__ void __launch_bounds__(256) k_prep(TabArgs ta, const int* __restrict__ idx, const float* __restrict__ w,
-                                              const __nv_bfloat16* __restrict__ x, int H, uint8_t* __restrict__ xq,
-                                              SlotTab* __restrict__ out, int* __restrict__ status) {
-  __shared__ SlotTab tab;
-  __shared__ uint32_t bm[16];
-  pdl_launch_dependents();
-  pdl_wait();
-  if (blockIdx.x == 0) {
-    build_slot_tab(tab, bm, idx, w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
-    if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
-    store_tab(tab, out);
-    return;
-  }
-  const int lane = threadIdx.x & 31, gw = ((int)blockIdx.x - 1) * 8 + (threadIdx.x >> 5);
-  const int j = gw >> 3, r = gw & 7;
-  if (j < H / 128) quant_x_block(x, ta.M, H, xq, j, r, lane);
-}
-
-// -------------------------------------------------------------------------------------------------------------- k_up
 template <class V>
 __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p) {
   constexpr int kWarps = V::kWarps, kKCH = V::kKCH, kNST = V::kNST, kUpStage = V::kUpStage;
@@ -497,13 +362,6 @@ cudaError_t launch_down(const DecodeParams& p, cudaStream_t st, bool pdl) {
   return launch_k(k_down_fp8<V>, dim3(sm_count()), dim3(V::kThreads), down_smem<V>(), st, pdl, p);
 }
 
-TabArgs tab_args(const DecodeParams& p) {
-  TabArgs ta;
-  ta.M = p.M, ta.topk = p.topk, ta.E = p.E, ta.e_lo = p.e_lo, ta.e_hi = p.e_hi;
-  ta.pool = p.pool, ta.desc = p.desc, ta.sh = p.sh, ta.fmt = DSGX_FMT_FP8;
-  return ta;
-}
-
 }  // namespace
 
 int decode_fp8_up_variants() { return 7; }
@@ -538,23 +396,16 @@ static cudaError_t launch_up_down(const DecodeParams& p, cudaStream_t st, bool p
 // The expert step on the caller's idx / w: k_prep, k_up, k_down.
 cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
   if (parts & 1) {
-    const int qctas = (p.H / 128 * 8 + 7) / 8;
-    cudaError_t e = launch_k(k_prep, dim3(1 + qctas), dim3(256), 0, st, pdl, tab_args(p), p.idx, p.w, x, p.H, p.ws.xq,
-                             p.ws.tab, p.ws.status);
+    cudaError_t e = launch_prep(p, DSGX_FMT_FP8, x, st, pdl);
     if (e != cudaSuccess) return e;
   }
   return launch_up_down(p, st, pdl, parts);
 }
 
-// The whole layer step: k_front, k_route_union, k_up, k_down (p.idx / p.w / logits are outputs of the routing).
+// The whole layer step: k_front, k_route_union, k_up, k_down (idx / w / logits are outputs of the routing).
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl) {
-  const int KS = (p.H + 1023) / 1024;
-  const int nlog = (p.E * KS + 7) / 8, qctas = (p.H / 128 * 8 + 7) / 8;
-  cudaError_t e = launch_k(k_front, dim3(nlog + qctas), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq);
-  if (e != cudaSuccess) return e;
-  e = launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p), (const float*)p.ws.lpart, KS,
-               bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
+  cudaError_t e = launch_front_route(p, DSGX_FMT_FP8, rp, x, wr, bias, logits, idx, w, st, pdl);
   if (e != cudaSuccess) return e;
   return launch_up_down(p, st, pdl, 3);
 }

@@ -1,0 +1,162 @@
+// The front of a decode step, shared by every expert format: router logit slices, activation staging (FP8: quantised
+// blocks; INT4 layers: bf16 tiles), routing of the rows and the slot table.
+//
+//   k_front:       (layer step) router logit partial sums, one warp per (expert, 1024-k slice), all loads in one
+//                  round trip; the other CTAs stage x.
+//   k_route_union: (layer step) one CTA a row, one thread an expert: sums the slices and routes the row (route.cuh);
+//                  the last CTA to finish builds the slot table (a ticket, no waiting).
+//   k_prep:        (moe_decode with the caller's idx / w) the slot table + the staging of x.
+#include "common.cuh"
+#include "decode_common.cuh"
+#include "kernels.h"
+#include "route.cuh"
+
+namespace dsgx {
+
+namespace {
+
+// One CTA's share of staging x for the expert kernels.  FP8: one warp a (128-k block, row), quantised blocks.
+// Other formats: one thread a (16-value group, row) of the bf16 tile.
+DSGX_DEV void stage_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t* __restrict__ out, int fmt, int cta) {
+  if (fmt == DSGX_FMT_FP8) {
+    const int gw = cta * 8 + (threadIdx.x >> 5);
+    const int j = gw >> 3, r = gw & 7;
+    if (j < H / 128) quant_x_block(x, M, H, out, j, r, threadIdx.x & 31);
+  } else {
+    const int R = rows_pow2(M);
+    const int i = cta * 256 + threadIdx.x;
+    if (i < H / 16 * R) tile_x_group(x, M, H, R, out, i / R, i % R);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------- k_front
+// CTAs [0, nlog): one warp per (expert, slice of 1024 k): the slice's partial logit of every row, in the router's
+// summation order (lane j: k = base + 128 i + 4 j + c by fma, then the butterfly).  CTAs [nlog, ..): x -> blocks.
+__global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M,
+                                               int H, int E, int nlog, float* __restrict__ lpart, uint8_t* __restrict__ xq,
+                                               int fmt) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if ((int)blockIdx.x >= nlog) {
+    stage_x(x, M, H, xq, fmt, (int)blockIdx.x - nlog);
+    return;
+  }
+  const int KS = (H + 1023) / 1024;
+  const int gw = blockIdx.x * 8 + warp;
+  const int e = gw / KS, sl = gw % KS;
+  if (e >= E) return;
+  const int base = sl * 1024, nit = min(1024, H - base) / 128;
+  float4 wv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    wv[i] = i < nit ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)e * H + base + 128 * i + 4 * lane))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < M; ++r) {
+    uint2 xv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      xv[i] = i < nit ? __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * H + base + 128 * i + 4 * lane)) : make_uint2(0, 0);
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nit) {
+        a = fmaf(bf16_bits_to_f(xv[i].x & 0xffffu), wv[i].x, a);
+        a = fmaf(bf16_bits_to_f(xv[i].x >> 16), wv[i].y, a);
+        a = fmaf(bf16_bits_to_f(xv[i].y & 0xffffu), wv[i].z, a);
+        a = fmaf(bf16_bits_to_f(xv[i].y >> 16), wv[i].w, a);
+      }
+    a = warp_sum(a);
+    if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------- k_route_union
+DSGX_DEV void store_tab(const SlotTab& tab, SlotTab* out) {
+  const uint4* s = reinterpret_cast<const uint4*>(&tab);
+  uint4* d = reinterpret_cast<uint4*>(out);
+  for (int i = threadIdx.x; i < (int)(sizeof(SlotTab) / 16); i += blockDim.x) d[i] = s[i];
+}
+
+// One CTA a row, one thread an expert (route.cuh: route_row_cta); the last CTA to finish builds the slot table (a ticket).
+__global__ void __launch_bounds__(512) k_route_union(RouteParams rp, TabArgs ta, const float* __restrict__ lpart, int nsplit,
+                                                     const float* __restrict__ bias, float* __restrict__ logits,
+                                                     int* __restrict__ idx, float* __restrict__ w, SlotTab* __restrict__ out,
+                                                     int* __restrict__ status, int* __restrict__ cnt) {
+  __shared__ SlotTab tab;
+  __shared__ RouteSmem rs;
+  __shared__ uint32_t bm[16];
+  __shared__ int s_idx[kMaxRows * kMaxTopK];
+  __shared__ float s_w[kMaxRows * kMaxTopK];
+  __shared__ int s_ticket;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  route_row_cta(rp, lpart + (size_t)row * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, rs,
+                logits ? logits + (size_t)row * rp.E : nullptr, idx + row * rp.topk, w + row * rp.topk);
+  // the last row to finish builds the slot table of the step
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = ta.M > 1 ? atomicAdd(cnt, 1) : 0;
+  __syncthreads();
+  if (s_ticket != ta.M - 1) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < ta.M * ta.topk; i += blockDim.x) s_idx[i] = __ldcg(idx + i), s_w[i] = __ldcg(w + i);
+  if (threadIdx.x == 0 && ta.M > 1) *cnt = 0;
+  __syncthreads();
+  build_slot_tab(tab, bm, s_idx, s_w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
+  if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
+  store_tab(tab, out);
+}
+
+// ------------------------------------------------------------------------------------------------------------ k_prep
+// CTA 0: the slot table from the caller's idx / w.  CTAs 1..: x -> blocks.
+__global__ void __launch_bounds__(256) k_prep(TabArgs ta, const int* __restrict__ idx, const float* __restrict__ w,
+                                              const __nv_bfloat16* __restrict__ x, int H, uint8_t* __restrict__ xq,
+                                              SlotTab* __restrict__ out, int* __restrict__ status) {
+  __shared__ SlotTab tab;
+  __shared__ uint32_t bm[16];
+  pdl_launch_dependents();
+  pdl_wait();
+  if (blockIdx.x == 0) {
+    build_slot_tab(tab, bm, idx, w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
+    if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
+    store_tab(tab, out);
+    return;
+  }
+  stage_x(x, ta.M, H, xq, (int)ta.fmt, (int)blockIdx.x - 1);
+}
+
+// -------------------------------------------------------------------------------------------------------------- k_up
+
+TabArgs tab_args(const DecodeParams& p, uint32_t fmt) {
+  TabArgs ta;
+  ta.M = p.M, ta.topk = p.topk, ta.E = p.E, ta.e_lo = p.e_lo, ta.e_hi = p.e_hi;
+  ta.pool = p.pool, ta.desc = p.desc, ta.sh = p.sh, ta.fmt = fmt;
+  return ta;
+}
+
+int stage_ctas(const DecodeParams& p, uint32_t fmt) {
+  return fmt == DSGX_FMT_FP8 ? (p.H / 128 * 8 + 7) / 8 : (p.H / 16 * rows_pow2(p.M) + 255) / 256;
+}
+
+}  // namespace
+
+cudaError_t launch_prep(const DecodeParams& p, uint32_t fmt, const __nv_bfloat16* x, cudaStream_t st, bool pdl) {
+  return launch_k(k_prep, dim3(1 + stage_ctas(p, fmt)), dim3(256), 0, st, pdl, tab_args(p, fmt), p.idx, p.w, x, p.H, p.ws.xq,
+                  p.ws.tab, p.ws.status);
+}
+
+cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteParams& rp, const __nv_bfloat16* x,
+                               const float* wr, const float* bias, float* logits, int* idx, float* w, cudaStream_t st,
+                               bool pdl) {
+  const int KS = (p.H + 1023) / 1024;
+  const int nlog = (p.E * KS + 7) / 8;
+  cudaError_t e = launch_k(k_front, dim3(nlog + stage_ctas(p, fmt)), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog,
+                           p.ws.lpart, p.ws.xq, (int)fmt);
+  if (e != cudaSuccess) return e;
+  return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, fmt),
+                  (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
+}
+
+}  // namespace dsgx

@@ -36,8 +36,8 @@ cudaError_t launch_finalize(const float* R, const float* S, int M, int H, __nv_b
 // base).  Zeroed once by the caller; the kernels leave every counter at zero.
 struct DecodeWs {
   int* status;      // [0]: a dsgx_status recorded by a kernel, 0 if none
-  uint8_t* xq;      // [H/128] activation blocks of x (FP8)
-  __nv_bfloat16* h; // [kMaxSlots][8][I] bf16 h before quantisation
+  uint8_t* xq;      // FP8: [H/128] activation blocks of x; INT4 layers: the bf16 tile of x [H/16][R][32 B]
+  __nv_bfloat16* h; // FP8: [kMaxSlots][8][I] bf16 h before quantisation; INT4 layers: the bf16 tiles of h [slot][I/16][R][32 B]
   uint8_t* hq;      // [kMaxSlots][I/128] activation blocks of h
   float* ypick;     // [kMaxSlots][H/16][16][8] every pick's down output (bf16-rounded values kept as f32)
   int* cnt_h;       // [kMaxSlots][I/128] arrivals of the 16 gate/up units of a 128-group of h
@@ -69,6 +69,17 @@ int decode_fp8_up_variants();
 int decode_fp8_down_variants();
 // parts: 1 = activation quantisation + gate/up, 2 = down + combine, 3 = both
 cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
+
+cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
+cudaError_t launch_layer_int4(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
+                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
+bool decode_int4_fits(int H, int M);
+
+// the front of a decode step (decode_front.cu); fmt selects how x is staged for the expert kernels
+cudaError_t launch_prep(const DecodeParams& p, uint32_t fmt, const __nv_bfloat16* x, cudaStream_t st, bool pdl);
+cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteParams& rp, const __nv_bfloat16* x,
+                               const float* wr, const float* bias, float* logits, int* idx, float* w, cudaStream_t st,
+                               bool pdl);
 
 int sm_count();
 

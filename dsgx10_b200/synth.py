@@ -137,3 +137,71 @@ def int4_tensors(N, K, seed):
     wp = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
     s = (((118 + rng.integers(0, 2, (N, K // 32))) << 7) | rng.integers(0, 128, (N, K // 32))).astype(np.uint16)
     return wp, s
+
+
+def pack_int4_block(wp, s):
+    """canonical symmetric INT4 (wp uint8 [N][K/2], s bf16 bits [N][K/32]) -> the engine's blocks of 8 rows x 512 k,
+    2368 B each, [N/8][K/512] (altar1 engine/experts/layout.h:50-58, 78-95); the zero point is 8 everywhere."""
+    N, K = wp.shape[0], wp.shape[1] * 2
+    B = K // 512
+    v = wp.reshape(N // 8, 8, B, 4, 2, 4, 8)                       # n8, g, b, jj, q, t, byte
+    vals = np.ascontiguousarray(v.transpose(0, 2, 3, 1, 5, 4, 6)).reshape(N // 8, B, 2048)   # n8, b, jj, g, t, q, byte
+    sc = s.reshape(N // 8, 8, B, 4, 2, 2)                          # n8, g, b, jj, q, h   (group 16 b + 4 jj + 2 q + h)
+    sc = np.ascontiguousarray(sc.transpose(0, 2, 1, 5, 3, 4)).reshape(N // 8, B, 128)        # n8, b, g, h, jj, q
+    out = np.empty((N // 8, B, 2368), np.uint8)
+    out[:, :, :2048] = vals
+    out[:, :, 2048:2304] = sc.view(np.uint8).reshape(N // 8, B, 256)
+    out[:, :, 2304:] = 0x88
+    return out.reshape(-1)
+
+
+def tile_bf16(w):
+    """bf16 bits [N][K] (torch int16 / numpy uint16) -> blocks of 8 rows x 128 k, 2048 B, [N/8][K/128]: the lane's 16 B
+    at 512 p + 16 (4 g + t) are k = 64 (p >> 1) + 16 t + 8 (p & 1) + 0..7 (altar1 engine/experts/layout.h:96-107)."""
+    N, K = w.shape
+    v = w.reshape(N // 8, 8, K // 128, 2, 4, 2, 8)                  # n8, g, b, q, t, half, 8 values
+    return np.ascontiguousarray(v.transpose(0, 2, 3, 5, 1, 4, 6)).reshape(-1).view(np.uint8)  # n8, b, q, half, g, t, 8
+
+
+class Int4Layer:
+    """One INT4-g32 layer: `E` routed experts in the engine's block layout + (optionally) a bf16 shared expert."""
+
+    def __init__(self, H, I, E, seed, device="cpu", shared=True, e_range=None):
+        self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_INT4
+        self.device = torch.device(device)
+        shapes = ((I, H), (I, H), (H, I))
+        mat_b = (I // 8) * (H // 512) * 2368
+        assert mat_b == (H // 8) * (I // 512) * 2368 and mat_b % 256 == 0
+        lo, hi = e_range if e_range is not None else (0, E)
+        self.raw = {}
+        pool = np.empty(max(hi - lo, 1) * 3 * mat_b, np.uint8)
+        self.desc_host = (_lib.MatDesc * (E * 3))()
+        for n, e in enumerate(range(lo, hi)):
+            self.raw[e] = []
+            for m, (N, K) in enumerate(shapes):
+                wp, s = int4_tensors(N, K, seed * 1000 + e * 3 + m)
+                self.raw[e].append((wp, s))
+                off = (n * 3 + m) * mat_b
+                pool[off:off + mat_b] = pack_int4_block(wp, s)
+                d = self.desc_host[e * 3 + m]
+                d.off, d.s2, d.fmt = off, 1.0, _lib.FMT_INT4
+        self.pool = torch.from_numpy(pool).to(self.device)
+        self.desc = torch.frombuffer(bytearray(bytes(self.desc_host)), dtype=torch.uint8).to(self.device)
+        self.shared = shared
+        if shared:
+            self.sh_bits = [bf16_bits((torch.randn(n, k, generator=_gen("cpu", seed + 9 + i)) * 0.02).to(torch.bfloat16))
+                            for i, (n, k) in enumerate(shapes)]
+            self.sh_dev = [torch.from_numpy(tile_bf16(b)).to(self.device) for b in self.sh_bits]
+
+    def layer_w(self):
+        L = _lib.LayerW()
+        L.pool, L.desc, L.fmt = self.pool.data_ptr(), self.desc.data_ptr(), _lib.FMT_INT4
+        if self.shared:
+            L.sh.bg, L.sh.bu, L.sh.bd = (t.data_ptr() for t in self.sh_dev)
+        return L
+
+    def expert_bytes(self):
+        return 3 * (self.I // 8) * (self.H // 512) * 2368
+
+    def shared_bytes(self):
+        return 3 * self.I * self.H * 2

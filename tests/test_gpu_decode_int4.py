@@ -1,0 +1,87 @@
+"""GPU parity of the INT4-g32 decode expert step (bf16 activations, bf16 shared expert) against the CPU oracle."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def _oracle(orc, layer, xb, idx, w, e_lo=0, e_hi=None, with_shared=True):
+    picked = sorted(set(int(e) for e in np.asarray(idx).ravel()))
+    e_hi = layer.E if e_hi is None else e_hi
+    deq = {e: tuple(orc.int4_dequant(wp, s, None) for wp, s in layer.raw[e]) for e in picked if e_lo <= e < e_hi}
+    if not deq:
+        e = next(iter(layer.raw))
+        deq = {e: tuple(orc.int4_dequant(wp, s, None) for wp, s in layer.raw[e])}
+    sh = tuple(layer.sh_bits) if (layer.shared and with_shared) else None
+    return orc.moe_bf16w_layer(xb, idx, w, deq, sh, e_lo=e_lo, e_hi=e_hi, with_shared=with_shared)
+
+
+def _run(orc, H, I, E, topk, M, seed, score=1, scale=1.0, shared=True, e_lo=0, e_hi=None):
+    from dsgx10_b200 import _lib, moe, synth
+    from tests.util import oracle_route, rowmax_err
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4, score_fn=score, route_scale=scale, e_lo=e_lo, e_hi=e_hi)
+    layer = synth.Int4Layer(H, I, E, seed, device="cuda", shared=shared, e_range=(e_lo, E if e_hi is None else e_hi))
+    x = synth.activations(M, H, seed + 1000).cuda()
+    wr = synth.router_weights(E, H, seed + 2000).cuda()
+    step = moe.LayerStep(shp, wr)
+    outs = []
+    for _ in range(2):
+        out = step.run(layer.layer_w(), x)
+        torch.cuda.synchronize()
+        assert moe.ws_status(step.ws) == 0
+        outs.append((step.yr[:M].cpu().numpy().copy(), step.ys[:M].cpu().numpy().copy(), synth.bf16_bits(out).copy()))
+    assert (outs[0][0] == outs[1][0]).all() and (outs[0][2] == outs[1][2]).all()
+    xb = synth.bf16_bits(x)
+    _, oi, ow = oracle_route(orc, xb, wr.cpu().numpy(), None, shp)
+    assert (step.idx[:M].cpu().numpy() == oi).all()
+    assert (step.w[:M].cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+    acc_r, _ = _oracle(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=False)
+    acc_all, out_all = _oracle(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=shared)
+    yr, ys, outb = outs[0]
+    assert rowmax_err(yr, acc_r) <= TOL
+    if shared:
+        assert rowmax_err(yr + ys, acc_all) <= TOL
+    assert rowmax_err(orc.bf16_to_f32(outb), orc.bf16_to_f32(out_all)) <= TOL + 2 ** -8
+    # the separate-call path (caller's idx / w) gives the same bits
+    ws = moe.decode_ws(shp)
+    yr2, ys2 = moe.moe_decode(shp, layer.layer_w(), x, step.idx[:M].contiguous(), step.w[:M].contiguous(), ws)
+    torch.cuda.synchronize()
+    assert (yr2.cpu().numpy() == yr).all()
+    if shared:
+        assert (ys2.cpu().numpy() == ys).all()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8])
+def test_small_layer(orc, M):
+    _run(orc, 1024, 512, 16, 4, M, seed=100 + M)
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_config3_shapes_fewer_experts(orc, M):
+    """hidden 6144, intermediate 2048, top-8 softmax, bf16 shared expert; 24 experts instead of 168 to stay small."""
+    _run(orc, 6144, 2048, 24, 8, M, seed=20261103 + M)
+
+
+def test_sigmoid_scaled_no_shared_and_expert_parallel(orc):
+    _run(orc, 1024, 1024, 16, 8, 5, seed=120, score=0, scale=2.5, shared=False)
+    _run(orc, 1024, 512, 16, 4, 6, seed=121, e_lo=8, e_hi=16, shared=False)
+    _run(orc, 1024, 512, 16, 4, 6, seed=121, e_lo=0, e_hi=8)
+
+
+def test_batch_invariance(orc):
+    from dsgx10_b200 import _lib, moe, synth
+    H, I, E, topk = 1024, 512, 16, 4
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4)
+    layer = synth.Int4Layer(H, I, E, 131, device="cuda")
+    x = synth.activations(8, H, 132).cuda()
+    wr = synth.router_weights(E, H, 133).cuda()
+    step = moe.LayerStep(shp, wr)
+    step.run(layer.layer_w(), x)
+    yr8, ys8 = step.yr.clone(), step.ys.clone()
+    for r in range(8):
+        step.run(layer.layer_w(), x[r:r + 1].contiguous())
+        torch.cuda.synchronize()
+        assert torch.equal(step.yr[0], yr8[r]) and torch.equal(step.ys[0], ys8[r])
