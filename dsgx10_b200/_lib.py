@@ -54,6 +54,10 @@ SYMBOLS = {
     "dsgx_finalize": (_I, [_V, _V, _I, _I, _V, _I, _V]),
     "dsgx_moe_layer_decode": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _I, C.POINTER(LayerStep), _I, _V]),
     "dsgx_moe_layer_decode_host": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _I, C.POINTER(LayerStep), _V, _V]),
+    "dsgx_prefill_weights_bytes": (_Z, [C.POINTER(MoeShape)]),
+    "dsgx_prefill_prepare": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V]),
+    "dsgx_prefill_ws_bytes": (_Z, [C.POINTER(MoeShape), _I]),
+    "dsgx_moe_prefill": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _V, _I, _V, _V, _V, _V, _I, _V]),
     "dsgx_ws_status": (_I, [_V]),
 }
 

@@ -240,6 +240,87 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* s, const dsgx_layer_w* L, c
   return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
 }
 
+static int check_prefill_shape(const dsgx_moe_shape* s) {
+  const int rc = check_shape(s);
+  if (rc) return rc;
+  if (s->fmt != DSGX_FMT_FP8) return DSGX_ERR_UNSUPPORTED;
+  if (s->H % 256 || s->I % 128) return DSGX_ERR_SHAPE;
+  return DSGX_OK;
+}
+
+size_t dsgx_prefill_weights_bytes(const dsgx_moe_shape* s) {
+  if (check_prefill_shape(s)) return 0;
+  return prefill_weights_bytes(s->H, s->I, s->E);
+}
+
+int dsgx_prefill_prepare(const dsgx_moe_shape* s, const dsgx_layer_w* L, void* wbuf, void* stream) {
+  const int rc = check_prefill_shape(s);
+  if (rc) return rc;
+  if (!L || !L->pool || !L->desc || !wbuf || L->fmt != s->fmt) return DSGX_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int H = s->H, I = s->I, E = s->E;
+  PrefillWeights pw = prefill_weights_carve(wbuf, H, I, E);
+  const int nloc = s->e_hi - s->e_lo;
+  dsgx_mat_desc* hd = nloc > 0 ? new dsgx_mat_desc[(size_t)nloc * 3] : nullptr;
+  cudaError_t e = cudaSuccess;
+  if (nloc > 0) e = cudaMemcpy(hd, L->desc + (size_t)s->e_lo * 3, sizeof(dsgx_mat_desc) * nloc * 3, cudaMemcpyDeviceToHost);
+  int bad = 0;
+  const size_t mat = (size_t)I * H, sc = (size_t)(I / 128) * (H / 128);
+  for (int i = 0; e == cudaSuccess && i < nloc; ++i) {
+    const int ex = s->e_lo + i;
+    for (int m = 0; m < 3; ++m) {
+      const dsgx_mat_desc& d = hd[i * 3 + m];
+      if (d.fmt != DSGX_FMT_FP8 || (d.off & 255)) {
+        bad = 1;
+        break;
+      }
+      const uint8_t* src = L->pool + d.off;
+      const float* ssrc = reinterpret_cast<const float*>(L->pool + ((uint64_t)d.rsv[0] | (uint64_t)d.rsv[1] << 32));
+      uint8_t* dst = (m == 0 ? pw.g : m == 1 ? pw.u : pw.d) + (size_t)ex * mat;
+      float* sdst = (m == 0 ? pw.sg : m == 1 ? pw.su : pw.sd) + (size_t)ex * sc;
+      e = retile_matrix(src, ssrc, m == 2 ? H : I, m == 2 ? I : H, dst, sdst, st);
+      if (e != cudaSuccess) break;
+    }
+    if (bad) break;
+  }
+  delete[] hd;
+  if (bad) return DSGX_ERR_FORMAT;
+  if (e == cudaSuccess && L->sh.g) {
+    if (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds) return DSGX_ERR_ARG;
+    e = retile_matrix(L->sh.g, L->sh.gs, I, H, pw.g + (size_t)E * mat, pw.sg + (size_t)E * sc, st);
+    if (e == cudaSuccess) e = retile_matrix(L->sh.u, L->sh.us, I, H, pw.u + (size_t)E * mat, pw.su + (size_t)E * sc, st);
+    if (e == cudaSuccess) e = retile_matrix(L->sh.d, L->sh.ds, H, I, pw.d + (size_t)E * mat, pw.sd + (size_t)E * sc, st);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+size_t dsgx_prefill_ws_bytes(const dsgx_moe_shape* s, int T) {
+  if (check_prefill_shape(s) || T < 1) return 0;
+  return prefill_ws_bytes(T, s->H, s->I, s->E, s->topk);
+}
+
+int dsgx_moe_prefill(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* wbuf, const void* x, const int32_t* idx,
+                     const float* w, int T, void* ws, float* yr, float* ys, void* out, int ysum, void* stream) {
+  const int rc = check_prefill_shape(s);
+  if (rc) return rc;
+  if (!L || !wbuf || !x || !idx || !w || !ws || !yr || T < 1) return DSGX_ERR_ARG;
+  if (((uintptr_t)wbuf & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
+  const bool sh = L->sh.g != nullptr;
+  if (sh && !ys && !ysum && !out) return DSGX_ERR_ARG;
+  if ((size_t)T * s->topk > (size_t)1 << 30) return DSGX_ERR_SHAPE;
+  PrefillParams q;
+  q.T = T, q.H = s->H, q.I = s->I, q.E = s->E, q.topk = s->topk, q.has_shared = sh, q.ysum = ysum;
+  q.e_lo = s->e_lo, q.e_hi = s->e_hi;
+  q.x = reinterpret_cast<const __nv_bfloat16*>(x), q.idx = idx, q.w = w;
+  q.pw = prefill_weights_carve(const_cast<void*>(wbuf), s->H, s->I, s->E);
+  q.ws = prefill_ws_carve(ws, T, s->H, s->I, s->E, s->topk);
+  q.yr = yr, q.ys = ys, q.out = reinterpret_cast<__nv_bfloat16*>(out);
+  cudaError_t e = cudaMemsetAsync(q.ws.status, 0, 4, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = launch_prefill_fp8(q, (cudaStream_t)stream);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
 int dsgx_ws_status(const void* ws) {
   if (!ws) return DSGX_ERR_ARG;
   int v = 0;

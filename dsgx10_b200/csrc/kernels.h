@@ -81,6 +81,41 @@ cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteP
                                const float* wr, const float* bias, float* logits, int* idx, float* w, cudaStream_t st,
                                bool pdl);
 
+// ---- prefill (FP8) ----------------------------------------------------------------------------------------------------
+struct PrefillWeights {  // K-major row-major copies of the layer's matrices, [E + 1 experts] each (index E: shared)
+  uint8_t *g, *u, *d;
+  float *sg, *su, *sd;
+};
+size_t prefill_weights_bytes(int H, int I, int E);
+PrefillWeights prefill_weights_carve(void* buf, int H, int I, int E);
+cudaError_t retile_matrix(const uint8_t* tiled, const float* scales, int N, int K, uint8_t* out, float* sout, cudaStream_t st);
+
+struct PrefillWs {
+  int* status;
+  uint8_t* xq;   float* xs;                  // per token
+  uint8_t* xq_s; float* xs_s; float* w_s;    // per sorted pick
+  uint8_t* hq;   float* hs;                  // routed h
+  uint8_t* hq_sh; float* hs_sh;              // shared h
+  __nv_bfloat16* y; __nv_bfloat16* y_sh;
+  int *perm_tok, *perm_slot, *pos_of, *row_order, *counts, *offsets, *tile_off;
+  void* sort_ws;
+};
+size_t prefill_ws_bytes(int T, int H, int I, int E, int topk);
+PrefillWs prefill_ws_carve(void* ws, int T, int H, int I, int E, int topk);
+
+struct PrefillParams {
+  int T, H, I, E, topk, has_shared, ysum, e_lo, e_hi;
+  const __nv_bfloat16* x;
+  const int* idx;
+  const float* w;
+  PrefillWeights pw;
+  PrefillWs ws;
+  float* yr;
+  float* ys;
+  __nv_bfloat16* out;
+};
+cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st);
+
 int sm_count();
 
 }  // namespace dsgx

@@ -1,0 +1,590 @@
+// Prefill / verify path of the FP8 (W8A8-g128) layer: the experts as grouped GEMMs over token-sorted ragged segments
+// on the 5th-generation tensor cores.
+//
+//   k_quant_rows   x bf16 [T][H] -> e4m3 [T][H] + f32 scales [T][H/128] (once per token)
+//   k_gather_rows  the quantised rows, scales and routing weights into the (expert id, token) order of the sort
+//   k_tile_offsets prefix of the 128-row tiles per expert segment
+//   k_gemm_fp8     C = A B^T per 128-row tile: operands staged by TMA (128-byte swizzle) through a 4-stage ring,
+//                  tcgen05.mma kind::f8f6f4 M 128 x N 256 x K 32 issued by one thread, accumulators in TMEM (two
+//                  buffers of 256 columns); after every 128-k block the eight epilogue warps read the block's partial
+//                  sums with tcgen05.ld and promote them into f32 registers with the product of the row's activation
+//                  scale and the weight block's scale, while the next block's MMAs fill the other TMEM buffer.
+//                  UP:   B = 128 gate + 128 up channels; epilogue: bf16 rounding, SwiGLU, routing weight, bf16 h,
+//                        quantisation of the 128 channels (one scale group) to e4m3.
+//                  DOWN: B = 256 output channels; epilogue: every pick's output rounded to bf16.
+//   k_combine      per token: the picks' outputs added in f32 in ascending expert id, then the shared expert's.
+//
+// The weights are read from a K-major row-major copy ([expert][N][K] e4m3, scales [expert][N/128][K/128]) made once at
+// load time by k_retile_fp8 from the engine's tile_fp8 blocks (the reference re-tiles its checkpoints the same way:
+// ds41f engine/kernels/moe.cu:1187-1265, 1332-1336), because a TMA box wants whole rows.
+// No cluster multicast anywhere: every CTA fetches its own tiles (L2 serves the reuse).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dsgx {
+
+namespace {
+
+// ---- tcgen05 / TMA wrappers ------------------------------------------------------------------------------------------
+DSGX_DEV void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_u32(dst)),
+               "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+               : "memory");
+}
+DSGX_DEV void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+DSGX_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+DSGX_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+DSGX_DEV void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] B[smem]^T, e4m3 operands, M 128, N 256, K 32
+DSGX_DEV void tc_mma_f8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+DSGX_DEV void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+DSGX_DEV void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with 128-byte rows and the 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart
+DSGX_DEV uint64_t umma_desc_sw128(const void* smem) {
+  uint64_t d = (uint64_t)((smem_u32(smem) >> 4) & 0x3FFFu);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused for swizzled K-major), 16 B
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset: 8 rows
+  d |= (uint64_t)1 << 46;            // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor: f32 accumulate, e4m3 x e4m3, both K-major, M 128, N 256
+constexpr uint32_t kIdesc = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+
+constexpr int kGThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..9: epilogue
+constexpr int kGStages = 4;
+constexpr int kATile = 128 * 128, kBTile = 256 * 128, kGStage = kATile + kBTile;
+
+// ---- small kernels -------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_retile_fp8(const uint8_t* __restrict__ tiled, int N, int K, uint8_t* __restrict__ out) {
+  // one thread a 16-byte piece: tile_fp8 [N/8][K/128][32 lanes][32 B], lane 4 g + t: row 8 n8 + g, k = 128 j + 64 q + 16 t + i
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * K / 16) return;
+  const size_t blk = i >> 6;
+  const int within = (int)(i & 63), lane = within >> 1, q = within & 1, g = lane >> 2, t = lane & 3;
+  const int J = K / 128;
+  const int n8 = (int)(blk / J), j = (int)(blk % J);
+  const uint4 v = __ldg(reinterpret_cast<const uint4*>(tiled) + i);
+  *reinterpret_cast<uint4*>(out + (size_t)(8 * n8 + g) * K + 128 * j + 64 * q + 16 * t) = v;
+}
+
+__global__ void __launch_bounds__(256) k_quant_rows(const __nv_bfloat16* __restrict__ x, int T, int K, uint8_t* __restrict__ q,
+                                                    float* __restrict__ s) {
+  const int lane = threadIdx.x & 31;
+  const size_t gw = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int KB = K / 128;
+  if (gw >= (size_t)T * KB) return;
+  const size_t r = gw / KB;
+  const int j = (int)(gw % KB);
+  const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + r * K + 128 * j + 4 * lane));
+  const float v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
+  const float v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+  const float sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
+  *reinterpret_cast<uint32_t*>(q + r * K + 128 * j + 4 * lane) =
+      quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  if (lane == 0) s[r * KB + j] = sc;
+}
+
+// sorted position -> its token's quantised row, scales and routing weight
+__global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__ q, const float* __restrict__ s,
+                                                     const float* __restrict__ w, const int* __restrict__ perm_tok,
+                                                     const int* __restrict__ perm_slot, int P, int K, int topk,
+                                                     uint8_t* __restrict__ qs, float* __restrict__ ss, float* __restrict__ ws) {
+  const int per = K / 16;  // 16-byte pieces a row
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)P * per) return;
+  const size_t pos = i / per;
+  const int c = (int)(i % per);
+  const int t = perm_tok[pos];
+  reinterpret_cast<uint4*>(qs)[i] = __ldg(reinterpret_cast<const uint4*>(q + (size_t)t * K) + c);
+  const int KB = K / 128;
+  if (c < KB) ss[pos * KB + c] = s[(size_t)t * KB + c];
+  if (c == 0) ws[pos] = w[(size_t)t * topk + perm_slot[pos]];
+}
+
+// only this GPU's experts [e_lo, e_hi) get tiles
+__global__ void k_tile_offsets(const int* __restrict__ counts, int E, int e_lo, int e_hi, int* __restrict__ tile_off) {
+  if (threadIdx.x == 0) {
+    int a = 0;
+    for (int e = 0; e < E; ++e) tile_off[e] = a, a += e >= e_lo && e < e_hi ? (counts[e] + 127) >> 7 : 0;
+    tile_off[E] = a;
+  }
+}
+
+// ---- the grouped GEMM ---------------------------------------------------------------------------------------------
+struct GemmArgs {
+  int mode;            // 0 UP, 1 DOWN
+  int K;               // H (UP) or I (DOWN)
+  int N;               // I (UP: channels) or H (DOWN)
+  int E;               // segments (1 for the shared expert's dense pass)
+  int rows_total;      // rows of A
+  int wrow0;           // first weight row block: expert e's rows start at (wrow0 + e) * N in the weight tensors
+  const int* seg_off;  // [E + 1] row offsets of the segments (null: one segment [0, rows_total))
+  const int* tile_off; // [E + 1] 128-row tile prefix (null with seg_off null)
+  const float* sa;     // [rows_total][K / 128] activation scales
+  const float* sb0;    // UP: gate scales, DOWN: down scales; [.. experts][N / 128][K / 128]
+  const float* sb1;    // UP: up scales
+  const float* wrow;   // UP: routing weight of every row (null: none)
+  uint8_t* hq;         // UP out: e4m3 [rows][N]
+  float* hs;           // UP out: [rows][N / 128]
+  __nv_bfloat16* y;    // DOWN out: [rows][N]
+  int* status;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant__ CUtensorMap mapA,
+                                                          const __grid_constant__ CUtensorMap mapB0,
+                                                          const __grid_constant__ CUtensorMap mapB1, const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGStages * kGStage);
+  uint64_t* empty = full + kGStages;
+  uint64_t* tfull = empty + kGStages;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* xbar = tempty + 2;  // the epilogue warps' exchange of row maxima
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 1);
+  float* amax_x = reinterpret_cast<float*>(tmem_slot + 6);  // [2 buffers][2 halves][128 rows]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGStages; ++s) mbar_init(full + s, 1), mbar_init(empty + s, 1);
+    for (int b = 0; b < 2; ++b) mbar_init(tfull + b, 1), mbar_init(tempty + b, 8);
+    mbar_init(xbar, 8);
+    mbar_fence_init();
+  }
+  if (warp == 1) {  // 512 TMEM columns: two accumulator buffers of 256
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  const int KB = a.K / 128;
+  const int ntn = MODE == 0 ? a.N / 128 : a.N / 256;  // n-tiles
+  const int mtiles = a.seg_off ? a.tile_off[a.E] : (a.rows_total + 127) / 128;
+  const int items = mtiles * ntn;
+  bool dead = false;
+
+  // item -> (segment, first row, row end, n-tile)
+  auto locate = [&](int item, int& e, int& row0, int& rend, int& nt) {
+    const int mt = item / ntn;
+    nt = item % ntn;
+    if (!a.seg_off) {
+      e = 0, row0 = mt * 128, rend = a.rows_total;
+      return;
+    }
+    int lo = 0, hi = a.E;  // the last e with tile_off[e] <= mt
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (a.tile_off[mid] <= mt) lo = mid;
+      else hi = mid;
+    }
+    e = lo;
+    row0 = a.seg_off[e] + (mt - a.tile_off[e]) * 128;
+    rend = a.seg_off[e + 1];
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
+        int e, row0, rend, nt;
+        locate(item, e, row0, rend, nt);
+        const int wr = (a.wrow0 + e) * a.N + nt * (MODE == 0 ? 128 : 256);
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % kGStages;
+          if (it >= kGStages && !mbar_wait(empty + s, ((it / kGStages) - 1) & 1)) {
+            dead = true;
+            break;
+          }
+          uint8_t* st = smem + s * kGStage;
+          mbar_expect_tx(full + s, kGStage);
+          tma_load_2d(st, &mapA, kb * 128, row0, full + s);
+          tma_load_2d(st + kATile, &mapB0, kb * 128, wr, full + s);
+          tma_load_2d(st + kATile + kATile, MODE == 0 ? &mapB1 : &mapB0, kb * 128, MODE == 0 ? wr : wr + 128, full + s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % kGStages, b = it & 1;
+          if (!mbar_wait(full + s, (it / kGStages) & 1)) {
+            dead = true;
+            break;
+          }
+          if (it >= 2 && !mbar_wait(tempty + b, ((it >> 1) - 1) & 1)) {
+            dead = true;
+            break;
+          }
+          tc_fence_after();
+          const uint8_t* st = smem + s * kGStage;
+          const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + kATile);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)  // 32 k = 32 bytes along the swizzled row: the start address moves by 2 x 16 B
+            tc_mma_f8(tmem + b * 256, da + 2 * j, db + 2 * j, kIdesc, j ? 1u : 0u);
+          tc_commit(empty + s);   // the stage is free when these MMAs have read it
+          tc_commit(tfull + b);   // and the block's partial sums are in TMEM
+        }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------------------------------------- epilogue
+    const int ew = warp - 2, quarter = warp & 3, half = ew >> 2;
+    const int trow = quarter * 32 + lane;  // the tile row (TMEM lane) of this thread
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    uint32_t it = 0, xn = 0;
+    for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
+      int e, row0, rend, nt;
+      locate(item, e, row0, rend, nt);
+      const int row = row0 + trow;
+      const bool live = row < rend;
+      const int srow = live ? row : row0;  // a safe row to read scales from
+      const float* sap = a.sa + (size_t)srow * KB;
+      const size_t sbase = (size_t)(a.wrow0 + e) * (a.N / 128) * KB;
+      const float* sb0p = MODE == 0 ? a.sb0 + sbase + (size_t)nt * KB : a.sb0 + sbase + (size_t)(2 * nt) * KB;
+      const float* sb1p = MODE == 0 ? a.sb1 + sbase + (size_t)nt * KB : a.sb0 + sbase + (size_t)(2 * nt + 1) * KB;
+      float acc0[64], acc1[64];  // columns [64 half, 64 half + 64) of the first and of the second 128
+#pragma unroll
+      for (int c = 0; c < 64; ++c) acc0[c] = 0.f, acc1[c] = 0.f;
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const uint32_t b = it & 1;
+        const float sa = __ldg(sap + kb);
+        const float s0 = sa * __ldg(sb0p + kb), s1 = sa * __ldg(sb1p + kb);
+        if (!mbar_wait(tfull + b, (it >> 1) & 1)) {
+          dead = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t t0 = tmem + lane_addr + b * 256 + half * 64;
+        uint32_t r[32];
+        tc_ld32(t0, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc0[c] = fmaf(__uint_as_float(r[c]), s0, acc0[c]);
+        tc_ld32(t0 + 32, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc0[32 + c] = fmaf(__uint_as_float(r[c]), s0, acc0[32 + c]);
+        tc_ld32(t0 + 128, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc1[c] = fmaf(__uint_as_float(r[c]), s1, acc1[c]);
+        tc_ld32(t0 + 160, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc1[32 + c] = fmaf(__uint_as_float(r[c]), s1, acc1[32 + c]);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty + b);
+      }
+      if (dead) break;
+      if (MODE == 0) {
+        // g, u rounded to bf16; h = bf16(w_route * silu(g) * u); the tile's 128 channels are one quantisation group
+        const float wr = a.wrow ? __ldg(a.wrow + srow) : 1.f;
+        float am = 0.f;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float h = __fmul_rn(silu(bf16_round(acc0[c])), bf16_round(acc1[c]));
+          if (a.wrow) h = __fmul_rn(wr, h);
+          h = bf16_round(h);
+          acc0[c] = h;
+          am = fmaxf(am, fabsf(h));
+        }
+        // the other half's maximum: through shared memory, two buffers by item parity, one bounded barrier an item
+        float* ax = amax_x + (xn & 1) * 256;
+        ax[half * 128 + trow] = am;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xbar);
+        if (!mbar_wait(xbar, xn & 1)) {
+          dead = true;
+          break;
+        }
+        ++xn;
+        const float sc = act_scale(fmaxf(ax[trow], ax[128 + trow]));
+        if (live) {
+          uint4* dst = reinterpret_cast<uint4*>(a.hq + (size_t)row * a.N + nt * 128 + half * 64);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int c = 16 * v + 4 * k;
+              wd[k] = quant_e4m3(acc0[c], sc) | quant_e4m3(acc0[c + 1], sc) << 8 | quant_e4m3(acc0[c + 2], sc) << 16 |
+                      quant_e4m3(acc0[c + 3], sc) << 24;
+            }
+            dst[v] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          }
+          if (half == 0) a.hs[(size_t)row * (a.N / 128) + nt] = sc;
+        }
+      } else if (live) {
+        // every pick's output rounded to bf16
+        __nv_bfloat16* y0 = a.y + (size_t)row * a.N + nt * 256 + half * 64;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint4* dst = reinterpret_cast<uint4*>(y0 + hh * 128);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int c = 8 * v + 2 * k;
+              const float f0 = hh ? acc1[c] : acc0[c], f1 = hh ? acc1[c + 1] : acc0[c + 1];
+              wd[k] = f_to_bf16_bits(f0) | f_to_bf16_bits(f1) << 16;
+            }
+            dst[v] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          }
+        }
+      }
+    }
+  }
+  if (dead && lane == 0) atomicCAS(a.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+
+// ---- combine ------------------------------------------------------------------------------------------------------
+// One thread 8 columns of one token: the picks' bf16 outputs added in f32 in ascending expert id, then the shared one.
+__global__ void __launch_bounds__(256) k_combine(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ ysh,
+                                                 const int* __restrict__ idx, int e_lo, int e_hi,
+                                                 const int* __restrict__ pos_of, const int* __restrict__ row_order, int T, int H,
+                                                 int topk, float* __restrict__ yr, float* __restrict__ ys,
+                                                 __nv_bfloat16* __restrict__ out, int ysum) {
+  const int per = H / 8;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)T * per) return;
+  const size_t t = i / per;
+  const int c = (int)(i % per) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < topk; ++j) {
+    const int jj = row_order[t * topk + j];
+    const int e = idx[t * topk + jj];
+    if (e < e_lo || e >= e_hi) continue;  // another GPU's expert
+    const int pos = pos_of[t * topk + jj];
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + (size_t)pos * H + c));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc[2 * k] = __fadd_rn(acc[2 * k], bf16_bits_to_f(w[k] & 0xffffu));
+      acc[2 * k + 1] = __fadd_rn(acc[2 * k + 1], bf16_bits_to_f(w[k] >> 16));
+    }
+  }
+  float sh[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (ysh) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(ysh + t * H + c));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) sh[2 * k] = bf16_bits_to_f(w[k] & 0xffffu), sh[2 * k + 1] = bf16_bits_to_f(w[k] >> 16);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float both = __fadd_rn(acc[k], sh[k]);
+    yr[t * H + c + k] = ysum && ysh ? both : acc[k];
+    if (ys && ysh) ys[t * H + c + k] = sh[k];
+    if (out) out[t * H + c + k] = __float2bfloat16_rn(both);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  }
+  return fn;
+}
+
+// a [rows][K] e4m3 row-major tensor, boxes of 128 rows x 128 bytes, 128-byte swizzle
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t K) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {K, rows};
+  const cuuint64_t strides[1] = {K};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t es[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + 256 + 4 * 128 * 4;
+
+template <int MODE>
+cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const GemmArgs& a,
+                        cudaStream_t st) {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_fp8<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+    if (e != cudaSuccess) return e;
+    done[dev & 63] = true;
+  }
+  k_gemm_fp8<MODE><<<sm_count(), kGThreads, kGemmSmem, st>>>(mA, mB0, mB1, a);
+  return cudaGetLastError();
+}
+
+size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+}  // namespace
+
+// ---- weights prepared for the prefill path ----------------------------------------------------------------------------
+// [E + 1 experts] (index E: the shared expert, absent: E only): gate [I][H], up [I][H], down [H][I] row-major e4m3, then
+// the f32 scales in the same order.
+size_t prefill_weights_bytes(int H, int I, int E) {
+  const size_t n = (size_t)E + 1;
+  return 3 * al256(n * I * H) + 3 * al256(n * (I / 128) * (H / 128) * 4);
+}
+PrefillWeights prefill_weights_carve(void* buf, int H, int I, int E) {
+  const size_t n = (size_t)E + 1;
+  char* p = reinterpret_cast<char*>(buf);
+  PrefillWeights w;
+  w.g = reinterpret_cast<uint8_t*>(p), p += al256(n * I * H);
+  w.u = reinterpret_cast<uint8_t*>(p), p += al256(n * I * H);
+  w.d = reinterpret_cast<uint8_t*>(p), p += al256(n * I * H);
+  w.sg = reinterpret_cast<float*>(p), p += al256(n * (I / 128) * (H / 128) * 4);
+  w.su = reinterpret_cast<float*>(p), p += al256(n * (I / 128) * (H / 128) * 4);
+  w.sd = reinterpret_cast<float*>(p);
+  return w;
+}
+
+cudaError_t retile_matrix(const uint8_t* tiled, const float* scales, int N, int K, uint8_t* out, float* sout, cudaStream_t st) {
+  const size_t pieces = (size_t)N * K / 16;
+  k_retile_fp8<<<(unsigned)((pieces + 255) / 256), 256, 0, st>>>(tiled, N, K, out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  return cudaMemcpyAsync(sout, scales, (size_t)(N / 128) * (K / 128) * 4, cudaMemcpyDeviceToDevice, st);
+}
+
+// ---- workspace ---------------------------------------------------------------------------------------------------------
+size_t prefill_ws_bytes(int T, int H, int I, int E, int topk) {
+  const size_t P = (size_t)T * topk, HB = H / 128, IB = I / 128;
+  size_t n = 256;
+  n += al256((size_t)T * H) + al256((size_t)T * HB * 4);                           // xq, xs
+  n += al256(P * H) + al256(P * HB * 4) + al256(P * 4);                            // sorted xq, xs, w
+  n += al256(P * I) + al256(P * IB * 4);                                           // hq, hs (routed)
+  n += al256((size_t)T * I) + al256((size_t)T * IB * 4);                           // hq, hs (shared)
+  n += al256(P * H * 2) + al256((size_t)T * H * 2);                                // y (routed), y (shared)
+  n += 6 * al256(P * 4) + 2 * al256((size_t)(E + 1) * 4) + al256((size_t)(E + 1) * 4);  // sort outputs + tile offsets
+  n += al256(sort_ws_bytes(T, topk, E));
+  return n;
+}
+
+PrefillWs prefill_ws_carve(void* ws, int T, int H, int I, int E, int topk) {
+  const size_t P = (size_t)T * topk, HB = H / 128, IB = I / 128;
+  char* p = reinterpret_cast<char*>(ws);
+  PrefillWs w;
+  w.status = reinterpret_cast<int*>(p), p += 256;
+  w.xq = reinterpret_cast<uint8_t*>(p), p += al256((size_t)T * H);
+  w.xs = reinterpret_cast<float*>(p), p += al256((size_t)T * HB * 4);
+  w.xq_s = reinterpret_cast<uint8_t*>(p), p += al256(P * H);
+  w.xs_s = reinterpret_cast<float*>(p), p += al256(P * HB * 4);
+  w.w_s = reinterpret_cast<float*>(p), p += al256(P * 4);
+  w.hq = reinterpret_cast<uint8_t*>(p), p += al256(P * I);
+  w.hs = reinterpret_cast<float*>(p), p += al256(P * IB * 4);
+  w.hq_sh = reinterpret_cast<uint8_t*>(p), p += al256((size_t)T * I);
+  w.hs_sh = reinterpret_cast<float*>(p), p += al256((size_t)T * IB * 4);
+  w.y = reinterpret_cast<__nv_bfloat16*>(p), p += al256(P * H * 2);
+  w.y_sh = reinterpret_cast<__nv_bfloat16*>(p), p += al256((size_t)T * H * 2);
+  w.perm_tok = reinterpret_cast<int*>(p), p += al256(P * 4);
+  w.perm_slot = reinterpret_cast<int*>(p), p += al256(P * 4);
+  w.pos_of = reinterpret_cast<int*>(p), p += al256(P * 4);
+  w.row_order = reinterpret_cast<int*>(p), p += 3 * al256(P * 4);
+  w.counts = reinterpret_cast<int*>(p), p += al256((size_t)(E + 1) * 4);
+  w.offsets = reinterpret_cast<int*>(p), p += al256((size_t)(E + 1) * 4);
+  w.tile_off = reinterpret_cast<int*>(p), p += al256((size_t)(E + 1) * 4);
+  w.sort_ws = p;
+  return w;
+}
+
+// ---- the whole prefill expert pass -----------------------------------------------------------------------------------
+cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
+  const int T = q.T, H = q.H, I = q.I, E = q.E, topk = q.topk, P = T * topk;
+  const PrefillWs& w = q.ws;
+  const PrefillWeights& pw = q.pw;
+  CUtensorMap mX, mXs, mHq, mHsh, mG, mU, mD;
+  const uint64_t nexp = (uint64_t)E + 1;
+  if (!make_map(&mX, w.xq, T, H) || !make_map(&mXs, w.xq_s, P, H) || !make_map(&mHq, w.hq, P, I) ||
+      !make_map(&mHsh, w.hq_sh, T, I) || !make_map(&mG, pw.g, nexp * I, H) || !make_map(&mU, pw.u, nexp * I, H) ||
+      !make_map(&mD, pw.d, nexp * H, I))
+    return cudaErrorInvalidValue;
+  cudaError_t e;
+  // order, quantise, gather
+  e = launch_sort_pack(q.idx, T, topk, E, w.counts, w.offsets, w.perm_tok, w.perm_slot, w.pos_of, w.row_order, w.sort_ws, st);
+  if (e != cudaSuccess) return e;
+  k_tile_offsets<<<1, 32, 0, st>>>(w.counts, E, q.e_lo, q.e_hi, w.tile_off);
+  {
+    const size_t warps = (size_t)T * (H / 128);
+    k_quant_rows<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(q.x, T, H, w.xq, w.xs);
+    const size_t pieces = (size_t)P * (H / 16);
+    k_gather_rows<<<(unsigned)((pieces + 255) / 256), 256, 0, st>>>(w.xq, w.xs, q.w, w.perm_tok, w.perm_slot, P, H, topk,
+                                                                    w.xq_s, w.xs_s, w.w_s);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  GemmArgs a;
+  a.status = w.status;
+  // routed gate/up
+  a.mode = 0, a.K = H, a.N = I, a.E = E, a.rows_total = P, a.wrow0 = 0, a.seg_off = w.offsets, a.tile_off = w.tile_off;
+  a.sa = w.xs_s, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = w.w_s, a.hq = w.hq, a.hs = w.hs, a.y = nullptr;
+  e = launch_gemm<0>(mXs, mG, mU, a, st);
+  if (e != cudaSuccess) return e;
+  // routed down
+  a.mode = 1, a.K = I, a.N = H, a.sa = w.hs, a.sb0 = pw.sd, a.sb1 = nullptr, a.wrow = nullptr, a.hq = nullptr, a.hs = nullptr;
+  a.y = w.y;
+  e = launch_gemm<1>(mHq, mD, mD, a, st);
+  if (e != cudaSuccess) return e;
+  if (q.has_shared) {
+    a.mode = 0, a.K = H, a.N = I, a.E = 1, a.rows_total = T, a.wrow0 = E, a.seg_off = nullptr, a.tile_off = nullptr;
+    a.sa = w.xs, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = nullptr, a.hq = w.hq_sh, a.hs = w.hs_sh, a.y = nullptr;
+    e = launch_gemm<0>(mX, mG, mU, a, st);
+    if (e != cudaSuccess) return e;
+    a.mode = 1, a.K = I, a.N = H, a.sa = w.hs_sh, a.sb0 = pw.sd, a.hq = nullptr, a.hs = nullptr, a.y = w.y_sh;
+    e = launch_gemm<1>(mHsh, mD, mD, a, st);
+    if (e != cudaSuccess) return e;
+  }
+  const size_t n = (size_t)T * (H / 8);
+  k_combine<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.y, q.has_shared ? w.y_sh : nullptr, q.idx, q.e_lo, q.e_hi, w.pos_of,
+                                                         w.row_order, T, H,
+                                                         topk, q.yr, q.ys, q.out, q.ysum);
+  return cudaGetLastError();
+}
+
+}  // namespace dsgx

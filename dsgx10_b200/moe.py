@@ -124,3 +124,28 @@ class LayerStep:
         check(lib().dsgx_moe_layer_decode_host(C.byref(self.shp), C.byref(layer_w), _ptr(x_host), M, C.byref(self.c),
                                                _ptr(out_host), _stream()), "dsgx_moe_layer_decode_host")
         return out_host
+
+
+class PrefillLayer:
+    """A layer prepared for the prefill path: the K-major weight copy (made once) and a workspace for up to T_max rows."""
+
+    def __init__(self, shp, layer_w, T_max, device="cuda"):
+        self.shp, self.layer_w, self.T_max = shp, layer_w, T_max
+        nb = lib().dsgx_prefill_weights_bytes(C.byref(shp))
+        if nb == 0:
+            raise _lib.DsgxError(_lib.ERR_SHAPE, "dsgx_prefill_weights_bytes")
+        self.wbuf = torch.empty(nb, dtype=torch.uint8, device=device)
+        check(lib().dsgx_prefill_prepare(C.byref(shp), C.byref(layer_w), _ptr(self.wbuf), _stream()), "dsgx_prefill_prepare")
+        self.ws = torch.empty(lib().dsgx_prefill_ws_bytes(C.byref(shp), T_max), dtype=torch.uint8, device=device)
+
+    def run(self, x, idx, w, yr=None, ys=None, out=None, ysum=False):
+        """x bf16 [T][H]; idx, w from route(); returns (yr, ys, out): f32 partial sums and bf16(yr + ys)."""
+        T, H = x.shape
+        assert T <= self.T_max
+        f32 = dict(dtype=torch.float32, device=x.device)
+        yr = torch.empty(T, H, **f32) if yr is None else yr
+        ys = torch.empty(T, H, **f32) if ys is None else ys
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if out is None else out
+        check(lib().dsgx_moe_prefill(C.byref(self.shp), C.byref(self.layer_w), _ptr(self.wbuf), _ptr(x), _ptr(idx), _ptr(w), T,
+                                     _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum), _stream()), "dsgx_moe_prefill")
+        return yr, ys, out

@@ -159,6 +159,24 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, co
 int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_host, int M,
                                const dsgx_layer_step* step, void* out_host, void* stream);
 
+/* ---- prefill / verify (any number of rows; FP8 layers) --------------------------------------------------------------
+ * Stands in for gx::prefill_ws_bytes / gx::moe_prefill (altar1 engine/experts/experts.h:149-182) and dsk::moe_prefill
+ * (ds41f engine/kernels/dsk.h:238-293): the rows' picks ordered by (expert id, token), the experts as grouped GEMMs on
+ * the tensor cores, every pick's output added per row in ascending expert id.  x bf16 [T][H], idx / w from dsgx_route;
+ * yr, ys f32 [T][H] as dsgx_moe_decode; out_bf16 (may be null) receives bf16(yr + ys).
+ *
+ * The tensor-core path reads the weights K-major: dsgx_prefill_prepare re-tiles a layer's tile_fp8 blocks once at load
+ * time into wbuf (dsgx_prefill_weights_bytes(shape) bytes of device memory), as the reference re-tiles its checkpoints
+ * (ds41f engine/kernels/moe.cu:1332-1336); it reads the descriptors back to the host and synchronises, so it is a
+ * load-time call.  Only the experts in [e_lo, e_hi) (and the shared expert, when the layer has one) are prepared and run.
+ * ws: dsgx_prefill_ws_bytes(shape, T) bytes, T <= the value given there; no zeroing needed. */
+size_t dsgx_prefill_weights_bytes(const dsgx_moe_shape* shape);
+int dsgx_prefill_prepare(const dsgx_moe_shape* shape, const dsgx_layer_w* L, void* wbuf, void* stream);
+size_t dsgx_prefill_ws_bytes(const dsgx_moe_shape* shape, int T);
+int dsgx_moe_prefill(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* wbuf, const void* x_bf16,
+                     const int32_t* idx, const float* w, int T, void* ws, float* yr, float* ys, void* out_bf16, int ysum,
+                     void* stream);
+
 /* Reads (synchronously) the device status word of a workspace: DSGX_OK or DSGX_ERR_DEVICE_WAIT. */
 int dsgx_ws_status(const void* ws);
 

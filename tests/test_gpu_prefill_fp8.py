@@ -1,0 +1,102 @@
+"""GPU parity of the FP8 prefill path (token sort + tcgen05 grouped GEMMs + combine) against the CPU oracle and the
+decode path, through the C ABI."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def _setup(H, I, E, topk, T, seed, ng=1, tg=1, shared=True, e_lo=0, e_hi=None, zipf=False):
+    from dsgx10_b200 import moe, synth
+    shp = moe.shape(H, I, E, topk, n_group=ng, topk_group=tg, e_lo=e_lo, e_hi=e_hi)
+    layer = synth.Fp8Layer(H, I, E, seed, device="cuda", shared=shared)
+    x = synth.activations(T, H, seed + 1000).cuda()
+    wr = synth.router_weights(E, H, seed + 2000).cuda()
+    bias = None
+    if zipf:  # a selection bias that makes expert popularity very uneven (empty and huge segments)
+        p = 1.0 / np.arange(1, E + 1) ** 1.1
+        bias = torch.from_numpy((0.25 * np.log(p / p.max())).astype(np.float32)).cuda()
+    idx, w = moe.route(shp, moe.router_logits(x, wr), bias)
+    return shp, layer, x, wr, bias, idx, w
+
+
+def _check(orc, shp, layer, x, idx, w, yr, ys, out, shared=True, e_lo=0, e_hi=None, rows=None):
+    from dsgx10_b200 import synth
+    from tests.util import oracle_fp8_layer, rowmax_err
+    rows = np.arange(x.shape[0]) if rows is None else np.asarray(rows)
+    xb = synth.bf16_bits(x)[rows]
+    oi, ow = idx.cpu().numpy()[rows], w.cpu().numpy()[rows]
+    acc_r, _ = oracle_fp8_layer(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=False)
+    acc_all, out_all = oracle_fp8_layer(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=shared)
+    yr, ys, out = yr.cpu().numpy()[rows], ys.cpu().numpy()[rows], synth.bf16_bits(out)[rows]
+    assert rowmax_err(yr, acc_r) <= TOL, rowmax_err(yr, acc_r)
+    if shared:
+        assert rowmax_err(yr + ys, acc_all) <= TOL
+    assert rowmax_err(orc.bf16_to_f32(out), orc.bf16_to_f32(out_all)) <= TOL + 2 ** -8
+
+
+@pytest.mark.parametrize("T", [1, 7, 130, 300])
+def test_small_layer(orc, T):
+    from dsgx10_b200 import moe
+    shp, layer, x, wr, bias, idx, w = _setup(512, 256, 8, 2, T, seed=200 + T)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    yr2, ys2, out2 = pl.run(x, idx, w)            # twice on one workspace: deterministic
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    assert torch.equal(yr, yr2) and torch.equal(out, out2)
+    _check(orc, shp, layer, x, idx, w, yr, ys, out)
+
+
+def test_ragged_segments_config1_shapes(orc):
+    """hidden 2048, 64 experts of 1024, top-6: Zipf-biased routing gives empty experts and segments of many tiles;
+    a sample of rows is checked against the oracle, all rows against the decode path (same contract)."""
+    from dsgx10_b200 import moe
+    T = 1500
+    shp, layer, x, wr, bias, idx, w = _setup(2048, 1024, 64, 6, T, seed=20261104, zipf=True)
+    counts = torch.bincount(idx.flatten().long(), minlength=64)
+    assert int(counts.max()) > 512 and int((counts == 0).sum()) >= 0
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    rows = np.random.default_rng(0).choice(T, 12, replace=False)
+    _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=rows)
+    # decode path on chunks of 8 rows: same numerics contract, outputs within tolerance of each other
+    from tests.util import rowmax_err
+    ws = moe.decode_ws(shp)
+    for r0 in range(0, 64, 8):
+        yd, sd = moe.moe_decode(shp, layer.layer_w(), x[r0:r0 + 8].contiguous(), idx[r0:r0 + 8].contiguous(),
+                                w[r0:r0 + 8].contiguous(), ws)
+        torch.cuda.synchronize()
+        assert rowmax_err(yr[r0:r0 + 8].cpu().numpy(), yd.cpu().numpy()) <= TOL
+        assert rowmax_err(ys[r0:r0 + 8].cpu().numpy(), sd.cpu().numpy()) <= TOL
+
+
+def test_expert_parallel_and_no_shared(orc):
+    from dsgx10_b200 import moe
+    T = 200
+    for e_lo, e_hi, shared in ((0, 4, True), (4, 8, False)):
+        shp, layer, x, wr, bias, idx, w = _setup(512, 256, 8, 2, T, seed=260, shared=shared, e_lo=e_lo, e_hi=e_hi)
+        pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+        yr, ys, out = pl.run(x, idx, w)
+        torch.cuda.synchronize()
+        assert moe.ws_status(pl.ws) == 0
+        _check(orc, shp, layer, x, idx, w, yr, ys, out, shared=shared, e_lo=e_lo, e_hi=e_hi)
+
+
+def test_chunk_invariance(orc):
+    """A row's bits do not depend on the other rows of the chunk (altar1 engine/experts/tests/test_prefill.inc:293-302)."""
+    from dsgx10_b200 import moe
+    T = 260
+    shp, layer, x, wr, bias, idx, w = _setup(512, 256, 8, 2, T, seed=270)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    yr, ys = yr.clone(), ys.clone()
+    for a, b in ((0, 100), (100, 260), (37, 38)):
+        yr2, ys2, _ = pl.run(x[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
+        torch.cuda.synchronize()
+        assert torch.equal(yr2, yr[a:b]) and torch.equal(ys2, ys[a:b])
