@@ -21,7 +21,7 @@ def _oracle(orc, layer, xb, idx, w, e_lo=0, e_hi=None, with_shared=True):
 
 def _run(orc, H, I, E, topk, M, seed, score=1, scale=1.0, shared=True, e_lo=0, e_hi=None):
     from dsgx10_b200 import _lib, moe, synth
-    from tests.util import oracle_route, rowmax_err
+    from tests.util import assert_rows_close, oracle_route, rowmax_err
     shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4, score_fn=score, route_scale=scale, e_lo=e_lo, e_hi=e_hi)
     layer = synth.Int4Layer(H, I, E, seed, device="cuda", shared=shared, e_range=(e_lo, E if e_hi is None else e_hi))
     x = synth.activations(M, H, seed + 1000).cuda()
@@ -41,10 +41,10 @@ def _run(orc, H, I, E, topk, M, seed, score=1, scale=1.0, shared=True, e_lo=0, e
     acc_r, _ = _oracle(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=False)
     acc_all, out_all = _oracle(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=shared)
     yr, ys, outb = outs[0]
-    assert rowmax_err(yr, acc_r) <= TOL
+    assert_rows_close(yr, acc_r, TOL, what="yr")
     if shared:
-        assert rowmax_err(yr + ys, acc_all) <= TOL
-    assert rowmax_err(orc.bf16_to_f32(outb), orc.bf16_to_f32(out_all)) <= TOL + 2 ** -8
+        assert_rows_close(yr + ys, acc_all, TOL, what="yr + ys")
+    assert_rows_close(orc.bf16_to_f32(outb), orc.bf16_to_f32(out_all), TOL, frac=0.99, what="out")
     # the separate-call path (caller's idx / w) gives the same bits
     ws = moe.decode_ws(shp)
     yr2, ys2 = moe.moe_decode(shp, layer.layer_w(), x, step.idx[:M].contiguous(), step.w[:M].contiguous(), ws)
