@@ -1,0 +1,81 @@
+"""Expert parallelism over the GPUs of one box: contiguous expert ranges per rank (ds41f ref/inference/model.py:863-870),
+one exchange step per layer.
+
+Two schemes, both on `torch.distributed` process groups (NCCL over NVLink on GPUs, gloo in the CPU tests):
+
+  reduce (decode, and prefill when every rank holds every row): every rank routes all rows (the router is replicated
+      and deterministic, so all ranks choose the same experts), runs only its own experts and the f32 partial sums
+      `[rows][H]` are all-reduced; the shared expert runs on rank 0 and travels in the same message
+      (model.py:901-902: `dist.all_reduce(y)`).
+
+  all-to-all (prefill / ragged batches with the rows partitioned over the ranks): a row is sent once to every rank that
+      owns at least one of its picked experts, together with its picks; the owner returns the row's f32 partial sum; the
+      source adds the partial sums in rank order (a fixed order, so the result is deterministic) and the shared
+      expert's output, which it computes itself for its own rows.
+
+The exchange is plumbing: what is computed between the collectives is the CUDA library (or, in the CPU tests, the
+oracle passed in as `local_compute`).
+"""
+import torch
+import torch.distributed as dist
+
+
+def expert_range(rank, world, E):
+    """Rank's experts [lo, hi): contiguous ids, as the reference's MoE.__init__ partitions them."""
+    assert E % world == 0, "the number of experts must be divisible by the number of ranks"
+    n = E // world
+    return rank * n, (rank + 1) * n
+
+
+def allreduce_partials(yr, ys, group=None):
+    """yr, ys: f32 [rows][H] partial sums of this rank (ys zero on ranks without the shared expert) -> summed in place."""
+    buf = torch.stack([yr, ys])
+    dist.all_reduce(buf, group=group)
+    yr.copy_(buf[0])
+    ys.copy_(buf[1])
+    return yr, ys
+
+
+def dispatch_plan(idx, world, E):
+    """idx int32 [T][topk] -> (send_rows: list per destination of the local row numbers it gets, mask [T][world])."""
+    n = E // world
+    owner = torch.div(idx, n, rounding_mode="floor")                       # [T][topk] rank owning each pick
+    mask = torch.zeros(idx.shape[0], world, dtype=torch.bool, device=idx.device)
+    mask.scatter_(1, owner.long(), True)
+    return [torch.nonzero(mask[:, d], as_tuple=False).flatten() for d in range(world)], mask
+
+
+def all_to_all_experts(x, idx, w, E, local_compute, group=None):
+    """x bf16 [T_local][H], idx int32 [T_local][topk], w f32 [T_local][topk]: this rank's rows.
+    local_compute(x_rows, idx_rows, w_rows) -> f32 [rows][H]: the partial sum of the rows over THIS rank's experts only.
+    Returns f32 [T_local][H]: the routed experts' sum of every local row (the shared expert is the caller's)."""
+    world = dist.get_world_size(group)
+    T, H = x.shape
+    topk = idx.shape[1]
+    dev = x.device
+    send_rows, _ = dispatch_plan(idx, world, E)
+    send_counts = torch.tensor([r.numel() for r in send_rows], dtype=torch.int64, device=dev)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()
+    order = torch.cat(send_rows) if T else torch.zeros(0, dtype=torch.int64, device=dev)
+    # three messages per direction: rows, picks, weights
+    xs, ids, ws = x[order].contiguous(), idx[order].contiguous(), w[order].contiguous()
+    n_in = int(sum(rc))
+    xr = torch.empty(n_in, H, dtype=x.dtype, device=dev)
+    ir = torch.empty(n_in, topk, dtype=idx.dtype, device=dev)
+    wr = torch.empty(n_in, topk, dtype=w.dtype, device=dev)
+    for out, inp in ((xr, xs), (ir, ids), (wr, ws)):
+        dist.all_to_all_single(out, inp, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    y_in = local_compute(xr, ir, wr) if n_in else torch.zeros(0, H, dtype=torch.float32, device=dev)
+    y_back = torch.empty(order.numel(), H, dtype=torch.float32, device=dev)
+    dist.all_to_all_single(y_back, y_in.contiguous(), output_split_sizes=sc, input_split_sizes=rc, group=group)
+    # add the partial sums in rank order
+    acc = torch.zeros(T, H, dtype=torch.float32, device=dev)
+    off = 0
+    for d in range(world):
+        rows = send_rows[d]
+        if rows.numel():
+            acc.index_add_(0, rows, y_back[off:off + rows.numel()])
+        off += rows.numel()
+    return acc

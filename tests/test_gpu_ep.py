@@ -1,0 +1,93 @@
+"""Expert parallelism on two GPUs (NCCL): the decode all-reduce scheme and the prefill all-to-all scheme against the
+single-GPU result.  Skipped on a box with one GPU."""
+import os
+import socket
+import sys
+
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    from dsgx10_b200 import ep, moe, synth
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        H, I, E, topk = 1024, 512, 16, 4
+        lo, hi = ep.expert_range(rank, world, E)
+        full_shp = moe.shape(H, I, E, topk)
+        my_shp = moe.shape(H, I, E, topk, e_lo=lo, e_hi=hi)
+        full = synth.Fp8Layer(H, I, E, 300, device=dev)                       # the single-GPU reference layer
+        mine = synth.Fp8Layer(H, I, E, 300, device=dev, shared=(rank == 0), e_range=(lo, hi))
+        wr = synth.router_weights(E, H, 301).to(dev)
+        res = {}
+        # decode: all-reduce of the partial sums
+        x = synth.activations(5, H, 302).to(dev)
+        ref = moe.LayerStep(full_shp, wr, device=dev)
+        ref.run(full.layer_w(), x)
+        st = moe.LayerStep(my_shp, wr, device=dev)
+        st.run(mine.layer_w(), x, finalize=False)
+        if rank != 0:
+            st.ys.zero_()
+        ep.allreduce_partials(st.yr, st.ys)
+        torch.cuda.synchronize()
+        den = float(ref.yr[:5].abs().max())
+        res["decode_yr"] = float((st.yr[:5] - ref.yr[:5]).abs().max()) / den
+        res["decode_ys"] = float((st.ys[:5] - ref.ys[:5]).abs().max())
+        res["decode_idx"] = bool(torch.equal(st.idx[:5], ref.idx[:5]))
+        # prefill: rows partitioned, all-to-all dispatch and combine
+        T = 96
+        xa = synth.activations(T, H, 303).to(dev)
+        idx, w = moe.route(full_shp, moe.router_logits(xa, wr), None)
+        pl_full = moe.PrefillLayer(full_shp, full.layer_w(), T, device=dev)
+        yr_full, _, _ = pl_full.run(xa, idx, w)
+        pl = moe.PrefillLayer(my_shp, mine.layer_w(), T, device=dev)
+        rows = torch.arange(rank, T, world, device=dev)
+
+        def local(xr, ir, wr_):
+            yr, _, _ = pl.run(xr, ir, wr_)
+            return yr.clone()
+
+        acc = ep.all_to_all_experts(xa[rows].contiguous(), idx[rows].contiguous(), w[rows].contiguous(), E, local)
+        torch.cuda.synchronize()
+        res["prefill"] = float((acc - yr_full[rows]).abs().max()) / float(yr_full.abs().max())
+        res["status"] = max(moe.ws_status(st.ws), moe.ws_status(pl.ws))
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_match_one():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    for rank, res in sorted(q.get(timeout=5) for _ in range(2)):
+        assert res["decode_idx"] and res["status"] == 0
+        assert res["decode_yr"] <= 1e-6 and res["decode_ys"] == 0.0, res    # only the association of the f32 adds differs
+        assert res["prefill"] <= 1e-6, res
