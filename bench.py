@@ -214,10 +214,11 @@ def run_gpu(args):
     def timed(fn, n):
         """Device time of exactly n steps.  One GPU: the n steps are captured in one CUDA graph (as a serving engine
         replays its step graph; the reference benches a graph of 64 steps, altar1
-        engine/experts/tests/bench_experts.cu:46-82) and the replay is timed.  Several GPUs: eager launches."""
+        engine/experts/tests/bench_experts.cu:46-82) and the replay is timed; with several GPUs the NCCL all-reduce is
+        captured in the same graph."""
         graph = None
-        if world == 1 and not args.eager:
-            torch.cuda.synchronize()
+        if not args.eager:
+            barrier()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for i in range(n):
@@ -287,7 +288,7 @@ def run_gpu(args):
         "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
                                f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows,
                    "parallelism": f"ep{world}", "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
-                   "launch": "eager" if (world > 1 or args.eager) else "one CUDA graph of the timed steps"},
+                   "launch": "eager" if args.eager else "one CUDA graph of the timed steps"},
         "tokens_per_s": rows / (us * 1e-6),
         "step_hbm_gbs": sb_bytes / (us * 1e-6) / 1e9,
         "step_frac_of_measured_hbm": sb_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
@@ -329,7 +330,11 @@ def main():
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="profiling only: a layer with fewer routed experts (same matrices), to keep an ncu capture small")
     args = ap.parse_args()
+    if args.experts:
+        CFG["E"] = args.experts
     if args.impl == "reference":
         run_reference(args)
     else:
