@@ -1,0 +1,60 @@
+// Header-only C++ mirror of the engines' MoE operator interface (altar1 engine/experts/experts.h:99-193) over the C ABI
+// of libdsgx_moe.so (include/dsgx_moe.h).  Same function names, argument order and meaning as the reference's `gx::`
+// functions; the compile-time shape constants of the reference (experts.h:18-26) become a `MoeShape` the caller
+// passes, and a failed call throws gx::Error(status) where the reference aborts the process (common/check.h).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "dsgx_moe.h"
+
+namespace gx {
+
+using MoeShape = dsgx_moe_shape;
+using MatDesc = dsgx_mat_desc;   // experts.h:58-64
+using SharedW = dsgx_shared_w;   // experts.h:66-87
+using LayerW = dsgx_layer_w;     // experts.h:92-97
+using DecodeCfg = dsgx_decode_cfg;
+
+struct Error : std::runtime_error {
+  int status;
+  Error(int s, const char* where) : std::runtime_error(std::string(where) + ": " + dsgx_status_name(s)), status(s) {}
+};
+inline void check(int status, const char* where) {
+  if (status != DSGX_OK) throw Error(status, where);
+}
+
+// logits f32 [M][E] -> idx [M][topk] (descending selection score, ties to the lower id), w [M][topk].  experts.h:99-102
+inline void route(const MoeShape& s, const float* logits, const float* bias, int M, int* idx, float* w, cudaStream_t st) {
+  check(dsgx_route(&s, logits, bias, M, idx, w, st), "gx::route");
+}
+// the runner's router GEMV (engine/model/model.cu:309-311)
+inline void router_logits(const __nv_bfloat16* x, const float* wr, int M, int H, int E, float* logits, cudaStream_t st) {
+  check(dsgx_router_logits(x, wr, M, H, E, logits, st), "gx::router_logits");
+}
+// experts.h:139-141
+inline size_t decode_ws_bytes(const MoeShape& s) { return dsgx_decode_ws_bytes(&s); }
+inline void moe_decode(const MoeShape& s, const LayerW& L, const __nv_bfloat16* x, const int* idx, const float* w, int M,
+                       void* ws, float* yr, float* ys, cudaStream_t st, const DecodeCfg& cfg = DecodeCfg{0, 1, 0, 0, 0, {0, 0, 0}}) {
+  check(dsgx_moe_decode(&s, &L, x, idx, w, M, ws, yr, ys, st, &cfg), "gx::moe_decode");
+}
+// experts.h:146-147 (mode 1 is the reference's bf16(bf16(R) + bf16(S)); mode 0 rounds the f32 sum once)
+inline void finalize(const float* R, const float* S, int M, int H, __nv_bfloat16* out, cudaStream_t st, int mode = 0) {
+  check(dsgx_finalize(R, S, M, H, out, mode, st), "gx::finalize");
+}
+// experts.h:180-182; wbuf: the K-major weight copy made once by prefill_prepare
+inline size_t prefill_weights_bytes(const MoeShape& s) { return dsgx_prefill_weights_bytes(&s); }
+inline void prefill_prepare(const MoeShape& s, const LayerW& L, void* wbuf, cudaStream_t st) {
+  check(dsgx_prefill_prepare(&s, &L, wbuf, st), "gx::prefill_prepare");
+}
+inline size_t prefill_ws_bytes(const MoeShape& s, int T) { return dsgx_prefill_ws_bytes(&s, T); }
+inline void moe_prefill(const MoeShape& s, const LayerW& L, const void* wbuf, const __nv_bfloat16* x, const int* idx,
+                        const float* w, int T, void* ws, float* yr, float* ys, cudaStream_t st, __nv_bfloat16* out = nullptr,
+                        bool ysum = false) {
+  check(dsgx_moe_prefill(&s, &L, wbuf, x, idx, w, T, ws, yr, ys, out, ysum ? 1 : 0, st), "gx::moe_prefill");
+}
+
+}  // namespace gx
