@@ -36,7 +36,8 @@ class DecodeCfg(C.Structure):
 
 
 class LayerStep(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("wr", "bias", "logits", "idx", "w", "ws", "yr", "ys", "out_bf16", "x_stage")]
+    _fields_ = [(n, C.c_void_p) for n in ("wr", "bias", "logits", "idx", "w", "ws", "yr", "ys", "out_bf16", "x_stage")] + \
+               [("flags", C.c_int32), ("reserved", C.c_int32)]
 
 
 # every symbol include/dsgx_moe.h declares: name -> (restype, argtypes)

@@ -40,6 +40,7 @@ size_t decode_ws_bytes(int H, int I) {
   n += al256((size_t)(H / 16) * 4);
   n += kSlotTabBytes;
   n += al256((size_t)((H + 1023) / 1024) * kMaxRows * 512 * 4);
+  n += al256(sizeof(StepSync));
   return n;
 }
 DecodeWs decode_ws_carve(void* ws, int H, int I) {
@@ -54,7 +55,8 @@ DecodeWs decode_ws_carve(void* ws, int H, int I) {
   w.cnt_h = reinterpret_cast<int*>(p), p += al256((size_t)kMaxSlots * IB * 4);
   w.cnt_y = reinterpret_cast<int*>(p), p += al256((size_t)(H / 16) * 4);
   w.tab = reinterpret_cast<SlotTab*>(p), p += kSlotTabBytes;
-  w.lpart = reinterpret_cast<float*>(p);
+  w.lpart = reinterpret_cast<float*>(p), p += al256((size_t)((H + 1023) / 1024) * kMaxRows * 512 * 4);
+  w.sync = reinterpret_cast<StepSync*>(p);
   return w;
 }
 
@@ -221,6 +223,13 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    if (fp8 && !(st->flags & 1) && step_fp8_fits(s->H, s->I, s->E, M)) {  // the whole step as one persistent kernel
+      StepParams sp;
+      sp.d = p, sp.rp = rp, sp.x = xb, sp.wr = st->wr, sp.bias = st->bias, sp.logits = st->logits, sp.idx = st->idx;
+      sp.w = st->w, sp.sync = p.ws.sync, sp.R = 0, sp.sh_slot = 0, sp.has_sh = 0;
+      cudaError_t e = launch_step_fp8(sp, (cudaStream_t)stream);
+      return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+    }
     cudaError_t e = fp8 ? launch_layer_fp8(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true)
                         : launch_layer_int4(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);

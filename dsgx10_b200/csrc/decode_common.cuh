@@ -147,6 +147,35 @@ DSGX_DEV void tile_x_group(const __nv_bfloat16* __restrict__ x, int M, int K, in
   d[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
+// One (expert, 1024-k slice) of the router logits for every row, in the router's summation order: lane j accumulates
+// k = base + 128 i + 4 j + c (i ascending, c = 0..3) by fma from zero, then the butterfly.  All weight loads go out first.
+DSGX_DEV void logit_slice_task(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M, int H, int E, int e,
+                               int sl, float* __restrict__ lpart, int lane) {
+  const int base = sl * 1024, nit = min(1024, H - base) / 128;
+  float4 wv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    wv[i] = i < nit ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)e * H + base + 128 * i + 4 * lane))
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < M; ++r) {
+    uint2 xv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      xv[i] = i < nit ? __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * H + base + 128 * i + 4 * lane)) : make_uint2(0, 0);
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nit) {
+        a = fmaf(bf16_bits_to_f(xv[i].x & 0xffffu), wv[i].x, a);
+        a = fmaf(bf16_bits_to_f(xv[i].x >> 16), wv[i].y, a);
+        a = fmaf(bf16_bits_to_f(xv[i].y & 0xffffu), wv[i].z, a);
+        a = fmaf(bf16_bits_to_f(xv[i].y >> 16), wv[i].w, a);
+      }
+    a = warp_sum(a);
+    if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
+  }
+}
+
 struct TabArgs {
   int M, topk, E, e_lo, e_hi;
   const uint8_t* pool;

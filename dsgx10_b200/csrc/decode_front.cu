@@ -46,29 +46,7 @@ __global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__
   const int gw = blockIdx.x * 8 + warp;
   const int e = gw / KS, sl = gw % KS;
   if (e >= E) return;
-  const int base = sl * 1024, nit = min(1024, H - base) / 128;
-  float4 wv[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    wv[i] = i < nit ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)e * H + base + 128 * i + 4 * lane))
-                    : make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int r = 0; r < M; ++r) {
-    uint2 xv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      xv[i] = i < nit ? __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * H + base + 128 * i + 4 * lane)) : make_uint2(0, 0);
-    float a = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (i < nit) {
-        a = fmaf(bf16_bits_to_f(xv[i].x & 0xffffu), wv[i].x, a);
-        a = fmaf(bf16_bits_to_f(xv[i].x >> 16), wv[i].y, a);
-        a = fmaf(bf16_bits_to_f(xv[i].y & 0xffffu), wv[i].z, a);
-        a = fmaf(bf16_bits_to_f(xv[i].y >> 16), wv[i].w, a);
-      }
-    a = warp_sum(a);
-    if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
-  }
+  logit_slice_task(x, wr, M, H, E, e, sl, lpart, lane);
 }
 
 // ----------------------------------------------------------------------------------------------------- k_route_union

@@ -1,0 +1,484 @@
+// The whole FP8 decode layer step as ONE persistent kernel: router logits, routing, slot table, gate/up with SwiGLU and
+// requantisation, down, ordered combine and the final rounding.  One CTA a SM, sixteen warps a CTA, launched once a step.
+//
+// Why one kernel: at one row the step streams ~231 MB in ~35 us, so every kernel boundary (launch, prologue, pipeline
+// fill, tail) costs several per cent.  Here the phases overlap instead:
+//   - every CTA quantises x into its own shared memory (no global round trip);
+//   - the router's logit slices (one warp per expert and 1024-k slice) and the shared expert's gate/up units (which need
+//     no routing) start at once on disjoint warps;
+//   - the last M CTAs wait for the logit slices, route one row each (route.cuh: a CTA a row) and the last of them
+//     builds the slot table and raises a flag;
+//   - every warp then takes its routed gate/up units, and after them its down units; a down unit's weight copies are
+//     issued before its slot's h is ready (the weights do not depend on h), only the copy of h waits for the slot's
+//     quantisation counter, so the rings keep HBM busy across the gate/up -> down dependency.
+// Waits between CTAs (logit slices done, table ready, h of a slot ready) are polls of global counters; every poll is
+// bounded (common.cuh kWaitCycles) and a run-out is recorded in the workspace status word.  The grid is at most one CTA
+// a SM, so all CTAs become resident together; no CTA waits for work that itself waits for that CTA.
+// The last CTA to leave resets every counter, so the workspace is ready for the next launch.
+//
+// The per-unit arithmetic (block order, scale promotion, rounding points) is that of the separate kernels
+// (decode_fp8.cu), so both paths give the same bits.  Activation blocks here hold R = 1, 2, 4 or 8 rows (M rounded up).
+#include "common.cuh"
+#include "decode_common.cuh"
+#include "kernels.h"
+#include "route.cuh"
+
+namespace dsgx {
+
+namespace {
+
+constexpr int kFW = 16, kFThreads = kFW * 32;
+constexpr int kTabSmem = (sizeof(SlotTab) + 127) & ~127;
+
+// compact activation block of R rows x 128 k: [2 halves q][R rows][4 t][16 B] e4m3, then R f32 scales (padded to 16 B)
+__host__ __device__ constexpr int cblk_bytes(int R) { return R * 128 + (R <= 4 ? 16 : 32); }
+
+DSGX_DEV int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// bounded poll until *p >= target
+DSGX_DEV bool poll_ge(const int* p, int target) {
+  if (ld_acquire(p) >= target) return true;
+  const long long t0 = clock64();
+  while (ld_acquire(p) < target) {
+    __nanosleep(40);
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+
+// one row's 128 values (4 per lane) -> compact block
+DSGX_DEV void cquant_row(uint8_t* blk, int R, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {
+  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
+  uint32_t packed = 0;
+  float sc = 0.f;
+  if (valid) {
+    sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
+    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  }
+  *reinterpret_cast<uint32_t*>(blk + ((q * R + r) * 4 + t) * 16 + i) = packed;
+  if (lane == 0) reinterpret_cast<float*>(blk + R * 128)[r] = sc;
+}
+
+// One 128-k block: A rows 0-7 from strip a, rows 8-15 from strip b, B from a compact activation block.
+// Same MMA order as decode_fp8.cu's block_mma (same bits).
+DSGX_DEV void cblock_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int R, int lane) {
+  const uint4 a0 = lds128(a + 32 * lane), a1 = lds128(a + 32 * lane + 16);
+  const uint4 b0 = lds128(b + 32 * lane), b1 = lds128(b + 32 * lane + 16);
+  const int row = (lane >> 2) & (R - 1), t = lane & 3;
+  const uint4 x0 = lds128(act + (row * 4 + t) * 16), x1 = lds128(act + ((R + row) * 4 + t) * 16);
+  float e[4] = {0.f, 0.f, 0.f, 0.f};
+  d[0] = d[1] = d[2] = d[3] = 0.f;
+  mma_e4m3(d, a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
+  mma_e4m3(e, a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
+  mma_e4m3(d, a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
+  mma_e4m3(e, a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+  d[0] += e[0], d[1] += e[1], d[2] += e[2], d[3] += e[3];
+}
+
+template <int KCH, int NST>
+__global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) {
+  const DecodeParams& p = sp.d;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int R = sp.R, CB = cblk_bytes(R);
+  const int HB = p.H / 128, IB = p.I / 128, NT = p.H / 16, upp = p.I / 8;
+  const int stage = 2 * KCH * 1024 + ((KCH * CB + 127) & ~127);
+  const int xq_bytes = (HB * CB + 127) & ~127;
+  uint8_t* xq = smem;
+  SlotTab& tab = *reinterpret_cast<SlotTab*>(smem + xq_bytes);
+  uint8_t* ringbase = smem + xq_bytes + kTabSmem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ringbase + (size_t)kFW * NST * stage);
+  uint64_t* tabbar = bars + kFW * NST;
+  int* s_int = reinterpret_cast<int*>(tabbar + 1);  // [0] table loader elected, [1] logit warps done, [2] ticket / poll result
+  RouteSmem& rs = *reinterpret_cast<RouteSmem*>(s_int + 4);
+  int* s_idx = reinterpret_cast<int*>(&rs + 1);
+  float* s_w = reinterpret_cast<float*>(s_idx + kMaxRows * kMaxTopK);
+  uint32_t* s_bm = reinterpret_cast<uint32_t*>(s_w + kMaxRows * kMaxTopK);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int GW = gridDim.x * kFW, gw = blockIdx.x * kFW + warp;
+  StepSync* sy = sp.sync;
+  uint8_t* myring = ringbase + (size_t)warp * NST * stage;
+  uint64_t* mybar = bars + warp * NST;
+  uint32_t issued = 0, consumed = 0;
+  bool dead = false;
+
+  if (lane == 0)
+    for (int s = 0; s < NST; ++s) mbar_init(mybar + s, 1);
+  if (threadIdx.x == 0) {
+    mbar_init(tabbar, 1);
+    s_int[0] = 0, s_int[1] = 0, s_int[2] = 0;
+  }
+  mbar_fence_init();
+  // ---- every CTA quantises x into its own shared memory -----------------------------------------------------------
+  for (int task = warp; task < HB * R; task += kFW) {
+    const int j = task / R, r = task % R;
+    float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+    if (r < p.M) {
+      const uint2 xv = __ldg(reinterpret_cast<const uint2*>(sp.x + (size_t)r * p.H + 128 * j + 4 * lane));
+      v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
+      v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+    }
+    cquant_row(xq + j * CB, R, r, lane, r < p.M, v0, v1, v2, v3);
+  }
+  __syncthreads();
+
+  const uint64_t pol = policy_evict_first();
+  const int KS = (p.H + 1023) / 1024, ntask = p.E * KS;
+  const int nroute = p.M;  // the last nroute CTAs route one row each
+  const bool router_cta = (int)blockIdx.x >= (int)gridDim.x - nroute;
+  const int GWn = GW - nroute * kFW;  // warps that take the logit slices and the shared expert's gate/up units
+  const int sh_units = sp.has_sh ? upp : 0;
+
+  // ---- the outstanding ticket of the unit a warp finished last --------------------------------------------------------
+  int pend = 0, pend_kind = 0, pend_a = 0, pend_b = 0, pend_ticket = 0;  // kind 1: h group (slot a, group b); 2: tile a
+  auto advance = [&]() {
+    if (pend == 1) {
+      __threadfence();
+      __syncwarp();
+      if (lane == 0)
+        pend_ticket = pend_kind == 1 ? atomicAdd(p.ws.cnt_h + pend_a * IB + pend_b, 1) : atomicAdd(p.ws.cnt_y + pend_a, 1);
+      pend = 2;
+    } else if (pend == 2) {
+      const int ticket = __shfl_sync(0xffffffffu, pend_ticket, 0);
+      if (pend_kind == 1 && ticket == 15) {  // the 16th unit of a 128-group of h quantises it and reports the group
+        __threadfence();
+        const int slot = pend_a, gi = pend_b;
+        const __nv_bfloat16* hrow = p.ws.h + (size_t)slot * 8 * p.I + 128 * gi + 4 * lane;
+        uint8_t* blk = p.ws.hq + ((size_t)slot * IB + gi) * CB;
+        uint2 hv[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          hv[r] = r < p.M ? __ldcg(reinterpret_cast<const uint2*>(hrow + (size_t)r * p.I)) : make_uint2(0, 0);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < R)
+            cquant_row(blk, R, r, lane, r < p.M, bf16_bits_to_f(hv[r].x & 0xffffu), bf16_bits_to_f(hv[r].x >> 16),
+                       bf16_bits_to_f(hv[r].y & 0xffffu), bf16_bits_to_f(hv[r].y >> 16));
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          p.ws.cnt_h[slot * IB + gi] = 0;
+          atomicAdd(&sy->cnt_hq[slot], 1);
+        }
+      } else if (pend_kind == 2 && ticket == tab.ntot - 1) {  // the tile's last slot adds its picks in ascending expert id
+        __threadfence();
+        const int n16 = pend_a, ch = lane >> 1, r0 = 4 * (lane & 1);
+        const float* yt = p.ws.ypick + (size_t)n16 * 128 + ch * 8 + r0;
+        const bool sh = tab.ntot > tab.nslots;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        int s = 0;
+        for (; s + 4 <= tab.nslots; s += 4) {
+          float4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)(s + j) * NT * 128));
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            a.x = __fadd_rn(a.x, v[j].x), a.y = __fadd_rn(a.y, v[j].y), a.z = __fadd_rn(a.z, v[j].z), a.w = __fadd_rn(a.w, v[j].w);
+        }
+        for (; s < tab.nslots; ++s) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)s * NT * 128));
+          a.x = __fadd_rn(a.x, v.x), a.y = __fadd_rn(a.y, v.y), a.z = __fadd_rn(a.z, v.z), a.w = __fadd_rn(a.w, v.w);
+        }
+        float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sh) sv = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)tab.nslots * NT * 128));
+        const float av[4] = {a.x, a.y, a.z, a.w}, svv[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (r0 + c < p.M) {
+            const size_t o = (size_t)(r0 + c) * p.H + n16 * 16 + ch;
+            const float both = __fadd_rn(av[c], svv[c]);
+            p.yr[o] = p.ysum && sh ? both : av[c];
+            if (sh && p.ys) p.ys[o] = svv[c];
+            if (p.out) p.out[o] = __float2bfloat16_rn(both);
+          }
+        if (lane == 0) p.ws.cnt_y[n16] = 0;
+      }
+      pend = 0;
+    }
+  };
+
+  // ---- gate/up units: unit u = first, first + stride, .. < total; routed: slot u / upp; shared: the shared expert ------
+  auto up_units = [&](int first, int stride, int total, bool shared) {
+    const int cpu = HB / KCH;
+    const size_t strip = (size_t)8 * p.H;
+    int pu = first, pc = 0;
+    auto issue = [&]() {
+      const int s = shared ? -1 : pu / upp, i8 = pu % upp;
+      const uint8_t* gp = shared ? p.sh.g : tab.g[s];
+      const uint8_t* up = shared ? p.sh.u : tab.u[s];
+      const size_t off = (size_t)i8 * strip + (size_t)pc * KCH * 1024;
+      uint8_t* st = myring + (size_t)(issued % NST) * stage;
+      uint64_t* bar = mybar + issued % NST;
+      mbar_expect_tx(bar, 2 * KCH * 1024);
+      bulk_g2s_hint(st, gp + off, KCH * 1024, bar, pol);
+      bulk_g2s_hint(st + KCH * 1024, up + off, KCH * 1024, bar, pol);
+      ++issued;
+      if (++pc == cpu) pc = 0, pu += stride;
+    };
+    if (lane == 0)
+      for (int s = 0; s < NST && pu < total; ++s) issue();
+    for (int unit = first; unit < total && !dead; unit += stride) {
+      const int s = shared ? -1 : unit / upp, i8 = unit % upp;
+      const int wslot = shared ? sp.sh_slot : s;  // where this unit's h lives in the workspace
+      const int srow = (i8 * 8) / 128;
+      const float* sgp = shared ? p.sh.gs : tab.sg[s];
+      const float* sup = shared ? p.sh.us : tab.su[s];
+      const float sgl = lane < HB ? __ldg(sgp + (size_t)srow * HB + lane) : 0.f;
+      const float sul = lane < HB ? __ldg(sup + (size_t)srow * HB + lane) : 0.f;
+      float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
+      for (int c = 0; c < cpu; ++c) {
+        const uint32_t sidx = consumed % NST;
+        if (!mbar_wait(mybar + sidx, (consumed / NST) & 1)) {
+          dead = true;
+          break;
+        }
+        const uint8_t* st = myring + (size_t)sidx * stage;
+#pragma unroll
+        for (int b = 0; b < KCH; ++b) {
+          const int kb = c * KCH + b;
+          const uint8_t* act = xq + kb * CB;
+          float d[4];
+          cblock_mma(d, st + b * 1024, st + KCH * 1024 + b * 1024, act, R, lane);
+          const float* xs = reinterpret_cast<const float*>(act + R * 128);
+          const float x0 = xs[(2 * t) & (R - 1)], x1 = xs[(2 * t + 1) & (R - 1)];
+          const float sg = __shfl_sync(0xffffffffu, sgl, kb), su = __shfl_sync(0xffffffffu, sul, kb);
+          ag0 = fmaf(d[0], sg * x0, ag0), ag1 = fmaf(d[1], sg * x1, ag1);
+          au0 = fmaf(d[2], su * x0, au0), au1 = fmaf(d[3], su * x1, au1);
+        }
+        ++consumed;
+        __syncwarp();
+        if (lane == 0 && pu < total) issue();
+        advance();
+      }
+      if (dead) break;
+      while (pend) advance();
+      const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
+      float h0 = __fmul_rn(silu(bf16_round(ag0)), bf16_round(au0));
+      float h1 = __fmul_rn(silu(bf16_round(ag1)), bf16_round(au1));
+      if (!shared) h0 = __fmul_rn(tab.w[s][r0], h0), h1 = __fmul_rn(tab.w[s][r1], h1);
+      __nv_bfloat16* hrow = p.ws.h + (size_t)wslot * 8 * p.I;
+      if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
+      if (r1 < p.M) hrow[(size_t)r1 * p.I + ch] = __float2bfloat16_rn(h1);
+      pend = 1, pend_kind = 1, pend_a = wslot, pend_b = i8 / 16;
+    }
+    if (!dead)
+      while (pend) advance();
+  };
+
+  // ---- phase 1: logit slices and the shared expert's gate/up units, on disjoint warps -------------------------------------
+  if (!router_cta) {
+    int mine = 0;
+    for (int task = gw; task < ntask; task += GWn) {
+      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
+      ++mine;
+    }
+    if (mine) {  // one global add a CTA: its last logit warp reports all of the CTA's slices
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        const int cta_first = blockIdx.x * kFW;
+        int nw = 0, nt = 0;
+        for (int w2 = 0; w2 < kFW; ++w2)
+          for (int task = cta_first + w2; task < ntask; task += GWn) ++nt, nw += task == cta_first + w2;
+        if (atomicAdd(&s_int[1], 1) == nw - 1) atomicAdd(&sy->cnt_lp, nt);
+      }
+    }
+    if (sh_units) {  // shared unit u -> warp (ntask + u) mod GWn
+      const int first = ((gw - ntask % GWn) % GWn + GWn) % GWn;
+      up_units(first, GWn, sh_units, true);
+    }
+  } else {
+    // ---- phase 2 (router CTAs): wait for the slices, route a row, the last one builds the slot table -------------------
+    const int row = (int)blockIdx.x - ((int)gridDim.x - nroute);
+    if (threadIdx.x == 0) s_int[2] = poll_ge(&sy->cnt_lp, ntask) ? 1 : 0;
+    __syncthreads();
+    const bool ok = s_int[2] != 0;
+    __syncthreads();
+    if (ok) {
+      route_row_cta(sp.rp, p.ws.lpart + (size_t)row * p.E, KS, (size_t)kMaxRows * p.E, sp.bias, rs,
+                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk);
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) s_int[2] = atomicAdd(&sy->cnt_rt, 1);
+      __syncthreads();
+      if (s_int[2] == p.M - 1) {
+        __threadfence();
+        for (int i = threadIdx.x; i < p.M * p.topk; i += kFThreads) s_idx[i] = __ldcg(sp.idx + i), s_w[i] = __ldcg(sp.w + i);
+        __syncthreads();
+        build_slot_tab(tab, s_bm, s_idx, s_w, p.M, p.topk, p.E, p.e_lo, p.e_hi, p.pool, p.desc, p.sh, DSGX_FMT_FP8);
+        if (threadIdx.x == 0 && tab.bad) atomicCAS(p.ws.status, 0, tab.bad);
+        {
+          const uint4* s4 = reinterpret_cast<const uint4*>(&tab);
+          uint4* d4 = reinterpret_cast<uint4*>(p.ws.tab);
+          for (int i = threadIdx.x; i < (int)(sizeof(SlotTab) / 16); i += kFThreads) d4[i] = s4[i];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicExch(&sy->tab_ready, 1);
+      }
+    } else {
+      dead = true;
+    }
+    __syncthreads();
+  }
+
+  // ---- phase 3: the slot table into shared memory (the first warp to get here loads it for the CTA) --------------------
+  {
+    int winner = 0;
+    if (lane == 0) winner = atomicCAS(&s_int[0], 0, 1) == 0;
+    winner = __shfl_sync(0xffffffffu, winner, 0);
+    if (winner) {
+      int ok = 0;
+      if (lane == 0) ok = !dead && poll_ge(&sy->tab_ready, 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (ok) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(p.ws.tab);
+        uint4* d4 = reinterpret_cast<uint4*>(&tab);
+        for (int i = lane; i < (int)(sizeof(SlotTab) / 16); i += 32) d4[i] = __ldcg(s4 + i);
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tabbar)) : "memory");
+      }
+    }
+    if (!mbar_wait(tabbar, 0)) dead = true;
+  }
+
+  // ---- phase 4: routed gate/up units, continuing the round-robin after the first phase's work ------------------------------
+  if (!dead) {
+    const int base = (ntask + sh_units) % GW;
+    up_units(((gw - base) % GW + GW) % GW, GW, tab.nslots * upp, false);
+  }
+
+  // ---- phase 5: down units (slot, 16 output channels), shared expert first ------------------------------------------------
+  if (!dead && tab.ntot == 0) {
+    for (size_t i = (size_t)blockIdx.x * kFThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kFThreads) {
+      p.yr[i] = 0.f;
+      if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
+    }
+  } else if (!dead) {
+    const int total = tab.ntot * NT;
+    const int cpu = IB / KCH;
+    const size_t strip = (size_t)8 * p.I;
+    const int base = (ntask + sh_units + tab.nslots * upp) % GW;
+    const int first = ((gw - base) % GW + GW) % GW;
+    const uint32_t stage_bytes = 2 * KCH * 1024 + KCH * CB;
+    int pu = first, pc = 0, ready_slot = -1;
+    bool poll_failed = false;
+    auto issue = [&]() {
+      const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
+      const int hslot = slot >= tab.nslots ? sp.sh_slot : slot;  // where the slot's h lives
+      const size_t off = (size_t)(2 * n16) * strip + (size_t)pc * KCH * 1024;
+      uint8_t* st = myring + (size_t)(issued % NST) * stage;
+      uint64_t* bar = mybar + issued % NST;
+      mbar_expect_tx(bar, stage_bytes);
+      bulk_g2s_hint(st, tab.d[slot] + off, KCH * 1024, bar, pol);
+      bulk_g2s_hint(st + KCH * 1024, tab.d[slot] + off + strip, KCH * 1024, bar, pol);
+      if (ready_slot != hslot && !poll_failed) {  // the weights are on their way; h needs the slot's 128-groups quantised
+        if (poll_ge(&sy->cnt_hq[hslot], IB)) ready_slot = hslot;
+        else poll_failed = true;
+        asm volatile("fence.proxy.async;" ::: "memory");  // the bulk copy below reads what other SMs' stores wrote
+      }
+      if (!poll_failed)
+        bulk_g2s(st + 2 * KCH * 1024, p.ws.hq + ((size_t)hslot * IB + (size_t)pc * KCH) * CB, KCH * CB, bar);
+      ++issued;
+      if (++pc == cpu) pc = 0, pu += GW;
+    };
+    if (lane == 0)
+      for (int s = 0; s < NST && pu < total; ++s) issue();
+    for (int unit = first; unit < total && !dead; unit += GW) {
+      const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
+      const int srow = (n16 * 16) / 128;
+      const float sdl = lane < IB ? __ldg(tab.sd[slot] + (size_t)srow * IB + lane) : 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < cpu; ++c) {
+        const uint32_t sidx = consumed % NST;
+        if (!mbar_wait(mybar + sidx, (consumed / NST) & 1)) {
+          dead = true;
+          break;
+        }
+        const uint8_t* st = myring + (size_t)sidx * stage;
+#pragma unroll
+        for (int b = 0; b < KCH; ++b) {
+          const int kb = c * KCH + b;
+          const uint8_t* act = st + 2 * KCH * 1024 + b * CB;
+          float d[4];
+          cblock_mma(d, st + b * 1024, st + KCH * 1024 + b * 1024, act, R, lane);
+          const float* hs = reinterpret_cast<const float*>(act + R * 128);
+          const float h0 = hs[(2 * t) & (R - 1)], h1 = hs[(2 * t + 1) & (R - 1)];
+          const float sd = __shfl_sync(0xffffffffu, sdl, kb);
+          acc[0] = fmaf(d[0], sd * h0, acc[0]), acc[1] = fmaf(d[1], sd * h1, acc[1]);
+          acc[2] = fmaf(d[2], sd * h0, acc[2]), acc[3] = fmaf(d[3], sd * h1, acc[3]);
+        }
+        ++consumed;
+        __syncwarp();
+        if (lane == 0 && pu < total) issue();
+        advance();
+      }
+      if (dead) break;
+      while (pend) advance();
+      float* yt = p.ws.ypick + ((size_t)slot * NT + n16) * 128;
+      *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
+      *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
+      pend = 1, pend_kind = 2, pend_a = n16;
+    }
+    if (!dead)
+      while (pend) advance();
+  }
+  if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+
+  // ---- the last CTA to leave resets the step's counters -------------------------------------------------------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_int[2] = atomicAdd(&sy->cnt_exit, 1);
+  __syncthreads();
+  if (s_int[2] == (int)gridDim.x - 1) {
+    for (int i = threadIdx.x; i < kMaxSlots + 1; i += kFThreads) sy->cnt_hq[i] = 0;
+    if (threadIdx.x == 0) sy->cnt_lp = 0, sy->cnt_rt = 0, sy->tab_ready = 0, sy->cnt_exit = 0;
+  }
+}
+
+template <int KCH, int NST>
+size_t step_smem(int H, int R) {
+  const int CB = cblk_bytes(R);
+  const size_t stage = 2 * KCH * 1024 + ((KCH * CB + 127) & ~127);
+  return (size_t)(((H / 128) * CB + 127) & ~127) + kTabSmem + (size_t)kFW * NST * stage + (kFW * NST + 1) * 8 + 16 +
+         sizeof(RouteSmem) + kMaxRows * kMaxTopK * 8 + 64 + 128;
+}
+
+template <int KCH, int NST>
+cudaError_t launch_step(const StepParams& sp, cudaStream_t st) {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const size_t smem = step_smem<KCH, NST>(sp.d.H, sp.R);
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  if (!done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(k_step_fp8<KCH, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    done[dev & 63] = true;
+  }
+  k_step_fp8<KCH, NST><<<sm_count(), kFThreads, smem, st>>>(sp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool step_fp8_fits(int H, int I, int E, int M) {
+  const int KS = (H + 1023) / 1024;
+  // the first phase's work must fit the non-routing warps once, and the routing CTAs need a thread per expert
+  return E <= kFThreads && M <= kMaxRows && sm_count() > M + 1 && H <= 4096 && I <= 4096 && KS >= 1;
+}
+
+cudaError_t launch_step_fp8(StepParams sp, cudaStream_t st) {
+  sp.R = rows_pow2(sp.d.M);
+  sp.sh_slot = kMaxSlots - 1;
+  sp.has_sh = sp.d.sh.g != nullptr;
+  if (sp.R == 1) return launch_step<2, 3>(sp, st);
+  if (sp.R <= 4) return launch_step<2, 2>(sp, st);
+  return launch_step<1, 3>(sp, st);
+}
+
+}  // namespace dsgx

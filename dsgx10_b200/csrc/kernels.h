@@ -42,6 +42,7 @@ struct DecodeWs {
   float* ypick;     // [kMaxSlots][H/16][16][8] every pick's down output (bf16-rounded values kept as f32)
   int* cnt_h;       // [kMaxSlots][I/128] arrivals of the 16 gate/up units of a 128-group of h
   int* cnt_y;       // [H/16] arrivals of the slots of an output tile
+  struct StepSync* sync;  // counters of the one-kernel step (decode_fused.cu)
   struct SlotTab* tab;  // the step's slot table (decode_common.cuh)
   float* lpart;     // [H/1024 slices][8][E] partial router logits of the layer step
 };
@@ -69,6 +70,29 @@ int decode_fp8_up_variants();
 int decode_fp8_down_variants();
 // parts: 1 = activation quantisation + gate/up, 2 = down + combine, 3 = both
 cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
+
+// the one-kernel FP8 layer step (decode_fused.cu)
+struct StepSync {
+  int cnt_lp;     // router logit slices done
+  int cnt_rt;     // rows routed
+  int tab_ready;  // the slot table is in the workspace
+  int cnt_exit;   // CTAs that left
+  int cnt_hq[kMaxSlots + 1];  // quantised 128-groups of a slot's h
+};
+struct StepParams {
+  DecodeParams d;
+  RouteParams rp;
+  const __nv_bfloat16* x;
+  const float* wr;
+  const float* bias;
+  float* logits;
+  int* idx;
+  float* w;
+  StepSync* sync;
+  int R, sh_slot, has_sh;
+};
+bool step_fp8_fits(int H, int I, int E, int M);
+cudaError_t launch_step_fp8(StepParams sp, cudaStream_t st);
 
 cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
 cudaError_t launch_layer_int4(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,

@@ -151,6 +151,9 @@ typedef struct dsgx_layer_step {
   float* ys;
   void* out_bf16;
   void* x_stage;      /* device staging for dsgx_moe_layer_decode_host */
+  int32_t flags;      /* bit 0: run the step as separate kernels (front, route, gate/up, down) instead of the one
+                         persistent kernel FP8 layers use by default; both give the same bits */
+  int32_t reserved;
 } dsgx_layer_step;
 int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, int M,
                           const dsgx_layer_step* step, int finalize, void* stream);

@@ -167,3 +167,26 @@ def test_kernel_variants_same_bits(orc):
                 base = (yr.clone(), ys.clone())
             assert torch.equal(yr, base[0]) and torch.equal(ys, base[1]), (up, down)
     assert moe.ws_status(ws) == 0
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8])
+def test_one_kernel_step_equals_separate_kernels(orc, M):
+    """The persistent one-kernel layer step and the four-kernel step give the same bits, run after run on one workspace
+    (its counters reset themselves), for every row count (activation blocks of 1, 2, 4, 8 rows)."""
+    from dsgx10_b200 import moe, synth
+    H, I, E, topk = 1024, 512, 32, 6
+    shp = moe.shape(H, I, E, topk, n_group=4, topk_group=2)
+    layer = synth.Fp8Layer(H, I, E, 400 + M, device="cuda")
+    wr = synth.router_weights(E, H, 401).cuda()
+    fused = moe.LayerStep(shp, wr, fused=True)
+    sep = moe.LayerStep(shp, wr, fused=False)
+    for it in range(3):
+        x = synth.activations(M, H, 410 + it).cuda()
+        a = fused.run(layer.layer_w(), x).clone()
+        b = sep.run(layer.layer_w(), x).clone()
+        torch.cuda.synchronize()
+        assert moe.ws_status(fused.ws) == 0 and moe.ws_status(sep.ws) == 0
+        assert torch.equal(fused.logits[:M], sep.logits[:M])
+        assert torch.equal(fused.idx[:M], sep.idx[:M]) and torch.equal(fused.w[:M], sep.w[:M])
+        assert torch.equal(fused.yr[:M], sep.yr[:M]) and torch.equal(fused.ys[:M], sep.ys[:M])
+        assert torch.equal(a, b)
