@@ -37,7 +37,7 @@ class DecodeCfg(C.Structure):
 
 class LayerStep(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("wr", "bias", "logits", "idx", "w", "ws", "yr", "ys", "out_bf16", "x_stage")] + \
-               [("flags", C.c_int32), ("reserved", C.c_int32)]
+               [("flags", C.c_int32), ("reserved", C.c_int32), ("reserved_ptr", C.c_void_p)]
 
 
 # every symbol include/dsgx_moe.h declares: name -> (restype, argtypes)

@@ -227,6 +227,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
       StepParams sp;
       sp.d = p, sp.rp = rp, sp.x = xb, sp.wr = st->wr, sp.bias = st->bias, sp.logits = st->logits, sp.idx = st->idx;
       sp.w = st->w, sp.sync = p.ws.sync, sp.R = 0, sp.sh_slot = 0, sp.has_sh = 0;
+      sp.stamps = (st->flags & 2) ? reinterpret_cast<unsigned long long*>(st->reserved_ptr) : nullptr;
       cudaError_t e = launch_step_fp8(sp, (cudaStream_t)stream);
       return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
     }

@@ -9,31 +9,31 @@ namespace dsgx {
 // The slot table of a step, built once by one CTA and read by every CTA of the expert kernels.
 // Slots 0 .. nslots-1: the picked experts this GPU owns, ascending id; slot nslots: the shared expert (if any).
 // A row that did not pick a slot's expert has weight 0 there.  Size a multiple of 16 bytes (bulk-copied).
+struct alignas(16) SlotEnt {
+  const uint8_t *g, *u, *d;      // gate, up, down blocks
+  const float *sg, *su, *sd;     // FP8: their f32 block scales
+  float w[8];                    // the rows' routing weights
+  int e;                         // expert id (-1: the shared expert)
+  int pad[3];
+};
 struct alignas(16) SlotTab {
   int nslots;  // routed slots
   int ntot;    // + the shared expert's
   int bad;     // a dsgx_status when the picks or descriptors were refused (the routed work is then dropped)
   int pad;
-  int e[kMaxSlots + 3];
-  float w[kMaxSlots][8];
-  const uint8_t* g[kMaxSlots + 1];  // gate, up, down blocks
-  const uint8_t* u[kMaxSlots + 1];
-  const uint8_t* d[kMaxSlots + 1];
-  const float* sg[kMaxSlots + 1];  // FP8: their f32 block scales
-  const float* su[kMaxSlots + 1];
-  const float* sd[kMaxSlots + 1];
+  SlotEnt ent[kMaxSlots + 1];
 };
-static_assert(sizeof(SlotTab) % 16 == 0, "SlotTab is bulk-copied");
+static_assert(sizeof(SlotEnt) == 96 && sizeof(SlotTab) % 16 == 0, "SlotTab is copied in 16-byte pieces");
 
 // Builds the table in shared memory from the step's picks (idx, w: M x topk, shared or global memory), by one whole CTA.
-// scratch: 16 words of shared memory.
+// bm: 16 words of shared memory.
 DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const float* w, int M, int topk, int E, int e_lo,
                              int e_hi, const uint8_t* pool, const dsgx_mat_desc* desc, const dsgx_shared_w& sh,
                              uint32_t fmt) {
   const int tid = threadIdx.x, nt = blockDim.x;
   if (tid < 16) bm[tid] = 0;
   if (tid == 0) tab.bad = 0, tab.pad = 0;
-  for (int i = tid; i < kMaxSlots * 8; i += nt) (&tab.w[0][0])[i] = 0.f;
+  for (int i = tid; i < (kMaxSlots + 1) * 8; i += nt) tab.ent[i >> 3].w[i & 7] = 0.f;
   __syncthreads();
   const int np = M * topk;
   for (int i = tid; i < np; i += nt) {
@@ -47,24 +47,25 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
     for (int k = 0; k < (e >> 5); ++k) r += __popc(bm[k]);
     return r;
   };
-  for (int e = tid; e < E; e += nt)
-    if ((bm[e >> 5] >> (e & 31)) & 1) {
-      const int s = rank_of(e);
-      tab.e[s] = e;
-      const dsgx_mat_desc* d = desc + (size_t)e * 3;
-      if (d[0].fmt != fmt || d[1].fmt != fmt || d[2].fmt != fmt) tab.bad = DSGX_ERR_FORMAT;
-      tab.g[s] = pool + d[0].off, tab.u[s] = pool + d[1].off, tab.d[s] = pool + d[2].off;
-      if (fmt == DSGX_FMT_FP8) {
-        tab.sg[s] = reinterpret_cast<const float*>(pool + ((uint64_t)d[0].rsv[0] | (uint64_t)d[0].rsv[1] << 32));
-        tab.su[s] = reinterpret_cast<const float*>(pool + ((uint64_t)d[1].rsv[0] | (uint64_t)d[1].rsv[1] << 32));
-        tab.sd[s] = reinterpret_cast<const float*>(pool + ((uint64_t)d[2].rsv[0] | (uint64_t)d[2].rsv[1] << 32));
-      } else {
-        tab.sg[s] = tab.su[s] = tab.sd[s] = nullptr;
-      }
-    }
+  // one thread a pick: the pick's expert (a slot may be written by several rows' threads with the same values)
   for (int i = tid; i < np; i += nt) {
     const int e = idx[i];
-    if (e >= 0 && e < E && e >= e_lo && e < e_hi) tab.w[rank_of(e)][i / topk] = w[i];
+    if (e < 0 || e >= E || e < e_lo || e >= e_hi) continue;
+    const int s = rank_of(e);
+    SlotEnt& en = tab.ent[s];
+    en.w[i / topk] = w[i];
+    const dsgx_mat_desc* d = desc + (size_t)e * 3;
+    const uint64_t o0 = d[0].off, o1 = d[1].off, o2 = d[2].off;
+    if (d[0].fmt != fmt || d[1].fmt != fmt || d[2].fmt != fmt) tab.bad = DSGX_ERR_FORMAT;
+    en.e = e;
+    en.g = pool + o0, en.u = pool + o1, en.d = pool + o2;
+    if (fmt == DSGX_FMT_FP8) {
+      en.sg = reinterpret_cast<const float*>(pool + ((uint64_t)d[0].rsv[0] | (uint64_t)d[0].rsv[1] << 32));
+      en.su = reinterpret_cast<const float*>(pool + ((uint64_t)d[1].rsv[0] | (uint64_t)d[1].rsv[1] << 32));
+      en.sd = reinterpret_cast<const float*>(pool + ((uint64_t)d[2].rsv[0] | (uint64_t)d[2].rsv[1] << 32));
+    } else {
+      en.sg = en.su = en.sd = nullptr;
+    }
   }
   __syncthreads();
   if (tid == 0) {
@@ -74,15 +75,45 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
     const bool has_sh = fmt == DSGX_FMT_FP8 ? sh.g != nullptr : sh.bg != nullptr;
     tab.nslots = n, tab.ntot = n + (has_sh ? 1 : 0);
     if (has_sh) {
-      tab.e[n] = -1;
+      SlotEnt& en = tab.ent[n];
+      en.e = -1;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) en.w[r] = 0.f;
       if (fmt == DSGX_FMT_FP8) {
-        tab.g[n] = sh.g, tab.u[n] = sh.u, tab.d[n] = sh.d, tab.sg[n] = sh.gs, tab.su[n] = sh.us, tab.sd[n] = sh.ds;
+        en.g = sh.g, en.u = sh.u, en.d = sh.d, en.sg = sh.gs, en.su = sh.us, en.sd = sh.ds;
       } else {
-        tab.g[n] = sh.bg, tab.u[n] = sh.bu, tab.d[n] = sh.bd, tab.sg[n] = tab.su[n] = tab.sd[n] = nullptr;
+        en.g = sh.bg, en.u = sh.bu, en.d = sh.bd, en.sg = en.su = en.sd = nullptr;
       }
     }
   }
   __syncthreads();
+}
+
+// The table from global memory into shared memory by one warp, in as few round trips as its size allows: the header
+// and the first 15 slots together, the rest (wide steps only) after.
+DSGX_DEV void load_slot_tab(SlotTab& dst, const SlotTab* src, int lane) {
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+  uint4* d4 = reinterpret_cast<uint4*>(&dst);
+  constexpr int kFirst = 1 + 15 * 6;  // header + 15 entries, 16-byte pieces (91: three per lane)
+  uint4 v[3];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) v[i] = lane + 32 * i < kFirst ? __ldcg(s4 + lane + 32 * i) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    if (lane + 32 * i < kFirst) d4[lane + 32 * i] = v[i];
+  __syncwarp();
+  const int ntot = dst.ntot;
+  if (ntot > 15) {
+    const int total = 1 + ntot * 6;
+    for (int i = kFirst + lane; i < total; i += 128) {
+      uint4 u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u[k] = i + 32 * k < total ? __ldcg(s4 + i + 32 * k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (i + 32 * k < total) d4[i + 32 * k] = u[k];
+    }
+  }
 }
 
 // order position -> slot: the shared expert's units come first (they are the same every step)

@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
     uint8_t* st = myring + (issued % kNST) * kUpStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, kUpStage);
-    bulk_g2s_hint(st, tab.g[slot] + off, kKCH * 1024, bar, pol);
-    bulk_g2s_hint(st + kKCH * 1024, tab.u[slot] + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st, tab.ent[slot].g + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st + kKCH * 1024, tab.ent[slot].u + off, kKCH * 1024, bar, pol);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   for (int unit = gw; unit < total && !dead; unit += GW) {
     const int slot = ord_slot(tab, unit / upp), i8 = unit % upp;
     const int srow = (i8 * 8) / 128;
-    const float sgl = lane < HB ? __ldg(tab.sg[slot] + (size_t)srow * HB + lane) : 0.f;
-    const float sul = lane < HB ? __ldg(tab.su[slot] + (size_t)srow * HB + lane) : 0.f;
+    const float sgl = lane < HB ? __ldg(tab.ent[slot].sg + (size_t)srow * HB + lane) : 0.f;
+    const float sul = lane < HB ? __ldg(tab.ent[slot].su + (size_t)srow * HB + lane) : 0.f;
     float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
     for (int c = 0; c < cpu; ++c) {
       const uint32_t sidx = consumed % kNST;
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
     const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
     float h0 = __fmul_rn(silu(bf16_round(ag0)), bf16_round(au0));
     float h1 = __fmul_rn(silu(bf16_round(ag1)), bf16_round(au1));
-    if (routed) h0 = __fmul_rn(tab.w[slot][r0], h0), h1 = __fmul_rn(tab.w[slot][r1], h1);
+    if (routed) h0 = __fmul_rn(tab.ent[slot].w[r0], h0), h1 = __fmul_rn(tab.ent[slot].w[r1], h1);
     __nv_bfloat16* hrow = p.ws.h + (size_t)slot * 8 * p.I;
     if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
     if (r1 < p.M) hrow[(size_t)r1 * p.I + ch] = __float2bfloat16_rn(h1);
@@ -230,8 +230,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
     uint8_t* st = myring + (issued % kNST) * kDownStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, kDownStage);
-    bulk_g2s_hint(st, tab.d[slot] + off, kKCH * 1024, bar, pol);
-    bulk_g2s_hint(st + kKCH * 1024, tab.d[slot] + off + strip, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st, tab.ent[slot].d + off, kKCH * 1024, bar, pol);
+    bulk_g2s_hint(st + kKCH * 1024, tab.ent[slot].d + off + strip, kKCH * 1024, bar, pol);
     bulk_g2s(st + 2 * kKCH * 1024, p.ws.hq + ((size_t)slot * IB + (size_t)pc * kKCH) * kActBlk, kKCH * kActBlk, bar);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   for (int unit = gw; unit < total && !dead; unit += GW) {
     const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
     const int srow = (n16 * 16) / 128;
-    const float sdl = lane < IB ? __ldg(tab.sd[slot] + (size_t)srow * IB + lane) : 0.f;
+    const float sdl = lane < IB ? __ldg(tab.ent[slot].sd + (size_t)srow * IB + lane) : 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 0; c < cpu; ++c) {
       const uint32_t sidx = consumed % kNST;

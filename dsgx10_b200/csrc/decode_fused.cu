@@ -33,6 +33,11 @@ constexpr int kTabSmem = (sizeof(SlotTab) + 127) & ~127;
 // compact activation block of R rows x 128 k: [2 halves q][R rows][4 t][16 B] e4m3, then R f32 scales (padded to 16 B)
 __host__ __device__ constexpr int cblk_bytes(int R) { return R * 128 + (R <= 4 ? 16 : 32); }
 
+DSGX_DEV unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 DSGX_DEV int ld_acquire(const int* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -105,6 +110,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   uint32_t issued = 0, consumed = 0;
   bool dead = false;
 
+  unsigned long long* stamp = sp.stamps ? sp.stamps + (size_t)gw * 8 : nullptr;  // optional phase timestamps (ns)
+  if (stamp && lane == 0) stamp[0] = gtime();
   if (lane == 0)
     for (int s = 0; s < NST; ++s) mbar_init(mybar + s, 1);
   if (threadIdx.x == 0) {
@@ -124,16 +131,18 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     cquant_row(xq + j * CB, R, r, lane, r < p.M, v0, v1, v2, v3);
   }
   __syncthreads();
+  if (stamp && lane == 0) stamp[1] = gtime();
 
   const uint64_t pol = policy_evict_first();
   const int KS = (p.H + 1023) / 1024, ntask = p.E * KS;
   const int nroute = p.M;  // the last nroute CTAs route one row each
   const bool router_cta = (int)blockIdx.x >= (int)gridDim.x - nroute;
   const int GWn = GW - nroute * kFW;  // warps that take the logit slices and the shared expert's gate/up units
-  const int sh_units = sp.has_sh ? upp : 0;
+  const int sh_units = sp.has_sh ? upp : 0, sh_down = sp.has_sh ? NT : 0;
 
   // ---- the outstanding ticket of the unit a warp finished last --------------------------------------------------------
   int pend = 0, pend_kind = 0, pend_a = 0, pend_b = 0, pend_ticket = 0;  // kind 1: h group (slot a, group b); 2: tile a
+  bool tab_loaded = false;
   auto advance = [&]() {
     if (pend == 1) {
       __threadfence();
@@ -142,6 +151,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         pend_ticket = pend_kind == 1 ? atomicAdd(p.ws.cnt_h + pend_a * IB + pend_b, 1) : atomicAdd(p.ws.cnt_y + pend_a, 1);
       pend = 2;
     } else if (pend == 2) {
+      if (pend_kind == 2 && !tab_loaded) return;  // the tile's slot count is in the table: look again later
       const int ticket = __shfl_sync(0xffffffffu, pend_ticket, 0);
       if (pend_kind == 1 && ticket == 15) {  // the 16th unit of a 128-group of h quantises it and reports the group
         __threadfence();
@@ -183,7 +193,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
           a.x = __fadd_rn(a.x, v.x), a.y = __fadd_rn(a.y, v.y), a.z = __fadd_rn(a.z, v.z), a.w = __fadd_rn(a.w, v.w);
         }
         float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (sh) sv = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)tab.nslots * NT * 128));
+        if (sh) sv = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)sp.sh_slot * NT * 128));
         const float av[4] = {a.x, a.y, a.z, a.w}, svv[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -207,8 +217,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     int pu = first, pc = 0;
     auto issue = [&]() {
       const int s = shared ? -1 : pu / upp, i8 = pu % upp;
-      const uint8_t* gp = shared ? p.sh.g : tab.g[s];
-      const uint8_t* up = shared ? p.sh.u : tab.u[s];
+      const uint8_t* gp = shared ? p.sh.g : tab.ent[s].g;
+      const uint8_t* up = shared ? p.sh.u : tab.ent[s].u;
       const size_t off = (size_t)i8 * strip + (size_t)pc * KCH * 1024;
       uint8_t* st = myring + (size_t)(issued % NST) * stage;
       uint64_t* bar = mybar + issued % NST;
@@ -224,8 +234,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       const int s = shared ? -1 : unit / upp, i8 = unit % upp;
       const int wslot = shared ? sp.sh_slot : s;  // where this unit's h lives in the workspace
       const int srow = (i8 * 8) / 128;
-      const float* sgp = shared ? p.sh.gs : tab.sg[s];
-      const float* sup = shared ? p.sh.us : tab.su[s];
+      const float* sgp = shared ? p.sh.gs : tab.ent[s].sg;
+      const float* sup = shared ? p.sh.us : tab.ent[s].su;
       const float sgl = lane < HB ? __ldg(sgp + (size_t)srow * HB + lane) : 0.f;
       const float sul = lane < HB ? __ldg(sup + (size_t)srow * HB + lane) : 0.f;
       float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
@@ -258,7 +268,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
       float h0 = __fmul_rn(silu(bf16_round(ag0)), bf16_round(au0));
       float h1 = __fmul_rn(silu(bf16_round(ag1)), bf16_round(au1));
-      if (!shared) h0 = __fmul_rn(tab.w[s][r0], h0), h1 = __fmul_rn(tab.w[s][r1], h1);
+      if (!shared) h0 = __fmul_rn(tab.ent[s].w[r0], h0), h1 = __fmul_rn(tab.ent[s].w[r1], h1);
       __nv_bfloat16* hrow = p.ws.h + (size_t)wslot * 8 * p.I;
       if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
       if (r1 < p.M) hrow[(size_t)r1 * p.I + ch] = __float2bfloat16_rn(h1);
@@ -268,130 +278,41 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       while (pend) advance();
   };
 
-  // ---- phase 1: logit slices and the shared expert's gate/up units, on disjoint warps -------------------------------------
-  if (!router_cta) {
-    int mine = 0;
-    for (int task = gw; task < ntask; task += GWn) {
-      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
-      ++mine;
-    }
-    if (mine) {  // one global add a CTA: its last logit warp reports all of the CTA's slices
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) {
-        const int cta_first = blockIdx.x * kFW;
-        int nw = 0, nt = 0;
-        for (int w2 = 0; w2 < kFW; ++w2)
-          for (int task = cta_first + w2; task < ntask; task += GWn) ++nt, nw += task == cta_first + w2;
-        if (atomicAdd(&s_int[1], 1) == nw - 1) atomicAdd(&sy->cnt_lp, nt);
-      }
-    }
-    if (sh_units) {  // shared unit u -> warp (ntask + u) mod GWn
-      const int first = ((gw - ntask % GWn) % GWn + GWn) % GWn;
-      up_units(first, GWn, sh_units, true);
-    }
-  } else {
-    // ---- phase 2 (router CTAs): wait for the slices, route a row, the last one builds the slot table -------------------
-    const int row = (int)blockIdx.x - ((int)gridDim.x - nroute);
-    if (threadIdx.x == 0) s_int[2] = poll_ge(&sy->cnt_lp, ntask) ? 1 : 0;
-    __syncthreads();
-    const bool ok = s_int[2] != 0;
-    __syncthreads();
-    if (ok) {
-      route_row_cta(sp.rp, p.ws.lpart + (size_t)row * p.E, KS, (size_t)kMaxRows * p.E, sp.bias, rs,
-                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk);
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) s_int[2] = atomicAdd(&sy->cnt_rt, 1);
-      __syncthreads();
-      if (s_int[2] == p.M - 1) {
-        __threadfence();
-        for (int i = threadIdx.x; i < p.M * p.topk; i += kFThreads) s_idx[i] = __ldcg(sp.idx + i), s_w[i] = __ldcg(sp.w + i);
-        __syncthreads();
-        build_slot_tab(tab, s_bm, s_idx, s_w, p.M, p.topk, p.E, p.e_lo, p.e_hi, p.pool, p.desc, p.sh, DSGX_FMT_FP8);
-        if (threadIdx.x == 0 && tab.bad) atomicCAS(p.ws.status, 0, tab.bad);
-        {
-          const uint4* s4 = reinterpret_cast<const uint4*>(&tab);
-          uint4* d4 = reinterpret_cast<uint4*>(p.ws.tab);
-          for (int i = threadIdx.x; i < (int)(sizeof(SlotTab) / 16); i += kFThreads) d4[i] = s4[i];
-        }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) atomicExch(&sy->tab_ready, 1);
-      }
-    } else {
-      dead = true;
-    }
-    __syncthreads();
-  }
-
-  // ---- phase 3: the slot table into shared memory (the first warp to get here loads it for the CTA) --------------------
-  {
-    int winner = 0;
-    if (lane == 0) winner = atomicCAS(&s_int[0], 0, 1) == 0;
-    winner = __shfl_sync(0xffffffffu, winner, 0);
-    if (winner) {
-      int ok = 0;
-      if (lane == 0) ok = !dead && poll_ge(&sy->tab_ready, 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (ok) {
-        const uint4* s4 = reinterpret_cast<const uint4*>(p.ws.tab);
-        uint4* d4 = reinterpret_cast<uint4*>(&tab);
-        for (int i = lane; i < (int)(sizeof(SlotTab) / 16); i += 32) d4[i] = __ldcg(s4 + i);
-        __threadfence_block();
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tabbar)) : "memory");
-      }
-    }
-    if (!mbar_wait(tabbar, 0)) dead = true;
-  }
-
-  // ---- phase 4: routed gate/up units, continuing the round-robin after the first phase's work ------------------------------
-  if (!dead) {
-    const int base = (ntask + sh_units) % GW;
-    up_units(((gw - base) % GW + GW) % GW, GW, tab.nslots * upp, false);
-  }
-
-  // ---- phase 5: down units (slot, 16 output channels), shared expert first ------------------------------------------------
-  if (!dead && tab.ntot == 0) {
-    for (size_t i = (size_t)blockIdx.x * kFThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kFThreads) {
-      p.yr[i] = 0.f;
-      if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
-    }
-  } else if (!dead) {
-    const int total = tab.ntot * NT;
+  // ---- down units (slot, 16 output channels): unit v = first, first + stride, .. < total ---------------------------------
+  // shared: the shared expert's units (before the routing is known: its weights and its h need no table); else routed
+  // slot v / NT.  A unit's weight copies go out first; the copy of h waits for the slot's 128-groups to be quantised.
+  auto down_units = [&](int first, int stride, int total, bool shared) {
     const int cpu = IB / KCH;
     const size_t strip = (size_t)8 * p.I;
-    const int base = (ntask + sh_units + tab.nslots * upp) % GW;
-    const int first = ((gw - base) % GW + GW) % GW;
     const uint32_t stage_bytes = 2 * KCH * 1024 + KCH * CB;
     int pu = first, pc = 0, ready_slot = -1;
     bool poll_failed = false;
     auto issue = [&]() {
-      const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
-      const int hslot = slot >= tab.nslots ? sp.sh_slot : slot;  // where the slot's h lives
+      const int slot = shared ? sp.sh_slot : pu / NT, n16 = pu % NT;  // the slot's index in the workspace
+      const uint8_t* dp = shared ? p.sh.d : tab.ent[slot].d;
       const size_t off = (size_t)(2 * n16) * strip + (size_t)pc * KCH * 1024;
       uint8_t* st = myring + (size_t)(issued % NST) * stage;
       uint64_t* bar = mybar + issued % NST;
       mbar_expect_tx(bar, stage_bytes);
-      bulk_g2s_hint(st, tab.d[slot] + off, KCH * 1024, bar, pol);
-      bulk_g2s_hint(st + KCH * 1024, tab.d[slot] + off + strip, KCH * 1024, bar, pol);
-      if (ready_slot != hslot && !poll_failed) {  // the weights are on their way; h needs the slot's 128-groups quantised
-        if (poll_ge(&sy->cnt_hq[hslot], IB)) ready_slot = hslot;
+      bulk_g2s_hint(st, dp + off, KCH * 1024, bar, pol);
+      bulk_g2s_hint(st + KCH * 1024, dp + off + strip, KCH * 1024, bar, pol);
+      if (ready_slot != slot && !poll_failed) {
+        if (poll_ge(&sy->cnt_hq[slot], IB)) ready_slot = slot;
         else poll_failed = true;
         asm volatile("fence.proxy.async;" ::: "memory");  // the bulk copy below reads what other SMs' stores wrote
       }
       if (!poll_failed)
-        bulk_g2s(st + 2 * KCH * 1024, p.ws.hq + ((size_t)hslot * IB + (size_t)pc * KCH) * CB, KCH * CB, bar);
+        bulk_g2s(st + 2 * KCH * 1024, p.ws.hq + ((size_t)slot * IB + (size_t)pc * KCH) * CB, KCH * CB, bar);
       ++issued;
-      if (++pc == cpu) pc = 0, pu += GW;
+      if (++pc == cpu) pc = 0, pu += stride;
     };
     if (lane == 0)
       for (int s = 0; s < NST && pu < total; ++s) issue();
-    for (int unit = first; unit < total && !dead; unit += GW) {
-      const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
+    for (int unit = first; unit < total && !dead; unit += stride) {
+      const int slot = shared ? sp.sh_slot : unit / NT, n16 = unit % NT;
       const int srow = (n16 * 16) / 128;
-      const float sdl = lane < IB ? __ldg(tab.sd[slot] + (size_t)srow * IB + lane) : 0.f;
+      const float* sdp = shared ? p.sh.ds : tab.ent[slot].sd;
+      const float sdl = lane < IB ? __ldg(sdp + (size_t)srow * IB + lane) : 0.f;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       for (int c = 0; c < cpu; ++c) {
         const uint32_t sidx = consumed % NST;
@@ -418,16 +339,118 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         advance();
       }
       if (dead) break;
-      while (pend) advance();
+      while (pend && (pend_kind != 2 || pend != 2 || tab_loaded)) advance();
+      if (pend) break;  // cannot happen: a warp has at most one early shared unit
       float* yt = p.ws.ypick + ((size_t)slot * NT + n16) * 128;
       *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
       *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
       pend = 1, pend_kind = 2, pend_a = n16;
     }
-    if (!dead)
+    if (!dead && tab_loaded)
       while (pend) advance();
+  };
+
+  // ---- phase 1: logit slices and the shared expert's gate/up units, on disjoint warps -------------------------------------
+  if (!router_cta) {
+    int mine = 0;
+    for (int task = gw; task < ntask; task += GWn) {
+      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
+      ++mine;
+    }
+    if (mine) {  // one global add a CTA: its last logit warp reports all of the CTA's slices
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        const int cta_first = blockIdx.x * kFW;
+        int nw = 0, nt = 0;
+        for (int w2 = 0; w2 < kFW; ++w2)
+          for (int task = cta_first + w2; task < ntask; task += GWn) ++nt, nw += task == cta_first + w2;
+        if (atomicAdd(&s_int[1], 1) == nw - 1) atomicAdd(&sy->cnt_lp, nt);
+      }
+    }
+    if (sh_units) {  // shared unit u -> warp (ntask + u) mod GWn
+      const int first = ((gw - ntask % GWn) % GWn + GWn) % GWn;
+      up_units(first, GWn, sh_units, true);
+      // and its down units (their h is the shared expert's own): unit v -> warp (ntask + sh_units + v) mod GWn
+      down_units(((gw - (ntask + sh_units) % GWn) % GWn + GWn) % GWn, GWn, sh_down, true);
+    }
+  } else {
+    // ---- phase 2 (router CTAs): wait for the slices, route a row, the last one builds the slot table -------------------
+    const int row = (int)blockIdx.x - ((int)gridDim.x - nroute);
+    if (threadIdx.x == 0) s_int[2] = poll_ge(&sy->cnt_lp, ntask) ? 1 : 0;
+    __syncthreads();
+    const bool ok = s_int[2] != 0;
+    __syncthreads();
+    if (ok) {
+      route_row_cta(sp.rp, p.ws.lpart + (size_t)row * p.E, KS, (size_t)kMaxRows * p.E, sp.bias, rs,
+                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk);
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) s_int[2] = p.M > 1 ? atomicAdd(&sy->cnt_rt, 1) : 0;  // one row: no ticket to take
+      __syncthreads();
+      if (s_int[2] == p.M - 1) {
+        __threadfence();
+        for (int i = threadIdx.x; i < p.M * p.topk; i += kFThreads) s_idx[i] = __ldcg(sp.idx + i), s_w[i] = __ldcg(sp.w + i);
+        __syncthreads();
+        build_slot_tab(tab, s_bm, s_idx, s_w, p.M, p.topk, p.E, p.e_lo, p.e_hi, p.pool, p.desc, p.sh, DSGX_FMT_FP8);
+        if (threadIdx.x == 0 && tab.bad) atomicCAS(p.ws.status, 0, tab.bad);
+        {
+          const uint4* s4 = reinterpret_cast<const uint4*>(&tab);
+          uint4* d4 = reinterpret_cast<uint4*>(p.ws.tab);
+          for (int i = threadIdx.x; i < 1 + tab.ntot * 6; i += kFThreads) d4[i] = s4[i];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicExch(&sy->tab_ready, 1);
+      }
+    } else {
+      dead = true;
+    }
+    __syncthreads();
+  }
+
+  if (stamp && lane == 0) stamp[2] = gtime();
+  // ---- phase 3: the slot table into shared memory (the first warp to get here loads it for the CTA) --------------------
+  {
+    int winner = 0;
+    if (lane == 0) winner = atomicCAS(&s_int[0], 0, 1) == 0;
+    winner = __shfl_sync(0xffffffffu, winner, 0);
+    if (winner) {
+      int ok = 0;
+      if (lane == 0) ok = !dead && poll_ge(&sy->tab_ready, 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (ok) {
+        load_slot_tab(tab, p.ws.tab, lane);
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tabbar)) : "memory");
+      }
+    }
+    if (!mbar_wait(tabbar, 0)) dead = true;
+    tab_loaded = !dead;
+  }
+
+  if (stamp && lane == 0) stamp[3] = gtime();
+  // ---- phase 4: routed gate/up units, continuing the round-robin after the first phase's work ------------------------------
+  if (!dead) {
+    const int base = (ntask + sh_units) % GW;
+    up_units(((gw - base) % GW + GW) % GW, GW, tab.nslots * upp, false);
+  }
+
+  if (stamp && lane == 0) stamp[4] = gtime();
+  // ---- phase 5: the routed slots' down units ------------------------------------------------------------------------------
+  if (!dead && tab.ntot == 0) {
+    for (size_t i = (size_t)blockIdx.x * kFThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kFThreads) {
+      p.yr[i] = 0.f;
+      if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
+    }
+  } else if (!dead) {
+    const int base = (ntask + sh_units + sh_down + tab.nslots * upp) % GW;
+    down_units(((gw - base) % GW + GW) % GW, GW, tab.nslots * NT, false);
+    while (pend) advance();
   }
   if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+  if (stamp && lane == 0) stamp[5] = gtime();
 
   // ---- the last CTA to leave resets the step's counters -------------------------------------------------------------------
   __threadfence();

@@ -164,8 +164,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
     uint8_t* st = myring + (issued % kNST) * kUpStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, 2 * blk);
-    bulk_g2s_hint(st, tab.g[slot] + off, blk, bar, pol);
-    bulk_g2s_hint(st + kI4Blk, tab.u[slot] + off, blk, bar, pol);
+    bulk_g2s_hint(st, tab.ent[slot].g + off, blk, bar, pol);
+    bulk_g2s_hint(st + kI4Blk, tab.ent[slot].u + off, blk, bar, pol);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
@@ -258,8 +258,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
     uint8_t* st = myring + (size_t)(issued % kNST) * stage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, 2 * blk + hb);
-    bulk_g2s_hint(st, tab.d[slot] + off, blk, bar, pol);
-    bulk_g2s_hint(st + kI4Blk, tab.d[slot] + off + (size_t)cpu * blk, blk, bar, pol);
+    bulk_g2s_hint(st, tab.ent[slot].d + off, blk, bar, pol);
+    bulk_g2s_hint(st + kI4Blk, tab.ent[slot].d + off + (size_t)cpu * blk, blk, bar, pol);
     bulk_g2s(st + kStageW, reinterpret_cast<const uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + (size_t)pc * (sh ? 8 : 32)) * R * 32, hb, bar);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int s = 0; s < tab.nslots; ++s) {
           const float4 v = __ldcg(reinterpret_cast<const float4*>(yt + (size_t)s * NT * 128));
-          const float4 wv = *reinterpret_cast<const float4*>(&tab.w[s][r0]);
+          const float4 wv = *reinterpret_cast<const float4*>(&tab.ent[s].w[r0]);
           a.x = __fadd_rn(a.x, __fmul_rn(v.x, wv.x)), a.y = __fadd_rn(a.y, __fmul_rn(v.y, wv.y));
           a.z = __fadd_rn(a.z, __fmul_rn(v.z, wv.z)), a.w = __fadd_rn(a.w, __fmul_rn(v.w, wv.w));
         }

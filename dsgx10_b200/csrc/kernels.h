@@ -89,6 +89,7 @@ struct StepParams {
   int* idx;
   float* w;
   StepSync* sync;
+  unsigned long long* stamps;  // optional [warps][8] phase timestamps (profiling aid), or null
   int R, sh_slot, has_sh;
 };
 bool step_fp8_fits(int H, int I, int E, int M);

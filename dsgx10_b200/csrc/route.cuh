@@ -179,20 +179,15 @@ DSGX_DEV void route_row(const RouteParams& p, const float* __restrict__ l, int n
 
 namespace dsgx {
 
-// ---- the same routing function by one whole CTA, one thread per expert (blockDim.x = E rounded up to 32) ----------
-// For decode widths the routing is a chain of dependent steps, so a row is spread over the CTA: scores in parallel,
-// each pick a block-wide arg-max.  Comparisons are exact and every sum keeps the order of route_row, so the bits
-// are the same.
+// ---- the same routing function by one whole CTA (blockDim.x = E rounded up to 32, at least 32) ------------------------
+// For decode widths the routing is a chain of dependent steps, so the scores are computed one thread an expert (all
+// slice loads in one round trip), and one warp then selects from shared memory with the keys in registers: no block-wide
+// barrier inside the pick loop.  Comparisons are exact and every sum keeps the order of route_row: the same bits.
 struct RouteSmem {
   float key[512];
-  float wv[16];
-  int wi[16];
+  float s[512];
   float red[16];
-  float picked[8];
-  int ids[8];
-  float gsc[32];
   float S;
-  uint32_t keep;
 };
 
 DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
@@ -201,9 +196,15 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   const bool valid = e < p.E;
   float lg = -INFINITY, b = 0.f;
   if (valid) {
-    lg = __ldcg(l + e);
+    float part[8];
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp) part[sp] = sp < nsplit ? __ldcg(l + sp * split_stride + e) : 0.f;
     if (bias) b = __ldg(bias + e);
-    for (int sp = 1; sp < nsplit; ++sp) lg = __fadd_rn(lg, __ldcg(l + sp * split_stride + e));
+    lg = part[0];
+#pragma unroll
+    for (int sp = 1; sp < 8; ++sp)
+      if (sp < nsplit) lg = __fadd_rn(lg, part[sp]);
+    for (int sp = 8; sp < nsplit; ++sp) lg = __fadd_rn(lg, __ldcg(l + sp * split_stride + e));
     if (logits_out) logits_out[e] = lg;
   }
   float s;
@@ -232,77 +233,91 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     s = __fdiv_rn(t, sm.S);
     __syncthreads();
   }
-  float key = valid ? __fadd_rn(s, b) : -INFINITY;
+  sm.s[e] = s;
+  sm.key[e] = valid ? __fadd_rn(s, b) : -INFINITY;
+  __syncthreads();
+  if (warp != 0) return;
+
+  // ---- one warp selects: expert e = lane + 32 j in register j -------------------------------------------------------
+  float key[kRJ];
+#pragma unroll
+  for (int j = 0; j < kRJ; ++j) key[j] = lane + 32 * j < p.E ? sm.key[lane + 32 * j] : -INFINITY;
   if (p.n_group > 1) {
     const int gs = p.E / p.n_group;
-    sm.key[e] = key;
-    __syncthreads();
-    if (e < p.n_group) {
+    float mine = -INFINITY;  // lane g < n_group: the sum of group g's two largest keys, scanned in ascending id
+    if (lane < p.n_group) {
       float a = -INFINITY, c = -INFINITY;
-      for (int i = e * gs; i < (e + 1) * gs; ++i) {
+      for (int i = lane * gs; i < (lane + 1) * gs; ++i) {
         const float v = sm.key[i];
         if (v > a) c = a, a = v;
         else if (v > c) c = v;
       }
-      sm.gsc[e] = __fadd_rn(a, c);
+      mine = __fadd_rn(a, c);
     }
-    __syncthreads();
-    if (warp == 0) {
-      const float mine = lane < p.n_group ? sm.gsc[lane] : -INFINITY;
-      uint32_t keep = 0;
-      for (int t = 0; t < p.topk_group; ++t) {
-        float bv = lane < p.n_group && !((keep >> lane) & 1) ? mine : -INFINITY;
-        int bg = lane < p.n_group && !((keep >> lane) & 1) ? lane : 1 << 30;
-        if (bv != bv) bv = -INFINITY;
+    uint32_t keep = 0;
+    for (int t = 0; t < p.topk_group; ++t) {
+      float bv = lane < p.n_group && !((keep >> lane) & 1) ? mine : -INFINITY;
+      int bg = lane < p.n_group && !((keep >> lane) & 1) ? lane : 1 << 30;
+      if (bv != bv) bv = -INFINITY;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-          const int og = __shfl_xor_sync(0xffffffffu, bg, o);
-          if (og < (1 << 30) && (bg == (1 << 30) || ov > bv || (ov == bv && og < bg))) bv = ov, bg = og;
-        }
-        if (bg < 32) keep |= 1u << bg;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (og < (1 << 30) && (bg == (1 << 30) || ov > bv || (ov == bv && og < bg))) bv = ov, bg = og;
       }
-      if (lane == 0) sm.keep = keep;
+      if (bg < 32) keep |= 1u << bg;
     }
-    __syncthreads();
-    if (valid && !((sm.keep >> (e / gs)) & 1)) key = -INFINITY;
-  }
-  for (int k = 0; k < p.topk; ++k) {
-    float bv = key;
-    int be = key == -INFINITY ? 1 << 30 : e;
+    const uint32_t inv = ((1u << 20) + gs - 1) / gs;  // e / gs == (e * inv) >> 20 for e < 512
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-      if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
+    for (int j = 0; j < kRJ; ++j) {
+      const uint32_t ee = lane + 32 * j;
+      if (ee < (uint32_t)p.E && !((keep >> ((ee * inv) >> 20)) & 1)) key[j] = -INFINITY;
     }
-    if (lane == 0) sm.wv[warp] = bv, sm.wi[warp] = be;
-    __syncthreads();
-    bv = sm.wv[0], be = sm.wi[0];
-    for (int w = 1; w < nW; ++w) {
-      const float ov = sm.wv[w];
-      const int oe = sm.wi[w];
-      if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
-    }
-    if (be == 1 << 30) be = 0;
-    if (e == be) sm.picked[k] = s, sm.ids[k] = be, key = -INFINITY;
-    __syncthreads();
   }
-  if (e < p.topk) {
-    float t[4];
+  float picked[8];
+  int ids[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) t[j] = j < p.topk ? sm.picked[j] : 0.f;
-    for (int i = 4; i < p.topk; ++i) t[i & 3] = __fadd_rn(t[i & 3], sm.picked[i]);
-    float sum;
-    if (p.topk <= 1) sum = t[0];
-    else if (p.topk == 2) sum = __fadd_rn(t[0], t[1]);
-    else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
-    else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
-    sum = __fadd_rn(sum, 1e-20f);
-    const float pk = sm.picked[e];
-    idx_out[e] = sm.ids[e];
-    w_out[e] = p.norm_topk ? __fmul_rn(__fdiv_rn(pk, sum), p.route_scale) : __fmul_rn(pk, p.route_scale);
+  for (int k = 0; k < 8; ++k) {
+    picked[k] = 0.f, ids[k] = 0;
+    if (k < p.topk) {
+      float bv = -INFINITY;
+      int bj = 0;
+#pragma unroll
+      for (int j = 0; j < kRJ; ++j)
+        if (key[j] > bv) bv = key[j], bj = j;
+      int be = bv == -INFINITY ? 1 << 30 : lane + 32 * bj;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
+      }
+      if (be == 1 << 30) be = 0;
+      ids[k] = be;
+#pragma unroll
+      for (int j = 0; j < kRJ; ++j)
+        if (lane + 32 * j == be) key[j] = -INFINITY;
+      picked[k] = sm.s[be];
+    }
   }
+  float t[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) t[j] = j < p.topk ? picked[j] : 0.f;
+#pragma unroll
+  for (int i = 4; i < 8; ++i)
+    if (i < p.topk) t[i & 3] = __fadd_rn(t[i & 3], picked[i]);
+  float sum;
+  if (p.topk <= 1) sum = t[0];
+  else if (p.topk == 2) sum = __fadd_rn(t[0], t[1]);
+  else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
+  else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
+  sum = __fadd_rn(sum, 1e-20f);
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (k < p.topk && lane == k) {
+      idx_out[k] = ids[k];
+      w_out[k] = p.norm_topk ? __fmul_rn(__fdiv_rn(picked[k], sum), p.route_scale) : __fmul_rn(picked[k], p.route_scale);
+    }
 }
 
 }  // namespace dsgx

@@ -154,6 +154,8 @@ typedef struct dsgx_layer_step {
   int32_t flags;      /* bit 0: run the step as separate kernels (front, route, gate/up, down) instead of the one
                          persistent kernel FP8 layers use by default; both give the same bits */
   int32_t reserved;
+  void* reserved_ptr; /* with flags bit 1: device memory for [warps][8] u64 phase timestamps of the one-kernel step
+                         (a profiling aid; warps = 16 x SM count) */
 } dsgx_layer_step;
 int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, int M,
                           const dsgx_layer_step* step, int finalize, void* stream);
