@@ -103,14 +103,16 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   uint32_t* s_bm = reinterpret_cast<uint32_t*>(s_w + kMaxRows * kMaxTopK);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int GW = gridDim.x * kFW, gw = blockIdx.x * kFW + warp;
+  // Work is dealt to warps CTA-interleaved (consecutive work items go to different SMs): one SM pulls at most ~50 GB/s,
+  // so a small phase must not sit on a few SMs.
+  const int GW = gridDim.x * kFW, gw = warp * gridDim.x + blockIdx.x;
   StepSync* sy = sp.sync;
   uint8_t* myring = ringbase + (size_t)warp * NST * stage;
   uint64_t* mybar = bars + warp * NST;
   uint32_t issued = 0, consumed = 0;
   bool dead = false;
 
-  unsigned long long* stamp = sp.stamps ? sp.stamps + (size_t)gw * 8 : nullptr;  // optional phase timestamps (ns)
+  unsigned long long* stamp = sp.stamps ? sp.stamps + (size_t)(blockIdx.x * kFW + warp) * 8 : nullptr;  // phase timestamps
   if (stamp && lane == 0) stamp[0] = gtime();
   if (lane == 0)
     for (int s = 0; s < NST; ++s) mbar_init(mybar + s, 1);
@@ -137,7 +139,9 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   const int KS = (p.H + 1023) / 1024, ntask = p.E * KS;
   const int nroute = p.M;  // the last nroute CTAs route one row each
   const bool router_cta = (int)blockIdx.x >= (int)gridDim.x - nroute;
-  const int GWn = GW - nroute * kFW;  // warps that take the logit slices and the shared expert's gate/up units
+  const int nrc = (int)gridDim.x - nroute;       // CTAs that do not route
+  const int GWn = nrc * kFW;                     // their warps take the logit slices and the shared expert's units
+  const int gwn = warp * nrc + blockIdx.x;       // this warp's index among them (valid when !router_cta)
   const int sh_units = sp.has_sh ? upp : 0, sh_down = sp.has_sh ? NT : 0;
 
   // ---- the outstanding ticket of the unit a warp finished last --------------------------------------------------------
@@ -353,7 +357,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   // ---- phase 1: logit slices and the shared expert's gate/up units, on disjoint warps -------------------------------------
   if (!router_cta) {
     int mine = 0;
-    for (int task = gw; task < ntask; task += GWn) {
+    for (int task = gwn; task < ntask; task += GWn) {
       logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
       ++mine;
     }
@@ -361,18 +365,19 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       __threadfence();
       __syncwarp();
       if (lane == 0) {
-        const int cta_first = blockIdx.x * kFW;
-        int nw = 0, nt = 0;
-        for (int w2 = 0; w2 < kFW; ++w2)
-          for (int task = cta_first + w2; task < ntask; task += GWn) ++nt, nw += task == cta_first + w2;
+        int nw = 0, nt = 0;  // this CTA's logit warps and slices
+        for (int w2 = 0; w2 < kFW; ++w2) {
+          const int f = w2 * nrc + (int)blockIdx.x;
+          for (int task = f; task < ntask; task += GWn) ++nt, nw += task == f;
+        }
         if (atomicAdd(&s_int[1], 1) == nw - 1) atomicAdd(&sy->cnt_lp, nt);
       }
     }
     if (sh_units) {  // shared unit u -> warp (ntask + u) mod GWn
-      const int first = ((gw - ntask % GWn) % GWn + GWn) % GWn;
+      const int first = ((gwn - ntask % GWn) % GWn + GWn) % GWn;
       up_units(first, GWn, sh_units, true);
       // and its down units (their h is the shared expert's own): unit v -> warp (ntask + sh_units + v) mod GWn
-      down_units(((gw - (ntask + sh_units) % GWn) % GWn + GWn) % GWn, GWn, sh_down, true);
+      down_units(((gwn - (ntask + sh_units) % GWn) % GWn + GWn) % GWn, GWn, sh_down, true);
     }
   } else {
     // ---- phase 2 (router CTAs): wait for the slices, route a row, the last one builds the slot table -------------------
@@ -381,9 +386,11 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     __syncthreads();
     const bool ok = s_int[2] != 0;
     __syncthreads();
+    if (stamp && lane == 0) stamp[6] = gtime();
     if (ok) {
       route_row_cta(sp.rp, p.ws.lpart + (size_t)row * p.E, KS, (size_t)kMaxRows * p.E, sp.bias, rs,
                     sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk);
+      if (stamp && lane == 0) stamp[7] = gtime();
       __threadfence();
       __syncthreads();
       if (threadIdx.x == 0) s_int[2] = p.M > 1 ? atomicAdd(&sy->cnt_rt, 1) : 0;  // one row: no ticket to take
