@@ -118,11 +118,45 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     for (int s = 0; s < NST; ++s) mbar_init(mybar + s, 1);
   if (threadIdx.x == 0) {
     mbar_init(tabbar, 1);
-    s_int[0] = 0, s_int[1] = 0, s_int[2] = 0;
+    s_int[0] = 0, s_int[1] = 0, s_int[2] = 0, s_int[3] = 0;
   }
   mbar_fence_init();
-  // ---- every CTA quantises x into its own shared memory -----------------------------------------------------------
-  for (int task = warp; task < HB * R; task += kFW) {
+  __syncthreads();
+  const uint64_t pol = policy_evict_first();
+  const int KS = (p.H + 1023) / 1024, ntask = p.E * KS;
+  const int nroute = p.M;  // the last nroute CTAs route one row each
+  const bool router_cta = (int)blockIdx.x >= (int)gridDim.x - nroute;
+  const int nrc = (int)gridDim.x - nroute;       // CTAs that do not route
+  const int GWn = nrc * kFW;                     // their warps take the logit slices and the shared expert's units
+  const int gwn = warp * nrc + blockIdx.x;       // this warp's index among them (valid when !router_cta)
+  const int sh_units = sp.has_sh ? upp : 0, sh_down = sp.has_sh ? NT : 0;
+
+  // ---- the router's logit slices first: they head the longest chain of the step -------------------------------------------
+  if (!router_cta) {
+    int mine = 0;
+    for (int task = gwn; task < ntask; task += GWn) {
+      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
+      ++mine;
+    }
+    if (mine) {  // one global add a CTA: its last logit warp reports all of the CTA's slices
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        int nw = 0, nt = 0;  // this CTA's logit warps and slices
+        for (int w2 = 0; w2 < kFW; ++w2) {
+          const int f = w2 * nrc + (int)blockIdx.x;
+          for (int task = f; task < ntask; task += GWn) ++nt, nw += task == f;
+        }
+        if (atomicAdd(&s_int[1], 1) == nw - 1) atomicAdd(&sy->cnt_lp, nt);
+      }
+    }
+  }
+  // ---- every CTA quantises x into its own shared memory (warps take (block, row) tasks as they become free) ---------------
+  for (;;) {
+    int task = 0;
+    if (lane == 0) task = atomicAdd(&s_int[3], 1);
+    task = __shfl_sync(0xffffffffu, task, 0);
+    if (task >= HB * R) break;
     const int j = task / R, r = task % R;
     float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
     if (r < p.M) {
@@ -134,15 +168,6 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   }
   __syncthreads();
   if (stamp && lane == 0) stamp[1] = gtime();
-
-  const uint64_t pol = policy_evict_first();
-  const int KS = (p.H + 1023) / 1024, ntask = p.E * KS;
-  const int nroute = p.M;  // the last nroute CTAs route one row each
-  const bool router_cta = (int)blockIdx.x >= (int)gridDim.x - nroute;
-  const int nrc = (int)gridDim.x - nroute;       // CTAs that do not route
-  const int GWn = nrc * kFW;                     // their warps take the logit slices and the shared expert's units
-  const int gwn = warp * nrc + blockIdx.x;       // this warp's index among them (valid when !router_cta)
-  const int sh_units = sp.has_sh ? upp : 0, sh_down = sp.has_sh ? NT : 0;
 
   // ---- the outstanding ticket of the unit a warp finished last --------------------------------------------------------
   int pend = 0, pend_kind = 0, pend_a = 0, pend_b = 0, pend_ticket = 0;  // kind 1: h group (slot a, group b); 2: tile a
@@ -356,23 +381,6 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
 
   // ---- phase 1: logit slices and the shared expert's gate/up units, on disjoint warps -------------------------------------
   if (!router_cta) {
-    int mine = 0;
-    for (int task = gwn; task < ntask; task += GWn) {
-      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
-      ++mine;
-    }
-    if (mine) {  // one global add a CTA: its last logit warp reports all of the CTA's slices
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) {
-        int nw = 0, nt = 0;  // this CTA's logit warps and slices
-        for (int w2 = 0; w2 < kFW; ++w2) {
-          const int f = w2 * nrc + (int)blockIdx.x;
-          for (int task = f; task < ntask; task += GWn) ++nt, nw += task == f;
-        }
-        if (atomicAdd(&s_int[1], 1) == nw - 1) atomicAdd(&sy->cnt_lp, nt);
-      }
-    }
     if (sh_units) {  // shared unit u -> warp (ntask + u) mod GWn
       const int first = ((gwn - ntask % GWn) % GWn + GWn) % GWn;
       up_units(first, GWn, sh_units, true);

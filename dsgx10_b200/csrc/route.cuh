@@ -183,6 +183,13 @@ namespace dsgx {
 // For decode widths the routing is a chain of dependent steps, so the scores are computed one thread an expert (all
 // slice loads in one round trip), and one warp then selects from shared memory with the keys in registers: no block-wide
 // barrier inside the pick loop.  Comparisons are exact and every sum keeps the order of route_row: the same bits.
+// float -> unsigned with the same order (and back); 0 is below every float
+DSGX_DEV uint32_t ord_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+DSGX_DEV float ord_float(uint32_t u) { return __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u); }
+
 struct RouteSmem {
   float key[512];
   float s[512];
@@ -239,39 +246,57 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   if (warp != 0) return;
 
   // ---- one warp selects: expert e = lane + 32 j in register j -------------------------------------------------------
-  float key[kRJ];
+  // Keys as order-preserving unsigned integers (0 = not a candidate), so a pick is two warp reductions: the largest key,
+  // then the lowest expert id that holds it.
+  const int nj = (p.E + 31) >> 5;
+  uint32_t ku[kRJ];
 #pragma unroll
-  for (int j = 0; j < kRJ; ++j) key[j] = lane + 32 * j < p.E ? sm.key[lane + 32 * j] : -INFINITY;
+  for (int j = 0; j < kRJ; ++j) ku[j] = j < nj && lane + 32 * j < p.E ? ord_key(sm.key[lane + 32 * j]) : 0u;
   if (p.n_group > 1) {
     const int gs = p.E / p.n_group;
-    float mine = -INFINITY;  // lane g < n_group: the sum of group g's two largest keys, scanned in ascending id
-    if (lane < p.n_group) {
+    uint32_t mine = 0;  // lane g < n_group: the ordered sum of group g's two largest keys
+    if ((gs & 31) == 0) {
+      // a group is gs / 32 whole registers of every lane
+      const int rg = gs >> 5;
+      for (int g = 0; g < p.n_group; ++g) {
+        uint32_t lm = 0;
+#pragma unroll
+        for (int j = 0; j < kRJ; ++j)
+          if (j >= g * rg && j < (g + 1) * rg) lm = max(lm, ku[j]);
+        const uint32_t m1 = __reduce_max_sync(0xffffffffu, lm);
+        const uint32_t holder = __reduce_min_sync(0xffffffffu, lm == m1 ? (uint32_t)lane : 32u);
+        uint32_t second = 0;  // the largest key left once one instance of m1 is taken out
+        bool taken = lane != (int)holder;
+#pragma unroll
+        for (int j = 0; j < kRJ; ++j)
+          if (j >= g * rg && j < (g + 1) * rg) {
+            if (!taken && ku[j] == m1) taken = true;
+            else second = max(second, ku[j]);
+          }
+        const uint32_t m2 = __reduce_max_sync(0xffffffffu, second);
+        if (lane == g) mine = ord_key(__fadd_rn(ord_float(m1), ord_float(m2)));
+      }
+    } else if (lane < p.n_group) {
       float a = -INFINITY, c = -INFINITY;
       for (int i = lane * gs; i < (lane + 1) * gs; ++i) {
         const float v = sm.key[i];
         if (v > a) c = a, a = v;
         else if (v > c) c = v;
       }
-      mine = __fadd_rn(a, c);
+      mine = ord_key(__fadd_rn(a, c));
     }
     uint32_t keep = 0;
     for (int t = 0; t < p.topk_group; ++t) {
-      float bv = lane < p.n_group && !((keep >> lane) & 1) ? mine : -INFINITY;
-      int bg = lane < p.n_group && !((keep >> lane) & 1) ? lane : 1 << 30;
-      if (bv != bv) bv = -INFINITY;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
-        if (og < (1 << 30) && (bg == (1 << 30) || ov > bv || (ov == bv && og < bg))) bv = ov, bg = og;
-      }
-      if (bg < 32) keep |= 1u << bg;
+      const bool cand = lane < p.n_group && !((keep >> lane) & 1);
+      const uint32_t m = __reduce_max_sync(0xffffffffu, cand ? mine : 0u);
+      const uint32_t gsel = __reduce_min_sync(0xffffffffu, cand && mine == m ? (uint32_t)lane : 32u);
+      if (gsel < 32) keep |= 1u << gsel;
     }
     const uint32_t inv = ((1u << 20) + gs - 1) / gs;  // e / gs == (e * inv) >> 20 for e < 512
 #pragma unroll
     for (int j = 0; j < kRJ; ++j) {
       const uint32_t ee = lane + 32 * j;
-      if (ee < (uint32_t)p.E && !((keep >> ((ee * inv) >> 20)) & 1)) key[j] = -INFINITY;
+      if (j < nj && !((keep >> ((ee * inv) >> 20)) & 1)) ku[j] = 0u;
     }
   }
   float picked[8];
@@ -280,23 +305,21 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   for (int k = 0; k < 8; ++k) {
     picked[k] = 0.f, ids[k] = 0;
     if (k < p.topk) {
-      float bv = -INFINITY;
-      int bj = 0;
+      uint32_t lm = 0;
 #pragma unroll
       for (int j = 0; j < kRJ; ++j)
-        if (key[j] > bv) bv = key[j], bj = j;
-      int be = bv == -INFINITY ? 1 << 30 : lane + 32 * bj;
+        if (j < nj) lm = max(lm, ku[j]);
+      const uint32_t m = __reduce_max_sync(0xffffffffu, lm);
+      uint32_t cand = 1u << 30;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-        if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
-      }
-      if (be == 1 << 30) be = 0;
-      ids[k] = be;
+      for (int j = kRJ - 1; j >= 0; --j)
+        if (j < nj && ku[j] == m) cand = lane + 32 * j;
+      uint32_t be = __reduce_min_sync(0xffffffffu, m ? cand : (1u << 30));
+      if (be == 1u << 30) be = 0;
+      ids[k] = (int)be;
 #pragma unroll
       for (int j = 0; j < kRJ; ++j)
-        if (lane + 32 * j == be) key[j] = -INFINITY;
+        if (j < nj && lane + 32 * j == (int)be) ku[j] = 0u;
       picked[k] = sm.s[be];
     }
   }
