@@ -40,12 +40,15 @@ DSGX_DEV bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait on a phase; false when the limit ran out.
-DSGX_DEV bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait on a phase; false when the limit ran out.  sleep_ns > 0: back off between tries (for waits that are
+// expected to be long, so that the waiting warps leave the issue slots to the warps that work).
+DSGX_DEV bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity))
+  while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (clock64() - t0 > kWaitCycles) return false;
+  }
   return true;
 }
 // global -> shared bulk copy (the untiled TMA path): both addresses 16-byte aligned, bytes a multiple of 16.

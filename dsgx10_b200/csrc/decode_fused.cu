@@ -48,7 +48,7 @@ DSGX_DEV bool poll_ge(const int* p, int target) {
   if (ld_acquire(p) >= target) return true;
   const long long t0 = clock64();
   while (ld_acquire(p) < target) {
-    __nanosleep(40);
+    __nanosleep(128);
     if (clock64() - t0 > kWaitCycles) return false;
   }
   return true;
@@ -244,17 +244,22 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     const int cpu = HB / KCH;
     const size_t strip = (size_t)8 * p.H;
     int pu = first, pc = 0;
+    const uint8_t *pgp = nullptr, *pup = nullptr;  // the producer's place in the unit's two strips
+    uint32_t pst = issued % NST;                   // and its stage
     auto issue = [&]() {
-      const int s = shared ? -1 : pu / upp, i8 = pu % upp;
-      const uint8_t* gp = shared ? p.sh.g : tab.ent[s].g;
-      const uint8_t* up = shared ? p.sh.u : tab.ent[s].u;
-      const size_t off = (size_t)i8 * strip + (size_t)pc * KCH * 1024;
-      uint8_t* st = myring + (size_t)(issued % NST) * stage;
-      uint64_t* bar = mybar + issued % NST;
+      if (pc == 0) {
+        const int s = shared ? -1 : pu / upp, i8 = pu % upp;
+        pgp = (shared ? p.sh.g : tab.ent[s].g) + (size_t)i8 * strip;
+        pup = (shared ? p.sh.u : tab.ent[s].u) + (size_t)i8 * strip;
+      }
+      uint8_t* st = myring + (size_t)pst * stage;
+      uint64_t* bar = mybar + pst;
       mbar_expect_tx(bar, 2 * KCH * 1024);
-      bulk_g2s_hint(st, gp + off, KCH * 1024, bar, pol);
-      bulk_g2s_hint(st + KCH * 1024, up + off, KCH * 1024, bar, pol);
+      bulk_g2s_hint(st, pgp, KCH * 1024, bar, pol);
+      bulk_g2s_hint(st + KCH * 1024, pup, KCH * 1024, bar, pol);
+      pgp += KCH * 1024, pup += KCH * 1024;
       ++issued;
+      if (++pst == NST) pst = 0;
       if (++pc == cpu) pc = 0, pu += stride;
     };
     if (lane == 0)
@@ -314,25 +319,31 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     const int cpu = IB / KCH;
     const size_t strip = (size_t)8 * p.I;
     const uint32_t stage_bytes = 2 * KCH * 1024 + KCH * CB;
-    int pu = first, pc = 0, ready_slot = -1;
+    int pu = first, pc = 0, ready_slot = -1, pslot = 0;
     bool poll_failed = false;
+    const uint8_t *pdp = nullptr, *php = nullptr;  // the producer's place in the unit's two strips and in the slot's h
+    uint32_t pst = issued % NST;
     auto issue = [&]() {
-      const int slot = shared ? sp.sh_slot : pu / NT, n16 = pu % NT;  // the slot's index in the workspace
-      const uint8_t* dp = shared ? p.sh.d : tab.ent[slot].d;
-      const size_t off = (size_t)(2 * n16) * strip + (size_t)pc * KCH * 1024;
-      uint8_t* st = myring + (size_t)(issued % NST) * stage;
-      uint64_t* bar = mybar + issued % NST;
+      if (pc == 0) {
+        pslot = shared ? sp.sh_slot : pu / NT;  // the slot's index in the workspace
+        const int n16 = pu % NT;
+        pdp = (shared ? p.sh.d : tab.ent[pslot].d) + (size_t)(2 * n16) * strip;
+        php = p.ws.hq + (size_t)pslot * IB * CB;
+      }
+      uint8_t* st = myring + (size_t)pst * stage;
+      uint64_t* bar = mybar + pst;
       mbar_expect_tx(bar, stage_bytes);
-      bulk_g2s_hint(st, dp + off, KCH * 1024, bar, pol);
-      bulk_g2s_hint(st + KCH * 1024, dp + off + strip, KCH * 1024, bar, pol);
-      if (ready_slot != slot && !poll_failed) {
-        if (poll_ge(&sy->cnt_hq[slot], IB)) ready_slot = slot;
+      bulk_g2s_hint(st, pdp, KCH * 1024, bar, pol);
+      bulk_g2s_hint(st + KCH * 1024, pdp + strip, KCH * 1024, bar, pol);
+      if (ready_slot != pslot && !poll_failed) {
+        if (poll_ge(&sy->cnt_hq[pslot], IB)) ready_slot = pslot;
         else poll_failed = true;
         asm volatile("fence.proxy.async;" ::: "memory");  // the bulk copy below reads what other SMs' stores wrote
       }
-      if (!poll_failed)
-        bulk_g2s(st + 2 * KCH * 1024, p.ws.hq + ((size_t)slot * IB + (size_t)pc * KCH) * CB, KCH * CB, bar);
+      if (!poll_failed) bulk_g2s(st + 2 * KCH * 1024, php, KCH * CB, bar);
+      pdp += KCH * 1024, php += KCH * CB;
       ++issued;
+      if (++pst == NST) pst = 0;
       if (++pc == cpu) pc = 0, pu += stride;
     };
     if (lane == 0)
@@ -397,7 +408,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     if (stamp && lane == 0) stamp[6] = gtime();
     if (ok) {
       route_row_cta(sp.rp, p.ws.lpart + (size_t)row * p.E, KS, (size_t)kMaxRows * p.E, sp.bias, rs,
-                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk);
+                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk,
+                    sp.stamps ? sp.stamps + (size_t)GW * 8 + row * 8 : nullptr);
       if (stamp && lane == 0) stamp[7] = gtime();
       __threadfence();
       __syncthreads();
@@ -441,7 +453,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tabbar)) : "memory");
       }
     }
-    if (!mbar_wait(tabbar, 0)) dead = true;
+    if (!mbar_wait(tabbar, 0, 256)) dead = true;
     tab_loaded = !dead;
   }
 

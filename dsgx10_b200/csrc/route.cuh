@@ -194,12 +194,23 @@ struct RouteSmem {
   float key[512];
   float s[512];
   float red[16];
+  float gsc[32];
   float S;
+  uint32_t keep;
 };
 
 DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
-                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out) {
+                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out,
+                            unsigned long long* dbg = nullptr) {
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5, nW = blockDim.x >> 5;
+  auto mark = [&](int i) {
+    if (dbg && threadIdx.x == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      dbg[i] = t;
+    }
+  };
+  mark(0);
   const bool valid = e < p.E;
   float lg = -INFINITY, b = 0.f;
   if (valid) {
@@ -240,107 +251,96 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     s = __fdiv_rn(t, sm.S);
     __syncthreads();
   }
+  mark(1);
+  // keys as order-preserving unsigned integers in shared memory (0 = not a candidate)
+  uint32_t* ku = reinterpret_cast<uint32_t*>(sm.key);
   sm.s[e] = s;
-  sm.key[e] = valid ? __fadd_rn(s, b) : -INFINITY;
+  __syncthreads();  // (softmax read sm.key above)
+  ku[e] = valid ? ord_key(__fadd_rn(s, b)) : 0u;
   __syncthreads();
-  if (warp != 0) return;
-
-  // ---- one warp selects: expert e = lane + 32 j in register j -------------------------------------------------------
-  // Keys as order-preserving unsigned integers (0 = not a candidate), so a pick is two warp reductions: the largest key,
-  // then the lowest expert id that holds it.
-  const int nj = (p.E + 31) >> 5;
-  uint32_t ku[kRJ];
-#pragma unroll
-  for (int j = 0; j < kRJ; ++j) ku[j] = j < nj && lane + 32 * j < p.E ? ord_key(sm.key[lane + 32 * j]) : 0u;
+  mark(2);
+  // ---- selection, all warps: group scores one warp a group, then every candidate ranks itself --------------------------
+  float* picked = sm.red;  // [8] scores of the picks (sm.red is free by now)
+  int* ids = reinterpret_cast<int*>(sm.red + 8);
   if (p.n_group > 1) {
     const int gs = p.E / p.n_group;
-    uint32_t mine = 0;  // lane g < n_group: the ordered sum of group g's two largest keys
-    if ((gs & 31) == 0) {
-      // a group is gs / 32 whole registers of every lane
-      const int rg = gs >> 5;
-      for (int g = 0; g < p.n_group; ++g) {
-        uint32_t lm = 0;
-#pragma unroll
-        for (int j = 0; j < kRJ; ++j)
-          if (j >= g * rg && j < (g + 1) * rg) lm = max(lm, ku[j]);
-        const uint32_t m1 = __reduce_max_sync(0xffffffffu, lm);
-        const uint32_t holder = __reduce_min_sync(0xffffffffu, lm == m1 ? (uint32_t)lane : 32u);
-        uint32_t second = 0;  // the largest key left once one instance of m1 is taken out
-        bool taken = lane != (int)holder;
-#pragma unroll
-        for (int j = 0; j < kRJ; ++j)
-          if (j >= g * rg && j < (g + 1) * rg) {
-            if (!taken && ku[j] == m1) taken = true;
-            else second = max(second, ku[j]);
-          }
-        const uint32_t m2 = __reduce_max_sync(0xffffffffu, second);
-        if (lane == g) mine = ord_key(__fadd_rn(ord_float(m1), ord_float(m2)));
-      }
-    } else if (lane < p.n_group) {
-      float a = -INFINITY, c = -INFINITY;
-      for (int i = lane * gs; i < (lane + 1) * gs; ++i) {
-        const float v = sm.key[i];
-        if (v > a) c = a, a = v;
-        else if (v > c) c = v;
-      }
-      mine = ord_key(__fadd_rn(a, c));
-    }
-    uint32_t keep = 0;
-    for (int t = 0; t < p.topk_group; ++t) {
-      const bool cand = lane < p.n_group && !((keep >> lane) & 1);
-      const uint32_t m = __reduce_max_sync(0xffffffffu, cand ? mine : 0u);
-      const uint32_t gsel = __reduce_min_sync(0xffffffffu, cand && mine == m ? (uint32_t)lane : 32u);
-      if (gsel < 32) keep |= 1u << gsel;
-    }
-    const uint32_t inv = ((1u << 20) + gs - 1) / gs;  // e / gs == (e * inv) >> 20 for e < 512
-#pragma unroll
-    for (int j = 0; j < kRJ; ++j) {
-      const uint32_t ee = lane + 32 * j;
-      if (j < nj && !((keep >> ((ee * inv) >> 20)) & 1)) ku[j] = 0u;
-    }
-  }
-  float picked[8];
-  int ids[8];
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    picked[k] = 0.f, ids[k] = 0;
-    if (k < p.topk) {
+    uint32_t* gsc = reinterpret_cast<uint32_t*>(sm.gsc);
+#pragma unroll 1
+    for (int g = warp; g < p.n_group; g += nW) {  // the ordered sum of the group's two largest keys
       uint32_t lm = 0;
-#pragma unroll
-      for (int j = 0; j < kRJ; ++j)
-        if (j < nj) lm = max(lm, ku[j]);
-      const uint32_t m = __reduce_max_sync(0xffffffffu, lm);
-      uint32_t cand = 1u << 30;
-#pragma unroll
-      for (int j = kRJ - 1; j >= 0; --j)
-        if (j < nj && ku[j] == m) cand = lane + 32 * j;
-      uint32_t be = __reduce_min_sync(0xffffffffu, m ? cand : (1u << 30));
-      if (be == 1u << 30) be = 0;
-      ids[k] = (int)be;
-#pragma unroll
-      for (int j = 0; j < kRJ; ++j)
-        if (j < nj && lane + 32 * j == (int)be) ku[j] = 0u;
-      picked[k] = sm.s[be];
+#pragma unroll 1
+      for (int i = g * gs + lane; i < (g + 1) * gs; i += 32) lm = max(lm, ku[i]);
+      const uint32_t m1 = __reduce_max_sync(0xffffffffu, lm);
+      const uint32_t holder = __reduce_min_sync(0xffffffffu, lm == m1 ? (uint32_t)lane : 32u);
+      uint32_t second = 0;  // the largest key left once one instance of m1 is taken out
+      bool taken = lane != (int)holder;
+#pragma unroll 1
+      for (int i = g * gs + lane; i < (g + 1) * gs; i += 32) {
+        const uint32_t v = ku[i];
+        if (!taken && v == m1) taken = true;
+        else second = max(second, v);
+      }
+      const uint32_t m2 = __reduce_max_sync(0xffffffffu, second);
+      if (lane == 0) gsc[g] = ord_key(__fadd_rn(ord_float(m1), ord_float(m2)));
+    }
+    __syncthreads();
+    if (warp == 0) {  // keep the topk_group best groups, ties to the lower id
+      const uint32_t mine = lane < p.n_group ? gsc[lane] : 0u;
+      uint32_t keep = 0;
+#pragma unroll 1
+      for (int t = 0; t < p.topk_group; ++t) {
+        const bool cand = lane < p.n_group && !((keep >> lane) & 1);
+        const uint32_t m = __reduce_max_sync(0xffffffffu, cand ? mine : 0u);
+        const uint32_t gsel = __reduce_min_sync(0xffffffffu, cand && mine == m ? (uint32_t)lane : 32u);
+        if (gsel < 32) keep |= 1u << gsel;
+      }
+      if (lane == 0) sm.keep = keep;
+    }
+    __syncthreads();
+    if (valid && !((sm.keep >> (e / gs)) & 1)) ku[e] = 0u;
+    __syncthreads();
+  }
+  mark(3);
+  // rank of a candidate = keys above it + equal keys with a lower id; ranks 0 .. topk-1 are the picks in order
+  if (valid) {
+    const uint32_t mine = ku[e];
+    if (mine) {
+      int rank = 0;
+#pragma unroll 4
+      for (int i = 0; i < p.E; ++i) {
+        const uint32_t v = ku[i];
+        rank += (v > mine) || (v == mine && i < e);
+      }
+      if (rank < p.topk) ids[rank] = e, picked[rank] = s;
     }
   }
+  __syncthreads();
+  if (warp != 0) return;
+  mark(4);
+  // the sum of the picked scores: four running sums at stride 4, then (t0 + t2) + (t1 + t3)
   float t[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) t[j] = j < p.topk ? picked[j] : 0.f;
-#pragma unroll
-  for (int i = 4; i < 8; ++i)
-    if (i < p.topk) t[i & 3] = __fadd_rn(t[i & 3], picked[i]);
+#pragma unroll 1
+  for (int i = 4; i < p.topk; ++i) {
+    const float v = picked[i];
+    if ((i & 3) == 0) t[0] = __fadd_rn(t[0], v);
+    else if ((i & 3) == 1) t[1] = __fadd_rn(t[1], v);
+    else if ((i & 3) == 2) t[2] = __fadd_rn(t[2], v);
+    else t[3] = __fadd_rn(t[3], v);
+  }
   float sum;
   if (p.topk <= 1) sum = t[0];
   else if (p.topk == 2) sum = __fadd_rn(t[0], t[1]);
   else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
   else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
   sum = __fadd_rn(sum, 1e-20f);
-#pragma unroll
-  for (int k = 0; k < 8; ++k)
-    if (k < p.topk && lane == k) {
-      idx_out[k] = ids[k];
-      w_out[k] = p.norm_topk ? __fmul_rn(__fdiv_rn(picked[k], sum), p.route_scale) : __fmul_rn(picked[k], p.route_scale);
-    }
+  mark(5);
+  if (lane < p.topk) {
+    const float pk = picked[lane];
+    idx_out[lane] = ids[lane];
+    w_out[lane] = p.norm_topk ? __fmul_rn(__fdiv_rn(pk, sum), p.route_scale) : __fmul_rn(pk, p.route_scale);
+  }
 }
 
 }  // namespace dsgx
