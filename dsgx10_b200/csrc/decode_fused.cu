@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   // ---- the outstanding ticket of the unit a warp finished last --------------------------------------------------------
   int pend = 0, pend_kind = 0, pend_a = 0, pend_b = 0, pend_ticket = 0;  // kind 1: h group (slot a, group b); 2: tile a
   bool tab_loaded = false;
+  long long cyc_wait = 0, cyc_mma = 0, cyc_issue = 0;  // profiling aid: where a warp's gate/up chunk loop spends its cycles
   auto advance = [&]() {
     if (pend == 1) {
       __threadfence();
@@ -275,10 +276,12 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
       for (int c = 0; c < cpu; ++c) {
         const uint32_t sidx = consumed % NST;
+        const long long tq0 = stamp ? clock64() : 0;
         if (!mbar_wait(mybar + sidx, (consumed / NST) & 1)) {
           dead = true;
           break;
         }
+        const long long tq1 = stamp ? clock64() : 0;
         const uint8_t* st = myring + (size_t)sidx * stage;
 #pragma unroll
         for (int b = 0; b < KCH; ++b) {
@@ -294,8 +297,10 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         }
         ++consumed;
         __syncwarp();
+        const long long tq2 = stamp ? clock64() : 0;
         if (lane == 0 && pu < total) issue();
         advance();
+        if (stamp) cyc_wait += tq1 - tq0, cyc_mma += tq2 - tq1, cyc_issue += clock64() - tq2;
       }
       if (dead) break;
       while (pend) advance();
@@ -411,14 +416,22 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
                     sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk,
                     sp.stamps ? sp.stamps + (size_t)GW * 8 + row * 8 : nullptr);
       if (stamp && lane == 0) stamp[7] = gtime();
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) s_int[2] = p.M > 1 ? atomicAdd(&sy->cnt_rt, 1) : 0;  // one row: no ticket to take
-      __syncthreads();
-      if (s_int[2] == p.M - 1) {
+      bool last = true;
+      if (p.M > 1) {  // the last row to be routed builds the table
         __threadfence();
-        for (int i = threadIdx.x; i < p.M * p.topk; i += kFThreads) s_idx[i] = __ldcg(sp.idx + i), s_w[i] = __ldcg(sp.w + i);
         __syncthreads();
+        if (threadIdx.x == 0) s_int[2] = atomicAdd(&sy->cnt_rt, 1);
+        __syncthreads();
+        last = s_int[2] == p.M - 1;
+        if (last) {
+          __threadfence();
+          for (int i = threadIdx.x; i < p.M * p.topk; i += kFThreads) s_idx[i] = __ldcg(sp.idx + i), s_w[i] = __ldcg(sp.w + i);
+        }
+      } else if ((int)threadIdx.x < p.topk) {  // one row: the threads that wrote the picks hand them over
+        s_idx[threadIdx.x] = sp.idx[threadIdx.x], s_w[threadIdx.x] = sp.w[threadIdx.x];
+      }
+      __syncthreads();
+      if (last) {
         build_slot_tab(tab, s_bm, s_idx, s_w, p.M, p.topk, p.E, p.e_lo, p.e_hi, p.pool, p.desc, p.sh, DSGX_FMT_FP8);
         if (threadIdx.x == 0 && tab.bad) atomicCAS(p.ws.status, 0, tab.bad);
         {
@@ -465,6 +478,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   }
 
   if (stamp && lane == 0) stamp[4] = gtime();
+  if (stamp && lane == 0 && !router_cta) stamp[6] = (unsigned long long)cyc_wait << 32 | (unsigned long long)(cyc_mma & 0xffffffffll), stamp[7] = (unsigned long long)cyc_issue;
   // ---- phase 5: the routed slots' down units ------------------------------------------------------------------------------
   if (!dead && tab.ntot == 0) {
     for (size_t i = (size_t)blockIdx.x * kFThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kFThreads) {

@@ -12,6 +12,8 @@ namespace dsgx {
 // One warp computes rows [r0, r0 + 8) x experts [e0, e0 + ET).  Order of every sum (what the CPU oracle restates): K in
 // slices of 1024; in a slice lane j accumulates k = base + 128 i + 4 j + c (i ascending, c = 0..3) by fma from zero;
 // the 32 lane sums are combined by the xor butterfly; slice sums are added in ascending order.
+// The running total of output o = r * ET + j lives in lane o % 32 only (register o / 32), so a wide tile costs two
+// registers of totals, not 8 * ET.
 template <int ET>
 __global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr,
                                                        int M, int H, int E, float* __restrict__ logits) {
@@ -24,11 +26,10 @@ __global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __re
   const int r0 = rt * 8, e0 = et * ET;
   if (r0 >= M) return;
   const int nr = min(8, M - r0);
-  float total[8][ET];
+  constexpr int NO = 8 * ET, NTOT = (NO + 31) / 32;
+  float total[NTOT];
 #pragma unroll
-  for (int r = 0; r < 8; ++r)
-#pragma unroll
-    for (int j = 0; j < ET; ++j) total[r][j] = 0.f;
+  for (int i = 0; i < NTOT; ++i) total[i] = 0.f;
   for (int base = 0; base < H; base += 1024) {
     const int nit = min(1024, H - base) / 128;
     float acc[8][ET];
@@ -36,7 +37,7 @@ __global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __re
     for (int r = 0; r < 8; ++r)
 #pragma unroll
       for (int j = 0; j < ET; ++j) acc[r][j] = 0.f;
-#pragma unroll 2
+#pragma unroll 1
     for (int i = 0; i < nit; ++i) {
       const int k = base + 128 * i + 4 * lane;
       float4 wv[ET];
@@ -66,16 +67,19 @@ __global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __re
 #pragma unroll
       for (int j = 0; j < ET; ++j) {
         const float s = warp_sum(acc[r][j]);
-        total[r][j] = base ? __fadd_rn(total[r][j], s) : s;
+        constexpr int dummy = 0;
+        (void)dummy;
+        const int o = r * ET + j;
+        if (lane == (o & 31)) total[o >> 5] = base ? __fadd_rn(total[o >> 5], s) : s;
       }
   }
-  if (lane == 0) {
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
+  for (int r = 0; r < 8; ++r)
 #pragma unroll
-      for (int j = 0; j < ET; ++j)
-        if (r < nr && e0 + j < E) logits[(size_t)(r0 + r) * E + e0 + j] = total[r][j];
-  }
+    for (int j = 0; j < ET; ++j) {
+      const int o = r * ET + j;
+      if (lane == (o & 31) && r < nr && e0 + j < E) logits[(size_t)(r0 + r) * E + e0 + j] = total[o >> 5];
+    }
 }
 
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* wr, int M, int H, int E, float* logits,
@@ -85,8 +89,8 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* wr, int M,
     const int warps = rts * E;
     return launch_k(k_router_logits<1>, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, wr, M, H, E, logits);
   }
-  const int warps = rts * ((E + 3) / 4);
-  return launch_k(k_router_logits<4>, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, wr, M, H, E, logits);
+  const int warps = rts * ((E + 7) / 8);
+  return launch_k(k_router_logits<8>, dim3((warps + 7) / 8), dim3(256), 0, st, pdl, x, wr, M, H, E, logits);
 }
 
 // ------------------------------------------------------------------------------------------------------------ route

@@ -205,3 +205,44 @@ class Int4Layer:
 
     def shared_bytes(self):
         return 3 * self.I * self.H * 2
+
+
+# ------------------------------------------------------------------------------------------- Zipf-skewed routing bias
+
+def zipf_target_shares(E, topk, s=1.1):
+    """Pick shares of E experts under Zipf(s), with no expert above 1 / topk of the picks (a token picks an expert at
+    most once): the excess of the capped experts is spread over the others in proportion (water-filling)."""
+    p = 1.0 / np.arange(1, E + 1) ** s
+    p /= p.sum()
+    cap = 1.0 / topk
+    for _ in range(E):
+        over = p > cap
+        if not over.any():
+            break
+        excess = (p[over] - cap).sum()
+        p[over] = cap
+        p[~over] += excess * p[~over] / p[~over].sum()
+    return p
+
+
+def zipf_bias(E, alpha, seed, s=1.1):
+    """Selection bias b_e = alpha * ln(p_e / p_max) over a seeded permutation of the experts, p_e ~ rank^-s."""
+    p = 1.0 / np.arange(1, E + 1) ** s
+    perm = np.random.default_rng(seed).permutation(E)
+    b = np.empty(E, np.float32)
+    b[perm] = (alpha * np.log(p / p.max())).astype(np.float32)
+    return b
+
+
+def calibrate_zipf_bias(route_counts, E, topk, seed, s=1.1, alphas=None):
+    """route_counts(bias np.float32 [E]) -> pick counts [E].  Returns (alpha, bias, counts) whose sorted pick shares are
+    closest (least squares) to zipf_target_shares: the realised histogram of a benchmark's routing follows Zipf(s)."""
+    target = np.sort(zipf_target_shares(E, topk, s))[::-1]
+    best = None
+    for a in (alphas if alphas is not None else [0.005, 0.01, 0.015, 0.02, 0.03, 0.04, 0.06, 0.08, 0.12, 0.16, 0.24]):
+        b = zipf_bias(E, a, seed, s)
+        c = np.asarray(route_counts(b), np.float64)
+        err = float(((np.sort(c / c.sum())[::-1] - target) ** 2).sum())
+        if best is None or err < best[0]:
+            best = (err, a, b, c)
+    return best[1], best[2], best[3]
