@@ -172,7 +172,6 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   // ---- the outstanding ticket of the unit a warp finished last --------------------------------------------------------
   int pend = 0, pend_kind = 0, pend_a = 0, pend_b = 0, pend_ticket = 0;  // kind 1: h group (slot a, group b); 2: tile a
   bool tab_loaded = false;
-  long long cyc_wait = 0, cyc_mma = 0, cyc_issue = 0;  // profiling aid: where a warp's gate/up chunk loop spends its cycles
   auto advance = [&]() {
     if (pend == 1) {
       __threadfence();
@@ -240,16 +239,29 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     }
   };
 
-  // ---- gate/up units: unit u = first, first + stride, .. < total; routed: slot u / upp; shared: the shared expert ------
-  auto up_units = [&](int first, int stride, int total, bool shared) {
+  // ---- a warp's sequence of units: static (first, first + stride, ..) or claimed one by one from a global queue ----------
+  // (dynamic: a warp that is late takes fewer units; the claim of the unit after next is in flight while a unit streams)
+  auto claim = [&](int* q, int prev, int stride) {
+    if (!q) return prev + stride;
+    int v = 0;
+    if (lane == 0) v = atomicAdd(q, 1);
+    return v;  // lane 0 only
+  };
+
+  // ---- gate/up units.  routed: unit u = slot u / upp, strip u % upp; shared: the shared expert's strips ------------------
+  auto up_units = [&](int first, int stride, int total, bool shared, int* q) {
     const int cpu = HB / KCH;
     const size_t strip = (size_t)8 * p.H;
-    int pu = first, pc = 0;
-    const uint8_t *pgp = nullptr, *pup = nullptr;  // the producer's place in the unit's two strips
-    uint32_t pst = issued % NST;                   // and its stage
+    int u_cur = q ? __shfl_sync(0xffffffffu, claim(q, 0, 0), 0) : first;
+    int u_next = claim(q, u_cur, stride);  // dynamic: known to lane 0 only
+    int p_on = 0, pc = 0;                  // producer (lane 0): on u_cur (0), on u_next (1), waiting for the consumer (2)
+    const uint8_t *pgp = nullptr, *pup = nullptr;
+    uint32_t pst = issued % NST;
+    auto can_issue = [&]() { return p_on < 2 && (p_on ? u_next : u_cur) < total && issued - consumed < (uint32_t)NST; };
     auto issue = [&]() {
       if (pc == 0) {
-        const int s = shared ? -1 : pu / upp, i8 = pu % upp;
+        const int u = p_on ? u_next : u_cur;
+        const int s = shared ? -1 : u / upp, i8 = u % upp;
         pgp = (shared ? p.sh.g : tab.ent[s].g) + (size_t)i8 * strip;
         pup = (shared ? p.sh.u : tab.ent[s].u) + (size_t)i8 * strip;
       }
@@ -261,12 +273,12 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       pgp += KCH * 1024, pup += KCH * 1024;
       ++issued;
       if (++pst == NST) pst = 0;
-      if (++pc == cpu) pc = 0, pu += stride;
+      if (++pc == cpu) pc = 0, ++p_on;
     };
     if (lane == 0)
-      for (int s = 0; s < NST && pu < total; ++s) issue();
-    for (int unit = first; unit < total && !dead; unit += stride) {
-      const int s = shared ? -1 : unit / upp, i8 = unit % upp;
+      while (can_issue()) issue();
+    while (u_cur < total && !dead) {
+      const int s = shared ? -1 : u_cur / upp, i8 = u_cur % upp;
       const int wslot = shared ? sp.sh_slot : s;  // where this unit's h lives in the workspace
       const int srow = (i8 * 8) / 128;
       const float* sgp = shared ? p.sh.gs : tab.ent[s].sg;
@@ -276,12 +288,10 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
       for (int c = 0; c < cpu; ++c) {
         const uint32_t sidx = consumed % NST;
-        const long long tq0 = stamp ? clock64() : 0;
         if (!mbar_wait(mybar + sidx, (consumed / NST) & 1)) {
           dead = true;
           break;
         }
-        const long long tq1 = stamp ? clock64() : 0;
         const uint8_t* st = myring + (size_t)sidx * stage;
 #pragma unroll
         for (int b = 0; b < KCH; ++b) {
@@ -297,10 +307,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         }
         ++consumed;
         __syncwarp();
-        const long long tq2 = stamp ? clock64() : 0;
-        if (lane == 0 && pu < total) issue();
+        if (lane == 0 && can_issue()) issue();
         advance();
-        if (stamp) cyc_wait += tq1 - tq0, cyc_mma += tq2 - tq1, cyc_issue += clock64() - tq2;
       }
       if (dead) break;
       while (pend) advance();
@@ -312,27 +320,38 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
       if (r1 < p.M) hrow[(size_t)r1 * p.I + ch] = __float2bfloat16_rn(h1);
       pend = 1, pend_kind = 1, pend_a = wslot, pend_b = i8 / 16;
+      // on to the next unit of the sequence
+      u_cur = q ? __shfl_sync(0xffffffffu, u_next, 0) : u_next;
+      u_next = claim(q, u_cur, stride);
+      if (lane == 0) {
+        --p_on;
+        while (can_issue()) issue();
+      }
     }
     if (!dead)
       while (pend) advance();
   };
 
-  // ---- down units (slot, 16 output channels): unit v = first, first + stride, .. < total ---------------------------------
-  // shared: the shared expert's units (before the routing is known: its weights and its h need no table); else routed
-  // slot v / NT.  A unit's weight copies go out first; the copy of h waits for the slot's 128-groups to be quantised.
-  auto down_units = [&](int first, int stride, int total, bool shared) {
+  // ---- down units (slot, 16 output channels).  Unit v < sh_down: the shared expert's tile v; else routed slot
+  // (v - sh_down) / NT.  A unit's weight copies go out first; the copy of h waits for the slot's 128-groups. ---------------
+  auto down_units = [&](int first, int stride, int total, int* q) {
     const int cpu = IB / KCH;
     const size_t strip = (size_t)8 * p.I;
     const uint32_t stage_bytes = 2 * KCH * 1024 + KCH * CB;
-    int pu = first, pc = 0, ready_slot = -1, pslot = 0;
+    int u_cur = q ? __shfl_sync(0xffffffffu, claim(q, 0, 0), 0) : first;
+    int u_next = claim(q, u_cur, stride);
+    int p_on = 0, pc = 0, ready_slot = -1, pslot = 0;
     bool poll_failed = false;
-    const uint8_t *pdp = nullptr, *php = nullptr;  // the producer's place in the unit's two strips and in the slot's h
+    const uint8_t *pdp = nullptr, *php = nullptr;
     uint32_t pst = issued % NST;
+    auto can_issue = [&]() { return p_on < 2 && (p_on ? u_next : u_cur) < total && issued - consumed < (uint32_t)NST; };
     auto issue = [&]() {
       if (pc == 0) {
-        pslot = shared ? sp.sh_slot : pu / NT;  // the slot's index in the workspace
-        const int n16 = pu % NT;
-        pdp = (shared ? p.sh.d : tab.ent[pslot].d) + (size_t)(2 * n16) * strip;
+        const int v = p_on ? u_next : u_cur;
+        const bool sh = v < sh_down;
+        pslot = sh ? sp.sh_slot : (v - sh_down) / NT;  // the slot's index in the workspace
+        const int n16 = sh ? v : (v - sh_down) % NT;
+        pdp = (sh ? p.sh.d : tab.ent[pslot].d) + (size_t)(2 * n16) * strip;
         php = p.ws.hq + (size_t)pslot * IB * CB;
       }
       uint8_t* st = myring + (size_t)pst * stage;
@@ -349,14 +368,15 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       pdp += KCH * 1024, php += KCH * CB;
       ++issued;
       if (++pst == NST) pst = 0;
-      if (++pc == cpu) pc = 0, pu += stride;
+      if (++pc == cpu) pc = 0, ++p_on;
     };
     if (lane == 0)
-      for (int s = 0; s < NST && pu < total; ++s) issue();
-    for (int unit = first; unit < total && !dead; unit += stride) {
-      const int slot = shared ? sp.sh_slot : unit / NT, n16 = unit % NT;
+      while (can_issue()) issue();
+    while (u_cur < total && !dead) {
+      const bool sh = u_cur < sh_down;
+      const int slot = sh ? sp.sh_slot : (u_cur - sh_down) / NT, n16 = sh ? u_cur : (u_cur - sh_down) % NT;
       const int srow = (n16 * 16) / 128;
-      const float* sdp = shared ? p.sh.ds : tab.ent[slot].sd;
+      const float* sdp = sh ? p.sh.ds : tab.ent[slot].sd;
       const float sdl = lane < IB ? __ldg(sdp + (size_t)srow * IB + lane) : 0.f;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       for (int c = 0; c < cpu; ++c) {
@@ -380,18 +400,23 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         }
         ++consumed;
         __syncwarp();
-        if (lane == 0 && pu < total) issue();
+        if (lane == 0 && can_issue()) issue();
         advance();
       }
       if (dead) break;
-      while (pend && (pend_kind != 2 || pend != 2 || tab_loaded)) advance();
-      if (pend) break;  // cannot happen: a warp has at most one early shared unit
+      while (pend) advance();
       float* yt = p.ws.ypick + ((size_t)slot * NT + n16) * 128;
       *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
       *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
       pend = 1, pend_kind = 2, pend_a = n16;
+      u_cur = q ? __shfl_sync(0xffffffffu, u_next, 0) : u_next;
+      u_next = claim(q, u_cur, stride);
+      if (lane == 0) {
+        --p_on;
+        while (can_issue()) issue();
+      }
     }
-    if (!dead && tab_loaded)
+    if (!dead)
       while (pend) advance();
   };
 
@@ -399,9 +424,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   if (!router_cta) {
     if (sh_units) {  // shared unit u -> warp (ntask + u) mod GWn
       const int first = ((gwn - ntask % GWn) % GWn + GWn) % GWn;
-      up_units(first, GWn, sh_units, true);
-      // and its down units (their h is the shared expert's own): unit v -> warp (ntask + sh_units + v) mod GWn
-      down_units(((gwn - (ntask + sh_units) % GWn) % GWn + GWn) % GWn, GWn, sh_down, true);
+      up_units(first, GWn, sh_units, true, nullptr);
     }
   } else {
     // ---- phase 2 (router CTAs): wait for the slices, route a row, the last one builds the slot table -------------------
@@ -473,12 +496,10 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   if (stamp && lane == 0) stamp[3] = gtime();
   // ---- phase 4: routed gate/up units, continuing the round-robin after the first phase's work ------------------------------
   if (!dead) {
-    const int base = (ntask + sh_units) % GW;
-    up_units(((gw - base) % GW + GW) % GW, GW, tab.nslots * upp, false);
+    up_units(0, 0, tab.nslots * upp, false, &sy->q_up);  // claimed from a queue: late warps take fewer
   }
 
   if (stamp && lane == 0) stamp[4] = gtime();
-  if (stamp && lane == 0 && !router_cta) stamp[6] = (unsigned long long)cyc_wait << 32 | (unsigned long long)(cyc_mma & 0xffffffffll), stamp[7] = (unsigned long long)cyc_issue;
   // ---- phase 5: the routed slots' down units ------------------------------------------------------------------------------
   if (!dead && tab.ntot == 0) {
     for (size_t i = (size_t)blockIdx.x * kFThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kFThreads) {
@@ -486,9 +507,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
     }
   } else if (!dead) {
-    const int base = (ntask + sh_units + sh_down + tab.nslots * upp) % GW;
-    down_units(((gw - base) % GW + GW) % GW, GW, tab.nslots * NT, false);
-    while (pend) advance();
+    down_units(0, 0, sh_down + tab.nslots * NT, &sy->q_down);
   }
   if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
   if (stamp && lane == 0) stamp[5] = gtime();
@@ -500,7 +519,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   __syncthreads();
   if (s_int[2] == (int)gridDim.x - 1) {
     for (int i = threadIdx.x; i < kMaxSlots + 1; i += kFThreads) sy->cnt_hq[i] = 0;
-    if (threadIdx.x == 0) sy->cnt_lp = 0, sy->cnt_rt = 0, sy->tab_ready = 0, sy->cnt_exit = 0;
+    if (threadIdx.x == 0) sy->cnt_lp = 0, sy->cnt_rt = 0, sy->tab_ready = 0, sy->cnt_exit = 0, sy->q_up = 0, sy->q_down = 0;
   }
 }
 

@@ -77,6 +77,7 @@ struct StepSync {
   int cnt_rt;     // rows routed
   int tab_ready;  // the slot table is in the workspace
   int cnt_exit;   // CTAs that left
+  int q_up, q_down;  // next unclaimed gate/up unit, down unit
   int cnt_hq[kMaxSlots + 1];  // quantised 128-groups of a slot's h
 };
 struct StepParams {
