@@ -253,7 +253,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     const int cpu = HB / KCH;
     const size_t strip = (size_t)8 * p.H;
     int u_cur = q ? __shfl_sync(0xffffffffu, claim(q, 0, 0), 0) : first;
-    int u_next = claim(q, u_cur, stride);  // dynamic: known to lane 0 only
+    int u_next = q ? 0 : u_cur + stride;   // dynamic: claimed by lane 0 when its producer gets there, not earlier (a
+                                           // claim held in reserve is a unit another warp could be streaming)
     int p_on = 0, pc = 0;                  // producer (lane 0): on u_cur (0), on u_next (1), waiting for the consumer (2)
     const uint8_t *pgp = nullptr, *pup = nullptr;
     uint32_t pst = issued % NST;
@@ -273,7 +274,10 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       pgp += KCH * 1024, pup += KCH * 1024;
       ++issued;
       if (++pst == NST) pst = 0;
-      if (++pc == cpu) pc = 0, ++p_on;
+      if (++pc == cpu) {
+        pc = 0;
+        if (++p_on == 1 && q) u_next = atomicAdd(q, 1);
+      }
     };
     if (lane == 0)
       while (can_issue()) issue();
@@ -322,7 +326,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       pend = 1, pend_kind = 1, pend_a = wslot, pend_b = i8 / 16;
       // on to the next unit of the sequence
       u_cur = q ? __shfl_sync(0xffffffffu, u_next, 0) : u_next;
-      u_next = claim(q, u_cur, stride);
+      if (!q) u_next = u_cur + stride;
       if (lane == 0) {
         --p_on;
         while (can_issue()) issue();
@@ -339,7 +343,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     const size_t strip = (size_t)8 * p.I;
     const uint32_t stage_bytes = 2 * KCH * 1024 + KCH * CB;
     int u_cur = q ? __shfl_sync(0xffffffffu, claim(q, 0, 0), 0) : first;
-    int u_next = claim(q, u_cur, stride);
+    int u_next = q ? 0 : u_cur + stride;
     int p_on = 0, pc = 0, ready_slot = -1, pslot = 0;
     bool poll_failed = false;
     const uint8_t *pdp = nullptr, *php = nullptr;
@@ -368,7 +372,10 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       pdp += KCH * 1024, php += KCH * CB;
       ++issued;
       if (++pst == NST) pst = 0;
-      if (++pc == cpu) pc = 0, ++p_on;
+      if (++pc == cpu) {
+        pc = 0;
+        if (++p_on == 1 && q) u_next = atomicAdd(q, 1);
+      }
     };
     if (lane == 0)
       while (can_issue()) issue();
@@ -410,7 +417,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
       pend = 1, pend_kind = 2, pend_a = n16;
       u_cur = q ? __shfl_sync(0xffffffffu, u_next, 0) : u_next;
-      u_next = claim(q, u_cur, stride);
+      if (!q) u_next = u_cur + stride;
       if (lane == 0) {
         --p_on;
         while (can_issue()) issue();
