@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       u_cur = q ? __shfl_sync(0xffffffffu, u_next, 0) : u_next;
       if (!q) u_next = u_cur + stride;
       if (lane == 0) {
-        --p_on;
+        if (--p_on == 1 && q) u_next = atomicAdd(q, 1);  // the producer had finished the new current unit too
         while (can_issue()) issue();
       }
     }
@@ -419,7 +419,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       u_cur = q ? __shfl_sync(0xffffffffu, u_next, 0) : u_next;
       if (!q) u_next = u_cur + stride;
       if (lane == 0) {
-        --p_on;
+        if (--p_on == 1 && q) u_next = atomicAdd(q, 1);  // the producer had finished the new current unit too
         while (can_issue()) issue();
       }
     }
