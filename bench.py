@@ -176,7 +176,7 @@ def run_gpu(args):
         lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
         wr = synth.router_weights(E, H, SEED + 2000 + l, device="cpu").to(dev)
         layers.append((lay, lay.layer_w()))
-        steps_buf.append(moe.LayerStep(shp, wr, None, device=dev, fused=not args.separate))
+        steps_buf.append(moe.LayerStep(shp, wr, None, device=dev, fused=False if args.separate else True if args.fused else None))
     xs = [synth.activations(rows, H, SEED + 1000 + i, device="cpu").to(dev) for i in range(NX)]
     xs_host = [x.cpu().pin_memory() for x in xs]
     out_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
@@ -330,8 +330,8 @@ def main():
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
-    ap.add_argument("--separate", action="store_true",
-                    help="run the step as four kernels (front, route, gate/up, down) instead of the one persistent kernel")
+    ap.add_argument("--separate", action="store_true", help="always run the step as four kernels")
+    ap.add_argument("--fused", action="store_true", help="always run the step as the one persistent kernel")
     ap.add_argument("--experts", type=int, default=0,
                     help="profiling only: a layer with fewer routed experts (same matrices), to keep an ncu capture small")
     args = ap.parse_args()

@@ -223,7 +223,8 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-    if (fp8 && !(st->flags & 1) && step_fp8_fits(s->H, s->I, s->E, M)) {  // the whole step as one persistent kernel
+    // the whole step as one persistent kernel: measured faster from three rows up (flags bit 2 forces it, bit 0 forbids it)
+    if (fp8 && !(st->flags & 1) && (M >= 3 || (st->flags & 4)) && step_fp8_fits(s->H, s->I, s->E, M)) {
       StepParams sp;
       sp.d = p, sp.rp = rp, sp.x = xb, sp.wr = st->wr, sp.bias = st->bias, sp.logits = st->logits, sp.idx = st->idx;
       sp.w = st->w, sp.sync = p.ws.sync, sp.R = 0, sp.sh_slot = 0, sp.has_sh = 0;

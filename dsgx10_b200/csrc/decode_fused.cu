@@ -503,7 +503,15 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   if (stamp && lane == 0) stamp[3] = gtime();
   // ---- phase 4: routed gate/up units, continuing the round-robin after the first phase's work ------------------------------
   if (!dead) {
-    up_units(0, 0, tab.nslots * upp, false, &sy->q_up);  // claimed from a queue: late warps take fewer
+    if (p.M > 2) {
+      up_units(0, 0, tab.nslots * upp, false, &sy->q_up);  // claimed from a queue: late warps take fewer
+    } else {
+      // few units a warp: a fixed deal over the warps that had no shared-expert unit (those are still busy with it)
+      const int first = router_cta ? 0 : ((gwn - ntask % GWn) % GWn + GWn) % GWn;
+      const int wn = GW - sh_units;  // warps in the deal
+      const int pos = router_cta ? (GWn - sh_units) + ((int)blockIdx.x - nrc) * kFW + warp : first - sh_units;
+      if (pos >= 0) up_units(pos, wn, tab.nslots * upp, false, nullptr);
+    }
   }
 
   if (stamp && lane == 0) stamp[4] = gtime();
@@ -514,7 +522,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
     }
   } else if (!dead) {
-    down_units(0, 0, sh_down + tab.nslots * NT, &sy->q_down);
+    if (p.M > 2) down_units(0, 0, sh_down + tab.nslots * NT, &sy->q_down);
+    else down_units(gw, GW, sh_down + tab.nslots * NT, nullptr);
   }
   if (dead && lane == 0) atomicCAS(p.ws.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
   if (stamp && lane == 0) stamp[5] = gtime();

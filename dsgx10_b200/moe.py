@@ -97,7 +97,8 @@ def ws_status(ws):
 class LayerStep:
     """The buffers of one layer step (router to rounded output) and the two step calls."""
 
-    def __init__(self, shp, wr, bias=None, device="cuda", fused=True, stamps=None):
+    def __init__(self, shp, wr, bias=None, device="cuda", fused=None, stamps=None):
+        """fused: None = the library's choice by row count, True = always the one-kernel step, False = never."""
         f32 = dict(dtype=torch.float32, device=device)
         self.shp, self.wr, self.bias = shp, wr, bias
         self.logits = torch.empty(_lib.MAX_ROWS, shp.E, **f32)
@@ -110,7 +111,7 @@ class LayerStep:
         self.x_stage = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
         self.c = _lib.LayerStep(_ptr(wr), _ptr(bias), _ptr(self.logits), _ptr(self.idx), _ptr(self.w), _ptr(self.ws),
                                 _ptr(self.yr), _ptr(self.ys), _ptr(self.out), _ptr(self.x_stage),
-                                (0 if fused else 1) | (2 if stamps is not None else 0), 0, _ptr(stamps))
+                                (0 if fused is None else 4 if fused else 1) | (2 if stamps is not None else 0), 0, _ptr(stamps))
 
     def run(self, layer_w, x, finalize=True):
         """x bf16 [M][H] on the device -> self.out[:M] (bf16) when finalize, else self.yr / self.ys partial sums."""
