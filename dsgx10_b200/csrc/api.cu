@@ -224,8 +224,15 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
     // the whole step as one persistent kernel: measured faster from three rows up (flags bit 2 forces it, bit 0 forbids it)
-    if (fp8 && !(st->flags & 1) && (M >= 3 || (st->flags & 4)) && step_fp8_fits(s->H, s->I, s->E, M)) {
+    if (fp8 && !(st->flags & 1) && step_fp8_fits(s->H, s->I, s->E, M)) {
       StepParams sp;
+      // three rows and more: everything in the one kernel.  One or two rows: the routing chain is too long to hide
+      // behind the little work that needs no routing, so two small kernels route first (flags bit 2: one kernel anyway).
+      sp.pre_routed = (M >= 3 || (st->flags & 4)) ? 0 : 1;
+      if (sp.pre_routed) {
+        cudaError_t e0 = launch_front_route_only(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true);
+        if (e0 != cudaSuccess) return cuda_fail(e0);
+      }
       sp.d = p, sp.rp = rp, sp.x = xb, sp.wr = st->wr, sp.bias = st->bias, sp.logits = st->logits, sp.idx = st->idx;
       sp.w = st->w, sp.sync = p.ws.sync, sp.R = 0, sp.sh_slot = 0, sp.has_sh = 0;
       sp.stamps = (st->flags & 2) ? reinterpret_cast<unsigned long long*>(st->reserved_ptr) : nullptr;

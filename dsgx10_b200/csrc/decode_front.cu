@@ -137,4 +137,16 @@ cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteP
                   (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
 }
 
+// the same without staging x (the one-kernel step stages x itself)
+cudaError_t launch_front_route_only(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
+                                    const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl) {
+  const int KS = (p.H + 1023) / 1024;
+  const int nlog = (p.E * KS + 7) / 8;
+  cudaError_t e = launch_k(k_front, dim3(nlog), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq,
+                           (int)DSGX_FMT_FP8);
+  if (e != cudaSuccess) return e;
+  return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, DSGX_FMT_FP8),
+                  (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
+}
+
 }  // namespace dsgx

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   __syncthreads();
   const uint64_t pol = policy_evict_first();
   const int KS = (p.H + 1023) / 1024, ntask = p.E * KS;
-  const int nroute = p.M;  // the last nroute CTAs route one row each
+  const int nroute = sp.pre_routed ? 0 : p.M;  // the last nroute CTAs route one row each (none when earlier kernels routed)
   const bool router_cta = (int)blockIdx.x >= (int)gridDim.x - nroute;
   const int nrc = (int)gridDim.x - nroute;       // CTAs that do not route
   const int GWn = nrc * kFW;                     // their warps take the logit slices and the shared expert's units
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   const int sh_units = sp.has_sh ? upp : 0, sh_down = sp.has_sh ? NT : 0;
 
   // ---- the router's logit slices first: they head the longest chain of the step -------------------------------------------
-  if (!router_cta) {
+  if (!router_cta && !sp.pre_routed) {
     int mine = 0;
     for (int task = gwn; task < ntask; task += GWn) {
       logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
@@ -487,7 +487,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     winner = __shfl_sync(0xffffffffu, winner, 0);
     if (winner) {
       int ok = 0;
-      if (lane == 0) ok = !dead && poll_ge(&sy->tab_ready, 1);
+      if (lane == 0) ok = !dead && (sp.pre_routed || poll_ge(&sy->tab_ready, 1));
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (ok) {
         load_slot_tab(tab, p.ws.tab, lane);

@@ -92,9 +92,12 @@ struct StepParams {
   StepSync* sync;
   unsigned long long* stamps;  // optional [warps][8] phase timestamps (profiling aid), or null
   int R, sh_slot, has_sh;
+  int pre_routed;  // 1: earlier kernels routed the rows and built the slot table; the step starts at the experts
 };
 bool step_fp8_fits(int H, int I, int E, int M);
 cudaError_t launch_step_fp8(StepParams sp, cudaStream_t st);
+cudaError_t launch_front_route_only(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
+                                    const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
 
 cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
 cudaError_t launch_layer_int4(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
