@@ -224,11 +224,12 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
     // the whole step as one persistent kernel: measured faster from three rows up (flags bit 2 forces it, bit 0 forbids it)
-    if (fp8 && !(st->flags & 1) && step_fp8_fits(s->H, s->I, s->E, M)) {
+    // Three rows and more: the whole step as one persistent kernel.  One or two rows: the four-kernel step is faster
+    // (measured): the routing chain is too long to hide behind the little work that needs no routing.
+    // flags: bit 0 never the one kernel; bit 2 always; bit 3: route with two small kernels, experts in the one kernel.
+    if (fp8 && !(st->flags & 1) && (M >= 3 || (st->flags & 12)) && step_fp8_fits(s->H, s->I, s->E, M)) {
       StepParams sp;
-      // three rows and more: everything in the one kernel.  One or two rows: the routing chain is too long to hide
-      // behind the little work that needs no routing, so two small kernels route first (flags bit 2: one kernel anyway).
-      sp.pre_routed = (M >= 3 || (st->flags & 4)) ? 0 : 1;
+      sp.pre_routed = (st->flags & 8) ? 1 : 0;
       if (sp.pre_routed) {
         cudaError_t e0 = launch_front_route_only(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true);
         if (e0 != cudaSuccess) return cuda_fail(e0);

@@ -153,7 +153,8 @@ typedef struct dsgx_layer_step {
   void* x_stage;      /* device staging for dsgx_moe_layer_decode_host */
   int32_t flags;      /* FP8 layers run the step as four kernels (front, route, gate/up, down) at one or two rows and as
                          one persistent kernel from three rows up (the measured crossover); bit 0: always the four
-                         kernels; bit 2: always the one kernel; both give the same bits */
+                         kernels; bit 2: always the one kernel; bit 3: two small routing kernels, then the experts in the
+                         one kernel; every path gives the same bits */
   int32_t reserved;
   void* reserved_ptr; /* with flags bit 1: device memory for [warps][8] u64 phase timestamps of the one-kernel step
                          (a profiling aid; warps = 16 x SM count) */
