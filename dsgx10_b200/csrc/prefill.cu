@@ -286,26 +286,24 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         }
         tc_fence_after();
         const uint32_t t0 = tmem + lane_addr + b * 256 + half * 64;
-        uint32_t r[32];
+        uint32_t r[32], q[32];  // two loads in flight
         tc_ld32(t0, r);
+        tc_ld32(t0 + 32, q);
         tc_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; ++c) acc0[c] = fmaf(__uint_as_float(r[c]), s0, acc0[c]);
-        tc_ld32(t0 + 32, r);
-        tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc0[32 + c] = fmaf(__uint_as_float(r[c]), s0, acc0[32 + c]);
         tc_ld32(t0 + 128, r);
-        tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) acc1[c] = fmaf(__uint_as_float(r[c]), s1, acc1[c]);
-        tc_ld32(t0 + 160, r);
+        for (int c = 0; c < 32; ++c) acc0[32 + c] = fmaf(__uint_as_float(q[c]), s0, acc0[32 + c]);
+        tc_ld32(t0 + 160, q);
         tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc1[32 + c] = fmaf(__uint_as_float(r[c]), s1, acc1[32 + c]);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty + b);
+        if (lane == 0) mbar_arrive(tempty + b);  // the buffer is free for the MMAs of the block after next
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc1[c] = fmaf(__uint_as_float(r[c]), s1, acc1[c]);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc1[32 + c] = fmaf(__uint_as_float(q[c]), s1, acc1[32 + c]);
       }
       if (dead) break;
       if (MODE == 0) {
@@ -406,12 +404,23 @@ __global__ void __launch_bounds__(256) k_combine(const __nv_bfloat16* __restrict
 #pragma unroll
     for (int k = 0; k < 4; ++k) sh[2 * k] = bf16_bits_to_f(w[k] & 0xffffu), sh[2 * k + 1] = bf16_bits_to_f(w[k] >> 16);
   }
+  float both[8];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const float both = __fadd_rn(acc[k], sh[k]);
-    yr[t * H + c + k] = ysum && ysh ? both : acc[k];
-    if (ys && ysh) ys[t * H + c + k] = sh[k];
-    if (out) out[t * H + c + k] = __float2bfloat16_rn(both);
+  for (int k = 0; k < 8; ++k) both[k] = __fadd_rn(acc[k], sh[k]);
+  const bool sum = ysum && ysh;
+  float4* yr4 = reinterpret_cast<float4*>(yr + t * H + c);
+  yr4[0] = sum ? make_float4(both[0], both[1], both[2], both[3]) : make_float4(acc[0], acc[1], acc[2], acc[3]);
+  yr4[1] = sum ? make_float4(both[4], both[5], both[6], both[7]) : make_float4(acc[4], acc[5], acc[6], acc[7]);
+  if (ys && ysh) {
+    float4* ys4 = reinterpret_cast<float4*>(ys + t * H + c);
+    ys4[0] = make_float4(sh[0], sh[1], sh[2], sh[3]);
+    ys4[1] = make_float4(sh[4], sh[5], sh[6], sh[7]);
+  }
+  if (out) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w[k] = f_to_bf16_bits(both[2 * k]) | f_to_bf16_bits(both[2 * k + 1]) << 16;
+    *reinterpret_cast<uint4*>(out + t * H + c) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
