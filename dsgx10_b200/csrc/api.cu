@@ -326,10 +326,10 @@ int dsgx_moe_prefill(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void*
   if (!L || !wbuf || !x || !idx || !w || !ws || !yr || T < 1) return DSGX_ERR_ARG;
   if (((uintptr_t)wbuf & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh = L->sh.g != nullptr;
-  if (sh && !ys && !ysum && !out) return DSGX_ERR_ARG;
+  if (sh && !ys && !(ysum & 1) && !out) return DSGX_ERR_ARG;
   if ((size_t)T * s->topk > (size_t)1 << 30) return DSGX_ERR_SHAPE;
   PrefillParams q;
-  q.T = T, q.H = s->H, q.I = s->I, q.E = s->E, q.topk = s->topk, q.has_shared = sh, q.ysum = ysum;
+  q.T = T, q.H = s->H, q.I = s->I, q.E = s->E, q.topk = s->topk, q.has_shared = sh, q.ysum = ysum & 1, q.parts = (ysum >> 8) & 3;
   q.e_lo = s->e_lo, q.e_hi = s->e_hi;
   q.x = reinterpret_cast<const __nv_bfloat16*>(x), q.idx = idx, q.w = w;
   q.pw = prefill_weights_carve(const_cast<void*>(wbuf), s->H, s->I, s->E);

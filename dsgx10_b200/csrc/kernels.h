@@ -134,6 +134,7 @@ PrefillWs prefill_ws_carve(void* ws, int T, int H, int I, int E, int topk);
 
 struct PrefillParams {
   int T, H, I, E, topk, has_shared, ysum, e_lo, e_hi;
+  int parts;  // bench hook: 0 the whole pass, 1 the routed gate/up GEMM alone, 2 the routed down GEMM alone
   const __nv_bfloat16* x;
   const int* idx;
   const float* w;

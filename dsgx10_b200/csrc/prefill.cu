@@ -74,7 +74,10 @@ DSGX_DEV uint64_t umma_desc_sw128(const void* smem) {
 // instruction descriptor: f32 accumulate, e4m3 x e4m3, both K-major, M 128, N 256
 constexpr uint32_t kIdesc = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
 
-constexpr int kGThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..9: epilogue
+// warps 0..3: the producer group (warp 0 TMA, warp 1 MMA + TMEM, two spare), warps 4..11: epilogue.  After the set-up the
+// producer group gives registers back (40 a thread) and the epilogue warps take them (232 a thread): 384 x 168 in all.
+constexpr int kGThreads = 384;
+constexpr int kProdRegs = 40, kEpiRegs = 232;
 constexpr int kGStages = 4;
 constexpr int kATile = 128 * 128, kBTile = 256 * 128, kGStage = kATile + kBTile;
 
@@ -154,6 +157,21 @@ struct GemmArgs {
   int* status;
 };
 
+// acc[c] += part[c] * s for 32 columns, two a packed f32 instruction
+DSGX_DEV void promote32(float2* acc, const uint32_t (&part)[32], float2 s) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c)
+    acc[c] = __ffma2_rn(make_float2(__uint_as_float(part[2 * c]), __uint_as_float(part[2 * c + 1])), s, acc[c]);
+}
+// v / s for the quantisation of a group whose scale s is shared: with y = RN(1 / s), q0 = v y and the exact remainder
+// v - q0 s, RN(q0 + rem y) is the IEEE quotient (for every bf16 v and every scale this library forms, except quotients
+// below 2^-60, which are zero in e4m3 either way).  Two values -> two e4m3 bytes, saturating.
+DSGX_DEV uint32_t quant2_e4m3(float v0, float v1, float s, float y) {
+  const float q0 = __fmul_rn(v0, y), q1 = __fmul_rn(v1, y);
+  const float d0 = __fmaf_rn(__fmaf_rn(-q0, s, v0), y, q0), d1 = __fmaf_rn(__fmaf_rn(-q1, s, v1), y, q1);
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(d0, d1), __NV_SATFINITE, __NV_E4M3);
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant__ CUtensorMap mapA,
                                                           const __grid_constant__ CUtensorMap mapB0,
@@ -209,6 +227,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     rend = a.seg_off[e + 1];
   };
 
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProdRegs));
   if (warp == 0) {
     // ---------------------------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -257,9 +276,10 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         }
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // -------------------------------------------------------------------------------------------------- epilogue
-    const int ew = warp - 2, quarter = warp & 3, half = ew >> 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpiRegs));
+    const int ew = warp - 4, quarter = warp & 3, half = ew >> 2;
     const int trow = quarter * 32 + lane;  // the tile row (TMEM lane) of this thread
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     uint32_t it = 0, xn = 0;
@@ -273,37 +293,45 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
       const size_t sbase = (size_t)(a.wrow0 + e) * (a.N / 128) * KB;
       const float* sb0p = MODE == 0 ? a.sb0 + sbase + (size_t)nt * KB : a.sb0 + sbase + (size_t)(2 * nt) * KB;
       const float* sb1p = MODE == 0 ? a.sb1 + sbase + (size_t)nt * KB : a.sb0 + sbase + (size_t)(2 * nt + 1) * KB;
-      float acc0[64], acc1[64];  // columns [64 half, 64 half + 64) of the first and of the second 128
+      float2 acc0[32], acc1[32];  // columns [64 half, 64 half + 64) of the first and of the second 128, in pairs
 #pragma unroll
-      for (int c = 0; c < 64; ++c) acc0[c] = 0.f, acc1[c] = 0.f;
+      for (int c = 0; c < 32; ++c) acc0[c] = make_float2(0.f, 0.f), acc1[c] = make_float2(0.f, 0.f);
+      // the scales of a block are fetched two blocks ahead of their use
+      float pa[2], p0[2], p1[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int k = j < KB ? j : 0;
+        pa[j] = __ldg(sap + k), p0[j] = __ldg(sb0p + k), p1[j] = __ldg(sb1p + k);
+      }
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const uint32_t b = it & 1;
-        const float sa = __ldg(sap + kb);
-        const float s0 = sa * __ldg(sb0p + kb), s1 = sa * __ldg(sb1p + kb);
+        const float s0 = pa[0] * p0[0], s1 = pa[0] * p1[0];
+        pa[0] = pa[1], p0[0] = p0[1], p1[0] = p1[1];
+        {
+          const int k = kb + 2 < KB ? kb + 2 : 0;
+          pa[1] = __ldg(sap + k), p0[1] = __ldg(sb0p + k), p1[1] = __ldg(sb1p + k);
+        }
         if (!mbar_wait(tfull + b, (it >> 1) & 1)) {
           dead = true;
           break;
         }
         tc_fence_after();
         const uint32_t t0 = tmem + lane_addr + b * 256 + half * 64;
+        const float2 s02 = make_float2(s0, s0), s12 = make_float2(s1, s1);
         uint32_t r[32], q[32];  // two loads in flight
         tc_ld32(t0, r);
         tc_ld32(t0 + 32, q);
         tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc0[c] = fmaf(__uint_as_float(r[c]), s0, acc0[c]);
+        promote32(acc0, r, s02);
         tc_ld32(t0 + 128, r);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc0[32 + c] = fmaf(__uint_as_float(q[c]), s0, acc0[32 + c]);
+        promote32(acc0 + 16, q, s02);
         tc_ld32(t0 + 160, q);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty + b);  // the buffer is free for the MMAs of the block after next
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc1[c] = fmaf(__uint_as_float(r[c]), s1, acc1[c]);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) acc1[32 + c] = fmaf(__uint_as_float(q[c]), s1, acc1[32 + c]);
+        promote32(acc1, r, s12);
+        promote32(acc1 + 16, q, s12);
       }
       if (dead) break;
       if (MODE == 0) {
@@ -311,12 +339,13 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         const float wr = a.wrow ? __ldg(a.wrow + srow) : 1.f;
         float am = 0.f;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float h = __fmul_rn(silu(bf16_round(acc0[c])), bf16_round(acc1[c]));
-          if (a.wrow) h = __fmul_rn(wr, h);
-          h = bf16_round(h);
-          acc0[c] = h;
-          am = fmaxf(am, fabsf(h));
+        for (int c = 0; c < 32; ++c) {
+          float h0 = __fmul_rn(silu(bf16_round(acc0[c].x)), bf16_round(acc1[c].x));
+          float h1 = __fmul_rn(silu(bf16_round(acc0[c].y)), bf16_round(acc1[c].y));
+          if (a.wrow) h0 = __fmul_rn(wr, h0), h1 = __fmul_rn(wr, h1);
+          h0 = bf16_round(h0), h1 = bf16_round(h1);
+          acc0[c] = make_float2(h0, h1);
+          am = fmaxf(am, fmaxf(fabsf(h0), fabsf(h1)));
         }
         // the other half's maximum: through shared memory, two buffers by item parity, one bounded barrier an item
         float* ax = amax_x + (xn & 1) * 256;
@@ -329,6 +358,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         }
         ++xn;
         const float sc = act_scale(fmaxf(ax[trow], ax[128 + trow]));
+        const float rsc = __frcp_rn(sc);
         if (live) {
           uint4* dst = reinterpret_cast<uint4*>(a.hq + (size_t)row * a.N + nt * 128 + half * 64);
 #pragma unroll
@@ -336,9 +366,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
             uint32_t wd[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              const int c = 16 * v + 4 * k;
-              wd[k] = quant_e4m3(acc0[c], sc) | quant_e4m3(acc0[c + 1], sc) << 8 | quant_e4m3(acc0[c + 2], sc) << 16 |
-                      quant_e4m3(acc0[c + 3], sc) << 24;
+              const int c = 8 * v + 2 * k;
+              wd[k] = quant2_e4m3(acc0[c].x, acc0[c].y, sc, rsc) | quant2_e4m3(acc0[c + 1].x, acc0[c + 1].y, sc, rsc) << 16;
             }
             dst[v] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
@@ -355,9 +384,9 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
             uint32_t wd[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              const int c = 8 * v + 2 * k;
-              const float f0 = hh ? acc1[c] : acc0[c], f1 = hh ? acc1[c + 1] : acc0[c + 1];
-              wd[k] = f_to_bf16_bits(f0) | f_to_bf16_bits(f1) << 16;
+              const float2 f = hh ? acc1[4 * v + k] : acc0[4 * v + k];
+              const __nv_bfloat162 t = __float22bfloat162_rn(f);
+              wd[k] = *reinterpret_cast<const uint32_t*>(&t);
             }
             dst[v] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
@@ -383,14 +412,24 @@ __global__ void __launch_bounds__(256) k_combine(const __nv_bfloat16* __restrict
   if (i >= (size_t)T * per) return;
   const size_t t = i / per;
   const int c = (int)(i % per) * 8;
+  // all the picks' rows are fetched before the first add, so that the loads overlap; the adds keep their order
+  uint4 v[kMaxTopK];
+  bool on[kMaxTopK];
+#pragma unroll
+  for (int j = 0; j < kMaxTopK; ++j) {
+    on[j] = false;
+    if (j < topk) {
+      const int jj = row_order[t * topk + j];
+      const int e = idx[t * topk + jj];
+      on[j] = e >= e_lo && e < e_hi;  // else another GPU's expert
+      if (on[j]) v[j] = __ldg(reinterpret_cast<const uint4*>(y + (size_t)pos_of[t * topk + jj] * H + c));
+    }
+  }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int j = 0; j < topk; ++j) {
-    const int jj = row_order[t * topk + j];
-    const int e = idx[t * topk + jj];
-    if (e < e_lo || e >= e_hi) continue;  // another GPU's expert
-    const int pos = pos_of[t * topk + jj];
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + (size_t)pos * H + c));
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < kMaxTopK; ++j) {
+    if (!on[j]) continue;
+    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       acc[2 * k] = __fadd_rn(acc[2 * k], bf16_bits_to_f(w[k] & 0xffffu));
@@ -554,7 +593,10 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
       !make_map(&mHsh, w.hq_sh, T, I) || !make_map(&mG, pw.g, nexp * I, H) || !make_map(&mU, pw.u, nexp * I, H) ||
       !make_map(&mD, pw.d, nexp * H, I))
     return cudaErrorInvalidValue;
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
+  GemmArgs a;
+  a.status = w.status;
+  if (!q.parts) {  // (bench hook otherwise: the workspace holds the order and the operands of an earlier whole pass)
   // order, quantise, gather
   e = launch_sort_pack(q.idx, T, topk, E, w.counts, w.offsets, w.perm_tok, w.perm_slot, w.pos_of, w.row_order, w.sort_ws, st);
   if (e != cudaSuccess) return e;
@@ -568,18 +610,17 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  GemmArgs a;
-  a.status = w.status;
+  }
   // routed gate/up
   a.mode = 0, a.K = H, a.N = I, a.E = E, a.rows_total = P, a.wrow0 = 0, a.seg_off = w.offsets, a.tile_off = w.tile_off;
   a.sa = w.xs_s, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = w.w_s, a.hq = w.hq, a.hs = w.hs, a.y = nullptr;
-  e = launch_gemm<0>(mXs, mG, mU, a, st);
-  if (e != cudaSuccess) return e;
+  if (q.parts != 2) e = launch_gemm<0>(mXs, mG, mU, a, st);
+  if (e != cudaSuccess || q.parts == 1) return e;
   // routed down
   a.mode = 1, a.K = I, a.N = H, a.sa = w.hs, a.sb0 = pw.sd, a.sb1 = nullptr, a.wrow = nullptr, a.hq = nullptr, a.hs = nullptr;
   a.y = w.y;
   e = launch_gemm<1>(mHq, mD, mD, a, st);
-  if (e != cudaSuccess) return e;
+  if (e != cudaSuccess || q.parts == 2) return e;
   if (q.has_shared) {
     a.mode = 0, a.K = H, a.N = I, a.E = 1, a.rows_total = T, a.wrow0 = E, a.seg_off = nullptr, a.tile_off = nullptr;
     a.sa = w.xs, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = nullptr, a.hq = w.hq_sh, a.hs = w.hs_sh, a.y = nullptr;

@@ -140,7 +140,7 @@ class PrefillLayer:
         check(lib().dsgx_prefill_prepare(C.byref(shp), C.byref(layer_w), _ptr(self.wbuf), _stream()), "dsgx_prefill_prepare")
         self.ws = torch.empty(lib().dsgx_prefill_ws_bytes(C.byref(shp), T_max), dtype=torch.uint8, device=device)
 
-    def run(self, x, idx, w, yr=None, ys=None, out=None, ysum=False):
+    def run(self, x, idx, w, yr=None, ys=None, out=None, ysum=False, parts=0):
         """x bf16 [T][H]; idx, w from route(); returns (yr, ys, out): f32 partial sums and bf16(yr + ys)."""
         T, H = x.shape
         assert T <= self.T_max
@@ -149,5 +149,5 @@ class PrefillLayer:
         ys = torch.empty(T, H, **f32) if ys is None else ys
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if out is None else out
         check(lib().dsgx_moe_prefill(C.byref(self.shp), C.byref(self.layer_w), _ptr(self.wbuf), _ptr(x), _ptr(idx), _ptr(w), T,
-                                     _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum), _stream()), "dsgx_moe_prefill")
+                                     _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum) | parts << 8, _stream()), "dsgx_moe_prefill")
         return yr, ys, out

@@ -176,7 +176,9 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* 
  * time into wbuf (dsgx_prefill_weights_bytes(shape) bytes of device memory), as the reference re-tiles its checkpoints
  * (ds41f engine/kernels/moe.cu:1332-1336); it reads the descriptors back to the host and synchronises, so it is a
  * load-time call.  Only the experts in [e_lo, e_hi) (and the shared expert, when the layer has one) are prepared and run.
- * ws: dsgx_prefill_ws_bytes(shape, T) bytes, T <= the value given there; no zeroing needed. */
+ * ws: dsgx_prefill_ws_bytes(shape, T) bytes, T <= the value given there; no zeroing needed.
+ * ysum: bit 0 as dsgx_decode_cfg.ysum; bits 8-9 a bench hook like dsgx_decode_cfg.parts (experts.h:121): 1 launches the
+ * routed gate/up GEMM alone, 2 the routed down GEMM alone, over the operands a whole pass left in ws. */
 size_t dsgx_prefill_weights_bytes(const dsgx_moe_shape* shape);
 int dsgx_prefill_prepare(const dsgx_moe_shape* shape, const dsgx_layer_w* L, void* wbuf, void* stream);
 size_t dsgx_prefill_ws_bytes(const dsgx_moe_shape* shape, int T);
