@@ -127,6 +127,7 @@ struct PrefillWs {
   uint8_t* hq_sh; float* hs_sh;              // shared h
   __nv_bfloat16* y; __nv_bfloat16* y_sh;
   int *perm_tok, *perm_slot, *pos_of, *row_order, *counts, *offsets, *tile_off;
+  int4* tile_info;
   void* sort_ws;
 };
 size_t prefill_ws_bytes(int T, int H, int I, int E, int topk);

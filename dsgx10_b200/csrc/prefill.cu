@@ -42,14 +42,6 @@ DSGX_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;
 DSGX_DEV void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// D[tmem] (+)= A[smem] B[smem]^T, e4m3 operands, M 128, N 256, K 32
-DSGX_DEV void tc_mma_f8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 DSGX_DEV void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
@@ -128,13 +120,28 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   if (c == 0) ws[pos] = w[(size_t)t * topk + perm_slot[pos]];
 }
 
-// only this GPU's experts [e_lo, e_hi) get tiles
-__global__ void k_tile_offsets(const int* __restrict__ counts, int E, int e_lo, int e_hi, int* __restrict__ tile_off) {
-  if (threadIdx.x == 0) {
-    int a = 0;
-    for (int e = 0; e < E; ++e) tile_off[e] = a, a += e >= e_lo && e < e_hi ? (counts[e] + 127) >> 7 : 0;
-    tile_off[E] = a;
+// The 128-row tiles of the ragged segments: tile_off [E + 1] the prefix of the tiles per expert (only this GPU's experts
+// [e_lo, e_hi) get tiles) and, per tile, tile_info = {expert, first row, end of the segment's rows, 0}.
+__global__ void __launch_bounds__(512) k_tile_offsets(const int* __restrict__ counts, const int* __restrict__ offsets, int E,
+                                                      int e_lo, int e_hi, int* __restrict__ tile_off,
+                                                      int4* __restrict__ tile_info) {
+  __shared__ int pre[513];
+  const int e = threadIdx.x;
+  const int mine = e < E && e >= e_lo && e < e_hi ? (counts[e] + 127) >> 7 : 0;
+  pre[e] = mine;
+  __syncthreads();
+  if (e == 0) {
+    int acc = 0;
+    for (int i = 0; i < E; ++i) {
+      const int c = pre[i];
+      pre[i] = acc, acc += c;
+    }
+    pre[E] = acc;
   }
+  __syncthreads();
+  if (e <= E) tile_off[e] = pre[e];
+  if (e < E)
+    for (int t = 0; t < mine; ++t) tile_info[pre[e] + t] = make_int4(e, offsets[e] + t * 128, offsets[e + 1], 0);
 }
 
 // ---- the grouped GEMM ---------------------------------------------------------------------------------------------
@@ -145,8 +152,8 @@ struct GemmArgs {
   int E;               // segments (1 for the shared expert's dense pass)
   int rows_total;      // rows of A
   int wrow0;           // first weight row block: expert e's rows start at (wrow0 + e) * N in the weight tensors
-  const int* seg_off;  // [E + 1] row offsets of the segments (null: one segment [0, rows_total))
-  const int* tile_off; // [E + 1] 128-row tile prefix (null with seg_off null)
+  const int* tile_off;   // [E + 1] 128-row tile prefix of the ragged segments (null: one segment [0, rows_total))
+  const int4* tile_info; // per tile {segment, first row, row end, 0} (null with tile_off null)
   const float* sa;     // [rows_total][K / 128] activation scales
   const float* sb0;    // UP: gate scales, DOWN: down scales; [.. experts][N / 128][K / 128]
   const float* sb1;    // UP: up scales
@@ -171,6 +178,29 @@ DSGX_DEV uint32_t quant2_e4m3(float v0, float v1, float s, float y) {
   const float d0 = __fmaf_rn(__fmaf_rn(-q0, s, v0), y, q0), d1 = __fmaf_rn(__fmaf_rn(-q1, s, v1), y, q1);
   return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(d0, d1), __NV_SATFINITE, __NV_E4M3);
 }
+// The four MMAs of one 128-k block (K 32 each: the start address moves by 2 x 16 B along the swizzled row), the first
+// overwriting the accumulator.  Descriptors as (low word, high word); one asm statement, so that nothing is scheduled
+// between the issues.
+DSGX_DEV void tc_mma_block(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t d_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
+      "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p0;\n\t"
+      "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+      "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(b_lo), "r"(d_hi), "r"(idesc)
+      : "memory");
+}
+
+// Shared memory behind the operand ring: barriers, the TMEM address, and the epilogue warps' staging (UP: the row maxima
+// of the two column halves and 2 KB a warp for the e4m3 rows; DOWN: 4 KB a warp for the bf16 rows).
+constexpr int kGCtl = 256;
+constexpr int kGStageOut = 8 * 4096;
 
 template <int MODE>
 __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant__ CUtensorMap mapA,
@@ -184,7 +214,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
   uint64_t* tempty = tfull + 2;
   uint64_t* xbar = tempty + 2;  // the epilogue warps' exchange of row maxima
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 1);
-  float* amax_x = reinterpret_cast<float*>(tmem_slot + 6);  // [2 buffers][2 halves][128 rows]
+  uint8_t* outst = smem + kGStages * kGStage + kGCtl;          // per-warp output staging
+  float* amax_x = reinterpret_cast<float*>(outst + 8 * 2048);  // UP: [2 buffers][2 halves][128 rows]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -204,27 +235,16 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
 
   const int KB = a.K / 128;
   const int ntn = MODE == 0 ? a.N / 128 : a.N / 256;  // n-tiles
-  const int mtiles = a.seg_off ? a.tile_off[a.E] : (a.rows_total + 127) / 128;
+  const int mtiles = a.tile_off ? __ldg(a.tile_off + a.E) : (a.rows_total + 127) / 128;
   const int items = mtiles * ntn;
   bool dead = false;
 
-  // item -> (segment, first row, row end, n-tile)
-  auto locate = [&](int item, int& e, int& row0, int& rend, int& nt) {
+  // item -> {segment, first row, row end, n-tile}: one load
+  auto locate = [&](int item) -> int4 {
     const int mt = item / ntn;
-    nt = item % ntn;
-    if (!a.seg_off) {
-      e = 0, row0 = mt * 128, rend = a.rows_total;
-      return;
-    }
-    int lo = 0, hi = a.E;  // the last e with tile_off[e] <= mt
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (a.tile_off[mid] <= mt) lo = mid;
-      else hi = mid;
-    }
-    e = lo;
-    row0 = a.seg_off[e] + (mt - a.tile_off[e]) * 128;
-    rend = a.seg_off[e + 1];
+    int4 r = a.tile_info ? __ldg(a.tile_info + mt) : make_int4(0, mt * 128, a.rows_total, 0);
+    r.w = item - mt * ntn;
+    return r;
   };
 
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProdRegs));
@@ -233,9 +253,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
-        int e, row0, rend, nt;
-        locate(item, e, row0, rend, nt);
-        const int wr = (a.wrow0 + e) * a.N + nt * (MODE == 0 ? 128 : 256);
+        const int4 ti = locate(item);
+        const int wr = (a.wrow0 + ti.x) * a.N + ti.w * (MODE == 0 ? 128 : 256);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % kGStages;
           if (it >= kGStages && !mbar_wait(empty + s, ((it / kGStages) - 1) & 1)) {
@@ -244,7 +263,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
           }
           uint8_t* st = smem + s * kGStage;
           mbar_expect_tx(full + s, kGStage);
-          tma_load_2d(st, &mapA, kb * 128, row0, full + s);
+          tma_load_2d(st, &mapA, kb * 128, ti.y, full + s);
           tma_load_2d(st + kATile, &mapB0, kb * 128, wr, full + s);
           tma_load_2d(st + kATile + kATile, MODE == 0 ? &mapB1 : &mapB0, kb * 128, MODE == 0 ? wr : wr + 128, full + s);
         }
@@ -252,28 +271,24 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------------------------ MMA issuer
+    // One thread; the tensor pipe takes an MMA only when the one before has gone in, so whatever this thread does
+    // between two blocks is time the pipe may idle: the loop is kept to two barrier waits, one asm statement of four
+    // MMAs and two commits.
     if (lane == 0) {
-      uint32_t it = 0;
-      for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % kGStages, b = it & 1;
-          if (!mbar_wait(full + s, (it / kGStages) & 1)) {
-            dead = true;
-            break;
-          }
-          if (it >= 2 && !mbar_wait(tempty + b, ((it >> 1) - 1) & 1)) {
-            dead = true;
-            break;
-          }
-          tc_fence_after();
-          const uint8_t* st = smem + s * kGStage;
-          const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + kATile);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)  // 32 k = 32 bytes along the swizzled row: the start address moves by 2 x 16 B
-            tc_mma_f8(tmem + b * 256, da + 2 * j, db + 2 * j, kIdesc, j ? 1u : 0u);
-          tc_commit(empty + s);   // the stage is free when these MMAs have read it
-          tc_commit(tfull + b);   // and the block's partial sums are in TMEM
+      const uint64_t d0 = umma_desc_sw128(smem);
+      const uint32_t d_hi = (uint32_t)(d0 >> 32), a_lo0 = (uint32_t)d0, b_lo0 = a_lo0 + (kATile >> 4);
+      int nblk = 0;
+      for (int item = blockIdx.x; item < items; item += gridDim.x) nblk += KB;
+      for (int it = 0; it < nblk; ++it) {
+        const uint32_t s = it % kGStages, b = it & 1;
+        if (!mbar_wait(full + s, (it / kGStages) & 1) || (it >= 2 && !mbar_wait(tempty + b, ((it >> 1) - 1) & 1))) {
+          dead = true;
+          break;
         }
+        tc_fence_after();
+        tc_mma_block(tmem + b * 256, a_lo0 + s * (kGStage >> 4), b_lo0 + s * (kGStage >> 4), d_hi, kIdesc);
+        tc_commit(empty + s);   // the stage is free when these MMAs have read it
+        tc_commit(tfull + b);   // and the block's partial sums are in TMEM
       }
     }
   } else if (warp >= 4) {
@@ -282,35 +297,48 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     const int ew = warp - 4, quarter = warp & 3, half = ew >> 2;
     const int trow = quarter * 32 + lane;  // the tile row (TMEM lane) of this thread
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    uint8_t* stg = outst + ew * (MODE == 0 ? 2048 : 4096);
     uint32_t it = 0, xn = 0;
-    for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
-      int e, row0, rend, nt;
-      locate(item, e, row0, rend, nt);
-      const int row = row0 + trow;
-      const bool live = row < rend;
-      const int srow = live ? row : row0;  // a safe row to read scales from
-      const float* sap = a.sa + (size_t)srow * KB;
-      const size_t sbase = (size_t)(a.wrow0 + e) * (a.N / 128) * KB;
-      const float* sb0p = MODE == 0 ? a.sb0 + sbase + (size_t)nt * KB : a.sb0 + sbase + (size_t)(2 * nt) * KB;
-      const float* sb1p = MODE == 0 ? a.sb1 + sbase + (size_t)nt * KB : a.sb0 + sbase + (size_t)(2 * nt + 1) * KB;
-      float2 acc0[32], acc1[32];  // columns [64 half, 64 half + 64) of the first and of the second 128, in pairs
-#pragma unroll
-      for (int c = 0; c < 32; ++c) acc0[c] = make_float2(0.f, 0.f), acc1[c] = make_float2(0.f, 0.f);
-      // the scales of a block are fetched two blocks ahead of their use
-      float pa[2], p0[2], p1[2];
+    int item = blockIdx.x;
+    int4 ti = item < items ? locate(item) : make_int4(0, 0, 0, 0);
+    // the scales of a block are fetched two blocks ahead of their use; those of a tile's first two blocks before the
+    // tail of the tile before
+    float pa[2], p0[2], p1[2];
+    auto scale_ptrs = [&](const int4& t, const float*& sap, const float*& sb0p, const float*& sb1p) {
+      const int row = t.y + trow;
+      sap = a.sa + (size_t)(row < t.z ? row : t.y) * KB;  // (a safe row for the rows past the segment's end)
+      const size_t sbase = (size_t)(a.wrow0 + t.x) * (a.N / 128) * KB;
+      sb0p = MODE == 0 ? a.sb0 + sbase + (size_t)t.w * KB : a.sb0 + sbase + (size_t)(2 * t.w) * KB;
+      sb1p = MODE == 0 ? a.sb1 + sbase + (size_t)t.w * KB : a.sb0 + sbase + (size_t)(2 * t.w + 1) * KB;
+    };
+    auto first_scales = [&](const int4& t) {
+      const float *sap, *sb0p, *sb1p;
+      scale_ptrs(t, sap, sb0p, sb1p);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int k = j < KB ? j : 0;
         pa[j] = __ldg(sap + k), p0[j] = __ldg(sb0p + k), p1[j] = __ldg(sb1p + k);
       }
+    };
+    if (item < items) first_scales(ti);
+    while (item < items && !dead) {
+      const int next = item + gridDim.x;
+      int4 tn = make_int4(0, 0, 0, 0);
+      if (next < items) tn = locate(next);  // in flight during this tile's blocks
+      const int row0 = ti.y, rend = ti.z, nt = ti.w;
+      const int row = row0 + trow;
+      const bool live = row < rend;
+      const int srow = live ? row : row0;
+      const float *sap, *sb0p, *sb1p;
+      scale_ptrs(ti, sap, sb0p, sb1p);
+      float2 acc0[32], acc1[32];  // columns [64 half, 64 half + 64) of the first and of the second 128, in pairs
+#pragma unroll
+      for (int c = 0; c < 32; ++c) acc0[c] = make_float2(0.f, 0.f), acc1[c] = make_float2(0.f, 0.f);
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const uint32_t b = it & 1;
         const float s0 = pa[0] * p0[0], s1 = pa[0] * p1[0];
         pa[0] = pa[1], p0[0] = p0[1], p1[0] = p1[1];
-        {
-          const int k = kb + 2 < KB ? kb + 2 : 0;
-          pa[1] = __ldg(sap + k), p0[1] = __ldg(sb0p + k), p1[1] = __ldg(sb1p + k);
-        }
+        if (kb + 2 < KB) pa[1] = __ldg(sap + kb + 2), p0[1] = __ldg(sb0p + kb + 2), p1[1] = __ldg(sb1p + kb + 2);
         if (!mbar_wait(tfull + b, (it >> 1) & 1)) {
           dead = true;
           break;
@@ -334,6 +362,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         promote32(acc1 + 16, q, s12);
       }
       if (dead) break;
+      if (next < items) first_scales(tn);  // in flight during the tail
       if (MODE == 0) {
         // g, u rounded to bf16; h = bf16(w_route * silu(g) * u); the tile's 128 channels are one quantisation group
         const float wr = a.wrow ? __ldg(a.wrow + srow) : 1.f;
@@ -359,26 +388,33 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         ++xn;
         const float sc = act_scale(fmaxf(ax[trow], ax[128 + trow]));
         const float rsc = __frcp_rn(sc);
-        if (live) {
-          uint4* dst = reinterpret_cast<uint4*>(a.hq + (size_t)row * a.N + nt * 128 + half * 64);
+        if (live && half == 0) a.hs[(size_t)row * (a.N / 128) + nt] = sc;
+        // the row's 64 bytes through the warp's staging (units of 16 B, swizzled by the row), then whole 64-byte row
+        // pieces a quarter warp: 8 rows a store instruction
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t wd[4];
+        for (int v = 0; v < 4; ++v) {
+          uint32_t wd[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int c = 8 * v + 2 * k;
-              wd[k] = quant2_e4m3(acc0[c].x, acc0[c].y, sc, rsc) | quant2_e4m3(acc0[c + 1].x, acc0[c + 1].y, sc, rsc) << 16;
-            }
-            dst[v] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          for (int k = 0; k < 4; ++k) {
+            const int c = 8 * v + 2 * k;
+            wd[k] = quant2_e4m3(acc0[c].x, acc0[c].y, sc, rsc) | quant2_e4m3(acc0[c + 1].x, acc0[c + 1].y, sc, rsc) << 16;
           }
-          if (half == 0) a.hs[(size_t)row * (a.N / 128) + nt] = sc;
+          *reinterpret_cast<uint4*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
         }
-      } else if (live) {
-        // every pick's output rounded to bf16
-        __nv_bfloat16* y0 = a.y + (size_t)row * a.N + nt * 256 + half * 64;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = 8 * i + (lane >> 2), u = lane & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 64 + ((u ^ ((rr >> 1) & 3)) << 4));
+          const int grow = row0 + quarter * 32 + rr;
+          if (grow < rend) *reinterpret_cast<uint4*>(a.hq + (size_t)grow * a.N + nt * 128 + half * 64 + u * 16) = v;
+        }
+        __syncwarp();
+      } else {
+        // every pick's output rounded to bf16; the row's 128 bytes of each column half through the warp's staging, then
+        // whole 128-byte lines: 4 rows a store instruction
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          uint4* dst = reinterpret_cast<uint4*>(y0 + hh * 128);
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             uint32_t wd[4];
@@ -388,10 +424,21 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
               const __nv_bfloat162 t = __float22bfloat162_rn(f);
               wd[k] = *reinterpret_cast<const uint32_t*>(&t);
             }
-            dst[v] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + (lane >> 3), u = lane & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((u ^ (rr & 7)) << 4));
+            const int grow = row0 + quarter * 32 + rr;
+            if (grow < rend)
+              *reinterpret_cast<uint4*>(a.y + (size_t)grow * a.N + nt * 256 + hh * 128 + half * 64 + u * 8) = v;
+          }
+          __syncwarp();
         }
       }
+      ti = tn, item = next;
     }
   }
   if (dead && lane == 0) atomicCAS(a.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
@@ -492,7 +539,7 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t K) {
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + 256 + 4 * 128 * 4;
+constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + kGCtl + kGStageOut;  // (UP: 16 KB staging + 2 KB maxima)
 
 template <int MODE>
 cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const GemmArgs& a,
@@ -551,6 +598,7 @@ size_t prefill_ws_bytes(int T, int H, int I, int E, int topk) {
   n += al256((size_t)T * I) + al256((size_t)T * IB * 4);                           // hq, hs (shared)
   n += al256(P * H * 2) + al256((size_t)T * H * 2);                                // y (routed), y (shared)
   n += 6 * al256(P * 4) + 2 * al256((size_t)(E + 1) * 4) + al256((size_t)(E + 1) * 4);  // sort outputs + tile offsets
+  n += al256((P / 128 + E + 1) * 16);                                              // tile table
   n += al256(sort_ws_bytes(T, topk, E));
   return n;
 }
@@ -578,6 +626,7 @@ PrefillWs prefill_ws_carve(void* ws, int T, int H, int I, int E, int topk) {
   w.counts = reinterpret_cast<int*>(p), p += al256((size_t)(E + 1) * 4);
   w.offsets = reinterpret_cast<int*>(p), p += al256((size_t)(E + 1) * 4);
   w.tile_off = reinterpret_cast<int*>(p), p += al256((size_t)(E + 1) * 4);
+  w.tile_info = reinterpret_cast<int4*>(p), p += al256((P / 128 + E + 1) * 16);
   w.sort_ws = p;
   return w;
 }
@@ -600,7 +649,7 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   // order, quantise, gather
   e = launch_sort_pack(q.idx, T, topk, E, w.counts, w.offsets, w.perm_tok, w.perm_slot, w.pos_of, w.row_order, w.sort_ws, st);
   if (e != cudaSuccess) return e;
-  k_tile_offsets<<<1, 32, 0, st>>>(w.counts, E, q.e_lo, q.e_hi, w.tile_off);
+  k_tile_offsets<<<1, 512, 0, st>>>(w.counts, w.offsets, E, q.e_lo, q.e_hi, w.tile_off, w.tile_info);
   {
     const size_t warps = (size_t)T * (H / 128);
     k_quant_rows<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(q.x, T, H, w.xq, w.xs);
@@ -612,7 +661,7 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   if (e != cudaSuccess) return e;
   }
   // routed gate/up
-  a.mode = 0, a.K = H, a.N = I, a.E = E, a.rows_total = P, a.wrow0 = 0, a.seg_off = w.offsets, a.tile_off = w.tile_off;
+  a.mode = 0, a.K = H, a.N = I, a.E = E, a.rows_total = P, a.wrow0 = 0, a.tile_off = w.tile_off, a.tile_info = w.tile_info;
   a.sa = w.xs_s, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = w.w_s, a.hq = w.hq, a.hs = w.hs, a.y = nullptr;
   if (q.parts != 2) e = launch_gemm<0>(mXs, mG, mU, a, st);
   if (e != cudaSuccess || q.parts == 1) return e;
@@ -622,7 +671,7 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   e = launch_gemm<1>(mHq, mD, mD, a, st);
   if (e != cudaSuccess || q.parts == 2) return e;
   if (q.has_shared) {
-    a.mode = 0, a.K = H, a.N = I, a.E = 1, a.rows_total = T, a.wrow0 = E, a.seg_off = nullptr, a.tile_off = nullptr;
+    a.mode = 0, a.K = H, a.N = I, a.E = 1, a.rows_total = T, a.wrow0 = E, a.tile_off = nullptr, a.tile_info = nullptr;
     a.sa = w.xs, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = nullptr, a.hq = w.hq_sh, a.hs = w.hs_sh, a.y = nullptr;
     e = launch_gemm<0>(mX, mG, mU, a, st);
     if (e != cudaSuccess) return e;
