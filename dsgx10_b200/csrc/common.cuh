@@ -40,9 +40,23 @@ DSGX_DEV bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// the non-blocking test of a phase
+DSGX_DEV bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait on a phase; false when the limit ran out.  sleep_ns > 0: back off between tries (for waits that are
-// expected to be long, so that the waiting warps leave the issue slots to the warps that work).
+// expected to be long, so that the waiting warps leave the issue slots to the warps that work).  A phase that is already
+// complete is seen by the non-blocking test, which costs a fraction of a try_wait.
 DSGX_DEV bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned sleep_ns = 0) {
+  if (mbar_test_wait(bar, parity)) return true;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {

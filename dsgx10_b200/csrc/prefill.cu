@@ -4,10 +4,12 @@
 //   k_quant_rows   x bf16 [T][H] -> e4m3 [T][H] + f32 scales [T][H/128] (once per token)
 //   k_gather_rows  the quantised rows, scales and routing weights into the (expert id, token) order of the sort
 //   k_tile_offsets prefix of the 128-row tiles per expert segment
-//   k_gemm_fp8     C = A B^T per 128-row tile: operands staged by TMA (128-byte swizzle) through a 4-stage ring,
-//                  tcgen05.mma kind::f8f6f4 M 128 x N 256 x K 32 issued by one thread, accumulators in TMEM (two
-//                  buffers of 256 columns); after every 128-k block the eight epilogue warps read the block's partial
-//                  sums with tcgen05.ld and promote them into f32 registers with the product of the row's activation
+//   k_gemm_fp8     C = A B^T per 256-row tile on a pair of CTAs (a cluster of two, tcgen05 cta_group::2): each CTA stages its
+//                  128 rows of A and half of B by TMA (128-byte swizzle) through a 6-stage ring, so every byte of B
+//                  crosses into shared memory once for 256 rows; tcgen05.mma kind::f8f6f4 M 256 x N 256 x K 32 issued
+//                  by one thread of the pair's first CTA, accumulators in both CTAs' TMEM (two buffers of 256 columns);
+//                  after every 128-k block each CTA's eight epilogue warps read the block's partial sums of their 128
+//                  rows with tcgen05.ld and promote them into f32 registers with the product of the row's activation
 //                  scale and the weight block's scale, while the next block's MMAs fill the other TMEM buffer.
 //                  UP:   B = 128 gate + 128 up channels; epilogue: bf16 rounding, SwiGLU, routing weight, bf16 h,
 //                        quantisation of the 128 channels (one scale group) to e4m3.
@@ -17,7 +19,8 @@
 // The weights are read from a K-major row-major copy ([expert][N][K] e4m3, scales [expert][N/128][K/128]) made once at
 // load time by k_retile_fp8 from the engine's tile_fp8 blocks (the reference re-tiles its checkpoints the same way:
 // ds41f engine/kernels/moe.cu:1187-1265, 1332-1336), because a TMA box wants whole rows.
-// No cluster multicast anywhere: every CTA fetches its own tiles (L2 serves the reuse).
+// No multicast load anywhere: every CTA fetches its own tiles (L2 serves the reuse between pairs); the only multicast is
+// the MMA thread's tcgen05.commit, which signals the barriers of both CTAs of its pair.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -34,13 +37,44 @@ DSGX_DEV void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uin
                "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
                : "memory");
 }
+// the load of one CTA of a pair: the completion may be signalled on the barrier of the pair's other CTA
+// (a shared::cluster address)
+DSGX_DEV void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
 DSGX_DEV void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+DSGX_DEV uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address of a shared-memory object of the cluster's CTA `rank`
+DSGX_DEV uint32_t map_to_rank(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+DSGX_DEV void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+DSGX_DEV void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 DSGX_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 DSGX_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-DSGX_DEV void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are complete
+DSGX_DEV void tc_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
 }
 DSGX_DEV void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -63,15 +97,15 @@ DSGX_DEV uint64_t umma_desc_sw128(const void* smem) {
   d |= (uint64_t)2 << 61;            // SWIZZLE_128B
   return d;
 }
-// instruction descriptor: f32 accumulate, e4m3 x e4m3, both K-major, M 128, N 256
-constexpr uint32_t kIdesc = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+// instruction descriptor: f32 accumulate, e4m3 x e4m3, both K-major, M 256 (128 rows in each CTA of the pair), N 256
+constexpr uint32_t kIdesc = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
 
 // warps 0..3: the producer group (warp 0 TMA, warp 1 MMA + TMEM, two spare), warps 4..11: epilogue.  After the set-up the
 // producer group gives registers back (40 a thread) and the epilogue warps take them (232 a thread): 384 x 168 in all.
 constexpr int kGThreads = 384;
 constexpr int kProdRegs = 40, kEpiRegs = 232;
-constexpr int kGStages = 4;
-constexpr int kATile = 128 * 128, kBTile = 256 * 128, kGStage = kATile + kBTile;
+constexpr int kGStages = 6;
+constexpr int kATile = 128 * 128, kGStage = 2 * kATile;  // a stage of one CTA: 128 rows of A, 128 of the 256 rows of B
 
 // ---- small kernels -------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_retile_fp8(const uint8_t* __restrict__ tiled, int N, int K, uint8_t* __restrict__ out) {
@@ -120,14 +154,15 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   if (c == 0) ws[pos] = w[(size_t)t * topk + perm_slot[pos]];
 }
 
-// The 128-row tiles of the ragged segments: tile_off [E + 1] the prefix of the tiles per expert (only this GPU's experts
-// [e_lo, e_hi) get tiles) and, per tile, tile_info = {expert, first row, end of the segment's rows, 0}.
+// The 256-row tiles (128 rows for each CTA of a pair) of the ragged segments: tile_off [E + 1] the prefix of the tiles per
+// expert (only this GPU's experts [e_lo, e_hi) get tiles) and, per tile, tile_info = {expert, first row, end of the
+// segment's rows, 0}.
 __global__ void __launch_bounds__(512) k_tile_offsets(const int* __restrict__ counts, const int* __restrict__ offsets, int E,
                                                       int e_lo, int e_hi, int* __restrict__ tile_off,
                                                       int4* __restrict__ tile_info) {
   __shared__ int pre[513];
   const int e = threadIdx.x;
-  const int mine = e < E && e >= e_lo && e < e_hi ? (counts[e] + 127) >> 7 : 0;
+  const int mine = e < E && e >= e_lo && e < e_hi ? (counts[e] + 255) >> 8 : 0;
   pre[e] = mine;
   __syncthreads();
   if (e == 0) {
@@ -141,7 +176,7 @@ __global__ void __launch_bounds__(512) k_tile_offsets(const int* __restrict__ co
   __syncthreads();
   if (e <= E) tile_off[e] = pre[e];
   if (e < E)
-    for (int t = 0; t < mine; ++t) tile_info[pre[e] + t] = make_int4(e, offsets[e] + t * 128, offsets[e + 1], 0);
+    for (int t = 0; t < mine; ++t) tile_info[pre[e] + t] = make_int4(e, offsets[e] + t * 256, offsets[e + 1], 0);
 }
 
 // ---- the grouped GEMM ---------------------------------------------------------------------------------------------
@@ -152,7 +187,7 @@ struct GemmArgs {
   int E;               // segments (1 for the shared expert's dense pass)
   int rows_total;      // rows of A
   int wrow0;           // first weight row block: expert e's rows start at (wrow0 + e) * N in the weight tensors
-  const int* tile_off;   // [E + 1] 128-row tile prefix of the ragged segments (null: one segment [0, rows_total))
+  const int* tile_off;   // [E + 1] 256-row tile prefix of the ragged segments (null: one segment [0, rows_total))
   const int4* tile_info; // per tile {segment, first row, row end, 0} (null with tile_off null)
   const float* sa;     // [rows_total][K / 128] activation scales
   const float* sb0;    // UP: gate scales, DOWN: down scales; [.. experts][N / 128][K / 128]
@@ -181,18 +216,19 @@ DSGX_DEV uint32_t quant2_e4m3(float v0, float v1, float s, float y) {
 // The four MMAs of one 128-k block (K 32 each: the start address moves by 2 x 16 B along the swizzled row), the first
 // overwriting the accumulator.  Descriptors as (low word, high word); one asm statement, so that nothing is scheduled
 // between the issues.
+// cta_group::2: the pair's 256 x 256 tile; A and the accumulator split by rows, B by rows of N, between the two CTAs.
 DSGX_DEV void tc_mma_block(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t d_hi, uint32_t idesc) {
   asm volatile(
       "{\n\t.reg .pred p0, p1;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
       "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
       "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p0;\n\t"
       "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
       "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p1;\n\t"
       "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p1;\n\t}" ::"r"(tmem_d),
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p1;\n\t}" ::"r"(tmem_d),
       "r"(a_lo), "r"(b_lo), "r"(d_hi), "r"(idesc)
       : "memory");
 }
@@ -218,31 +254,36 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
   float* amax_x = reinterpret_cast<float*>(outst + 8 * 2048);  // UP: [2 buffers][2 halves][128 rows]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  // The pair: CTA 0 (the leader) issues the MMAs of both; its `full` and `tempty` barriers collect the loads and the
+  // epilogue warps of both CTAs; `empty`, `tfull` exist in both CTAs and are signalled by the leader's commits.
+  const uint32_t rank = cluster_rank();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGStages; ++s) mbar_init(full + s, 1), mbar_init(empty + s, 1);
-    for (int b = 0; b < 2; ++b) mbar_init(tfull + b, 1), mbar_init(tempty + b, 8);
+    for (int b = 0; b < 2; ++b) mbar_init(tfull + b, 1), mbar_init(tempty + b, 16);
     mbar_init(xbar, 8);
     mbar_fence_init();
   }
-  if (warp == 1) {  // 512 TMEM columns: two accumulator buffers of 256
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {  // 512 TMEM columns in each CTA: two accumulator buffers of 256
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // the other CTA's barriers are initialised before anything is signalled there
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
   const int KB = a.K / 128;
   const int ntn = MODE == 0 ? a.N / 128 : a.N / 256;  // n-tiles
-  const int mtiles = a.tile_off ? __ldg(a.tile_off + a.E) : (a.rows_total + 127) / 128;
+  const int mtiles = a.tile_off ? __ldg(a.tile_off + a.E) : (a.rows_total + 255) / 256;
   const int items = mtiles * ntn;
+  const int first = blockIdx.x >> 1, stride = gridDim.x >> 1;  // items go round the pairs
   bool dead = false;
 
   // item -> {segment, first row, row end, n-tile}: one load
   auto locate = [&](int item) -> int4 {
     const int mt = item / ntn;
-    int4 r = a.tile_info ? __ldg(a.tile_info + mt) : make_int4(0, mt * 128, a.rows_total, 0);
+    int4 r = a.tile_info ? __ldg(a.tile_info + mt) : make_int4(0, mt * 256, a.rows_total, 0);
     r.w = item - mt * ntn;
     return r;
   };
@@ -250,11 +291,16 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProdRegs));
   if (warp == 0) {
     // ---------------------------------------------------------------------------------------------- TMA producer
+    // Each CTA loads its 128 rows of A and its half of B (UP: the leader the gate rows, the other CTA the up rows; DOWN:
+    // 128 of the 256 output channels each); every load signals the leader's barrier, which expects both CTAs' bytes.
     if (lane == 0) {
+      const uint32_t full_leader = map_to_rank(full, 0);
+      const CUtensorMap* mapB = MODE == 0 && rank ? &mapB1 : &mapB0;
       uint32_t it = 0;
-      for (int item = blockIdx.x; item < items && !dead; item += gridDim.x) {
+      for (int item = first; item < items && !dead; item += stride) {
         const int4 ti = locate(item);
-        const int wr = (a.wrow0 + ti.x) * a.N + ti.w * (MODE == 0 ? 128 : 256);
+        const int arow = ti.y + (int)rank * 128;
+        const int brow = (a.wrow0 + ti.x) * a.N + ti.w * (MODE == 0 ? 128 : 256) + (MODE == 0 ? 0 : (int)rank * 128);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % kGStages;
           if (it >= kGStages && !mbar_wait(empty + s, ((it / kGStages) - 1) & 1)) {
@@ -262,10 +308,9 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
             break;
           }
           uint8_t* st = smem + s * kGStage;
-          mbar_expect_tx(full + s, kGStage);
-          tma_load_2d(st, &mapA, kb * 128, ti.y, full + s);
-          tma_load_2d(st + kATile, &mapB0, kb * 128, wr, full + s);
-          tma_load_2d(st + kATile + kATile, MODE == 0 ? &mapB1 : &mapB0, kb * 128, MODE == 0 ? wr : wr + 128, full + s);
+          if (rank == 0) mbar_expect_tx(full + s, 2 * kGStage);
+          tma_load_2d_pair(st, &mapA, kb * 128, arow, full_leader + s * 8);
+          tma_load_2d_pair(st + kATile, mapB, kb * 128, brow, full_leader + s * 8);
         }
       }
     }
@@ -274,11 +319,11 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     // One thread; the tensor pipe takes an MMA only when the one before has gone in, so whatever this thread does
     // between two blocks is time the pipe may idle: the loop is kept to two barrier waits, one asm statement of four
     // MMAs and two commits.
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       const uint64_t d0 = umma_desc_sw128(smem);
       const uint32_t d_hi = (uint32_t)(d0 >> 32), a_lo0 = (uint32_t)d0, b_lo0 = a_lo0 + (kATile >> 4);
       int nblk = 0;
-      for (int item = blockIdx.x; item < items; item += gridDim.x) nblk += KB;
+      for (int item = first; item < items; item += stride) nblk += KB;
       for (int it = 0; it < nblk; ++it) {
         const uint32_t s = it % kGStages, b = it & 1;
         if (!mbar_wait(full + s, (it / kGStages) & 1) || (it >= 2 && !mbar_wait(tempty + b, ((it >> 1) - 1) & 1))) {
@@ -287,25 +332,27 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         }
         tc_fence_after();
         tc_mma_block(tmem + b * 256, a_lo0 + s * (kGStage >> 4), b_lo0 + s * (kGStage >> 4), d_hi, kIdesc);
-        tc_commit(empty + s);   // the stage is free when these MMAs have read it
-        tc_commit(tfull + b);   // and the block's partial sums are in TMEM
+        tc_commit_pair(empty + s);   // the stage is free (in both CTAs) when these MMAs have read it
+        tc_commit_pair(tfull + b);   // and the block's partial sums are in both CTAs' TMEM
       }
     }
   } else if (warp >= 4) {
     // -------------------------------------------------------------------------------------------------- epilogue
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpiRegs));
     const int ew = warp - 4, quarter = warp & 3, half = ew >> 2;
-    const int trow = quarter * 32 + lane;  // the tile row (TMEM lane) of this thread
+    const int trow = quarter * 32 + lane;  // the row of this CTA's 128 (TMEM lane) of this thread
+    const int crow = (int)rank * 128;      // this CTA's first row in the pair's tile
+    const uint32_t tempty_leader = map_to_rank(tempty, 0);
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     uint8_t* stg = outst + ew * (MODE == 0 ? 2048 : 4096);
     uint32_t it = 0, xn = 0;
-    int item = blockIdx.x;
+    int item = first;
     int4 ti = item < items ? locate(item) : make_int4(0, 0, 0, 0);
     // the scales of a block are fetched two blocks ahead of their use; those of a tile's first two blocks before the
     // tail of the tile before
     float pa[2], p0[2], p1[2];
     auto scale_ptrs = [&](const int4& t, const float*& sap, const float*& sb0p, const float*& sb1p) {
-      const int row = t.y + trow;
+      const int row = t.y + crow + trow;
       sap = a.sa + (size_t)(row < t.z ? row : t.y) * KB;  // (a safe row for the rows past the segment's end)
       const size_t sbase = (size_t)(a.wrow0 + t.x) * (a.N / 128) * KB;
       sb0p = MODE == 0 ? a.sb0 + sbase + (size_t)t.w * KB : a.sb0 + sbase + (size_t)(2 * t.w) * KB;
@@ -322,13 +369,13 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     };
     if (item < items) first_scales(ti);
     while (item < items && !dead) {
-      const int next = item + gridDim.x;
+      const int next = item + stride;
       int4 tn = make_int4(0, 0, 0, 0);
       if (next < items) tn = locate(next);  // in flight during this tile's blocks
-      const int row0 = ti.y, rend = ti.z, nt = ti.w;
+      const int row0 = ti.y + crow, rend = ti.z, nt = ti.w;
       const int row = row0 + trow;
       const bool live = row < rend;
-      const int srow = live ? row : row0;
+      const int srow = live ? row : ti.y;
       const float *sap, *sb0p, *sb1p;
       scale_ptrs(ti, sap, sb0p, sb1p);
       float2 acc0[32], acc1[32];  // columns [64 half, 64 half + 64) of the first and of the second 128, in pairs
@@ -357,7 +404,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty + b);  // the buffer is free for the MMAs of the block after next
+        if (lane == 0) mbar_arrive_cluster(tempty_leader + b * 8);  // the buffer is free for the MMAs of the block after next
         promote32(acc1, r, s12);
         promote32(acc1 + 16, q, s12);
       }
@@ -444,7 +491,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
   if (dead && lane == 0) atomicCAS(a.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+  cluster_sync_all();  // neither CTA leaves while the other may still read its shared memory or signal its barriers
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
 // ---- combine ------------------------------------------------------------------------------------------------------
@@ -541,19 +589,30 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t K) {
 
 constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + kGCtl + kGStageOut;  // (UP: 16 KB staging + 2 KB maxima)
 
+// CTA pairs (clusters of two), one pair for two SMs: as many pairs as the device keeps resident at once.
 template <int MODE>
 cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const GemmArgs& a,
                         cudaStream_t st) {
-  static bool done[64] = {false};
+  static int pairs[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!done[dev & 63]) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kGThreads), cfg.dynamicSmemBytes = kGemmSmem, cfg.stream = st, cfg.attrs = at, cfg.numAttrs = 1;
+  if (!pairs[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(k_gemm_fp8<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
     if (e != cudaSuccess) return e;
-    done[dev & 63] = true;
+    int n = 0;
+    cfg.gridDim = dim3(sm_count() / 2 * 2);
+    e = cudaOccupancyMaxActiveClusters(&n, k_gemm_fp8<MODE>, &cfg);
+    if (e != cudaSuccess) return e;
+    if (n < 1) return cudaErrorLaunchOutOfResources;
+    pairs[dev & 63] = n < sm_count() / 2 ? n : sm_count() / 2;
   }
-  k_gemm_fp8<MODE><<<sm_count(), kGThreads, kGemmSmem, st>>>(mA, mB0, mB1, a);
-  return cudaGetLastError();
+  cfg.gridDim = dim3(2 * pairs[dev & 63]);
+  return cudaLaunchKernelEx(&cfg, k_gemm_fp8<MODE>, mA, mB0, mB1, a);
 }
 
 size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
