@@ -23,6 +23,8 @@
 // the MMA thread's tcgen05.commit, which signals the barriers of both CTAs of its pair.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -46,6 +48,17 @@ DSGX_DEV void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1
       "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
       : "memory");
 }
+// shared -> global store of one box (bulk group of the issuing thread)
+DSGX_DEV void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(src)),
+               "r"(c0), "r"(c1)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// the issuing thread's earlier stores have read their shared-memory source
+DSGX_DEV void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+DSGX_DEV void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+DSGX_DEV void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 DSGX_DEV void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -104,7 +117,7 @@ constexpr uint32_t kIdesc = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24
 // producer group gives registers back (40 a thread) and the epilogue warps take them (232 a thread): 384 x 168 in all.
 constexpr int kGThreads = 384;
 constexpr int kProdRegs = 40, kEpiRegs = 232;
-constexpr int kGStages = 6;
+constexpr int kGStages = 5;
 constexpr int kATile = 128 * 128, kGStage = 2 * kATile;  // a stage of one CTA: 128 rows of A, 128 of the 256 rows of B
 
 // ---- small kernels -------------------------------------------------------------------------------------------------
@@ -213,6 +226,16 @@ DSGX_DEV uint32_t quant2_e4m3(float v0, float v1, float s, float y) {
   const float d0 = __fmaf_rn(__fmaf_rn(-q0, s, v0), y, q0), d1 = __fmaf_rn(__fmaf_rn(-q1, s, v1), y, q1);
   return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(d0, d1), __NV_SATFINITE, __NV_E4M3);
 }
+// silu with the fast exponential and division (2 ulp each): the result is rounded to bf16 two operations later
+DSGX_DEV float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+// two floats rounded to bf16 (the values, as floats)
+DSGX_DEV float2 bf16_round2(float2 v) { return __bfloat1622float2(__float22bfloat162_rn(v)); }
+// acc[c] = part[c] * s: the first block of a tile
+DSGX_DEV void promote32_first(float2* acc, const uint32_t (&part)[32], float2 s) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c)
+    acc[c] = __fmul2_rn(make_float2(__uint_as_float(part[2 * c]), __uint_as_float(part[2 * c + 1])), s);
+}
 // The four MMAs of one 128-k block (K 32 each: the start address moves by 2 x 16 B along the swizzled row), the first
 // overwriting the accumulator.  Descriptors as (low word, high word); one asm statement, so that nothing is scheduled
 // between the issues.
@@ -233,15 +256,18 @@ DSGX_DEV void tc_mma_block(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32
       : "memory");
 }
 
-// Shared memory behind the operand ring: barriers, the TMEM address, and the epilogue warps' staging (UP: the row maxima
-// of the two column halves and 2 KB a warp for the e4m3 rows; DOWN: 4 KB a warp for the bf16 rows).
-constexpr int kGCtl = 256;
-constexpr int kGStageOut = 8 * 4096;
+// Shared memory behind the operand ring: barriers, the TMEM address, and the epilogue warps' staging (UP: 2 KB a warp for
+// the e4m3 rows, then the row maxima of the two column halves; DOWN: two buffers of 4 KB a warp for the bf16 rows of the
+// two column halves).  The staging is laid out as the TMA swizzles want it (64-byte rows: SWIZZLE_64B, 128-byte rows:
+// SWIZZLE_128B), which is also free of bank conflicts for a row a lane.
+constexpr int kGCtl = 1024;
+constexpr int kGStageOut = 8 * 8192;
 
 template <int MODE>
 __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant__ CUtensorMap mapA,
                                                           const __grid_constant__ CUtensorMap mapB0,
-                                                          const __grid_constant__ CUtensorMap mapB1, const GemmArgs a) {
+                                                          const __grid_constant__ CUtensorMap mapB1,
+                                                          const __grid_constant__ CUtensorMap mapOut, const GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGStages * kGStage);
@@ -344,7 +370,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     const int crow = (int)rank * 128;      // this CTA's first row in the pair's tile
     const uint32_t tempty_leader = map_to_rank(tempty, 0);
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    uint8_t* stg = outst + ew * (MODE == 0 ? 2048 : 4096);
+    uint8_t* stg = outst + ew * (MODE == 0 ? 2048 : 8192);
     uint32_t it = 0, xn = 0;
     int item = first;
     int4 ti = item < items ? locate(item) : make_int4(0, 0, 0, 0);
@@ -379,16 +405,16 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
       const float *sap, *sb0p, *sb1p;
       scale_ptrs(ti, sap, sb0p, sb1p);
       float2 acc0[32], acc1[32];  // columns [64 half, 64 half + 64) of the first and of the second 128, in pairs
-#pragma unroll
-      for (int c = 0; c < 32; ++c) acc0[c] = make_float2(0.f, 0.f), acc1[c] = make_float2(0.f, 0.f);
-      for (int kb = 0; kb < KB; ++kb, ++it) {
+      // one 128-k block; the tile's first block writes the accumulators (no zeroing pass)
+      auto block = [&](auto first_tag, int kb) {
+        constexpr bool kFirst = decltype(first_tag)::value;
         const uint32_t b = it & 1;
         const float s0 = pa[0] * p0[0], s1 = pa[0] * p1[0];
         pa[0] = pa[1], p0[0] = p0[1], p1[0] = p1[1];
         if (kb + 2 < KB) pa[1] = __ldg(sap + kb + 2), p0[1] = __ldg(sb0p + kb + 2), p1[1] = __ldg(sb1p + kb + 2);
         if (!mbar_wait(tfull + b, (it >> 1) & 1)) {
           dead = true;
-          break;
+          return;
         }
         tc_fence_after();
         const uint32_t t0 = tmem + lane_addr + b * 256 + half * 64;
@@ -397,31 +423,39 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         tc_ld32(t0, r);
         tc_ld32(t0 + 32, q);
         tc_wait_ld();
-        promote32(acc0, r, s02);
+        if (kFirst) promote32_first(acc0, r, s02);
+        else promote32(acc0, r, s02);
         tc_ld32(t0 + 128, r);
-        promote32(acc0 + 16, q, s02);
+        if (kFirst) promote32_first(acc0 + 16, q, s02);
+        else promote32(acc0 + 16, q, s02);
         tc_ld32(t0 + 160, q);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(tempty_leader + b * 8);  // the buffer is free for the MMAs of the block after next
-        promote32(acc1, r, s12);
-        promote32(acc1 + 16, q, s12);
-      }
+        if (kFirst) promote32_first(acc1, r, s12), promote32_first(acc1 + 16, q, s12);
+        else promote32(acc1, r, s12), promote32(acc1 + 16, q, s12);
+        ++it;
+      };
+      block(std::true_type{}, 0);
+      for (int kb = 1; kb < KB && !dead; ++kb) block(std::false_type{}, kb);
       if (dead) break;
       if (next < items) first_scales(tn);  // in flight during the tail
+      const bool warp_live = row0 + quarter * 32 + 31 < rend;  // all 32 rows of this warp: one TMA store; else row by row
+      if (lane == 0) tma_store_wait_read();  // the staging is free of the stores of the tile before
+      __syncwarp();
       if (MODE == 0) {
         // g, u rounded to bf16; h = bf16(w_route * silu(g) * u); the tile's 128 channels are one quantisation group
         const float wr = a.wrow ? __ldg(a.wrow + srow) : 1.f;
         float am = 0.f;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          float h0 = __fmul_rn(silu(bf16_round(acc0[c].x)), bf16_round(acc1[c].x));
-          float h1 = __fmul_rn(silu(bf16_round(acc0[c].y)), bf16_round(acc1[c].y));
-          if (a.wrow) h0 = __fmul_rn(wr, h0), h1 = __fmul_rn(wr, h1);
-          h0 = bf16_round(h0), h1 = bf16_round(h1);
-          acc0[c] = make_float2(h0, h1);
-          am = fmaxf(am, fmaxf(fabsf(h0), fabsf(h1)));
+          const float2 g = bf16_round2(acc0[c]), u = bf16_round2(acc1[c]);
+          float2 h = make_float2(__fmul_rn(silu_fast(g.x), u.x), __fmul_rn(silu_fast(g.y), u.y));
+          if (a.wrow) h = make_float2(__fmul_rn(wr, h.x), __fmul_rn(wr, h.y));
+          h = bf16_round2(h);
+          acc0[c] = h;
+          am = fmaxf(am, fmaxf(fabsf(h.x), fabsf(h.y)));
         }
         // the other half's maximum: through shared memory, two buffers by item parity, one bounded barrier an item
         float* ax = amax_x + (xn & 1) * 256;
@@ -436,8 +470,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         const float sc = act_scale(fmaxf(ax[trow], ax[128 + trow]));
         const float rsc = __frcp_rn(sc);
         if (live && half == 0) a.hs[(size_t)row * (a.N / 128) + nt] = sc;
-        // the row's 64 bytes through the warp's staging (units of 16 B, swizzled by the row), then whole 64-byte row
-        // pieces a quarter warp: 8 rows a store instruction
+        // the row's 64 bytes into the warp's staging (16-byte units, the 64-byte swizzle)
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint32_t wd[4];
@@ -448,20 +481,26 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
           }
           *reinterpret_cast<uint4*>(stg + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
         }
+        fence_async_smem();
         __syncwarp();
+        if (warp_live) {
+          if (lane == 0) tma_store_2d(&mapOut, nt * 128 + half * 64, row0 + quarter * 32, stg);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int rr = 8 * i + (lane >> 2), u = lane & 3;
-          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 64 + ((u ^ ((rr >> 1) & 3)) << 4));
-          const int grow = row0 + quarter * 32 + rr;
-          if (grow < rend) *reinterpret_cast<uint4*>(a.hq + (size_t)grow * a.N + nt * 128 + half * 64 + u * 16) = v;
+          for (int i = 0; i < 4; ++i) {  // whole 64-byte row pieces a quarter warp: 8 rows a store instruction
+            const int rr = 8 * i + (lane >> 2), u = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 64 + ((u ^ ((rr >> 1) & 3)) << 4));
+            const int grow = row0 + quarter * 32 + rr;
+            if (grow < rend) *reinterpret_cast<uint4*>(a.hq + (size_t)grow * a.N + nt * 128 + half * 64 + u * 16) = v;
+          }
+          __syncwarp();
         }
-        __syncwarp();
       } else {
-        // every pick's output rounded to bf16; the row's 128 bytes of each column half through the warp's staging, then
-        // whole 128-byte lines: 4 rows a store instruction
+        // every pick's output rounded to bf16; the row's 128 bytes of each column half into the warp's staging (16-byte
+        // units, the 128-byte swizzle), one buffer a half
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
+          uint8_t* sb = stg + hh * 4096;
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             uint32_t wd[4];
@@ -471,22 +510,28 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
               const __nv_bfloat162 t = __float22bfloat162_rn(f);
               wd[k] = *reinterpret_cast<const uint32_t*>(&t);
             }
-            *reinterpret_cast<uint4*>(stg + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            *reinterpret_cast<uint4*>(sb + lane * 128 + ((v ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
+          fence_async_smem();
           __syncwarp();
+          if (warp_live) {
+            if (lane == 0) tma_store_2d(&mapOut, nt * 256 + hh * 128 + half * 64, row0 + quarter * 32, sb);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = 4 * i + (lane >> 3), u = lane & 7;
-            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((u ^ (rr & 7)) << 4));
-            const int grow = row0 + quarter * 32 + rr;
-            if (grow < rend)
-              *reinterpret_cast<uint4*>(a.y + (size_t)grow * a.N + nt * 256 + hh * 128 + half * 64 + u * 8) = v;
+            for (int i = 0; i < 8; ++i) {  // whole 128-byte lines: 4 rows a store instruction
+              const int rr = 4 * i + (lane >> 3), u = lane & 7;
+              const uint4 v = *reinterpret_cast<const uint4*>(sb + rr * 128 + ((u ^ (rr & 7)) << 4));
+              const int grow = row0 + quarter * 32 + rr;
+              if (grow < rend)
+                *reinterpret_cast<uint4*>(a.y + (size_t)grow * a.N + nt * 256 + hh * 128 + half * 64 + u * 8) = v;
+            }
+            __syncwarp();
           }
-          __syncwarp();
         }
       }
       ti = tn, item = next;
     }
+    if (lane == 0) tma_store_wait_all();
   }
   if (dead && lane == 0) atomicCAS(a.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
   tc_fence_before();
@@ -587,12 +632,26 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t K) {
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + kGCtl + kGStageOut;  // (UP: 16 KB staging + 2 KB maxima)
+// the epilogue's output boxes of 32 rows: e4m3 h (64 bytes a row, SWIZZLE_64B) or bf16 y (64 values = 128 bytes a row,
+// SWIZZLE_128B)
+bool make_map_out(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, bool bf16) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * (bf16 ? 2 : 1)};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t es[2] = {1, 1};
+  return fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+            box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + kGCtl + kGStageOut;  // (UP uses 16 KB + 2 KB of the 64 KB)
 
 // CTA pairs (clusters of two), one pair for two SMs: as many pairs as the device keeps resident at once.
 template <int MODE>
-cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const GemmArgs& a,
-                        cudaStream_t st) {
+cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const CUtensorMap& mOut,
+                        const GemmArgs& a, cudaStream_t st) {
   static int pairs[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -612,7 +671,7 @@ cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUt
     pairs[dev & 63] = n < sm_count() / 2 ? n : sm_count() / 2;
   }
   cfg.gridDim = dim3(2 * pairs[dev & 63]);
-  return cudaLaunchKernelEx(&cfg, k_gemm_fp8<MODE>, mA, mB0, mB1, a);
+  return cudaLaunchKernelEx(&cfg, k_gemm_fp8<MODE>, mA, mB0, mB1, mOut, a);
 }
 
 size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -695,11 +754,13 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   const int T = q.T, H = q.H, I = q.I, E = q.E, topk = q.topk, P = T * topk;
   const PrefillWs& w = q.ws;
   const PrefillWeights& pw = q.pw;
-  CUtensorMap mX, mXs, mHq, mHsh, mG, mU, mD;
+  CUtensorMap mX, mXs, mHq, mHsh, mG, mU, mD, oHq, oHsh, oY, oYsh;
   const uint64_t nexp = (uint64_t)E + 1;
   if (!make_map(&mX, w.xq, T, H) || !make_map(&mXs, w.xq_s, P, H) || !make_map(&mHq, w.hq, P, I) ||
       !make_map(&mHsh, w.hq_sh, T, I) || !make_map(&mG, pw.g, nexp * I, H) || !make_map(&mU, pw.u, nexp * I, H) ||
-      !make_map(&mD, pw.d, nexp * H, I))
+      !make_map(&mD, pw.d, nexp * H, I) || !make_map_out(&oHq, w.hq, P, I, false) ||
+      !make_map_out(&oHsh, w.hq_sh, T, I, false) || !make_map_out(&oY, w.y, P, H, true) ||
+      !make_map_out(&oYsh, w.y_sh, T, H, true))
     return cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
   GemmArgs a;
@@ -722,20 +783,20 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   // routed gate/up
   a.mode = 0, a.K = H, a.N = I, a.E = E, a.rows_total = P, a.wrow0 = 0, a.tile_off = w.tile_off, a.tile_info = w.tile_info;
   a.sa = w.xs_s, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = w.w_s, a.hq = w.hq, a.hs = w.hs, a.y = nullptr;
-  if (q.parts != 2) e = launch_gemm<0>(mXs, mG, mU, a, st);
+  if (q.parts != 2) e = launch_gemm<0>(mXs, mG, mU, oHq, a, st);
   if (e != cudaSuccess || q.parts == 1) return e;
   // routed down
   a.mode = 1, a.K = I, a.N = H, a.sa = w.hs, a.sb0 = pw.sd, a.sb1 = nullptr, a.wrow = nullptr, a.hq = nullptr, a.hs = nullptr;
   a.y = w.y;
-  e = launch_gemm<1>(mHq, mD, mD, a, st);
+  e = launch_gemm<1>(mHq, mD, mD, oY, a, st);
   if (e != cudaSuccess || q.parts == 2) return e;
   if (q.has_shared) {
     a.mode = 0, a.K = H, a.N = I, a.E = 1, a.rows_total = T, a.wrow0 = E, a.tile_off = nullptr, a.tile_info = nullptr;
     a.sa = w.xs, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = nullptr, a.hq = w.hq_sh, a.hs = w.hs_sh, a.y = nullptr;
-    e = launch_gemm<0>(mX, mG, mU, a, st);
+    e = launch_gemm<0>(mX, mG, mU, oHsh, a, st);
     if (e != cudaSuccess) return e;
     a.mode = 1, a.K = I, a.N = H, a.sa = w.hs_sh, a.sb0 = pw.sd, a.hq = nullptr, a.hs = nullptr, a.y = w.y_sh;
-    e = launch_gemm<1>(mHsh, mD, mD, a, st);
+    e = launch_gemm<1>(mHsh, mD, mD, oYsh, a, st);
     if (e != cudaSuccess) return e;
   }
   const size_t n = (size_t)T * (H / 8);
