@@ -309,7 +309,9 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
   // item -> {segment, first row, row end, n-tile}: one load
   auto locate = [&](int item) -> int4 {
     const int mt = item / ntn;
-    int4 r = a.tile_info ? __ldg(a.tile_info + mt) : make_int4(0, mt * 256, a.rows_total, 0);
+    int4 r = make_int4(0, mt * 256, a.rows_total, 0);
+    if (a.tile_info)  // (a volatile asm: the load is issued here, not where its result is first used)
+      asm volatile("ld.global.nc.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(a.tile_info + mt));
     r.w = item - mt * ntn;
     return r;
   };
