@@ -298,7 +298,9 @@ def run_gpu(args):
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
                      "us_per_launch": us_up, "algorithmic_bytes": upb, "traffic": None},
         "e2e": {"value": us_e2e, "unit": "us", "h2d_bytes_per_step": rows * H * 2, "d2h_bytes_per_step": rows * H * 2},
-        "gpu_launches": args.steps * 6,
+        # this library's kernels a step: the one persistent kernel from three rows (or --fused), else front, route, gate/up,
+        # down; with several GPUs also the rounding kernel after the all-reduce
+        "gpu_launches": args.steps * ((1 if (args.fused or (rows >= 3 and not args.separate)) else 4) + (1 if world > 1 else 0)),
         "clocks": clocks,
         "device_status": status,
     }
@@ -309,10 +311,205 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-def cpu_baseline(rows):
+# ------------------------------------------------------------------------------------------- prefill workload (GPU)
+
+PF = dict(H=2048, I=1024, E=64, topk=6)   # the small layer's shapes: 16384 tokens, Zipf(1.1) expert popularity
+
+
+def prefill_flops(T):
+    """Useful FLOPs of the expert pass: every pick and the shared expert through three H x I matrices."""
+    return T * (PF["topk"] + 1) * 3 * PF["H"] * PF["I"] * 2
+
+
+def run_prefill_reference(args):
+    """The oracle port on the host cores over a bounded sample of the same token stream (64 tokens a step)."""
+    import numpy as np
+    from dsgx10_b200 import synth
+    from oracle import oracle as orc
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    H, I, E, topk = PF["H"], PF["I"], PF["E"], PF["topk"]
+    Ts = 64
+    lay = synth.Fp8Layer(H, I, E, SEED, device="cpu")
+    x = synth.bf16_bits(synth.activations(Ts, H, SEED + 1000))
+    wr = synth.router_weights(E, H, SEED + 2000).numpy()
+    experts = {e: lay.canonical(e) for e in range(E)}
+    shared = lay.canonical(E)
+
+    def one():
+        lg = orc.router_logits(x, wr)
+        ii, ww = orc.route(lg, None, topk, 0, 1, 1, True, 1.0)
+        picked = {int(e) for e in ii.ravel()}
+        return orc.moe_fp8_layer(x, ii, ww, {e: experts[e] for e in picked}, shared)
+
+    one()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    dt = (time.perf_counter() - t0) / steps
+    tf = prefill_flops(Ts) / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "moe_prefill_grouped_gemm_tflops", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
+        "config": {"workload": "config 4: prefill MoE, hidden 2048, 64 experts x 1024, top-6, + shared expert", "tokens": Ts},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": orc.num_threads(), "kind": "port",
+                         "sample": f"{steps} passes of {Ts} tokens through the C oracle (OpenMP)"},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": Ts / dt,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_prefill(args):
+    """Config 4: one layer's prefill over `--tokens` tokens whose expert popularity follows Zipf(1.1) (a router bias
+    calibrated so that the realised pick histogram matches), experts sharded over the ranks, partial sums all-reduced."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from dsgx10_b200 import _lib, moe, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this library has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+    H, I, E, topk = PF["H"], PF["I"], PF["E"], PF["topk"]
+    T = args.tokens
+    e_lo, e_hi = rank * E // world, (rank + 1) * E // world
+    shp_all = moe.shape(H, I, E, topk)
+    shp = moe.shape(H, I, E, topk, e_lo=e_lo, e_hi=e_hi)
+    lay = synth.Fp8Layer(H, I, E, SEED, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+    NX = 3  # distinct activation sets: 3 x 67 MB of inputs, and ~1.5 GB of intermediates a pass: nothing stays in L2
+    xs = [synth.activations(T, H, SEED + 1000 + i, device="cpu").to(dev) for i in range(NX)]
+    xs_host = [x.cpu().pin_memory() for x in xs]
+    out_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    wr = synth.router_weights(E, H, SEED + 2000, device="cpu").to(dev)
+    logits0 = moe.router_logits(xs[0], wr)
+
+    def counts_for(b):
+        idx, _ = moe.route(shp_all, logits0, torch.from_numpy(b).to(dev))
+        return torch.bincount(idx.flatten().long(), minlength=E).cpu().numpy()
+    alpha, b, counts = synth.calibrate_zipf_bias(counts_for, E, topk, SEED + 7)
+    bias = torch.from_numpy(b).to(dev)
+    pl = moe.PrefillLayer(shp, lay.layer_w(), T, device=dev)
+    routed = []
+    for x in xs:
+        lg = moe.router_logits(x, wr)
+        routed.append(moe.route(shp_all, lg, bias))
+    f32 = dict(dtype=torch.float32, device=dev)
+    yr, ys = torch.empty(T, H, **f32), torch.zeros(T, H, **f32)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    x_stage = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+    def experts(i):
+        idx, w = routed[i % NX]
+        pl.run(xs[i % NX], idx, w, yr=yr, ys=ys, out=out)
+        if world > 1:
+            dist.all_reduce(yr)
+            dist.all_reduce(ys)
+            out.copy_(moe.finalize(yr, ys))
+
+    def whole(i):  # end to end: host activations in, router, experts, host bf16 out
+        x_stage.copy_(xs_host[i % NX], non_blocking=True)
+        lg = moe.router_logits(x_stage, wr)
+        idx, w = moe.route(shp_all, lg, bias)
+        pl.run(x_stage, idx, w, yr=yr, ys=ys, out=out)
+        if world > 1:
+            dist.all_reduce(yr)
+            dist.all_reduce(ys)
+            out.copy_(moe.finalize(yr, ys))
+        out_host.copy_(out, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / n
+
+    W = max(args.warmup, 3)
+    for i in range(W):
+        experts(i)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(experts, args.steps)
+    for i in range(3):
+        whole(i)
+    ms_e2e = timed(whole, args.steps)
+    # the dominant kernel alone: the routed gate/up grouped GEMM over the operands the last pass left in the workspace
+    idx, w = routed[(args.steps - 1) % NX]
+    pl.run(xs[(args.steps - 1) % NX], idx, w, yr=yr, ys=ys, out=out)
+    up = lambda i: pl.run(xs[0], idx, w, yr=yr, ys=ys, out=out, parts=1)
+    for i in range(3):
+        up(i)
+    ms_up = timed(up, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    status = moe.ws_status(pl.ws)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks, peak_kind = measured_peaks()
+    local_picks = int(counts[e_lo:e_hi].sum())
+    fl_up = local_picks * 2 * H * I * 2
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    ach = fl_up / (ms_up * 1e-3) / 1e12
+    tf = prefill_flops(T) / (ms * 1e-3) / 1e12
+    tf_e2e = prefill_flops(T) / (ms_e2e * 1e-3) / 1e12
+    c = np.sort(counts)[::-1]
+    line = {
+        "metric": "moe_prefill_grouped_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"config 4: prefill MoE, hidden 2048, 64 experts x 1024, top-6, + shared expert, {T} tokens, "
+                               f"Zipf(1.1) expert popularity (router bias scale {alpha})", "tokens": T,
+                   "segments": {"max": int(c[0]), "median": int(np.median(c)), "min": int(c[-1])},
+                   "parallelism": f"ep{world}", "cold_inputs": f"{NX} activation sets cycled; inputs and intermediates larger than L2",
+                   "step": "sort/permute + quantise + gate/up GEMM (SwiGLU) + down GEMM + shared expert + combine"},
+        "tokens_per_s": T / (ms * 1e-3),
+        "roofline": {"bound": "tensor", "kernel": "k_gemm_fp8<up> (routed gate/up grouped GEMM, SwiGLU and h quantisation fused)",
+                     "achieved": ach, "peak": fp8_peak, "unit": "TFLOP/s", "frac": ach / fp8_peak,
+                     "peak_kind": f"2 x {peak_kind} bf16 burst (no FP8 figure is measured on this pool)",
+                     "frac_of_nominal_4500": ach / 4500.0, "us_per_launch": ms_up * 1e3, "algorithmic_flops": fl_up,
+                     "traffic": None},
+        "e2e": {"value": tf_e2e, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": T * H * 2,
+                "d2h_bytes_per_step": T * H * 2},
+        "gpu_launches": args.steps * (11 + (1 if world > 1 else 0)),
+        "clocks": clocks,
+        "device_status": status,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(1, workload="prefill")
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(rows, workload="decode"):
     """The oracle port on the host cores, a bounded sample: three whole layer-steps of the same workload."""
     r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "3", "--warmup", "1",
-                        "--rows", str(rows)], capture_output=True, text=True, timeout=600)
+                        "--rows", str(rows), "--workload", workload], capture_output=True, text=True, timeout=600)
     try:
         d = json.loads(r.stdout.strip().splitlines()[-1])
         return d["cpu_baseline"]
@@ -327,6 +524,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline layer-step (config 2); prefill: the grouped GEMM pass of config 4")
+    ap.add_argument("--tokens", type=int, default=16384, help="prefill: tokens a pass")
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
@@ -337,7 +537,11 @@ def main():
     args = ap.parse_args()
     if args.experts:
         CFG["E"] = args.experts
-    if args.impl == "reference":
+    if args.workload == "prefill":
+        if args.steps == 200:
+            args.steps = 20
+        run_prefill_reference(args) if args.impl == "reference" else run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
