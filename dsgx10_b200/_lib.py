@@ -6,7 +6,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libdsgx_moe.so")
 
-OK, ERR_ARG, ERR_FORMAT, ERR_SHAPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = range(7)
+OK, ERR_ARG, ERR_FORMAT, ERR_SHAPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED, ERR_LIMIT = range(8)
 FMT_NVFP4, FMT_RETIRED, FMT_INT4, FMT_BF16, FMT_FP8 = range(5)
 SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
 MAX_ROWS = 8
@@ -49,6 +49,7 @@ SYMBOLS = {
     "dsgx_route": (_I, [C.POINTER(MoeShape), _V, _V, _I, _V, _V, _V]),
     "dsgx_sort_ws_bytes": (_Z, [_I, _I, _I]),
     "dsgx_sort_pack": (_I, [_V, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V, _V]),
+    "dsgx_sort_pack_static": (_I, [_V, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V]),
     "dsgx_decode_ws_bytes": (_Z, [C.POINTER(MoeShape)]),
     "dsgx_moe_decode": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _I, _V, _V, _V, _V,
                              C.POINTER(DecodeCfg)]),

@@ -100,6 +100,7 @@ const char* dsgx_status_name(int s) {
     case DSGX_ERR_CUDA: return "CUDA error";
     case DSGX_ERR_DEVICE_WAIT: return "a bounded device wait ran out";
     case DSGX_ERR_UNSUPPORTED: return "unsupported";
+    case DSGX_ERR_LIMIT: return "beyond a fixed built-in size";
   }
   return "unknown status";
 }
@@ -136,6 +137,21 @@ int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, 
   }
   cudaError_t e = launch_sort_pack(idx, T, topk, E, counts, offsets, perm_tok, perm_slot, pos_of, row_order, ws,
                                    (cudaStream_t)stream);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+int dsgx_sort_pack_static(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
+                          int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* stream) {
+  if (!idx || !counts || !offsets || !perm_tok || !perm_slot || !pos_of || !row_order) return DSGX_ERR_ARG;
+  if (T < 0 || topk < 1 || topk > kMaxTopK || E < 1 || E > 512) return DSGX_ERR_SHAPE;
+  if (sort_ws_bytes(T, topk, E) > kSortStaticBytes) return DSGX_ERR_LIMIT;
+  if (T == 0) {
+    cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * E, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(offsets, 0, sizeof(int) * (E + 1), (cudaStream_t)stream);
+    return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+  }
+  cudaError_t e = launch_sort_pack_static(idx, T, topk, E, counts, offsets, perm_tok, perm_slot, pos_of, row_order,
+                                          (cudaStream_t)stream);
   return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
 }
 

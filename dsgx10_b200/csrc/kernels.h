@@ -25,6 +25,9 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* wr, int M,
 cudaError_t launch_route(const RouteParams& p, const float* logits, const float* bias, int M, int* idx, float* w,
                          cudaStream_t st, bool pdl);
 size_t sort_ws_bytes(int T, int topk, int E);
+constexpr size_t kSortStaticBytes = DSGX_SORT_STATIC_MAX_BYTES;  // the fixed scratch of launch_sort_pack_static
+cudaError_t launch_sort_pack_static(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
+                                    int* perm_slot, int* pos_of, int* row_order, cudaStream_t st);
 cudaError_t launch_sort_pack(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
                              int* perm_slot, int* pos_of, int* row_order, void* ws, cudaStream_t st);
 cudaError_t launch_act_quant_tiled(const __nv_bfloat16* x, int M, int K, uint8_t* out, cudaStream_t st, bool pdl);

@@ -239,6 +239,29 @@ cudaError_t launch_sort_pack(const int* idx, int T, int topk, int E, int* counts
   return cudaGetLastError();
 }
 
+// The same sort with its scratch in a fixed array of this module instead of a caller's workspace: for callers that have
+// no device allocator to ask (see dsgx_sort_pack_static).  The array is shared by every call on the device: it keeps
+// the last call's histograms (every word a call reads it writes first; only the error word must be zero and is cleared
+// by the call), and two calls that overlap on the device race on it.
+static __device__ __align__(256) unsigned char g_sort_scratch[kSortStaticBytes];
+
+cudaError_t launch_sort_pack_static(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
+                                    int* perm_slot, int* pos_of, int* row_order, cudaStream_t st) {
+  // set-up, once per device: the array's device address (this may load the module, so the first call is not the one to
+  // time, and it belongs before any stream capture)
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  void* p = dev >= 0 && dev < 64 ? addr[dev] : nullptr;
+  if (!p) {
+    e = cudaGetSymbolAddress(&p, g_sort_scratch);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) addr[dev] = p;
+  }
+  return launch_sort_pack(idx, T, topk, E, counts, offsets, perm_tok, perm_slot, pos_of, row_order, p, st);
+}
+
 // ------------------------------------------------------------------------------------------ activation quantisation
 // x bf16 [M][K] -> blocks of 1056 B, one per 128 k: [2 halves q][32 lanes][16 B] e4m3 codes in the operand order of the
 // decode MMAs (lane 4 r + t of half q holds row r, k = 128 j + 64 q + 16 t + 0..15) followed by the 8 rows' f32 scales.

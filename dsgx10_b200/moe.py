@@ -58,6 +58,18 @@ def sort_pack(idx, E):
     return out
 
 
+def sort_pack_static(idx, E):
+    """sort_pack through the entry point that takes no workspace and allocates nothing (fixed scratch in the library)."""
+    T, k = idx.shape
+    i32 = dict(dtype=torch.int32, device=idx.device)
+    out = dict(counts=torch.empty(E, **i32), offsets=torch.empty(E + 1, **i32), perm_tok=torch.empty(T * k, **i32),
+               perm_slot=torch.empty(T * k, **i32), pos_of=torch.empty(T, k, **i32), row_order=torch.empty(T, k, **i32))
+    check(lib().dsgx_sort_pack_static(_ptr(idx), T, k, E, _ptr(out["counts"]), _ptr(out["offsets"]), _ptr(out["perm_tok"]),
+                                      _ptr(out["perm_slot"]), _ptr(out["pos_of"]), _ptr(out["row_order"]), _stream()),
+          "dsgx_sort_pack_static")
+    return out
+
+
 def decode_ws_bytes(shp):
     n = lib().dsgx_decode_ws_bytes(C.byref(shp))
     if n == 0:

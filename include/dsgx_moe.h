@@ -33,7 +33,8 @@ typedef enum dsgx_status {
   DSGX_ERR_SHAPE = 3,       /* H, I, E, topk, groups not supported by the kernels */
   DSGX_ERR_CUDA = 4,        /* a CUDA runtime call failed; dsgx_last_cuda_error() has the code */
   DSGX_ERR_DEVICE_WAIT = 5, /* a bounded device-side wait ran out (read from the workspace's status word) */
-  DSGX_ERR_UNSUPPORTED = 6
+  DSGX_ERR_UNSUPPORTED = 6,
+  DSGX_ERR_LIMIT = 7        /* the request is beyond a fixed built-in size (dsgx_sort_pack_static) */
 } dsgx_status;
 
 /* Expert formats.  Tags 2 and 3 are the reference's (altar1 engine/experts/experts.h:39); tag 4 is this library's
@@ -112,6 +113,22 @@ int dsgx_route(const dsgx_moe_shape* shape, const float* logits, const float* bi
 size_t dsgx_sort_ws_bytes(int T, int topk, int E);
 int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
                    int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* ws, void* stream);
+
+/* dsgx_sort_pack without a workspace argument and without any allocation: the scratch is a fixed array inside the
+ * library's device module.  It has no counterpart in the reference, whose callers always bring a workspace.  It is for
+ * callers that cannot get device memory at the moment of the call: an engine that gave all device memory to its own pools
+ * at start-up and has no spare block to hand out, or a thin foreign-function binding (cgo, JNI) that passes pointers
+ * through but owns no device allocator.
+ *   Limit: dsgx_sort_ws_bytes(T, topk, E) <= DSGX_SORT_STATIC_MAX_BYTES (for instance 8192 rows x 512 experts or
+ *   16384 rows x 256 experts); beyond it the call does nothing and returns DSGX_ERR_LIMIT.
+ *   The first call on a device looks up the array's address (and may load the module): make it once at start-up, before
+ *   any stream capture begins; later calls only launch.
+ *   The array is shared: it keeps what the last call left (each call clears the one word that must be zero), and calls
+ *   that overlap on the device, on any streams, race on it: serialise them.
+ * Same outputs, bit for bit, as dsgx_sort_pack. */
+#define DSGX_SORT_STATIC_MAX_BYTES 131328 /* 256 + 2 x 32 chunks x 512 experts x 4 bytes */
+int dsgx_sort_pack_static(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
+                          int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* stream);
 
 /* ---- decode (1..DSGX_MAX_ROWS rows) ------------------------------------------------------------------------------
  * Stands in for gx::decode_ws_bytes / gx::moe_decode (altar1 engine/experts/experts.h:104-141) and dsk::moe_routed
