@@ -181,6 +181,13 @@ def run_gpu(args):
     xs_host = [x.cpu().pin_memory() for x in xs]
     out_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
     red = torch.zeros(2, _lib.MAX_ROWS, H, dtype=torch.float32, device=dev) if world > 1 else None
+    # several GPUs: the partial sums are reduced and rounded by the library's kernel over peer memory (--nccl: by an
+    # NCCL all-reduce and the rounding kernel); the buffer half follows the step parity, so the graph holds an even count
+    peer = None
+    if world > 1 and not args.nccl:
+        from dsgx10_b200 import ep
+        peer = ep.PeerReduce(H, shared_rank=0)
+        args.steps += args.steps & 1
 
     def step(i, host=False):
         lay, lw = layers[i % NL]
@@ -195,6 +202,13 @@ def run_gpu(args):
         if host:
             sb.x_stage[:rows].copy_(xs_host[i % NX], non_blocking=True)
             x = sb.x_stage[:rows]
+        if peer is not None:
+            yr_p, ys_p = peer.parts(peer.launched + 1)
+            sb.run(lw, x, finalize=False, yr=yr_p, ys=ys_p)
+            out = peer.finalize(rows)
+            if host:
+                out_host.copy_(out, non_blocking=True)
+            return
         sb.run(lw, x, finalize=False)
         red[0].copy_(sb.yr)
         if rank == 0:
@@ -223,12 +237,14 @@ def run_gpu(args):
             with torch.cuda.graph(graph):
                 for i in range(n):
                     fn(i)
-            graph.replay()  # one untimed replay
+            graph.replay()  # one untimed replay (the launches the capture counted)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         if graph is not None:
             graph.replay()
+            if peer is not None:
+                peer.launched += n  # a second run of the captured steps
         else:
             for i in range(n):
                 fn(i)
@@ -267,6 +283,8 @@ def run_gpu(args):
     ms_up = timed(up_only, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     status = max(moe.ws_status(sb.ws) for sb in steps_buf)
+    if peer is not None:
+        status = max(status, int(peer.status.item()))
 
     if rank != 0:
         if world > 1:
@@ -287,7 +305,8 @@ def run_gpu(args):
         "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
         "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
                                f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows,
-                   "parallelism": f"ep{world}", "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
+                   "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
+                                                   " (partial sums reduced over peer memory by k_finalize_peers)"), "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
                    "launch": "eager" if args.eager else "one CUDA graph of the timed steps"},
         "tokens_per_s": rows / (us * 1e-6),
         "step_hbm_gbs": sb_bytes / (us * 1e-6) / 1e9,
@@ -530,6 +549,7 @@ def main():
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
+    ap.add_argument("--nccl", action="store_true", help="several GPUs: reduce with an NCCL all-reduce instead of the peer kernel")
     ap.add_argument("--separate", action="store_true", help="always run the step as four kernels")
     ap.add_argument("--fused", action="store_true", help="always run the step as the one persistent kernel")
     ap.add_argument("--experts", type=int, default=0,

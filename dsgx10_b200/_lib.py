@@ -30,6 +30,11 @@ class MoeShape(C.Structure):
                 ("route_scale", C.c_float), ("fmt", C.c_uint32), ("e_lo", C.c_int32), ("e_hi", C.c_int32)]
 
 
+class PeerSet(C.Structure):
+    _fields_ = [("parts", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p), ("rank", C.c_int32),
+                ("world", C.c_int32), ("rows_cap", C.c_int32), ("shared_rank", C.c_int32)]
+
+
 class DecodeCfg(C.Structure):
     _fields_ = [("ysum", C.c_int32), ("pdl", C.c_int32), ("parts", C.c_int32), ("up", C.c_int32),
                 ("down", C.c_int32), ("reserved", C.c_int32 * 3)]
@@ -49,6 +54,7 @@ SYMBOLS = {
     "dsgx_route": (_I, [C.POINTER(MoeShape), _V, _V, _I, _V, _V, _V]),
     "dsgx_sort_ws_bytes": (_Z, [_I, _I, _I]),
     "dsgx_sort_pack": (_I, [_V, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V, _V]),
+    "dsgx_finalize_peers": (_I, [_V, _I, _I, _V, _V, _V]),
     "dsgx_sort_pack_static": (_I, [_V, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V]),
     "dsgx_decode_ws_bytes": (_Z, [C.POINTER(MoeShape)]),
     "dsgx_moe_decode": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _I, _V, _V, _V, _V,

@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdsgx_moe.so")
-SOURCES = ["api.cu", "route.cu", "decode_front.cu", "decode_fp8.cu", "decode_fused.cu", "decode_int4.cu", "prefill.cu"]
+SOURCES = ["api.cu", "route.cu", "decode_front.cu", "decode_fp8.cu", "decode_fused.cu", "decode_int4.cu", "prefill.cu", "peer.cu"]
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
          "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 

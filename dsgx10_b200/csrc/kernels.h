@@ -152,4 +152,15 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st);
 
 int sm_count();
 
+// ---- reduction over peer memory (peer.cu)
+struct PeerParams {
+  const float* const* parts;  // device array [world]: rank r's partial sums, f32 [2 parities][yr, ys][rows_cap][H]
+  uint32_t* const* flags;     // device array [world]: rank r's flag words, u32 [world]
+  uint32_t* state;            // this rank's {step counter, CTA ticket}
+  int rank, world, rows_cap, shared_rank, M, H;
+  __nv_bfloat16* out;
+  int* status;
+};
+cudaError_t launch_finalize_peers(const PeerParams& p, cudaStream_t st);
+
 }  // namespace dsgx

@@ -1,0 +1,107 @@
+// Expert parallelism inside one box: the reduction of the ranks' partial sums and the rounding in one kernel over peer
+// memory (NVLink through NVSwitch, plain peer loads and stores).  It stands in for the all-reduce the reference issues
+// after its expert step (ds41f ref/inference/model.py:901-902, altar1 engine/model/model.cu: the ring reduce before
+// gx::finalize) followed by the rounding: every rank ends with out = bf16((sum over ranks, in rank order, of yr) + ys of
+// the rank that holds the shared expert).
+//
+// Protocol, one launch a step on every rank (exactly one of these kernels runs on a GPU at a time; the kernels of one
+// step on the different GPUs wait for one another, each wait bounded):
+//   1. the step number e is this rank's counter + 1 (the counter lives in the rank's own memory and is bumped by the
+//      last CTA of the launch, so every CTA of a launch reads the same value);
+//   2. CTA 0 stores e into its word of every rank's flag array (system-scope release: the partial sums of the step, which
+//      the kernels before this one on the stream wrote, are visible to whoever sees the flag);
+//   3. every CTA waits until all ranks' words in its own flag array have reached e (a rank can be one step ahead, never
+//      more: it needs this rank's flag of step e + 1 to finish that step), then adds the ranks' partial sums, read through
+//      the peer pointers, and rounds;
+//   4. the partial sums are double-buffered by the parity of e: a rank that is one step ahead writes the other half.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dsgx {
+
+namespace {
+
+DSGX_DEV uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+DSGX_DEV void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// a load that does not use a line an earlier step may have left in this SM's L1
+DSGX_DEV float4 ld_peer4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
+  __shared__ int ok;
+  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.state) + 1;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + p.rank, e);
+  }
+  if (threadIdx.x < p.world) {
+    const uint32_t* f = p.flags[p.rank] + threadIdx.x;
+    const long long t0 = clock64();
+    while ((int)(ld_acquire_sys(f) - e) < 0) {
+      __nanosleep(64);
+      if (clock64() - t0 > kWaitCycles) {
+        ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (ok) {
+    const size_t half = (size_t)2 * p.rows_cap * p.H;  // floats of one parity: yr then ys
+    const size_t off = (size_t)(e & 1) * half;
+    const int per = p.H / 4;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.M * per; i += gridDim.x * blockDim.x) {
+      const int r = i / per, c = (i - r * per) * 4;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = 0; q < p.world; ++q) {  // rank order, the same on every rank
+        const float4 v = ld_peer4(p.parts[q] + off + (size_t)r * p.H + c);
+        a.x = q ? __fadd_rn(a.x, v.x) : v.x, a.y = q ? __fadd_rn(a.y, v.y) : v.y;
+        a.z = q ? __fadd_rn(a.z, v.z) : v.z, a.w = q ? __fadd_rn(a.w, v.w) : v.w;
+      }
+      if (p.shared_rank >= 0) {
+        const float4 s = ld_peer4(p.parts[p.shared_rank] + off + (size_t)(p.rows_cap + r) * p.H + c);
+        a.x = __fadd_rn(a.x, s.x), a.y = __fadd_rn(a.y, s.y), a.z = __fadd_rn(a.z, s.z), a.w = __fadd_rn(a.w, s.w);
+      }
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&lo), o.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(p.out + (size_t)r * p.H + c) = o;
+    }
+  } else if (threadIdx.x == 0) {
+    atomicCAS(p.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+  }
+  // the last CTA of the launch closes the step
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.state + 1, 1u) == gridDim.x - 1) {
+      p.state[1] = 0;
+      __threadfence();
+      p.state[0] = e;
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_finalize_peers(const PeerParams& p, cudaStream_t st) {
+  const int n = p.M * (p.H / 4);
+  int grid = (n + 255) / 256;
+  if (grid > 32) grid = 32;
+  k_finalize_peers<<<grid, 256, 0, st>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace dsgx

@@ -15,7 +15,13 @@ Two schemes, both on `torch.distributed` process groups (NCCL over NVLink on GPU
 
 The exchange is plumbing: what is computed between the collectives is the CUDA library (or, in the CPU tests, the
 oracle passed in as `local_compute`).
+
+On GPUs the decode scheme has a second form, `PeerReduce`: the ranks' partial sums live in symmetric (peer-mapped) memory
+and one kernel of the library on every GPU adds them over NVLink and rounds (`dsgx_finalize_peers`), instead of an NCCL
+all-reduce followed by the rounding kernel.
 """
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
@@ -79,3 +85,58 @@ def all_to_all_experts(x, idx, w, E, local_compute, group=None):
             acc.index_add_(0, rows, y_back[off:off + rows.numel()])
         off += rows.numel()
     return acc
+
+
+class PeerReduce:
+    """The buffers of the peer-memory reduction of a decode step: this rank's partial sums and flag words in symmetric
+    memory (every rank of the box maps every rank's), the device arrays of peer pointers, the step state.
+
+        pr = PeerReduce(H, shared_rank=0)
+        yr, ys = pr.parts(pr.launched + 1)                 # where this step's expert kernels write
+        step.run(layer_w, x, finalize=False, yr=yr, ys=ys)
+        out = pr.finalize(M)                               # the reduced, rounded rows: the same bits on every rank
+
+    The half of the buffer a step uses follows the parity of its number (1, 2, ...): a CUDA graph that holds an even
+    number of steps can be replayed any number of times."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, H, rows_cap=8, shared_rank=0, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        self._lib = _lib
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.H, self.rows_cap = H, rows_cap
+        dev = torch.device("cuda", torch.cuda.current_device())
+        half = 2 * rows_cap * H
+        self.buf = symm_mem.empty(self.FLAG_BYTES + 2 * half * 4, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.hdl = symm_mem.rendezvous(self.buf, group=group)
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.flags = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+        self.parts_ptrs = torch.tensor([p + self.FLAG_BYTES for p in ptrs], dtype=torch.int64, device=dev)
+        self.state = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(rows_cap, H, dtype=torch.bfloat16, device=dev)
+        f = self.buf[self.FLAG_BYTES:].view(torch.float32).view(2, 2, rows_cap, H)
+        self._parts = f
+        self.set = _lib.PeerSet(self.parts_ptrs.data_ptr(), self.flags.data_ptr(), self.state.data_ptr(), self.rank,
+                                self.world, rows_cap, shared_rank)
+        self.launched = 0  # finalize launches executed or captured so far (the host's copy of the step counter)
+        torch.cuda.synchronize()
+        dist.barrier(group)  # every rank's flags are zero before anyone signals
+
+    def parts(self, step):
+        """(yr, ys) f32 [rows_cap][H] of step number `step` (1, 2, ...) in this rank's symmetric buffer."""
+        return self._parts[step & 1, 0], self._parts[step & 1, 1]
+
+    def finalize(self, M, count=True):
+        lib = self._lib.lib()
+        rc = lib.dsgx_finalize_peers(C.byref(self.set), M, self.H, C.c_void_p(self.out.data_ptr()),
+                                     C.c_void_p(self.status.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc:
+            raise self._lib.DsgxError(rc, "dsgx_finalize_peers")
+        if count:
+            self.launched += 1
+        return self.out[:M]

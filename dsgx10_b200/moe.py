@@ -125,10 +125,15 @@ class LayerStep:
                                 _ptr(self.yr), _ptr(self.ys), _ptr(self.out), _ptr(self.x_stage),
                                 (0 if fused is None else 4 if fused else 1) | (2 if stamps is not None else 0), 0, _ptr(stamps))
 
-    def run(self, layer_w, x, finalize=True):
-        """x bf16 [M][H] on the device -> self.out[:M] (bf16) when finalize, else self.yr / self.ys partial sums."""
+    def run(self, layer_w, x, finalize=True, yr=None, ys=None):
+        """x bf16 [M][H] on the device -> self.out[:M] (bf16) when finalize, else self.yr / self.ys partial sums
+        (or the f32 [8][H] buffers given as yr, ys: an expert-parallel rank's share of a peer-reduced step)."""
         M = x.shape[0]
-        check(lib().dsgx_moe_layer_decode(C.byref(self.shp), C.byref(layer_w), _ptr(x), M, C.byref(self.c),
+        c = self.c
+        if yr is not None:
+            c = _lib.LayerStep.from_buffer_copy(self.c)
+            c.yr, c.ys = _ptr(yr), _ptr(ys)
+        check(lib().dsgx_moe_layer_decode(C.byref(self.shp), C.byref(layer_w), _ptr(x), M, C.byref(c),
                                           int(finalize), _stream()), "dsgx_moe_layer_decode")
         return self.out[:M]
 

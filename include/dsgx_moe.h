@@ -151,6 +151,27 @@ int dsgx_moe_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const vo
  * gx::finalize (experts.h:146-147), whose bf16(bf16(R) + bf16(S)) order is mode 1. */
 int dsgx_finalize(const float* R, const float* S, int M, int H, void* out_bf16, int mode, void* stream);
 
+/* The reduction across the GPUs of one box and the rounding in one kernel over peer memory: stands in for the all-reduce
+ * the reference issues after its expert step (ds41f ref/inference/model.py:901-902; altar1 engine/model/model.cu, the ring
+ * reduce before gx::finalize) followed by dsgx_finalize(mode 0).  Every rank calls it once a step, after the kernels that
+ * wrote its partial sums, on buffers every rank can address (peer-mapped or symmetric memory, NVLink):
+ *   parts[r]  rank r's partial sums, f32 [2][2][rows_cap][H]: [parity of the step][yr, ys][row][column]; the caller's
+ *             expert step of step number e (1, 2, ...) writes the half (e & 1)
+ *   flags[r]  rank r's flag words, u32 [world], zeroed once before the first step
+ *   state     this rank's own u32 [2] {step counter, ticket}, zeroed once
+ *   parts, flags: device arrays of `world` pointers.
+ * out (this rank's memory) = bf16((yr of rank 0 + yr of rank 1 + ...) + ys of rank `shared_rank`), shared_rank < 0: no
+ * shared expert.  The same bits on every rank.  The kernels of one step on the different GPUs wait for one another (each
+ * wait bounded; on a run-out the status word, this rank's memory, gets DSGX_ERR_DEVICE_WAIT): launch nothing else that
+ * waits across GPUs at the same time, and one step at a time. */
+typedef struct dsgx_peer_set {
+  const float* const* parts;
+  uint32_t* const* flags;
+  uint32_t* state;
+  int32_t rank, world, rows_cap, shared_rank;
+} dsgx_peer_set;
+int dsgx_finalize_peers(const dsgx_peer_set* peers, int M, int H, void* out_bf16, int32_t* status_word, void* stream);
+
 /* ---- one layer step, router to rounded output --------------------------------------------------------------------
  * The sequence the engines' layer runners issue around the operator (altar1 engine/model/model.cu:308-352: router
  * GEMV, route, moe_decode, then the reduction and the rounding): logits = x wr^T, route, the expert step, and

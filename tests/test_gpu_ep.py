@@ -52,6 +52,29 @@ def _worker(rank, world, port, q):
         res["decode_yr"] = float((st.yr[:5] - ref.yr[:5]).abs().max()) / den
         res["decode_ys"] = float((st.ys[:5] - ref.ys[:5]).abs().max())
         res["decode_idx"] = bool(torch.equal(st.idx[:5], ref.idx[:5]))
+        # decode: the same reduction by the library's own kernel over peer memory, three steps in a row (both halves of
+        # the buffer and the step counter); the bits are those of bf16((yr0 + yr1) + ys0) and equal on both ranks
+        pr = ep.PeerReduce(H, shared_rank=0)
+        peer_ok, peer_same = True, True
+        for step_no in range(1, 4):
+            xs = synth.activations(3 + step_no, H, 310 + step_no).to(dev)
+            M = xs.shape[0]
+            st.run(mine.layer_w(), xs, finalize=False)
+            if rank != 0:
+                st.ys.zero_()
+            want_parts = torch.stack([st.yr[:M], st.ys[:M]]).clone()
+            gathered = [torch.empty_like(want_parts) for _ in range(world)]
+            dist.all_gather(gathered, want_parts)
+            want = moe.finalize(gathered[0][0] + gathered[1][0], gathered[0][1])
+            yr_p, ys_p = pr.parts(pr.launched + 1)
+            st.run(mine.layer_w(), xs, finalize=False, yr=yr_p, ys=ys_p)
+            got = pr.finalize(M).clone()
+            torch.cuda.synchronize()
+            peer_ok = peer_ok and bool(torch.equal(got, want))
+            both = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(both, got)
+            peer_same = peer_same and bool(torch.equal(both[0], both[1]))
+        res["peer_ok"], res["peer_same"], res["peer_status"] = peer_ok, peer_same, int(pr.status.item())
         # prefill: rows partitioned, all-to-all dispatch and combine
         T = 96
         xa = synth.activations(T, H, 303).to(dev)
@@ -91,3 +114,4 @@ def test_two_gpus_match_one():
         assert res["decode_idx"] and res["status"] == 0
         assert res["decode_yr"] <= 1e-6 and res["decode_ys"] == 0.0, res    # only the association of the f32 adds differs
         assert res["prefill"] <= 1e-6, res
+        assert res["peer_ok"] and res["peer_same"] and res["peer_status"] == 0, res
