@@ -429,21 +429,19 @@ def run_prefill(args):
 
     def experts(i):
         idx, w = routed[i % NX]
-        pl.run(xs[i % NX], idx, w, yr=yr, ys=ys, out=out)
-        if world > 1:
+        pl.run(xs[i % NX], idx, w, yr=yr, ys=ys, out=out, ysum=world > 1)
+        if world > 1:  # rank 0's partial sums hold the shared expert's output too: one buffer to reduce
             dist.all_reduce(yr)
-            dist.all_reduce(ys)
-            out.copy_(moe.finalize(yr, ys))
+            out.copy_(moe.finalize(yr))
 
     def whole(i):  # end to end: host activations in, router, experts, host bf16 out
         x_stage.copy_(xs_host[i % NX], non_blocking=True)
         lg = moe.router_logits(x_stage, wr)
         idx, w = moe.route(shp_all, lg, bias)
-        pl.run(x_stage, idx, w, yr=yr, ys=ys, out=out)
+        pl.run(x_stage, idx, w, yr=yr, ys=ys, out=out, ysum=world > 1)
         if world > 1:
             dist.all_reduce(yr)
-            dist.all_reduce(ys)
-            out.copy_(moe.finalize(yr, ys))
+            out.copy_(moe.finalize(yr))
         out_host.copy_(out, non_blocking=True)
 
     def barrier():
