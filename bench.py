@@ -315,7 +315,12 @@ def run_gpu(args):
         "step_algorithmic_bytes": sb_bytes,
         "roofline": {"bound": "hbm", "kernel": "k_up_fp8 (+ activation quantisation launch)", "achieved": ach,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
-                     "us_per_launch": us_up, "algorithmic_bytes": upb, "traffic": None},
+                     "us_per_launch": us_up, "algorithmic_bytes": upb,
+                     # one ncu capture of this kernel (profiles/decode_fp8_rows1_launches_k_up_k_down.md): 151.14 MB read +
+                     # 3.91 MB written for 151.03 MB algorithmic; the traffic grows with the experts a launch streams
+                     "traffic": upb * (151.142912 + 3.909120) / 151.031808,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "
+                                       "this launch's algorithmic bytes"},
         "e2e": {"value": us_e2e, "unit": "us", "h2d_bytes_per_step": rows * H * 2, "d2h_bytes_per_step": rows * H * 2},
         # this library's kernels a step: the one persistent kernel from three rows (or --fused), else front, route, gate/up,
         # down; with several GPUs also the rounding kernel after the all-reduce

@@ -151,6 +151,7 @@ struct PrefillParams {
 cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st);
 
 int sm_count();
+cudaError_t launch_copy_in(const void* src, void* dst, size_t bytes, cudaStream_t st);
 
 // ---- reduction over peer memory (peer.cu)
 struct PeerParams {

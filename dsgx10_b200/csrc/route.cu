@@ -305,6 +305,17 @@ __global__ void __launch_bounds__(256) k_finalize(const float* __restrict__ R, c
   const float r = R[i], s = S ? S[i] : 0.f;
   out[i] = mode == 1 ? __float2bfloat16_rn(__fadd_rn(bf16_round(r), bf16_round(s))) : __float2bfloat16_rn(__fadd_rn(r, s));
 }
+// a few KB from mapped host memory into device memory, 16 bytes a thread
+__global__ void __launch_bounds__(256) k_copy_in(const uint4* __restrict__ src, uint4* __restrict__ dst, int n) {
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
+cudaError_t launch_copy_in(const void* src, void* dst, size_t bytes, cudaStream_t st) {
+  const int n = (int)(bytes / 16);
+  return launch_k(k_copy_in, dim3((n + 255) / 256), dim3(256), 0, st, false, reinterpret_cast<const uint4*>(src),
+                  reinterpret_cast<uint4*>(dst), n);
+}
 cudaError_t launch_finalize(const float* R, const float* S, int M, int H, __nv_bfloat16* out, int mode, cudaStream_t st,
                             bool pdl) {
   const size_t n = (size_t)M * H;

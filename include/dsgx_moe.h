@@ -199,8 +199,10 @@ typedef struct dsgx_layer_step {
 } dsgx_layer_step;
 int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, int M,
                           const dsgx_layer_step* step, int finalize, void* stream);
-/* The same with HOST buffers: x_host bf16 [M][H] (pinned memory for an asynchronous copy) is copied to the device,
- * the step runs, and out_host bf16 [M][H] receives the result; all in stream order, the caller synchronises. */
+/* The same with HOST buffers: x_host bf16 [M][H] is brought to the device, the step runs, and out_host bf16 [M][H]
+ * receives the result; all in stream order, the caller synchronises.  Pinned (mapped) buffers are used in place: a small
+ * kernel reads x_host over PCIe and the step's last kernel writes out_host directly; other host memory goes through
+ * cudaMemcpyAsync. */
 int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_host, int M,
                                const dsgx_layer_step* step, void* out_host, void* stream);
 
