@@ -100,3 +100,37 @@ def test_chunk_invariance(orc):
         yr2, ys2, _ = pl.run(x[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
         torch.cuda.synchronize()
         assert torch.equal(yr2, yr[a:b]) and torch.equal(ys2, ys[a:b])
+
+
+def test_full_size_16384_tokens_properties(orc):
+    """The benchmark's size (hidden 2048, 64 experts x 1024, top-6, 16384 tokens, Zipf-skewed routing: segments from a few
+    rows to thousands): properties that do not need the oracle over every row -- the sort is a permutation with the
+    right counts, a chunk of rows run alone has the bits it has inside the whole pass, a second pass repeats the first
+    bit for bit, and sampled rows (the hot expert's, a rare expert's, the first and the last) match the oracle."""
+    from dsgx10_b200 import moe
+    T, H, I, E, topk = 16384, 2048, 1024, 64, 6
+    shp, layer, x, wr, bias, idx, w = _setup(H, I, E, topk, T, seed=20261104, zipf=True)
+    counts = torch.bincount(idx.flatten().long(), minlength=E)
+    assert int(counts.max()) > 2000 and int(counts.min()) < 256          # ragged: huge and tiny segments
+    sp = moe.sort_pack(idx, E)
+    assert torch.equal(sp["counts"].long(), counts)
+    assert torch.equal(torch.sort(sp["perm_tok"].long() * topk + sp["perm_slot"].long()).values,
+                       torch.arange(T * topk, device="cuda"))
+    e_sorted = idx.flatten()[(sp["perm_tok"].long() * topk + sp["perm_slot"].long())]
+    assert bool((e_sorted[1:] >= e_sorted[:-1]).all())                     # expert-major order
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    yr, ys, out = yr.clone(), ys.clone(), out.clone()
+    yr_b, ys_b, out_b = pl.run(x, idx, w)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    assert torch.equal(yr_b, yr) and torch.equal(ys_b, ys) and torch.equal(out_b, out)   # run to run
+    for a, b in ((0, 4096), (9000, 9300), (16383, 16384)):
+        yr2, ys2, out2 = pl.run(x[a:b].contiguous(), idx[a:b].contiguous(), w[a:b].contiguous())
+        torch.cuda.synchronize()
+        assert torch.equal(yr2, yr[a:b]) and torch.equal(ys2, ys[a:b]) and torch.equal(out2, out[a:b])
+    hot, rare = int(counts.argmax()), int(torch.where(counts > 0, counts, T * topk).argmin())
+    rows = [0, T - 1]
+    for e in (hot, rare):
+        rows += torch.nonzero((idx == e).any(dim=1)).flatten()[:3].tolist()
+    _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=sorted(set(rows)))
