@@ -180,14 +180,17 @@ DSGX_DEV void tile_x_group(const __nv_bfloat16* __restrict__ x, int M, int K, in
 
 // One (expert, 1024-k slice) of the router logits for every row, in the router's summation order: lane j accumulates
 // k = base + 128 i + 4 j + c (i ascending, c = 0..3) by fma from zero, then the butterfly.  All weight loads go out first.
-DSGX_DEV void logit_slice_task(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M, int H, int E, int e,
-                               int sl, float* __restrict__ lpart, int lane) {
+// The slice's router weights (they never change during a step: a kernel may fetch them before it waits for its inputs).
+DSGX_DEV void logit_slice_weights(const float* __restrict__ wr, int H, int e, int sl, int lane, float4 (&wv)[8]) {
   const int base = sl * 1024, nit = min(1024, H - base) / 128;
-  float4 wv[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
     wv[i] = i < nit ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)e * H + base + 128 * i + 4 * lane))
                     : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+DSGX_DEV void logit_slice_rows(const __nv_bfloat16* __restrict__ x, const float4 (&wv)[8], int M, int H, int E, int e, int sl,
+                               float* __restrict__ lpart, int lane) {
+  const int base = sl * 1024, nit = min(1024, H - base) / 128;
   for (int r = 0; r < M; ++r) {
     uint2 xv[8];
 #pragma unroll
@@ -205,6 +208,12 @@ DSGX_DEV void logit_slice_task(const __nv_bfloat16* __restrict__ x, const float*
     a = warp_sum(a);
     if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
   }
+}
+DSGX_DEV void logit_slice_task(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M, int H, int E, int e,
+                               int sl, float* __restrict__ lpart, int lane) {
+  float4 wv[8];
+  logit_slice_weights(wr, H, e, sl, lane, wv);
+  logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane);
 }
 
 struct TabArgs {

@@ -36,17 +36,21 @@ __global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__
                                                int H, int E, int nlog, float* __restrict__ lpart, uint8_t* __restrict__ xq,
                                                int fmt) {
   pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if ((int)blockIdx.x >= nlog) {
+    pdl_wait();
     stage_x(x, M, H, xq, fmt, (int)blockIdx.x - nlog);
     return;
   }
   const int KS = (H + 1023) / 1024;
   const int gw = blockIdx.x * 8 + warp;
   const int e = gw / KS, sl = gw % KS;
+  // the router weights are fetched while the kernels before this one still run; only x waits for them
+  float4 wv[8];
+  if (e < E) logit_slice_weights(wr, H, e, sl, lane, wv);
+  pdl_wait();
   if (e >= E) return;
-  logit_slice_task(x, wr, M, H, E, e, sl, lpart, lane);
+  logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane);
 }
 
 // ----------------------------------------------------------------------------------------------------- k_route_union

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   uint64_t* bars = reinterpret_cast<uint64_t*>(ringbase + (size_t)kFW * NST * stage);
   uint64_t* tabbar = bars + kFW * NST;
   int* s_int = reinterpret_cast<int*>(tabbar + 1);  // [0] table loader elected, [1] logit warps done, [2] ticket / poll result
-  RouteSmem& rs = *reinterpret_cast<RouteSmem*>(s_int + 4);
+  RouteSmem& rs = *reinterpret_cast<RouteSmem*>(((uintptr_t)(s_int + 4) + 15) & ~(uintptr_t)15);  // 16-byte aligned: vector loads
   int* s_idx = reinterpret_cast<int*>(&rs + 1);
   float* s_w = reinterpret_cast<float*>(s_idx + kMaxRows * kMaxTopK);
   uint32_t* s_bm = reinterpret_cast<uint32_t*>(s_w + kMaxRows * kMaxTopK);

@@ -190,7 +190,7 @@ DSGX_DEV uint32_t ord_key(float f) {
 }
 DSGX_DEV float ord_float(uint32_t u) { return __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u); }
 
-struct RouteSmem {
+struct __align__(16) RouteSmem {
   float key[512];
   float s[512];
   float red[16];
@@ -306,8 +306,18 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     const uint32_t mine = ku[e];
     if (mine) {
       int rank = 0;
-#pragma unroll 4
-      for (int i = 0; i < p.E; ++i) {
+      const uint4* k4 = reinterpret_cast<const uint4*>(ku);  // four keys a load, eight loads in flight
+      const int n4 = p.E >> 2;
+#pragma unroll 8
+      for (int i = 0; i < n4; ++i) {
+        const uint4 v = k4[i];
+        const int b = 4 * i;
+        rank += (v.x > mine) || (v.x == mine && b < e);
+        rank += (v.y > mine) || (v.y == mine && b + 1 < e);
+        rank += (v.z > mine) || (v.z == mine && b + 2 < e);
+        rank += (v.w > mine) || (v.w == mine && b + 3 < e);
+      }
+      for (int i = n4 << 2; i < p.E; ++i) {
         const uint32_t v = ku[i];
         rank += (v > mine) || (v == mine && i < e);
       }
