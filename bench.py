@@ -406,6 +406,11 @@ def run_prefill(args):
     _lib.lib()
     H, I, E, topk = PF["H"], PF["I"], PF["E"], PF["topk"]
     T = args.tokens
+    ragged = args.workload == "ragged"
+    if ragged:  # config 5: 64 requests packed into one token-sorted pass: 40 decode rows, 16 verify rows, 8 prefill chunks
+        rng = np.random.default_rng(SEED + 5)
+        reqs = [1] * 40 + [int(v) for v in rng.integers(2, 7, 16)] + [int(v) for v in rng.integers(512, 4097, 8)]
+        T = sum(reqs)
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     shp_all = moe.shape(H, I, E, topk)
     shp = moe.shape(H, I, E, topk, e_lo=e_lo, e_hi=e_hi)
@@ -420,7 +425,11 @@ def run_prefill(args):
     def counts_for(b):
         idx, _ = moe.route(shp_all, logits0, torch.from_numpy(b).to(dev))
         return torch.bincount(idx.flatten().long(), minlength=E).cpu().numpy()
-    alpha, b, counts = synth.calibrate_zipf_bias(counts_for, E, topk, SEED + 7)
+    if ragged:  # no popularity skew is asked for: the router's own picks
+        alpha, b = 0.0, np.zeros(E, np.float32)
+        counts = counts_for(b)
+    else:
+        alpha, b, counts = synth.calibrate_zipf_bias(counts_for, E, topk, SEED + 7)
     bias = torch.from_numpy(b).to(dev)
     pl = moe.PrefillLayer(shp, lay.layer_w(), T, device=dev)
     routed = []
@@ -434,20 +443,39 @@ def run_prefill(args):
 
     def experts(i):
         idx, w = routed[i % NX]
-        pl.run(xs[i % NX], idx, w, yr=yr, ys=ys, out=out, ysum=world > 1)
+        # one GPU: only the rounded rows; several: the f32 partial sums for the reduction
+        pl.run(xs[i % NX], idx, w, yr=yr if world > 1 else False, ys=ys if world > 1 else False, out=out, ysum=world > 1)
         if world > 1:  # rank 0's partial sums hold the shared expert's output too: one buffer to reduce
             dist.all_reduce(yr)
             out.copy_(moe.finalize(yr))
 
-    def whole(i):  # end to end: host activations in, router, experts, host bf16 out
-        x_stage.copy_(xs_host[i % NX], non_blocking=True)
-        lg = moe.router_logits(x_stage, wr)
-        idx, w = moe.route(shp_all, lg, bias)
-        pl.run(x_stage, idx, w, yr=yr, ys=ys, out=out, ysum=world > 1)
-        if world > 1:
-            dist.all_reduce(yr)
-            out.copy_(moe.finalize(yr))
-        out_host.copy_(out, non_blocking=True)
+    # end to end: host activations in, router, experts, host bf16 out; the pass is cut into chunks of tokens that go
+    # round two streams (each with its own workspace), so that the copies of one chunk overlap the kernels of another
+    NCH = 4 if T % 4 == 0 and T >= 4096 else 1
+    TC = T // NCH
+    streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
+    pls = [pl, moe.PrefillLayer(shp, lay.layer_w(), TC, device=dev, wbuf=pl.wbuf)] if NCH > 1 else [pl]
+
+    def whole(i):
+        xh = xs_host[i % NX]
+        cur = torch.cuda.current_stream()
+        for s in streams:
+            s.wait_stream(cur)
+        for c in range(NCH):
+            s, p2 = streams[c % 2], pls[c % len(pls)]
+            lo, hi = c * TC, (c + 1) * TC
+            with torch.cuda.stream(s):
+                x_stage[lo:hi].copy_(xh[lo:hi], non_blocking=True)
+                lg = moe.router_logits(x_stage[lo:hi], wr)
+                idx, w = moe.route(shp_all, lg, bias)
+                p2.run(x_stage[lo:hi], idx, w, yr=yr[lo:hi] if world > 1 else False, ys=ys[lo:hi] if world > 1 else False,
+                       out=out[lo:hi], ysum=world > 1)
+                if world > 1:
+                    dist.all_reduce(yr[lo:hi])
+                    out[lo:hi].copy_(moe.finalize(yr[lo:hi]))
+                out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
+        for s in streams:
+            cur.wait_stream(s)
 
     def barrier():
         if world > 1:
@@ -504,11 +532,14 @@ def run_prefill(args):
         "metric": "moe_prefill_grouped_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"config 4: prefill MoE, hidden 2048, 64 experts x 1024, top-6, + shared expert, {T} tokens, "
-                               f"Zipf(1.1) expert popularity (router bias scale {alpha})", "tokens": T,
+        "config": {"workload": (f"config 5: ragged batch of 64 requests (40 x 1, 16 x 2-6, 8 x 512-4096 tokens) in one pass, "
+                                f"hidden 2048, 64 experts x 1024, top-6, + shared expert, {T} tokens" if ragged else
+                                f"config 4: prefill MoE, hidden 2048, 64 experts x 1024, top-6, + shared expert, {T} tokens, "
+                                f"Zipf(1.1) expert popularity (router bias scale {alpha})"), "tokens": T,
                    "segments": {"max": int(c[0]), "median": int(np.median(c)), "min": int(c[-1])},
                    "parallelism": f"ep{world}", "cold_inputs": f"{NX} activation sets cycled; inputs and intermediates larger than L2",
-                   "step": "sort/permute + quantise + gate/up GEMM (SwiGLU) + down GEMM + shared expert + combine"},
+                   "step": "sort/permute + quantise + gate/up GEMM (SwiGLU) + down GEMM + shared expert + combine",
+                   "e2e": f"{NCH} chunks of {TC} tokens over two streams: copy in, router, expert pass, copy out"},
         "tokens_per_s": T / (ms * 1e-3),
         "roofline": {"bound": "tensor", "kernel": "k_gemm_fp8<up> (routed gate/up grouped GEMM, SwiGLU and h quantisation fused)",
                      "achieved": ach, "peak": fp8_peak, "unit": "TFLOP/s", "frac": ach / fp8_peak,
@@ -546,8 +577,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: the headline layer-step (config 2); prefill: the grouped GEMM pass of config 4")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ragged"],
+                    help="decode: the headline layer-step (config 2); prefill: the grouped GEMM pass of config 4; "
+                         "ragged: the mixed batch of config 5 through the same pass")
     ap.add_argument("--tokens", type=int, default=16384, help="prefill: tokens a pass")
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -560,7 +592,7 @@ def main():
     args = ap.parse_args()
     if args.experts:
         CFG["E"] = args.experts
-    if args.workload == "prefill":
+    if args.workload in ("prefill", "ragged"):
         if args.steps == 200:
             args.steps = 20
         run_prefill_reference(args) if args.impl == "reference" else run_prefill(args)

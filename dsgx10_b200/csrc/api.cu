@@ -375,7 +375,7 @@ int dsgx_moe_prefill(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void*
                      const float* w, int T, void* ws, float* yr, float* ys, void* out, int ysum, void* stream) {
   const int rc = check_prefill_shape(s);
   if (rc) return rc;
-  if (!L || !wbuf || !x || !idx || !w || !ws || !yr || T < 1) return DSGX_ERR_ARG;
+  if (!L || !wbuf || !x || !idx || !w || !ws || (!yr && !out) || T < 1) return DSGX_ERR_ARG;
   if (((uintptr_t)wbuf & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh = L->sh.g != nullptr;
   if (sh && !ys && !(ysum & 1) && !out) return DSGX_ERR_ARG;

@@ -589,9 +589,11 @@ __global__ void __launch_bounds__(256) k_combine(const __nv_bfloat16* __restrict
 #pragma unroll
   for (int k = 0; k < 8; ++k) both[k] = __fadd_rn(acc[k], sh[k]);
   const bool sum = ysum && ysh;
-  float4* yr4 = reinterpret_cast<float4*>(yr + t * H + c);
-  yr4[0] = sum ? make_float4(both[0], both[1], both[2], both[3]) : make_float4(acc[0], acc[1], acc[2], acc[3]);
-  yr4[1] = sum ? make_float4(both[4], both[5], both[6], both[7]) : make_float4(acc[4], acc[5], acc[6], acc[7]);
+  if (yr) {  // (a caller that only wants the rounded rows gives no yr: a third of this kernel's traffic)
+    float4* yr4 = reinterpret_cast<float4*>(yr + t * H + c);
+    yr4[0] = sum ? make_float4(both[0], both[1], both[2], both[3]) : make_float4(acc[0], acc[1], acc[2], acc[3]);
+    yr4[1] = sum ? make_float4(both[4], both[5], both[6], both[7]) : make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
   if (ys && ysh) {
     float4* ys4 = reinterpret_cast<float4*>(ys + t * H + c);
     ys4[0] = make_float4(sh[0], sh[1], sh[2], sh[3]);

@@ -148,13 +148,18 @@ class LayerStep:
 class PrefillLayer:
     """A layer prepared for the prefill path: the K-major weight copy (made once) and a workspace for up to T_max rows."""
 
-    def __init__(self, shp, layer_w, T_max, device="cuda"):
+    def __init__(self, shp, layer_w, T_max, device="cuda", wbuf=None):
+        """wbuf: the prepared weight copy of another PrefillLayer of the same layer (a second workspace, e.g. for a
+        second stream, shares it)."""
         self.shp, self.layer_w, self.T_max = shp, layer_w, T_max
         nb = lib().dsgx_prefill_weights_bytes(C.byref(shp))
         if nb == 0:
             raise _lib.DsgxError(_lib.ERR_SHAPE, "dsgx_prefill_weights_bytes")
-        self.wbuf = torch.empty(nb, dtype=torch.uint8, device=device)
-        check(lib().dsgx_prefill_prepare(C.byref(shp), C.byref(layer_w), _ptr(self.wbuf), _stream()), "dsgx_prefill_prepare")
+        if wbuf is not None:
+            self.wbuf = wbuf
+        else:
+            self.wbuf = torch.empty(nb, dtype=torch.uint8, device=device)
+            check(lib().dsgx_prefill_prepare(C.byref(shp), C.byref(layer_w), _ptr(self.wbuf), _stream()), "dsgx_prefill_prepare")
         self.ws = torch.empty(lib().dsgx_prefill_ws_bytes(C.byref(shp), T_max), dtype=torch.uint8, device=device)
 
     def run(self, x, idx, w, yr=None, ys=None, out=None, ysum=False, parts=0):
@@ -162,8 +167,8 @@ class PrefillLayer:
         T, H = x.shape
         assert T <= self.T_max
         f32 = dict(dtype=torch.float32, device=x.device)
-        yr = torch.empty(T, H, **f32) if yr is None else yr
-        ys = torch.empty(T, H, **f32) if ys is None else ys
+        yr = torch.empty(T, H, **f32) if yr is None else (None if yr is False else yr)   # False: rounded rows only
+        ys = torch.empty(T, H, **f32) if ys is None else (None if ys is False else ys)
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if out is None else out
         check(lib().dsgx_moe_prefill(C.byref(self.shp), C.byref(self.layer_w), _ptr(self.wbuf), _ptr(x), _ptr(idx), _ptr(w), T,
                                      _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum) | parts << 8, _stream()), "dsgx_moe_prefill")

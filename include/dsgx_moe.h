@@ -210,7 +210,8 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* 
  * Stands in for gx::prefill_ws_bytes / gx::moe_prefill (altar1 engine/experts/experts.h:149-182) and dsk::moe_prefill
  * (ds41f engine/kernels/dsk.h:238-293): the rows' picks ordered by (expert id, token), the experts as grouped GEMMs on
  * the tensor cores, every pick's output added per row in ascending expert id.  x bf16 [T][H], idx / w from dsgx_route;
- * yr, ys f32 [T][H] as dsgx_moe_decode; out_bf16 (may be null) receives bf16(yr + ys).
+ * yr, ys f32 [T][H] as dsgx_moe_decode; out_bf16 (may be null) receives bf16(yr + ys); with out_bf16 given, yr and ys may
+ * be null (one GPU: only the rounded rows are wanted, and the f32 sums are a third of the combine's traffic).
  *
  * The tensor-core path reads the weights K-major: dsgx_prefill_prepare re-tiles a layer's tile_fp8 blocks once at load
  * time into wbuf (dsgx_prefill_weights_bytes(shape) bytes of device memory), as the reference re-tiles its checkpoints
