@@ -22,7 +22,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-CFG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4)
+CFG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4, score_fn=0, fmt="fp8")
+CFG_INT4 = dict(H=6144, I=2048, E=168, topk=8, n_group=1, topk_group=1, score_fn=1, fmt="int4")   # config 3
 SEED = 20261102
 
 
@@ -77,12 +78,16 @@ def step_bytes(rows_union, rows):
     """Algorithmic bytes of one step: each distinct picked expert and the shared expert once (three matrices and
     their block scales), the router weights, the activations in and out."""
     H, I, E = CFG["H"], CFG["I"], CFG["E"]
+    if CFG["fmt"] == "int4":  # routed experts in 2368-byte blocks of 8 x 512 values, the shared expert bf16
+        return rows_union * 3 * I * H * 2368 // 4096 + 3 * I * H * 2 + E * H * 4 + rows * H * 2 * 2
     expert = 3 * I * H + 3 * (I // 128) * (H // 128) * 4
     return (rows_union + 1) * expert + E * H * 4 + rows * H * 2 * 2
 
 
 def up_bytes(rows_union):
     H, I = CFG["H"], CFG["I"]
+    if CFG["fmt"] == "int4":
+        return rows_union * 2 * I * H * 2368 // 4096 + 2 * I * H * 2
     return (rows_union + 1) * (2 * I * H + 2 * (I // 128) * (H // 128) * 4)
 
 
@@ -169,11 +174,16 @@ def run_gpu(args):
     H, I, E, topk = CFG["H"], CFG["I"], CFG["E"], CFG["topk"]
     rows = args.rows
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
-    shp = moe.shape(H, I, E, topk, n_group=CFG["n_group"], topk_group=CFG["topk_group"], e_lo=e_lo, e_hi=e_hi)
+    int4 = CFG["fmt"] == "int4"
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4 if int4 else _lib.FMT_FP8, n_group=CFG["n_group"],
+                    topk_group=CFG["topk_group"], score_fn=CFG["score_fn"], e_lo=e_lo, e_hi=e_hi)
     NL, NX = args.layers, 16
     layers, steps_buf = [], []
     for l in range(NL):
-        lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+        if int4:
+            lay = synth.Int4Layer.on_device(H, I, E, SEED + 7919 * l, dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+        else:
+            lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
         wr = synth.router_weights(E, H, SEED + 2000 + l, device="cpu").to(dev)
         layers.append((lay, lay.layer_w()))
         steps_buf.append(moe.LayerStep(shp, wr, None, device=dev, fused=False if args.separate else True if args.fused else None))
@@ -302,9 +312,12 @@ def run_gpu(args):
     line = {
         "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
-                               f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows,
+        "vs_baseline": None, "dtype": "int4-g32 weights, bf16 activations (f32 accumulate)" if int4 else "fp8_e4m3 (f32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": (f"config 3: INT4-g32 MoE decode layer-step, hidden 6144, 168 experts x 2048, top-8 softmax, "
+                                f"+ bf16 shared expert, rows {rows}" if int4 else
+                                f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
+                                f"(8 groups / 4), + shared expert, rows {rows}"), "rows": rows,
                    "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
                                                    " (partial sums reduced over peer memory by k_finalize_peers)"), "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
                    "launch": "eager" if args.eager else "one CUDA graph of the timed steps"},
@@ -313,12 +326,12 @@ def run_gpu(args):
         "step_frac_of_measured_hbm": sb_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
         "step_frac_of_8tbs": sb_bytes / (us * 1e-6) / 1e9 / 8000.0,
         "step_algorithmic_bytes": sb_bytes,
-        "roofline": {"bound": "hbm", "kernel": "k_up_fp8 (+ activation quantisation launch)", "achieved": ach,
+        "roofline": {"bound": "hbm", "kernel": ("k_up_i4" if int4 else "k_up_fp8") + " (+ activation staging launch)", "achieved": ach,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
                      "us_per_launch": us_up, "algorithmic_bytes": upb,
                      # one ncu capture of this kernel (profiles/decode_fp8_rows1_launches_k_up_k_down.md): 151.14 MB read +
                      # 3.91 MB written for 151.03 MB algorithmic; the traffic grows with the experts a launch streams
-                     "traffic": upb * (151.142912 + 3.909120) / 151.031808,
+                     "traffic": None if int4 else upb * (151.142912 + 3.909120) / 151.031808,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "
                                        "this launch's algorithmic bytes"},
         "e2e": {"value": us_e2e, "unit": "us", "h2d_bytes_per_step": rows * H * 2, "d2h_bytes_per_step": rows * H * 2},
@@ -328,7 +341,7 @@ def run_gpu(args):
         "clocks": clocks,
         "device_status": status,
     }
-    if not args.no_cpu_baseline and world == 1:
+    if not args.no_cpu_baseline and world == 1 and not int4:
         line["cpu_baseline"] = cpu_baseline(rows)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -577,7 +590,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ragged"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "int4", "prefill", "ragged"],
                     help="decode: the headline layer-step (config 2); prefill: the grouped GEMM pass of config 4; "
                          "ragged: the mixed batch of config 5 through the same pass")
     ap.add_argument("--tokens", type=int, default=16384, help="prefill: tokens a pass")
@@ -592,6 +605,10 @@ def main():
     args = ap.parse_args()
     if args.experts:
         CFG["E"] = args.experts
+    if args.workload == "int4":  # config 3: the same decode bench over an INT4-g32 layer
+        CFG.update(CFG_INT4)
+        if args.layers == 3:
+            args.layers = 2
     if args.workload in ("prefill", "ragged"):
         if args.steps == 200:
             args.steps = 20

@@ -193,6 +193,39 @@ class Int4Layer:
                             for i, (n, k) in enumerate(shapes)]
             self.sh_dev = [torch.from_numpy(tile_bf16(b)).to(self.device) for b in self.sh_bits]
 
+    @classmethod
+    def on_device(cls, H, I, E, seed, device, shared=True, e_range=None):
+        """A layer of the same format and value ranges built straight in the block layout on the device (uniform
+        nibbles, bf16 scales in [2^-9, 2^-7), zero point 8, bf16 shared expert N(0, 0.02)): for benchmarks of full-size
+        layers, where packing 168 experts through numpy takes minutes.  It keeps no canonical copy for the oracle."""
+        self = cls.__new__(cls)
+        self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_INT4
+        self.device = torch.device(device)
+        shapes = ((I, H), (I, H), (H, I))
+        mat_b = (I // 8) * (H // 512) * 2368
+        lo, hi = e_range if e_range is not None else (0, E)
+        g = _gen(self.device, seed)
+        nblk = max(hi - lo, 1) * 3 * mat_b // 2368
+        pool = torch.empty(nblk, 2368, dtype=torch.uint8, device=self.device)
+        pool[:, :2048] = torch.randint(0, 256, (nblk, 2048), generator=g, device=self.device, dtype=torch.uint8)
+        sc = pool[:, 2048:2304].view(nblk, 128, 2)           # little-endian bf16: random mantissa, exponent of 2^-9..2^-8
+        sc[:, :, 0] = torch.randint(0, 256, (nblk, 128), generator=g, device=self.device, dtype=torch.uint8)
+        sc[:, :, 1] = 0x3B
+        pool[:, 2304:] = 0x88
+        self.pool = pool.view(-1)
+        self.raw = {}
+        self.desc_host = (_lib.MatDesc * (E * 3))()
+        for n, e in enumerate(range(lo, hi)):
+            for m in range(3):
+                d = self.desc_host[e * 3 + m]
+                d.off, d.s2, d.fmt = (n * 3 + m) * mat_b, 1.0, _lib.FMT_INT4
+        self.desc = torch.frombuffer(bytearray(bytes(self.desc_host)), dtype=torch.uint8).to(self.device)
+        self.shared = shared
+        if shared:
+            self.sh_dev = [(torch.randn(n * k, generator=g, device=self.device) * 0.02).to(torch.bfloat16).view(torch.uint8)
+                           for n, k in shapes]   # any order of N(0, 0.02) values is a tiled N(0, 0.02) matrix
+        return self
+
     def layer_w(self):
         L = _lib.LayerW()
         L.pool, L.desc, L.fmt = self.pool.data_ptr(), self.desc.data_ptr(), _lib.FMT_INT4
