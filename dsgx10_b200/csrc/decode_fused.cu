@@ -443,8 +443,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
     if (stamp && lane == 0) stamp[6] = gtime();
     if (ok) {
       route_row_cta(sp.rp, p.ws.lpart + (size_t)row * p.E, KS, (size_t)kMaxRows * p.E, sp.bias, rs,
-                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk,
-                    sp.stamps ? sp.stamps + (size_t)GW * 8 + row * 8 : nullptr);
+                    sp.logits ? sp.logits + (size_t)row * p.E : nullptr, sp.idx + row * p.topk, sp.w + row * p.topk);
       if (stamp && lane == 0) stamp[7] = gtime();
       bool last = true;
       if (p.M > 1) {  // the last row to be routed builds the table

@@ -200,17 +200,8 @@ struct __align__(16) RouteSmem {
 };
 
 DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
-                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out,
-                            unsigned long long* dbg = nullptr) {
+                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out) {
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5, nW = blockDim.x >> 5;
-  auto mark = [&](int i) {
-    if (dbg && threadIdx.x == 0) {
-      unsigned long long t;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-      dbg[i] = t;
-    }
-  };
-  mark(0);
   const bool valid = e < p.E;
   float lg = -INFINITY, b = 0.f;
   if (valid) {
@@ -251,14 +242,12 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     s = __fdiv_rn(t, sm.S);
     __syncthreads();
   }
-  mark(1);
   // keys as order-preserving unsigned integers in shared memory (0 = not a candidate)
   uint32_t* ku = reinterpret_cast<uint32_t*>(sm.key);
   sm.s[e] = s;
   __syncthreads();  // (softmax read sm.key above)
   ku[e] = valid ? ord_key(__fadd_rn(s, b)) : 0u;
   __syncthreads();
-  mark(2);
   // ---- selection, all warps: group scores one warp a group, then every candidate ranks itself --------------------------
   float* picked = sm.red;  // [8] scores of the picks (sm.red is free by now)
   int* ids = reinterpret_cast<int*>(sm.red + 8);
@@ -300,7 +289,6 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     if (valid && !((sm.keep >> (e / gs)) & 1)) ku[e] = 0u;
     __syncthreads();
   }
-  mark(3);
   // rank of a candidate = keys above it + equal keys with a lower id; ranks 0 .. topk-1 are the picks in order
   if (valid) {
     const uint32_t mine = ku[e];
@@ -326,7 +314,6 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   }
   __syncthreads();
   if (warp != 0) return;
-  mark(4);
   // the sum of the picked scores: four running sums at stride 4, then (t0 + t2) + (t1 + t3)
   float t[4];
 #pragma unroll
@@ -345,7 +332,6 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   else if (p.topk == 3) sum = __fadd_rn(__fadd_rn(t[0], t[2]), t[1]);
   else sum = __fadd_rn(__fadd_rn(t[0], t[2]), __fadd_rn(t[1], t[3]));
   sum = __fadd_rn(sum, 1e-20f);
-  mark(5);
   if (lane < p.topk) {
     const float pk = picked[lane];
     idx_out[lane] = ids[lane];
