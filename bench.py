@@ -284,10 +284,14 @@ def run_gpu(args):
         sb = steps_buf[i]
         union.append(len(set(sb.idx[:rows].flatten().tolist()) & set(range(e_lo, e_hi))))
 
-    def up_only(i):
+    # (FP8: the kernel alone, hook 5, over the table and quantised rows that one hook-1 call a layer leaves in the
+    # workspace; INT4: with its preparation launch)
+    def up_only(i, parts=1 if int4 else 5):
         lay, lw = layers[i % NL]
         sb = steps_buf[i % NL]
-        moe.moe_decode(shp, lw, xs[i % NX], sb.idx, sb.w, sb.ws, sb.yr, sb.ys, parts=1)
+        moe.moe_decode(shp, lw, xs[i % NX], sb.idx, sb.w, sb.ws, sb.yr, sb.ys, parts=parts)
+    for i in range(NL):
+        up_only(i, parts=1)
     for i in range(3):
         up_only(i)
     ms_up = timed(up_only, args.steps)
@@ -326,7 +330,7 @@ def run_gpu(args):
         "step_frac_of_measured_hbm": sb_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
         "step_frac_of_8tbs": sb_bytes / (us * 1e-6) / 1e9 / 8000.0,
         "step_algorithmic_bytes": sb_bytes,
-        "roofline": {"bound": "hbm", "kernel": ("k_up_i4" if int4 else "k_up_fp8") + " (+ activation staging launch)", "achieved": ach,
+        "roofline": {"bound": "hbm", "kernel": ("k_up_i4 (+ activation staging launch)" if int4 else "k_up_fp8"), "achieved": ach,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
                      "us_per_launch": us_up, "algorithmic_bytes": upb,
                      # one ncu capture of this kernel (profiles/decode_fp8_rows1_launches_k_up_k_down.md): 151.14 MB read +

@@ -139,7 +139,8 @@ int dsgx_sort_pack_static(const int32_t* idx, int T, int topk, int E, int32_t* c
 typedef struct dsgx_decode_cfg {
   int32_t ysum;        /* 1: ys is added into yr after the routed experts and yr is the only output (experts.h:132-137) */
   int32_t pdl;         /* 1: launch with programmatic dependent launch (experts.h:120) */
-  int32_t parts;       /* bench hook (experts.h:121): 0 or 3 the whole step, 1 gate/up only, 2 down only */
+  int32_t parts;       /* bench hook (experts.h:121): 0 or 3 the whole step, 1 gate/up only, 2 down only; FP8 layers: 5 the
+                          gate/up kernel alone, over the slot table and quantised rows an earlier call left in ws */
   int32_t up, down;    /* kernel variants (experts.h:114-118): 0 the default; every variant gives the same bits */
   int32_t reserved[3];
 } dsgx_decode_cfg;
