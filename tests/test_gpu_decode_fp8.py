@@ -143,6 +143,18 @@ def test_layer_step_equals_separate_calls(orc, H, I, E, topk, M, ng, tg):
     step.run_host(layer.layer_w(), xh, oh)
     torch.cuda.synchronize()
     assert torch.equal(oh, out.cpu())
+    # pageable host memory goes through the copy engine instead of being used in place: the same bits
+    xp, op = x.cpu().clone(), torch.zeros(M, H, dtype=torch.bfloat16)
+    step.run_host(layer.layer_w(), xp, op)
+    torch.cuda.synchronize()
+    assert torch.equal(op, out.cpu())
+    # the gate/up kernel alone (bench hook 5) over what a hook-1 call left in the workspace repeats its h
+    moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws, parts=1)
+    torch.cuda.synchronize()
+    snap = ws.clone()
+    moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws, parts=5)
+    torch.cuda.synchronize()
+    assert torch.equal(ws, snap) and moe.ws_status(ws) == 0
 
 
 def test_kernel_variants_same_bits(orc):

@@ -88,6 +88,25 @@ def test_expert_parallel_and_no_shared(orc):
         _check(orc, shp, layer, x, idx, w, yr, ys, out, shared=shared, e_lo=e_lo, e_hi=e_hi)
 
 
+def test_rounded_rows_only_and_gemm_hooks(orc):
+    """Without the f32 outputs the rounded rows are the same; the bench hooks that launch one grouped GEMM alone over
+    the workspace of a whole pass change nothing."""
+    from dsgx10_b200 import moe
+    T = 300
+    shp, layer, x, wr, bias, idx, w = _setup(1024, 512, 16, 4, T, seed=280)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    out = out.clone()
+    _, _, out2 = pl.run(x, idx, w, yr=False, ys=False)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
+    snap = pl.ws.clone()
+    for parts in (1, 2):
+        pl.run(x, idx, w, yr=False, ys=False, parts=parts)
+        torch.cuda.synchronize()
+        assert torch.equal(pl.ws, snap) and moe.ws_status(pl.ws) == 0
+
+
 def test_chunk_invariance(orc):
     """A row's bits do not depend on the other rows of the chunk (altar1 engine/experts/tests/test_prefill.inc:293-302)."""
     from dsgx10_b200 import moe
