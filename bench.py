@@ -468,10 +468,11 @@ def run_prefill(args):
 
     # end to end: host activations in, router, experts, host bf16 out; the pass is cut into chunks of tokens that go
     # round two streams (each with its own workspace), so that the copies of one chunk overlap the kernels of another
-    NCH = 4 if T % 4 == 0 and T >= 4096 else 1
+    NCH = args.chunks if T % args.chunks == 0 and T >= 4096 else 1
     TC = T // NCH
-    streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
-    pls = [pl, moe.PrefillLayer(shp, lay.layer_w(), TC, device=dev, wbuf=pl.wbuf)] if NCH > 1 else [pl]
+    NS = 3 if NCH > 2 else 2
+    streams = [torch.cuda.Stream(device=dev) for _ in range(NS)]
+    pls = [pl] + [moe.PrefillLayer(shp, lay.layer_w(), TC, device=dev, wbuf=pl.wbuf) for _ in range(NS - 1)] if NCH > 1 else [pl]
 
     def whole(i):
         xh = xs_host[i % NX]
@@ -479,7 +480,7 @@ def run_prefill(args):
         for s in streams:
             s.wait_stream(cur)
         for c in range(NCH):
-            s, p2 = streams[c % 2], pls[c % len(pls)]
+            s, p2 = streams[c % NS], pls[c % len(pls)]
             lo, hi = c * TC, (c + 1) * TC
             with torch.cuda.stream(s):
                 x_stage[lo:hi].copy_(xh[lo:hi], non_blocking=True)
@@ -556,7 +557,7 @@ def run_prefill(args):
                    "segments": {"max": int(c[0]), "median": int(np.median(c)), "min": int(c[-1])},
                    "parallelism": f"ep{world}", "cold_inputs": f"{NX} activation sets cycled; inputs and intermediates larger than L2",
                    "step": "sort/permute + quantise + gate/up GEMM (SwiGLU) + down GEMM + shared expert + combine",
-                   "e2e": f"{NCH} chunks of {TC} tokens over two streams: copy in, router, expert pass, copy out"},
+                   "e2e": f"{NCH} chunks of {TC} tokens over {NS} streams: copy in, router, expert pass, copy out"},
         "tokens_per_s": T / (ms * 1e-3),
         "roofline": {"bound": "tensor", "kernel": "k_gemm_fp8<up> (routed gate/up grouped GEMM, SwiGLU and h quantisation fused)",
                      "achieved": ach, "peak": fp8_peak, "unit": "TFLOP/s", "frac": ach / fp8_peak,
@@ -598,6 +599,7 @@ def main():
                     help="decode: the headline layer-step (config 2); prefill: the grouped GEMM pass of config 4; "
                          "ragged: the mixed batch of config 5 through the same pass")
     ap.add_argument("--tokens", type=int, default=16384, help="prefill: tokens a pass")
+    ap.add_argument("--chunks", type=int, default=4, help="prefill end to end: chunks of tokens the pass is cut into")
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
