@@ -75,16 +75,18 @@ __global__ void __launch_bounds__(512) k_route_union(RouteParams rp, TabArgs ta,
   pdl_wait();
   const int row = blockIdx.x;
   route_row_cta(rp, lpart + (size_t)row * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, rs,
-                logits ? logits + (size_t)row * rp.E : nullptr, idx + row * rp.topk, w + row * rp.topk);
-  // the last row to finish builds the slot table of the step
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_ticket = ta.M > 1 ? atomicAdd(cnt, 1) : 0;
-  __syncthreads();
-  if (s_ticket != ta.M - 1) return;
-  __threadfence();
-  for (int i = threadIdx.x; i < ta.M * ta.topk; i += blockDim.x) s_idx[i] = __ldcg(idx + i), s_w[i] = __ldcg(w + i);
-  if (threadIdx.x == 0 && ta.M > 1) *cnt = 0;
+                logits ? logits + (size_t)row * rp.E : nullptr, idx + row * rp.topk, w + row * rp.topk,
+                ta.M == 1 ? s_idx : nullptr, s_w);
+  if (ta.M > 1) {  // the last row to finish builds the slot table of the step (one row: its picks are in shared memory)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(cnt, 1);
+    __syncthreads();
+    if (s_ticket != ta.M - 1) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < ta.M * ta.topk; i += blockDim.x) s_idx[i] = __ldcg(idx + i), s_w[i] = __ldcg(w + i);
+    if (threadIdx.x == 0) *cnt = 0;
+  }
   __syncthreads();
   build_slot_tab(tab, bm, s_idx, s_w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
   if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);

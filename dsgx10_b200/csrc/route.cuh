@@ -200,7 +200,8 @@ struct __align__(16) RouteSmem {
 };
 
 DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
-                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out) {
+                            const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out,
+                            int* idx_copy = nullptr, float* w_copy = nullptr) {
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5, nW = blockDim.x >> 5;
   const bool valid = e < p.E;
   float lg = -INFINITY, b = 0.f;
@@ -334,8 +335,10 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   sum = __fadd_rn(sum, 1e-20f);
   if (lane < p.topk) {
     const float pk = picked[lane];
+    const float wv = p.norm_topk ? __fmul_rn(__fdiv_rn(pk, sum), p.route_scale) : __fmul_rn(pk, p.route_scale);
     idx_out[lane] = ids[lane];
-    w_out[lane] = p.norm_topk ? __fmul_rn(__fdiv_rn(pk, sum), p.route_scale) : __fmul_rn(pk, p.route_scale);
+    w_out[lane] = wv;
+    if (idx_copy) idx_copy[lane] = ids[lane], w_copy[lane] = wv;  // (a copy in shared memory for the caller's next step)
   }
 }
 
