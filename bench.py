@@ -333,7 +333,7 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "kernel": ("k_up_i4 (+ activation staging launch)" if int4 else "k_up_fp8"), "achieved": ach,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
                      "us_per_launch": us_up, "algorithmic_bytes": upb,
-                     # one ncu capture of this kernel (profiles/decode_fp8_rows1_launches_k_up_k_down.md): 151.14 MB read +
+                     # one ncu capture of this kernel (its summary is among the committed profiles): 151.14 MB read +
                      # 3.91 MB written for 151.03 MB algorithmic; the traffic grows with the experts a launch streams
                      "traffic": None if int4 else upb * (151.142912 + 3.909120) / 151.031808,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Generates tests/golden/*.npz by running the reference's own Python CPU modules on small seeded layers.
 
-Run in a container that has the reference tree (default /root/reference); the fixtures it writes are committed, this
+Run in a container that has the reference tree (its location: DSGX_REFERENCE, default below); the fixtures it writes are committed, this
 script is how they were made.  Nothing of the reference is copied: its modules are imported from where they lie.
 
   FP8:  ds41f ref/inference/model.py (Gate, Expert, MoE) over ref/torchref/kernel.py, switched to the "g128" recipe the
