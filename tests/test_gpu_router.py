@@ -21,6 +21,8 @@ CASES = [
     (6144, 168, 8, 1, 1, 0, 2.5, 8),
     (256, 8, 2, 1, 1, 0, 1.0, 3),
     (1280, 40, 3, 4, 2, 1, 1.0, 7),
+    (1024, 512, 8, 16, 4, 0, 1.0, 2),     # the largest expert count, a CTA a row
+    (1024, 512, 8, 8, 3, 1, 1.0, 33),     # the same through the warp-a-row kernel
 ]
 
 
