@@ -209,15 +209,17 @@ def run_gpu(args):
                 sb.run(lw, xs[i % NX])
             return
         x = xs[i % NX]
-        if host:
+        if host and peer is None:
             sb.x_stage[:rows].copy_(xs_host[i % NX], non_blocking=True)
             x = sb.x_stage[:rows]
         if peer is not None:
             yr_p, ys_p = peer.parts(peer.launched + 1)
-            sb.run(lw, x, finalize=False, yr=yr_p, ys=ys_p)
-            out = peer.finalize(rows)
-            if host:
-                out_host.copy_(out, non_blocking=True)
+            if host:  # host buffers in place: copy-in kernel, partial sums, then the reduction writes the pinned rows
+                sb.run_host(lw, xs_host[i % NX], None, yr=yr_p, ys=ys_p)
+                peer.finalize(rows, out=out_host)
+            else:
+                sb.run(lw, x, finalize=False, yr=yr_p, ys=ys_p)
+                peer.finalize(rows)
             return
         sb.run(lw, x, finalize=False)
         red[0].copy_(sb.yr)

@@ -286,20 +286,22 @@ static void* mapped_alias(const void* host) {
 
 int dsgx_moe_layer_decode_host(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* x_host, int M,
                                const dsgx_layer_step* st, void* out_host, void* stream) {
-  if (!st || !st->x_stage || !st->out_bf16 || !x_host || !out_host || !s) return DSGX_ERR_ARG;
+  if (!st || !st->x_stage || !x_host || !s) return DSGX_ERR_ARG;
+  if (out_host && !st->out_bf16) return DSGX_ERR_ARG;
   if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
   const size_t bytes = (size_t)M * s->H * 2;
   // Host buffers the device can address (pinned, mapped memory) are used in place: a small kernel pulls x over PCIe
   // into the staging buffer, and the step's last kernel writes the rounded rows straight into out_host, instead of two
   // copy-engine transfers of a few KB whose fixed cost is several microseconds each.
   void* x_dev = mapped_alias(x_host);
-  void* out_dev = mapped_alias(out_host);
+  void* out_dev = out_host ? mapped_alias(out_host) : nullptr;
   cudaError_t e;
   if (x_dev && bytes % 16 == 0 && ((uintptr_t)x_dev & 15) == 0)
     e = launch_copy_in(x_dev, st->x_stage, bytes, (cudaStream_t)stream);
   else
     e = cudaMemcpyAsync(st->x_stage, x_host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream);
   if (e != cudaSuccess) return cuda_fail(e);
+  if (!out_host) return dsgx_moe_layer_decode(s, L, st->x_stage, M, st, 0, stream);  // the partial sums only
   if (out_dev && ((uintptr_t)out_dev & 15) == 0) {
     dsgx_layer_step direct = *st;
     direct.out_bf16 = out_dev;

@@ -131,12 +131,14 @@ class PeerReduce:
         """(yr, ys) f32 [rows_cap][H] of step number `step` (1, 2, ...) in this rank's symmetric buffer."""
         return self._parts[step & 1, 0], self._parts[step & 1, 1]
 
-    def finalize(self, M, count=True):
+    def finalize(self, M, count=True, out=None):
+        """out: where the rounded rows go (default: this object's device buffer; a pinned host tensor is written in place)."""
         lib = self._lib.lib()
-        rc = lib.dsgx_finalize_peers(C.byref(self.set), M, self.H, C.c_void_p(self.out.data_ptr()),
+        dst = self.out if out is None else out
+        rc = lib.dsgx_finalize_peers(C.byref(self.set), M, self.H, C.c_void_p(dst.data_ptr()),
                                      C.c_void_p(self.status.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
         if rc:
             raise self._lib.DsgxError(rc, "dsgx_finalize_peers")
         if count:
             self.launched += 1
-        return self.out[:M]
+        return dst[:M]

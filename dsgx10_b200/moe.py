@@ -137,10 +137,15 @@ class LayerStep:
                                           int(finalize), _stream()), "dsgx_moe_layer_decode")
         return self.out[:M]
 
-    def run_host(self, layer_w, x_host, out_host):
-        """x_host, out_host: pinned bf16 host tensors [M][H]; copies, the step and the read-back in stream order."""
+    def run_host(self, layer_w, x_host, out_host, yr=None, ys=None):
+        """x_host, out_host: pinned bf16 host tensors [M][H]; copies, the step and the read-back in stream order.
+        out_host None: the step stops at the partial sums (in yr, ys when given: a peer-reduced step's buffers)."""
         M = x_host.shape[0]
-        check(lib().dsgx_moe_layer_decode_host(C.byref(self.shp), C.byref(layer_w), _ptr(x_host), M, C.byref(self.c),
+        c = self.c
+        if yr is not None:
+            c = _lib.LayerStep.from_buffer_copy(self.c)
+            c.yr, c.ys = _ptr(yr), _ptr(ys)
+        check(lib().dsgx_moe_layer_decode_host(C.byref(self.shp), C.byref(layer_w), _ptr(x_host), M, C.byref(c),
                                                _ptr(out_host), _stream()), "dsgx_moe_layer_decode_host")
         return out_host
 

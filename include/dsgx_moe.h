@@ -203,7 +203,8 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, co
 /* The same with HOST buffers: x_host bf16 [M][H] is brought to the device, the step runs, and out_host bf16 [M][H]
  * receives the result; all in stream order, the caller synchronises.  Pinned (mapped) buffers are used in place: a small
  * kernel reads x_host over PCIe and the step's last kernel writes out_host directly; other host memory goes through
- * cudaMemcpyAsync. */
+ * cudaMemcpyAsync.  out_host null: the step stops at the f32 partial sums yr / ys (an expert-parallel rank, whose rows
+ * are rounded after the reduction: dsgx_finalize_peers may write its out_bf16 straight into mapped host memory). */
 int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_host, int M,
                                const dsgx_layer_step* step, void* out_host, void* stream);
 
