@@ -460,8 +460,20 @@ def run_prefill(args):
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     x_stage = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
 
+    # several GPUs: rank 0 adds the shared expert's output into its partial sums; the partial sums are written into
+    # symmetric memory and one kernel a GPU adds them over NVLink and rounds (--nccl: an NCCL all-reduce instead)
+    peer = None
+    if world > 1 and not args.nccl:
+        from dsgx10_b200 import ep
+        peer = ep.PeerReduce(H, rows_cap=T, shared_rank=-1)
+
     def experts(i):
         idx, w = routed[i % NX]
+        if peer is not None:
+            yr_p, _ = peer.parts(peer.launched + 1)
+            pl.run(xs[i % NX], idx, w, yr=yr_p, ys=False, out=False, ysum=True)
+            peer.finalize(T, out=out)
+            return
         # one GPU: only the rounded rows; several: the f32 partial sums for the reduction
         pl.run(xs[i % NX], idx, w, yr=yr if world > 1 else False, ys=ys if world > 1 else False, out=out, ysum=world > 1)
         if world > 1:  # rank 0's partial sums hold the shared expert's output too: one buffer to reduce
@@ -490,7 +502,7 @@ def run_prefill(args):
                 idx, w = moe.route(shp_all, lg, bias)
                 p2.run(x_stage[lo:hi], idx, w, yr=yr[lo:hi] if world > 1 else False, ys=ys[lo:hi] if world > 1 else False,
                        out=out[lo:hi], ysum=world > 1)
-                if world > 1:
+                if world > 1:  # (the chunked end-to-end pipeline keeps the NCCL reduction: one reduction a chunk and stream)
                     dist.all_reduce(yr[lo:hi])
                     out[lo:hi].copy_(moe.finalize(yr[lo:hi]))
                 out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
@@ -557,7 +569,9 @@ def run_prefill(args):
                                 f"config 4: prefill MoE, hidden 2048, 64 experts x 1024, top-6, + shared expert, {T} tokens, "
                                 f"Zipf(1.1) expert popularity (router bias scale {alpha})"), "tokens": T,
                    "segments": {"max": int(c[0]), "median": int(np.median(c)), "min": int(c[-1])},
-                   "parallelism": f"ep{world}", "cold_inputs": f"{NX} activation sets cycled; inputs and intermediates larger than L2",
+                   "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
+                                                   " (partial sums reduced over peer memory by k_finalize_peers)"),
+                   "cold_inputs": f"{NX} activation sets cycled; inputs and intermediates larger than L2",
                    "step": "sort/permute + quantise + gate/up GEMM (SwiGLU) + down GEMM + shared expert + combine",
                    "e2e": f"{NCH} chunks of {TC} tokens over {NS} streams: copy in, router, expert pass, copy out"},
         "tokens_per_s": T / (ms * 1e-3),

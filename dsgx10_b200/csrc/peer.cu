@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
 cudaError_t launch_finalize_peers(const PeerParams& p, cudaStream_t st) {
   const int n = p.M * (p.H / 4);
   int grid = (n + 255) / 256;
-  if (grid > 32) grid = 32;
+  const int cap = n > (1 << 16) ? 4 * sm_count() : 32;  // decode widths: a few CTAs; a prefill's rows: the whole GPU
+  if (grid > cap) grid = cap;
   k_finalize_peers<<<grid, 256, 0, st>>>(p);
   return cudaGetLastError();
 }

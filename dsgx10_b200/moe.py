@@ -174,7 +174,7 @@ class PrefillLayer:
         f32 = dict(dtype=torch.float32, device=x.device)
         yr = torch.empty(T, H, **f32) if yr is None else (None if yr is False else yr)   # False: rounded rows only
         ys = torch.empty(T, H, **f32) if ys is None else (None if ys is False else ys)
-        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if out is None else out
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if out is None else (None if out is False else out)
         check(lib().dsgx_moe_prefill(C.byref(self.shp), C.byref(self.layer_w), _ptr(self.wbuf), _ptr(x), _ptr(idx), _ptr(w), T,
                                      _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum) | parts << 8, _stream()), "dsgx_moe_prefill")
         return yr, ys, out

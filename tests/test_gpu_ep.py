@@ -75,6 +75,20 @@ def _worker(rank, world, port, q):
             dist.all_gather(both, got)
             peer_same = peer_same and bool(torch.equal(both[0], both[1]))
         res["peer_ok"], res["peer_same"], res["peer_status"] = peer_ok, peer_same, int(pr.status.item())
+        # the same kernel over a prefill's rows (its many-CTA form): f32 partial sums of 600 rows, no shared-expert term
+        prw = ep.PeerReduce(H, rows_cap=600, shared_rank=-1)
+        wide_ok = True
+        for step_no in range(1, 3):
+            part = torch.randn(600, H, device=dev, generator=torch.Generator(device=dev).manual_seed(500 + 10 * step_no + rank))
+            yr_p, _ = prw.parts(prw.launched + 1)
+            yr_p.copy_(part)
+            got = prw.finalize(600).clone()
+            both = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(both, part)
+            want = moe.finalize(both[0] + both[1])
+            torch.cuda.synchronize()
+            wide_ok = wide_ok and bool(torch.equal(got, want))
+        res["peer_wide_ok"], res["peer_wide_status"] = wide_ok, int(prw.status.item())
         # prefill: rows partitioned, all-to-all dispatch and combine
         T = 96
         xa = synth.activations(T, H, 303).to(dev)
@@ -115,3 +129,4 @@ def test_two_gpus_match_one():
         assert res["decode_yr"] <= 1e-6 and res["decode_ys"] == 0.0, res    # only the association of the f32 adds differs
         assert res["prefill"] <= 1e-6, res
         assert res["peer_ok"] and res["peer_same"] and res["peer_status"] == 0, res
+        assert res["peer_wide_ok"] and res["peer_wide_status"] == 0, res
