@@ -64,16 +64,25 @@ __global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
     const int per = p.H / 4;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.M * per; i += gridDim.x * blockDim.x) {
       const int r = i / per, c = (i - r * per) * 4;
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int q = 0; q < p.world; ++q) {  // rank order, the same on every rank
-        const float4 v = ld_peer4(p.parts[q] + off + (size_t)r * p.H + c);
-        a.x = q ? __fadd_rn(a.x, v.x) : v.x, a.y = q ? __fadd_rn(a.y, v.y) : v.y;
-        a.z = q ? __fadd_rn(a.z, v.z) : v.z, a.w = q ? __fadd_rn(a.w, v.w) : v.w;
+      // every rank's piece is requested before the first add (the loads cross NVLink: one round trip, not one a rank);
+      // the adds keep the rank order, the same on every rank
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), sv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.shared_rank >= 0) sv = ld_peer4(p.parts[p.shared_rank] + off + (size_t)(p.rows_cap + r) * p.H + c);
+      for (int q0 = 0; q0 < p.world; q0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (q0 + j < p.world) v[j] = ld_peer4(p.parts[q0 + j] + off + (size_t)r * p.H + c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (q0 + j < p.world) {
+            const bool first = q0 + j == 0;
+            a.x = first ? v[j].x : __fadd_rn(a.x, v[j].x), a.y = first ? v[j].y : __fadd_rn(a.y, v[j].y);
+            a.z = first ? v[j].z : __fadd_rn(a.z, v[j].z), a.w = first ? v[j].w : __fadd_rn(a.w, v[j].w);
+          }
       }
-      if (p.shared_rank >= 0) {
-        const float4 s = ld_peer4(p.parts[p.shared_rank] + off + (size_t)(p.rows_cap + r) * p.H + c);
-        a.x = __fadd_rn(a.x, s.x), a.y = __fadd_rn(a.y, s.y), a.z = __fadd_rn(a.z, s.z), a.w = __fadd_rn(a.w, s.w);
-      }
+      if (p.shared_rank >= 0)
+        a.x = __fadd_rn(a.x, sv.x), a.y = __fadd_rn(a.y, sv.y), a.z = __fadd_rn(a.z, sv.z), a.w = __fadd_rn(a.w, sv.w);
       const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
       uint2 o;
       o.x = *reinterpret_cast<const uint32_t*>(&lo), o.y = *reinterpret_cast<const uint32_t*>(&hi);
