@@ -465,14 +465,15 @@ def run_prefill(args):
     peer = None
     if world > 1 and not args.nccl:
         from dsgx10_b200 import ep
-        peer = ep.PeerReduce(H, rows_cap=T, shared_rank=-1)
+        # two GPUs: each reads the other's whole partial sums; more: each reduces 1 / N of the rows and stores them everywhere
+        peer = ep.PeerReduce(H, rows_cap=T, shared_rank=-1, sliced=world > 2)
 
     def experts(i):
         idx, w = routed[i % NX]
         if peer is not None:
             yr_p, _ = peer.parts(peer.launched + 1)
             pl.run(xs[i % NX], idx, w, yr=yr_p, ys=False, out=False, ysum=True)
-            peer.finalize(T, out=out)
+            peer.finalize(T, out=None if peer.sliced else out)   # (sliced: the rounded rows land in peer.out on every rank)
             return
         # one GPU: only the rounded rows; several: the f32 partial sums for the reduction
         pl.run(xs[i % NX], idx, w, yr=yr if world > 1 else False, ys=ys if world > 1 else False, out=out, ysum=world > 1)

@@ -32,7 +32,8 @@ class MoeShape(C.Structure):
 
 class PeerSet(C.Structure):
     _fields_ = [("parts", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p), ("rank", C.c_int32),
-                ("world", C.c_int32), ("rows_cap", C.c_int32), ("shared_rank", C.c_int32)]
+                ("world", C.c_int32), ("rows_cap", C.c_int32), ("shared_rank", C.c_int32),
+                ("outs", C.c_void_p), ("done", C.c_void_p)]
 
 
 class DecodeCfg(C.Structure):

@@ -156,13 +156,16 @@ int dsgx_sort_pack_static(const int32_t* idx, int T, int topk, int E, int32_t* c
 }
 
 int dsgx_finalize_peers(const dsgx_peer_set* ps, int M, int H, void* out, int32_t* status_word, void* stream) {
-  if (!ps || !ps->parts || !ps->flags || !ps->state || !out || !status_word) return DSGX_ERR_ARG;
+  if (!ps || !ps->parts || !ps->flags || !ps->state || (!out && !ps->outs) || !status_word) return DSGX_ERR_ARG;
+  if ((ps->outs != nullptr) != (ps->done != nullptr)) return DSGX_ERR_ARG;
+  if (ps->outs && H % 8) return DSGX_ERR_SHAPE;
   if (ps->world < 1 || ps->world > 32 || ps->rank < 0 || ps->rank >= ps->world || ps->shared_rank >= ps->world) return DSGX_ERR_ARG;
   if (M < 1 || M > ps->rows_cap || H < 4 || H % 4 || (size_t)M * H / 4 > (size_t)1 << 30) return DSGX_ERR_SHAPE;
   PeerParams p;
   p.parts = ps->parts, p.flags = ps->flags, p.state = ps->state, p.rank = ps->rank, p.world = ps->world;
   p.rows_cap = ps->rows_cap, p.shared_rank = ps->shared_rank, p.M = M, p.H = H;
   p.out = reinterpret_cast<__nv_bfloat16*>(out), p.status = status_word;
+  p.outs = reinterpret_cast<__nv_bfloat16* const*>(ps->outs), p.done = ps->done;
   cudaError_t e = launch_finalize_peers(p, (cudaStream_t)stream);
   return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
 }

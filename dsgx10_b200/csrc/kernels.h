@@ -161,6 +161,8 @@ struct PeerParams {
   int rank, world, rows_cap, shared_rank, M, H;
   __nv_bfloat16* out;
   int* status;
+  __nv_bfloat16* const* outs;  // sliced form: every rank's output rows (null: the plain form)
+  uint32_t* const* done;       // sliced form: rank r's "slices landed" words, u32 [world]
 };
 cudaError_t launch_finalize_peers(const PeerParams& p, cudaStream_t st);
 

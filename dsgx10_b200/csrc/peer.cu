@@ -58,7 +58,50 @@ __global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
     }
   }
   __syncthreads();
-  if (ok) {
+  if (ok && p.outs) {
+    // sliced form: this rank's rows only, eight columns a thread, the rounded rows stored into every rank's buffer
+    const size_t half = (size_t)2 * p.rows_cap * p.H;
+    const size_t off = (size_t)(e & 1) * half;
+    const int per = p.H / 8;
+    const int lo = (int)((long long)p.rank * p.M / p.world), hi = (int)((long long)(p.rank + 1) * p.M / p.world);
+    for (long long i = (long long)lo * per + blockIdx.x * blockDim.x + threadIdx.x; i < (long long)hi * per;
+         i += (long long)gridDim.x * blockDim.x) {
+      const int r = (int)(i / per), c = (int)(i - (long long)r * per) * 8;
+      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, s0 = a0, s1 = a0;
+      if (p.shared_rank >= 0) {
+        const float* sp = p.parts[p.shared_rank] + off + (size_t)(p.rows_cap + r) * p.H + c;
+        s0 = ld_peer4(sp), s1 = ld_peer4(sp + 4);
+      }
+      for (int q0 = 0; q0 < p.world; q0 += 8) {
+        float4 v0[8], v1[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (q0 + j < p.world) {
+            const float* pp = p.parts[q0 + j] + off + (size_t)r * p.H + c;
+            v0[j] = ld_peer4(pp), v1[j] = ld_peer4(pp + 4);
+          }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (q0 + j < p.world) {
+            const bool first = q0 + j == 0;
+            a0.x = first ? v0[j].x : __fadd_rn(a0.x, v0[j].x), a0.y = first ? v0[j].y : __fadd_rn(a0.y, v0[j].y);
+            a0.z = first ? v0[j].z : __fadd_rn(a0.z, v0[j].z), a0.w = first ? v0[j].w : __fadd_rn(a0.w, v0[j].w);
+            a1.x = first ? v1[j].x : __fadd_rn(a1.x, v1[j].x), a1.y = first ? v1[j].y : __fadd_rn(a1.y, v1[j].y);
+            a1.z = first ? v1[j].z : __fadd_rn(a1.z, v1[j].z), a1.w = first ? v1[j].w : __fadd_rn(a1.w, v1[j].w);
+          }
+      }
+      if (p.shared_rank >= 0) {
+        a0.x = __fadd_rn(a0.x, s0.x), a0.y = __fadd_rn(a0.y, s0.y), a0.z = __fadd_rn(a0.z, s0.z), a0.w = __fadd_rn(a0.w, s0.w);
+        a1.x = __fadd_rn(a1.x, s1.x), a1.y = __fadd_rn(a1.y, s1.y), a1.z = __fadd_rn(a1.z, s1.z), a1.w = __fadd_rn(a1.w, s1.w);
+      }
+      const __nv_bfloat162 b0 = __floats2bfloat162_rn(a0.x, a0.y), b1 = __floats2bfloat162_rn(a0.z, a0.w);
+      const __nv_bfloat162 b2 = __floats2bfloat162_rn(a1.x, a1.y), b3 = __floats2bfloat162_rn(a1.z, a1.w);
+      uint4 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&b0), o.y = *reinterpret_cast<const uint32_t*>(&b1);
+      o.z = *reinterpret_cast<const uint32_t*>(&b2), o.w = *reinterpret_cast<const uint32_t*>(&b3);
+      for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.outs[q] + (size_t)r * p.H + c) = o;
+    }
+  } else if (ok) {
     const size_t half = (size_t)2 * p.rows_cap * p.H;  // floats of one parity: yr then ys
     const size_t off = (size_t)(e & 1) * half;
     const int per = p.H / 4;
@@ -94,11 +137,33 @@ __global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
   // the last CTA of the launch closes the step
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    if (p.outs) __threadfence_system();
+    else __threadfence();
     if (atomicAdd(p.state + 1, 1u) == gridDim.x - 1) {
+      if (p.outs) {  // every CTA's stores to the peers are fenced (system scope) before its ticket
+        __threadfence_system();
+        for (int q = 0; q < p.world; ++q) st_release_sys(p.done[q] + p.rank, e);
+      }
       p.state[1] = 0;
       __threadfence();
       p.state[0] = e;
+    }
+  }
+}
+
+// sliced form, second kernel: every rank's slice of step e (the counter the first kernel just closed) is in this rank's
+// output rows
+__global__ void __launch_bounds__(32) k_wait_peers(PeerParams p) {
+  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.state);
+  if (threadIdx.x < p.world) {
+    const uint32_t* f = p.done[p.rank] + threadIdx.x;
+    const long long t0 = clock64();
+    while ((int)(ld_acquire_sys(f) - e) < 0) {
+      __nanosleep(64);
+      if (clock64() - t0 > kWaitCycles) {
+        atomicCAS(p.status, 0, (int)DSGX_ERR_DEVICE_WAIT);
+        break;
+      }
     }
   }
 }
@@ -111,6 +176,7 @@ cudaError_t launch_finalize_peers(const PeerParams& p, cudaStream_t st) {
   const int cap = n > (1 << 16) ? 4 * sm_count() : 32;  // decode widths: a few CTAs; a prefill's rows: the whole GPU
   if (grid > cap) grid = cap;
   k_finalize_peers<<<grid, 256, 0, st>>>(p);
+  if (p.outs) k_wait_peers<<<1, 32, 0, st>>>(p);
   return cudaGetLastError();
 }
 

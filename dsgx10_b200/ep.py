@@ -101,7 +101,9 @@ class PeerReduce:
 
     FLAG_BYTES = 256
 
-    def __init__(self, H, rows_cap=8, shared_rank=0, group=None):
+    def __init__(self, H, rows_cap=8, shared_rank=0, group=None, sliced=False):
+        """sliced: the form for many rows (a prefill's pass): every rank reduces 1 / world of the rows and stores the
+        rounded rows into every rank's output buffer, which then lives in the symmetric memory too."""
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib
         self._lib = _lib
@@ -110,7 +112,9 @@ class PeerReduce:
         self.H, self.rows_cap = H, rows_cap
         dev = torch.device("cuda", torch.cuda.current_device())
         half = 2 * rows_cap * H
-        self.buf = symm_mem.empty(self.FLAG_BYTES + 2 * half * 4, dtype=torch.uint8, device=dev)
+        parts_bytes = 2 * half * 4
+        out_bytes = rows_cap * H * 2 if sliced else 0
+        self.buf = symm_mem.empty(self.FLAG_BYTES + parts_bytes + out_bytes, dtype=torch.uint8, device=dev)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group=group)
         ptrs = [int(p) for p in self.hdl.buffer_ptrs]
@@ -118,11 +122,20 @@ class PeerReduce:
         self.parts_ptrs = torch.tensor([p + self.FLAG_BYTES for p in ptrs], dtype=torch.int64, device=dev)
         self.state = torch.zeros(2, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.out = torch.zeros(rows_cap, H, dtype=torch.bfloat16, device=dev)
-        f = self.buf[self.FLAG_BYTES:].view(torch.float32).view(2, 2, rows_cap, H)
+        f = self.buf[self.FLAG_BYTES:self.FLAG_BYTES + parts_bytes].view(torch.float32).view(2, 2, rows_cap, H)
         self._parts = f
+        if sliced:
+            o = self.FLAG_BYTES + parts_bytes
+            self.out = self.buf[o:].view(torch.bfloat16).view(rows_cap, H)
+            self.outs = torch.tensor([p + o for p in ptrs], dtype=torch.int64, device=dev)
+            self.done = torch.tensor([p + 128 for p in ptrs], dtype=torch.int64, device=dev)   # the flag block's second half
+            outs_p, done_p = self.outs.data_ptr(), self.done.data_ptr()
+        else:
+            self.out = torch.zeros(rows_cap, H, dtype=torch.bfloat16, device=dev)
+            outs_p, done_p = None, None
+        self.sliced = sliced
         self.set = _lib.PeerSet(self.parts_ptrs.data_ptr(), self.flags.data_ptr(), self.state.data_ptr(), self.rank,
-                                self.world, rows_cap, shared_rank)
+                                self.world, rows_cap, shared_rank, outs_p, done_p)
         self.launched = 0  # finalize launches executed or captured so far (the host's copy of the step counter)
         torch.cuda.synchronize()
         dist.barrier(group)  # every rank's flags are zero before anyone signals
@@ -134,6 +147,7 @@ class PeerReduce:
     def finalize(self, M, count=True, out=None):
         """out: where the rounded rows go (default: this object's device buffer; a pinned host tensor is written in place)."""
         lib = self._lib.lib()
+        assert out is None or not self.sliced, "the sliced form writes the symmetric output rows"
         dst = self.out if out is None else out
         rc = lib.dsgx_finalize_peers(C.byref(self.set), M, self.H, C.c_void_p(dst.data_ptr()),
                                      C.c_void_p(self.status.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))

@@ -170,6 +170,13 @@ typedef struct dsgx_peer_set {
   uint32_t* const* flags;
   uint32_t* state;
   int32_t rank, world, rows_cap, shared_rank;
+  /* Sliced form (for many rows, a prefill's pass), when outs is not null: rank r reduces and rounds only rows
+   * [r M / world, (r + 1) M / world) and stores them into every rank's outs[q] (bf16 [rows_cap][H], peer-mapped), then a
+   * second small kernel waits until every rank's slice has landed here (done[r]: u32 [world], zeroed once).  The
+   * out_bf16 argument is ignored: the rows are in outs[rank].  A rank then reads 1/world of the partial sums of the
+   * others instead of all of them. */
+  void* const* outs;
+  uint32_t* const* done;
 } dsgx_peer_set;
 int dsgx_finalize_peers(const dsgx_peer_set* peers, int M, int H, void* out_bf16, int32_t* status_word, void* stream);
 

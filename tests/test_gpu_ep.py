@@ -89,6 +89,20 @@ def _worker(rank, world, port, q):
             torch.cuda.synchronize()
             wide_ok = wide_ok and bool(torch.equal(got, want))
         res["peer_wide_ok"], res["peer_wide_status"] = wide_ok, int(prw.status.item())
+        # and its sliced form: each rank reduces half of the rows and stores them into both ranks' output rows
+        prs = ep.PeerReduce(H, rows_cap=601, shared_rank=-1, sliced=True)
+        sl_ok = True
+        for step_no in range(1, 4):
+            part = torch.randn(601, H, device=dev, generator=torch.Generator(device=dev).manual_seed(700 + 10 * step_no + rank))
+            yr_p, _ = prs.parts(prs.launched + 1)
+            yr_p.copy_(part)
+            got = prs.finalize(601).clone()
+            both = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(both, part)
+            want = moe.finalize(both[0] + both[1])
+            torch.cuda.synchronize()
+            sl_ok = sl_ok and bool(torch.equal(got, want))
+        res["peer_sliced_ok"], res["peer_sliced_status"] = sl_ok, int(prs.status.item())
         # prefill: rows partitioned, all-to-all dispatch and combine
         T = 96
         xa = synth.activations(T, H, 303).to(dev)
@@ -130,3 +144,4 @@ def test_two_gpus_match_one():
         assert res["prefill"] <= 1e-6, res
         assert res["peer_ok"] and res["peer_same"] and res["peer_status"] == 0, res
         assert res["peer_wide_ok"] and res["peer_wide_status"] == 0, res
+        assert res["peer_sliced_ok"] and res["peer_sliced_status"] == 0, res
