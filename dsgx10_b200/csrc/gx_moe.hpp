@@ -57,4 +57,17 @@ inline void moe_prefill(const MoeShape& s, const LayerW& L, const void* wbuf, co
   check(dsgx_moe_prefill(&s, &L, wbuf, x, idx, w, T, ws, yr, ys, out, ysum ? 1 : 0, st), "gx::moe_prefill");
 }
 
+// the all-reduce after the expert step and the rounding in one call over peer-mapped buffers (ds41f
+// ref/inference/model.py:901-902; altar1's ring reduce before gx::finalize)
+using PeerSet = dsgx_peer_set;
+inline void finalize_peers(const PeerSet& ps, int M, int H, __nv_bfloat16* out, int* status_word, cudaStream_t st) {
+  check(dsgx_finalize_peers(&ps, M, H, out, status_word, st), "gx::finalize_peers");
+}
+// one layer step, router to rounded rows (the sequence of engine/model/model.cu:308-352)
+using LayerStep = dsgx_layer_step;
+inline void layer_decode(const MoeShape& s, const LayerW& L, const __nv_bfloat16* x, int M, const LayerStep& step,
+                         cudaStream_t st, bool finalize = true) {
+  check(dsgx_moe_layer_decode(&s, &L, x, M, &step, finalize ? 1 : 0, st), "gx::layer_decode");
+}
+
 }  // namespace gx
