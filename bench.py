@@ -24,6 +24,18 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4, score_fn=0, fmt="fp8")
 CFG_INT4 = dict(H=6144, I=2048, E=168, topk=8, n_group=1, topk_group=1, score_fn=1, fmt="int4")   # config 3
+CFG_SMALL = dict(H=2048, I=1024, E=64, topk=6, n_group=1, topk_group=1, score_fn=0, fmt="fp8")      # config 1
+
+
+def workload_name(rows):
+    if CFG["fmt"] == "int4":
+        return (f"config 3: INT4-g32 MoE decode layer-step, hidden 6144, 168 experts x 2048, top-8 softmax, "
+                f"+ bf16 shared expert, rows {rows}")
+    if CFG["H"] == 2048:
+        return (f"config 1: FP8 MoE decode layer-step, hidden 2048, 64 experts x 1024, top-6 sigmoid, + shared expert, "
+                f"rows {rows}")
+    return (f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped (8 groups / 4), "
+            f"+ shared expert, rows {rows}")
 SEED = 20261102
 
 
@@ -103,6 +115,7 @@ def run_reference(args):
     if rank != 0:
         return
     orc.build(with_ref=False) if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")) else None
+    orc.set_threads()  # every host core, whatever OMP_NUM_THREADS the launcher exported
     H, I, E, topk = CFG["H"], CFG["I"], CFG["E"], CFG["topk"]
     rows = args.rows
     shp = moe.shape(H, I, E, topk, n_group=CFG["n_group"], topk_group=CFG["topk_group"])
@@ -131,7 +144,7 @@ def run_reference(args):
 
     for _ in range(max(1, min(args.warmup, 2))):
         one()
-    steps = max(1, min(args.steps, 10))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         one()
@@ -142,8 +155,7 @@ def run_reference(args):
         "impl": "reference", "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
-                               f"(8 groups / 4), + shared expert, rows {rows}", "rows": rows},
+        "config": {"workload": workload_name(rows), "rows": rows},
         "cpu_baseline": {"value": us, "unit": "us", "cores": cores, "kind": "port",
                          "sample": f"{steps} whole layer-steps ({rows} row(s), {len(picked)} experts + shared) through "
                                    "the C oracle (OpenMP)"},
@@ -320,10 +332,7 @@ def run_gpu(args):
         "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4-g32 weights, bf16 activations (f32 accumulate)" if int4 else "fp8_e4m3 (f32 accumulate)",
         "data": "synthetic",
-        "config": {"workload": (f"config 3: INT4-g32 MoE decode layer-step, hidden 6144, 168 experts x 2048, top-8 softmax, "
-                                f"+ bf16 shared expert, rows {rows}" if int4 else
-                                f"config 2: FP8 MoE decode layer-step, hidden 4096, 256 experts x 2048, top-8 grouped "
-                                f"(8 groups / 4), + shared expert, rows {rows}"), "rows": rows,
+        "config": {"workload": workload_name(rows), "rows": rows,
                    "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
                                                    " (partial sums reduced over peer memory by k_finalize_peers)"), "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
                    "launch": "eager" if args.eager else "one CUDA graph of the timed steps"},
@@ -341,14 +350,14 @@ def run_gpu(args):
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "
                                        "this launch's algorithmic bytes"},
         "e2e": {"value": us_e2e, "unit": "us", "h2d_bytes_per_step": rows * H * 2, "d2h_bytes_per_step": rows * H * 2},
-        # this library's kernels a step: the one persistent kernel from three rows (or --fused), else front, route, gate/up,
-        # down; with several GPUs also the rounding kernel after the all-reduce
-        "gpu_launches": args.steps * ((1 if (args.fused or (rows >= 3 and not args.separate)) else 4) + (1 if world > 1 else 0)),
+        # this library's kernels a step: the one persistent kernel from three rows (or --fused), else front (logits, routing,
+        # slot table), gate/up, down; with several GPUs also the reduction kernel
+        "gpu_launches": args.steps * ((1 if (args.fused or (rows >= 3 and not args.separate and not int4)) else 3) + (1 if world > 1 else 0)),
         "clocks": clocks,
         "device_status": status,
     }
     if not args.no_cpu_baseline and world == 1 and not int4:
-        line["cpu_baseline"] = cpu_baseline(rows)
+        line["cpu_baseline"] = cpu_baseline(rows, workload=args.workload)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -371,6 +380,7 @@ def run_prefill_reference(args):
     from oracle import oracle as orc
     if int(os.environ.get("RANK", "0")) != 0:
         return
+    orc.set_threads()
     H, I, E, topk = PF["H"], PF["I"], PF["E"], PF["topk"]
     Ts = 64
     lay = synth.Fp8Layer(H, I, E, SEED, device="cpu")
@@ -386,7 +396,7 @@ def run_prefill_reference(args):
         return orc.moe_fp8_layer(x, ii, ww, {e: experts[e] for e in picked}, shared)
 
     one()
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         one()
@@ -595,8 +605,8 @@ def run_prefill(args):
 
 
 def cpu_baseline(rows, workload="decode"):
-    """The oracle port on the host cores, a bounded sample: three whole layer-steps of the same workload."""
-    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "3", "--warmup", "1",
+    """The oracle port on the host cores, a bounded sample: ten whole layer-steps of the same workload."""
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "10", "--warmup", "1",
                         "--rows", str(rows), "--workload", workload], capture_output=True, text=True, timeout=600)
     try:
         d = json.loads(r.stdout.strip().splitlines()[-1])
@@ -612,9 +622,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--workload", default="decode", choices=["decode", "int4", "prefill", "ragged"],
-                    help="decode: the headline layer-step (config 2); prefill: the grouped GEMM pass of config 4; "
-                         "ragged: the mixed batch of config 5 through the same pass")
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode1", "int4", "prefill", "ragged"],
+                    help="decode: the headline layer-step (config 2); decode1: the small layer's step (config 1); int4: "
+                         "config 3; prefill: the grouped GEMM pass of config 4; ragged: the mixed batch of config 5 "
+                         "through the same pass")
     ap.add_argument("--tokens", type=int, default=16384, help="prefill: tokens a pass")
     ap.add_argument("--chunks", type=int, default=4, help="prefill end to end: chunks of tokens the pass is cut into")
     ap.add_argument("--layers", type=int, default=3)
@@ -628,6 +639,10 @@ def main():
     args = ap.parse_args()
     if args.experts:
         CFG["E"] = args.experts
+    if args.workload == "decode1":  # config 1: the same decode bench over the small FP8 layer
+        CFG.update(CFG_SMALL)
+        if args.layers == 3:
+            args.layers = 12  # 12 x 50 MB of picked experts between reuses: larger than L2
     if args.workload == "int4":  # config 3: the same decode bench over an INT4-g32 layer
         CFG.update(CFG_INT4)
         if args.layers == 3:

@@ -21,6 +21,7 @@ def _stale(target, deps):
 
 
 def build(verbose=False, force=False):
+    extra = os.environ.get("DSGX_NVCC_FLAGS", "").split()  # e.g. -DDSGX_STAMPS for a side build with time stamps
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(ROOT, "include", "dsgx_moe.h"))
     objdir = os.path.join(HERE, "build")
@@ -32,7 +33,7 @@ def build(verbose=False, force=False):
         obj = os.path.join(objdir, s.replace(".cu", ".o"))
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = ["nvcc"] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            cmd = ["nvcc"] + FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):

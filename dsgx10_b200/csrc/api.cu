@@ -41,6 +41,8 @@ size_t decode_ws_bytes(int H, int I) {
   n += kSlotTabBytes;
   n += al256((size_t)((H + 1023) / 1024) * kMaxRows * 512 * 4);
   n += al256(sizeof(StepSync));
+  n += al256((size_t)kPartUnits * kMaxPieces * 128 * 4);
+  n += al256((size_t)kPartUnits * 4);
   return n;
 }
 DecodeWs decode_ws_carve(void* ws, int H, int I) {
@@ -56,7 +58,9 @@ DecodeWs decode_ws_carve(void* ws, int H, int I) {
   w.cnt_y = reinterpret_cast<int*>(p), p += al256((size_t)(H / 16) * 4);
   w.tab = reinterpret_cast<SlotTab*>(p), p += kSlotTabBytes;
   w.lpart = reinterpret_cast<float*>(p), p += al256((size_t)((H + 1023) / 1024) * kMaxRows * 512 * 4);
-  w.sync = reinterpret_cast<StepSync*>(p);
+  w.sync = reinterpret_cast<StepSync*>(p), p += al256(sizeof(StepSync));
+  w.part = reinterpret_cast<float*>(p), p += al256((size_t)kPartUnits * kMaxPieces * 128 * 4);
+  w.cnt_u = reinterpret_cast<int*>(p);
   return w;
 }
 
@@ -198,6 +202,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.ws = decode_ws_carve(ws, s->H, s->I);
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr;
     p.up = cfg->up, p.down = cfg->down;
+    p.sh_lo = 0, p.sh_hi = s->I;
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                       cfg->parts == 0 ? 3 : cfg->parts);
@@ -215,6 +220,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
+    p.sh_lo = 0, p.sh_hi = s->I;
     cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                        cfg->parts == 0 ? 3 : cfg->parts);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
@@ -251,6 +257,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     p.idx = st->idx, p.w = st->w;
     p.ws = decode_ws_carve(st->ws, s->H, s->I);
     p.yr = st->yr, p.ys = st->ys, p.ysum = 0, p.up = 0, p.down = 0;
+    p.sh_lo = 0, p.sh_hi = s->I;
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);

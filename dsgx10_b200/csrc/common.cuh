@@ -85,6 +85,17 @@ DSGX_DEV void bulk_g2s_hint(void* dst_smem, const void* src, uint32_t bytes, uin
       : "memory");
 }
 
+// ---- a part of a CTA that works together: the first nt threads (a multiple of 32), with a barrier of their own -----------
+// (the whole CTA: nt = blockDim.x, barrier 0 = __syncthreads)
+struct CtaPart {
+  int nt, bar;
+  DSGX_DEV void sync() const {
+    if (bar == 0) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(nt) : "memory");
+  }
+};
+DSGX_DEV CtaPart whole_cta() { return CtaPart{(int)blockDim.x, 0}; }
+
 // ---- programmatic dependent launch ----------------------------------------------------------------------------------
 DSGX_DEV void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 DSGX_DEV void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -27,21 +27,55 @@ static_assert(sizeof(SlotEnt) == 96 && sizeof(SlotTab) % 16 == 0, "SlotTab is co
 
 // Builds the table in shared memory from the step's picks (idx, w: M x topk, shared or global memory), by one whole CTA.
 // bm: 16 words of shared memory.
+// The descriptor fields the table needs, of every expert, fetched into shared memory ahead of the selection (so that the
+// table costs no dependent round trip to memory once the picks are known).
+struct DescCache {
+  uint64_t off[3][512];   // MatDesc.off
+  uint64_t soff[3][512];  // FP8: the scales' offset
+  uint32_t fmt[3][512];
+};
+struct DescRegs {
+  uint4 a[3];
+  uint2 b[3];
+};
+// thread e: its expert's three descriptors into registers (experts this GPU does not own are not read) ...
+DSGX_DEV void desc_fetch(DescRegs& r, const dsgx_mat_desc* desc, int e, bool owned) {
+#pragma unroll
+  for (int m = 0; m < 3; ++m) {
+    r.a[m] = make_uint4(0, 0, 0, 0), r.b[m] = make_uint2(0, 0);
+    if (owned) {
+      const uint8_t* d = reinterpret_cast<const uint8_t*>(desc + (size_t)e * 3 + m);
+      r.a[m] = __ldg(reinterpret_cast<const uint4*>(d));
+      r.b[m] = __ldg(reinterpret_cast<const uint2*>(d + 16));
+    }
+  }
+}
+// ... and from there into the cache
+DSGX_DEV void desc_store(DescCache& dc, const DescRegs& r, int e) {
+#pragma unroll
+  for (int m = 0; m < 3; ++m) {
+    dc.off[m][e] = (uint64_t)r.a[m].x | (uint64_t)r.a[m].y << 32;
+    dc.fmt[m][e] = r.a[m].w;
+    dc.soff[m][e] = (uint64_t)r.b[m].x | (uint64_t)r.b[m].y << 32;
+  }
+}
+
 DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const float* w, int M, int topk, int E, int e_lo,
                              int e_hi, const uint8_t* pool, const dsgx_mat_desc* desc, const dsgx_shared_w& sh,
-                             uint32_t fmt) {
-  const int tid = threadIdx.x, nt = blockDim.x;
+                             uint32_t fmt, const DescCache* dc = nullptr, CtaPart cp = CtaPart{0, 0}) {
+  if (cp.nt == 0) cp = whole_cta();
+  const int tid = threadIdx.x, nt = cp.nt;
   if (tid < 16) bm[tid] = 0;
   if (tid == 0) tab.bad = 0, tab.pad = 0;
   for (int i = tid; i < (kMaxSlots + 1) * 8; i += nt) tab.ent[i >> 3].w[i & 7] = 0.f;
-  __syncthreads();
+  cp.sync();
   const int np = M * topk;
   for (int i = tid; i < np; i += nt) {
     const int e = idx[i];
     if (e < 0 || e >= E) tab.bad = DSGX_ERR_ARG;
     else if (e >= e_lo && e < e_hi) atomicOr(&bm[e >> 5], 1u << (e & 31));
   }
-  __syncthreads();
+  cp.sync();
   auto rank_of = [&](int e) {
     int r = __popc(bm[e >> 5] & ((1u << (e & 31)) - 1u));
     for (int k = 0; k < (e >> 5); ++k) r += __popc(bm[k]);
@@ -55,19 +89,28 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
     SlotEnt& en = tab.ent[s];
     en.w[i / topk] = w[i];
     const dsgx_mat_desc* d = desc + (size_t)e * 3;
-    const uint64_t o0 = d[0].off, o1 = d[1].off, o2 = d[2].off;
-    if (d[0].fmt != fmt || d[1].fmt != fmt || d[2].fmt != fmt) tab.bad = DSGX_ERR_FORMAT;
+    uint64_t o[3], so[3];
+    bool fmt_ok = true;
+#pragma unroll
+    for (int m = 0; m < 3; ++m) {
+      if (dc) {
+        o[m] = dc->off[m][e], so[m] = dc->soff[m][e], fmt_ok = fmt_ok && dc->fmt[m][e] == fmt;
+      } else {
+        o[m] = d[m].off, so[m] = (uint64_t)d[m].rsv[0] | (uint64_t)d[m].rsv[1] << 32, fmt_ok = fmt_ok && d[m].fmt == fmt;
+      }
+    }
+    if (!fmt_ok) tab.bad = DSGX_ERR_FORMAT;
     en.e = e;
-    en.g = pool + o0, en.u = pool + o1, en.d = pool + o2;
+    en.g = pool + o[0], en.u = pool + o[1], en.d = pool + o[2];
     if (fmt == DSGX_FMT_FP8) {
-      en.sg = reinterpret_cast<const float*>(pool + ((uint64_t)d[0].rsv[0] | (uint64_t)d[0].rsv[1] << 32));
-      en.su = reinterpret_cast<const float*>(pool + ((uint64_t)d[1].rsv[0] | (uint64_t)d[1].rsv[1] << 32));
-      en.sd = reinterpret_cast<const float*>(pool + ((uint64_t)d[2].rsv[0] | (uint64_t)d[2].rsv[1] << 32));
+      en.sg = reinterpret_cast<const float*>(pool + so[0]);
+      en.su = reinterpret_cast<const float*>(pool + so[1]);
+      en.sd = reinterpret_cast<const float*>(pool + so[2]);
     } else {
       en.sg = en.su = en.sd = nullptr;
     }
   }
-  __syncthreads();
+  cp.sync();
   if (tid == 0) {
     int n = 0;
     for (int k = 0; k < 16; ++k) n += __popc(bm[k]);
@@ -86,7 +129,7 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
       }
     }
   }
-  __syncthreads();
+  cp.sync();
 }
 
 // The table from global memory into shared memory by one warp, in as few round trips as its size allows: the header
@@ -122,6 +165,79 @@ DSGX_DEV int ord_slot(const SlotTab& tab, int ord) {
 }
 
 DSGX_DEV uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// ---- the summation order of a unit's K, and its split over warps --------------------------------------------------
+// A unit's sum over K is formed in pieces of kPB 128-k blocks: inside a piece the blocks' promoted partial sums are
+// accumulated by fma from zero, ascending; the pieces are then added ascending, starting from the first piece's sum.
+// That order is the same whether one warp runs all pieces of a unit or several warps (on different SMs) take
+// consecutive runs of pieces and the last one to finish adds the piece sums it finds in the workspace: a row's bits do
+// not depend on how a launch's pieces were dealt to the warps (the reference splits K over the warps of one CTA with one fixed
+// split per format for the same reason: altar1 engine/experts/decode.cu:117-408, docs/experts.md:29-32).
+// How many warps share a unit: the largest power of two that still leaves every run a warp of its own.
+DSGX_DEV int pick_split(int units, int NP, int GW, int cap_units) {
+  int s = 1;
+  while (s * 2 <= NP && s * 2 <= kMaxPieces && units * s * 2 <= GW) s *= 2;
+  return units > cap_units ? 1 : s;
+}
+DSGX_DEV bool piece_end(int kb, int KB) { return (kb % kPB) == kPB - 1 || kb == KB - 1; }
+// folds a finished piece's sums into the totals (`first`: the unit's first piece) and clears them
+DSGX_DEV void piece_fold(float (&tot)[4], float (&pc)[4], bool first) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) tot[i] = first ? pc[i] : __fadd_rn(tot[i], pc[i]), pc[i] = 0.f;
+}
+
+// ---- compact activation blocks (R = 1, 2, 4 or 8 rows), global-counter polls, the FP8 block product --------------------
+// compact activation block of R rows x 128 k: [2 halves q][R rows][4 t][16 B] e4m3, then R f32 scales (padded to 16 B)
+__host__ __device__ constexpr int cblk_bytes(int R) { return R * 128 + (R <= 4 ? 16 : 32); }
+
+DSGX_DEV unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+DSGX_DEV int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// bounded poll until *p >= target
+DSGX_DEV bool poll_ge(const int* p, int target) {
+  if (ld_acquire(p) >= target) return true;
+  const long long t0 = clock64();
+  while (ld_acquire(p) < target) {
+    __nanosleep(128);
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+
+// one row's 128 values (4 per lane) -> compact block
+DSGX_DEV void cquant_row(uint8_t* blk, int R, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {
+  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
+  uint32_t packed = 0;
+  float sc = 0.f;
+  if (valid) {
+    sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
+    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  }
+  *reinterpret_cast<uint32_t*>(blk + ((q * R + r) * 4 + t) * 16 + i) = packed;
+  if (lane == 0) reinterpret_cast<float*>(blk + R * 128)[r] = sc;
+}
+
+// One 128-k block: A rows 0-7 from strip a, rows 8-15 from strip b, B from a compact activation block.
+DSGX_DEV void cblock_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int R, int lane) {
+  const uint4 a0 = lds128(a + 32 * lane), a1 = lds128(a + 32 * lane + 16);
+  const uint4 b0 = lds128(b + 32 * lane), b1 = lds128(b + 32 * lane + 16);
+  const int row = (lane >> 2) & (R - 1), t = lane & 3;
+  const uint4 x0 = lds128(act + (row * 4 + t) * 16), x1 = lds128(act + ((R + row) * 4 + t) * 16);
+  float e[4] = {0.f, 0.f, 0.f, 0.f};
+  d[0] = d[1] = d[2] = d[3] = 0.f;
+  mma_e4m3(d, a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
+  mma_e4m3(e, a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
+  mma_e4m3(d, a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
+  mma_e4m3(e, a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
+  d[0] += e[0], d[1] += e[1], d[2] += e[2], d[3] += e[3];
+}
 
 // quantises one row's 128 values (4 per lane, k = 4 lane ..) into an activation block
 DSGX_DEV void quant_row_to_block(uint8_t* blk, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {

@@ -30,59 +30,6 @@ namespace {
 constexpr int kFW = 16, kFThreads = kFW * 32;
 constexpr int kTabSmem = (sizeof(SlotTab) + 127) & ~127;
 
-// compact activation block of R rows x 128 k: [2 halves q][R rows][4 t][16 B] e4m3, then R f32 scales (padded to 16 B)
-__host__ __device__ constexpr int cblk_bytes(int R) { return R * 128 + (R <= 4 ? 16 : 32); }
-
-DSGX_DEV unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-DSGX_DEV int ld_acquire(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// bounded poll until *p >= target
-DSGX_DEV bool poll_ge(const int* p, int target) {
-  if (ld_acquire(p) >= target) return true;
-  const long long t0 = clock64();
-  while (ld_acquire(p) < target) {
-    __nanosleep(128);
-    if (clock64() - t0 > kWaitCycles) return false;
-  }
-  return true;
-}
-
-// one row's 128 values (4 per lane) -> compact block
-DSGX_DEV void cquant_row(uint8_t* blk, int R, int r, int lane, bool valid, float v0, float v1, float v2, float v3) {
-  const int kl = 4 * lane, q = kl >> 6, t = (kl >> 4) & 3, i = kl & 15;
-  uint32_t packed = 0;
-  float sc = 0.f;
-  if (valid) {
-    sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
-    packed = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
-  }
-  *reinterpret_cast<uint32_t*>(blk + ((q * R + r) * 4 + t) * 16 + i) = packed;
-  if (lane == 0) reinterpret_cast<float*>(blk + R * 128)[r] = sc;
-}
-
-// One 128-k block: A rows 0-7 from strip a, rows 8-15 from strip b, B from a compact activation block.
-// Same MMA order as decode_fp8.cu's block_mma (same bits).
-DSGX_DEV void cblock_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int R, int lane) {
-  const uint4 a0 = lds128(a + 32 * lane), a1 = lds128(a + 32 * lane + 16);
-  const uint4 b0 = lds128(b + 32 * lane), b1 = lds128(b + 32 * lane + 16);
-  const int row = (lane >> 2) & (R - 1), t = lane & 3;
-  const uint4 x0 = lds128(act + (row * 4 + t) * 16), x1 = lds128(act + ((R + row) * 4 + t) * 16);
-  float e[4] = {0.f, 0.f, 0.f, 0.f};
-  d[0] = d[1] = d[2] = d[3] = 0.f;
-  mma_e4m3(d, a0.x, b0.x, a0.y, b0.y, x0.x, x0.y);
-  mma_e4m3(e, a1.x, b1.x, a1.y, b1.y, x1.x, x1.y);
-  mma_e4m3(d, a0.z, b0.z, a0.w, b0.w, x0.z, x0.w);
-  mma_e4m3(e, a1.z, b1.z, a1.w, b1.w, x1.z, x1.w);
-  d[0] += e[0], d[1] += e[1], d[2] += e[2], d[3] += e[3];
-}
-
 template <int KCH, int NST>
 __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) {
   const DecodeParams& p = sp.d;
@@ -289,7 +236,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       const float* sup = shared ? p.sh.us : tab.ent[s].su;
       const float sgl = lane < HB ? __ldg(sgp + (size_t)srow * HB + lane) : 0.f;
       const float sul = lane < HB ? __ldg(sup + (size_t)srow * HB + lane) : 0.f;
-      float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
+      float tot[4] = {0.f, 0.f, 0.f, 0.f}, pc4[4] = {0.f, 0.f, 0.f, 0.f};  // gate r0, gate r1, up r0, up r1
       for (int c = 0; c < cpu; ++c) {
         const uint32_t sidx = consumed % NST;
         if (!mbar_wait(mybar + sidx, (consumed / NST) & 1)) {
@@ -306,8 +253,9 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
           const float* xs = reinterpret_cast<const float*>(act + R * 128);
           const float x0 = xs[(2 * t) & (R - 1)], x1 = xs[(2 * t + 1) & (R - 1)];
           const float sg = __shfl_sync(0xffffffffu, sgl, kb), su = __shfl_sync(0xffffffffu, sul, kb);
-          ag0 = fmaf(d[0], sg * x0, ag0), ag1 = fmaf(d[1], sg * x1, ag1);
-          au0 = fmaf(d[2], su * x0, au0), au1 = fmaf(d[3], su * x1, au1);
+          pc4[0] = fmaf(d[0], sg * x0, pc4[0]), pc4[1] = fmaf(d[1], sg * x1, pc4[1]);
+          pc4[2] = fmaf(d[2], su * x0, pc4[2]), pc4[3] = fmaf(d[3], su * x1, pc4[3]);
+          if (piece_end(kb, HB)) piece_fold(tot, pc4, kb < kPB);  // the pieces' order of decode_common.cuh
         }
         ++consumed;
         __syncwarp();
@@ -317,8 +265,8 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       if (dead) break;
       while (pend) advance();
       const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
-      float h0 = __fmul_rn(silu(bf16_round(ag0)), bf16_round(au0));
-      float h1 = __fmul_rn(silu(bf16_round(ag1)), bf16_round(au1));
+      float h0 = __fmul_rn(silu(bf16_round(tot[0])), bf16_round(tot[2]));
+      float h1 = __fmul_rn(silu(bf16_round(tot[1])), bf16_round(tot[3]));
       if (!shared) h0 = __fmul_rn(tab.ent[s].w[r0], h0), h1 = __fmul_rn(tab.ent[s].w[r1], h1);
       __nv_bfloat16* hrow = p.ws.h + (size_t)wslot * 8 * p.I;
       if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
@@ -385,7 +333,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       const int srow = (n16 * 16) / 128;
       const float* sdp = sh ? p.sh.ds : tab.ent[slot].sd;
       const float sdl = lane < IB ? __ldg(sdp + (size_t)srow * IB + lane) : 0.f;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, pc4[4] = {0.f, 0.f, 0.f, 0.f};
       for (int c = 0; c < cpu; ++c) {
         const uint32_t sidx = consumed % NST;
         if (!mbar_wait(mybar + sidx, (consumed / NST) & 1)) {
@@ -402,8 +350,9 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
           const float* hs = reinterpret_cast<const float*>(act + R * 128);
           const float h0 = hs[(2 * t) & (R - 1)], h1 = hs[(2 * t + 1) & (R - 1)];
           const float sd = __shfl_sync(0xffffffffu, sdl, kb);
-          acc[0] = fmaf(d[0], sd * h0, acc[0]), acc[1] = fmaf(d[1], sd * h1, acc[1]);
-          acc[2] = fmaf(d[2], sd * h0, acc[2]), acc[3] = fmaf(d[3], sd * h1, acc[3]);
+          pc4[0] = fmaf(d[0], sd * h0, pc4[0]), pc4[1] = fmaf(d[1], sd * h1, pc4[1]);
+          pc4[2] = fmaf(d[2], sd * h0, pc4[2]), pc4[3] = fmaf(d[3], sd * h1, pc4[3]);
+          if (piece_end(kb, IB)) piece_fold(acc, pc4, kb < kPB);
         }
         ++consumed;
         __syncwarp();

@@ -48,7 +48,14 @@ struct DecodeWs {
   struct StepSync* sync;  // counters of the one-kernel step (decode_fused.cu)
   struct SlotTab* tab;  // the step's slot table (decode_common.cuh)
   float* lpart;     // [H/1024 slices][8][E] partial router logits of the layer step
+  float* part;      // [kPartUnits][kMaxPieces][32 lanes][4] piece sums of the units whose K is split over several warps
+  int* cnt_u;       // [kPartUnits] arrivals of a split unit's runs
 };
+// A unit's K is summed in pieces of kPB 128-k blocks (decode_common.cuh); when a launch has fewer units than warps, the
+// pieces of a unit go to several warps (of different SMs) and meet in `part`, indexed by the unit's number in the launch.
+constexpr int kPB = 4;
+constexpr int kMaxPieces = 8;          // H, I <= 4096
+constexpr int kPartUnits = 2048;
 constexpr size_t kSlotTabBytes = 8192;  // room reserved for a SlotTab
 size_t decode_ws_bytes(int H, int I);
 DecodeWs decode_ws_carve(void* ws, int H, int I);
@@ -66,6 +73,7 @@ struct DecodeParams {
   __nv_bfloat16* out;  // when set, k_down also writes bf16(yr + ys)
   int ysum;
   int up, down;  // kernel variants (same bits)
+  int sh_lo, sh_hi;  // the shared expert's intermediate channels this GPU computes (multiples of 512; the whole: 0, I)
 };
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);

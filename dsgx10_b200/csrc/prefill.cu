@@ -187,7 +187,8 @@ __global__ void __launch_bounds__(512) k_tile_offsets(const int* __restrict__ co
     pre[E] = acc;
   }
   __syncthreads();
-  if (e <= E) tile_off[e] = pre[e];
+  if (e < E) tile_off[e] = pre[e];
+  if (e == 0) tile_off[E] = pre[E];  // (E may equal the thread count: no thread has e == E then)
   if (e < E)
     for (int t = 0; t < mine; ++t) tile_info[pre[e] + t] = make_int4(e, offsets[e] + t * 256, offsets[e + 1], 0);
 }

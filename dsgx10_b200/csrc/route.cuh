@@ -42,7 +42,7 @@ DSGX_DEV void route_row(const RouteParams& p, const float* __restrict__ l, int n
 #pragma unroll
   for (int j = 0; j < kRJ; ++j) {
     const int e = lane + 32 * j;
-    s[j] = e < p.E ? __ldcg(l + e) : -INFINITY;
+    s[j] = e < p.E ? (nsplit ? __ldcg(l + e) : l[e]) : -INFINITY;  // (nsplit 0: summed logits behind a plain pointer)
     key[j] = e < p.E && bias ? __ldg(bias + e) : 0.f;
   }
   for (int sp = 1; sp < nsplit; ++sp) {
@@ -199,13 +199,19 @@ struct __align__(16) RouteSmem {
   uint32_t keep;
 };
 
+// nsplit 0: l is this thread's summed logit itself (l points at it); cp: the threads that take part (threadIdx.x < cp.nt).
 DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
                             const float* __restrict__ bias, RouteSmem& sm, float* logits_out, int* idx_out, float* w_out,
-                            int* idx_copy = nullptr, float* w_copy = nullptr) {
-  const int e = threadIdx.x, lane = e & 31, warp = e >> 5, nW = blockDim.x >> 5;
+                            int* idx_copy = nullptr, float* w_copy = nullptr, CtaPart cp = CtaPart{0, 0}) {
+  if (cp.nt == 0) cp = whole_cta();
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5, nW = cp.nt >> 5;
   const bool valid = e < p.E;
   float lg = -INFINITY, b = 0.f;
-  if (valid) {
+  if (valid && nsplit == 0) {
+    lg = *l;
+    if (bias) b = __ldg(bias + e);
+    if (logits_out) logits_out[e] = lg;
+  } else if (valid) {
     float part[8];
 #pragma unroll
     for (int sp = 0; sp < 8; ++sp) part[sp] = sp < nsplit ? __ldcg(l + sp * split_stride + e) : 0.f;
@@ -223,7 +229,7 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
   } else {
     float m = warp_max(lg);
     if (lane == 0) sm.red[warp] = m;
-    __syncthreads();
+    cp.sync();
     m = sm.red[0];
     for (int w = 1; w < nW; ++w) m = fmaxf(m, sm.red[w]);
     float t = 0.f;
@@ -232,23 +238,23 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
       t = d < -87.f ? 0.f : exp_ieee(d);
     }
     sm.key[e] = t;
-    __syncthreads();
+    cp.sync();
     if (warp == 0) {  // lane sums over j ascending, then the butterfly
       float ps = 0.f;
       for (int ee = lane; ee < p.E; ee += 32) ps = __fadd_rn(ps, sm.key[ee]);
       ps = warp_sum(ps);
       if (lane == 0) sm.S = ps;
     }
-    __syncthreads();
+    cp.sync();
     s = __fdiv_rn(t, sm.S);
-    __syncthreads();
+    cp.sync();
   }
   // keys as order-preserving unsigned integers in shared memory (0 = not a candidate)
   uint32_t* ku = reinterpret_cast<uint32_t*>(sm.key);
   sm.s[e] = s;
-  __syncthreads();  // (softmax read sm.key above)
+  cp.sync();  // (softmax read sm.key above)
   ku[e] = valid ? ord_key(__fadd_rn(s, b)) : 0u;
-  __syncthreads();
+  cp.sync();
   // ---- selection, all warps: group scores one warp a group, then every candidate ranks itself --------------------------
   float* picked = sm.red;  // [8] scores of the picks (sm.red is free by now)
   int* ids = reinterpret_cast<int*>(sm.red + 8);
@@ -273,7 +279,7 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
       const uint32_t m2 = __reduce_max_sync(0xffffffffu, second);
       if (lane == 0) gsc[g] = ord_key(__fadd_rn(ord_float(m1), ord_float(m2)));
     }
-    __syncthreads();
+    cp.sync();
     if (warp == 0) {  // keep the topk_group best groups, ties to the lower id
       const uint32_t mine = lane < p.n_group ? gsc[lane] : 0u;
       uint32_t keep = 0;
@@ -286,9 +292,9 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
       }
       if (lane == 0) sm.keep = keep;
     }
-    __syncthreads();
+    cp.sync();
     if (valid && !((sm.keep >> (e / gs)) & 1)) ku[e] = 0u;
-    __syncthreads();
+    cp.sync();
   }
   // rank of a candidate = keys above it + equal keys with a lower id; ranks 0 .. topk-1 are the picks in order
   if (valid) {
@@ -313,7 +319,7 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
       if (rank < p.topk) ids[rank] = e, picked[rank] = s;
     }
   }
-  __syncthreads();
+  cp.sync();
   if (warp != 0) return;
   // the sum of the picked scores: four running sums at stride 4, then (t0 + t2) + (t1 + t3)
   float t[4];

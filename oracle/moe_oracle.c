@@ -109,6 +109,48 @@ ORC_API float orc_route_sigmoid(float l) {
   return 1.f / (1.f + exp_ieee(x));
 }
 
+/* ln(y) for y in [1, 2^31): IEEE operations only, so that a GPU repeats the bits.  y = 2^n m with m in [1/sqrt2, sqrt2),
+ * s = (m - 1) / (m + 1), ln m = 2 s (1 + z/3 + z^2/5 + z^3/7 + z^4/9 + z^5/11), z = s^2 (Horner, fused steps);
+ * ln y = n ln2_hi + (n ln2_lo + ln m). */
+static inline float log_ieee(float y) {
+  uint32_t u;
+  memcpy(&u, &y, 4);
+  int n = (int)(u >> 23) - 127;
+  u = (u & 0x007FFFFFu) | 0x3F800000u;
+  float m;
+  memcpy(&m, &u, 4);
+  if (m > 1.41421356f) m = m * 0.5f, n += 1;
+  const float f = m - 1.f;
+  const float sv = f / (2.f + f);
+  const float z = sv * sv;
+  float p = 1.f / 11;
+  p = fmaf(p, z, 1.f / 9);
+  p = fmaf(p, z, 1.f / 7);
+  p = fmaf(p, z, 1.f / 5);
+  p = fmaf(p, z, 1.f / 3);
+  p = fmaf(p, z, 1.f);
+  const float lm = (2.f * sv) * p;
+  const float nf = (float)n;
+  return fmaf(nf, 0.693145751953125f, fmaf(nf, 1.428606765330187e-06f, lm));
+}
+/* sqrt(softplus(l)) with torch's softplus (l > 20 ? l : log1p(exp(l)); ds41f engine/kernels/common.cuh:264-287,
+ * ref/inference/model.py:818).  log1p(t) = ln(y) t / (y - 1) with y = fl(1 + t) (t itself when y == 1): a few ulp, and
+ * every step is an IEEE operation. */
+ORC_API float orc_route_sqrtsoftplus(float l) {
+  float sp;
+  if (l > 20.f) {
+    sp = l;
+  } else if (l < -87.f) {
+    sp = 0.f;
+  } else {
+    const float t = exp_ieee(l);
+    const float y = 1.f + t;
+    const float d = y - 1.f;
+    sp = d == 0.f ? t : (log_ieee(y) * t) / d;
+  }
+  return sqrtf(sp);
+}
+
 /* The sum of the picked scores p[0..k) (descending selection order): four running sums at stride 4, then
  * (t0 + t2) + (t1 + t3).  For k = 8 this is formats.cuh:166-168, for k = 6 common.cuh:307-310. */
 static float route_sum(const float* p, int k) {
@@ -184,8 +226,7 @@ static void row_scores(const float* l, int E, int score_fn, float* s) {
     const float S = butterfly32(p);
     for (int e = 0; e < E; ++e) s[e] = s[e] / S;
   } else {
-    /* sqrt(softplus(l)), torch's softplus threshold 20 (common.cuh:284-287); libm here, so not bit-pinned to a device */
-    for (int e = 0; e < E; ++e) s[e] = sqrtf(l[e] > 20.f ? l[e] : log1pf(expf(l[e])));
+    for (int e = 0; e < E; ++e) s[e] = orc_route_sqrtsoftplus(l[e]);
   }
 }
 
@@ -342,9 +383,10 @@ static inline float silu_f(float g) { return g / (1.f + expf(-g)); }
 
 /* One FP8 expert on one row (model.py:841-851): x bf16 [H] -> y [H] as bf16-rounded floats.
  * wroute: the routing weight applied to h in f32 before its rounding, or a negative number for "none" (shared expert).
- * h_out (optional): the bf16-rounded h [I] as floats. */
+ * limit > 0: the bf16 gate is clamped from above to limit and the bf16 up to +-limit before silu (model.py:845-847;
+ * ds41f engine/kernels/prefill.cu:153-158 fixes limit = 10).  h_out (optional): the bf16-rounded h [I] as floats. */
 ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* wg, const float* sg, const uint8_t* wu,
-                                const float* su, const uint8_t* wd, const float* sd, float wroute, float* y,
+                                const float* su, const uint8_t* wd, const float* sd, float wroute, float limit, float* y,
                                 float* h_out) {
   lut_init();
   float* xf = (float*)malloc(sizeof(float) * (H > I ? H : I));
@@ -357,7 +399,12 @@ ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* 
   fp8_gemv(q, s, wg, sg, I, H, g, 1);
   fp8_gemv(q, s, wu, su, I, H, u, 1);
   for (int i = 0; i < I; ++i) {
-    float t = silu_f(g[i]) * u[i];
+    float gv = g[i], uv = u[i];
+    if (limit > 0.f) {
+      uv = uv > limit ? limit : uv < -limit ? -limit : uv;
+      gv = gv > limit ? limit : gv;
+    }
+    float t = silu_f(gv) * uv;
     if (wroute >= 0.f) t = wroute * t;
     xf[i] = bf16r(t);
     if (h_out) h_out[i] = xf[i];
@@ -370,29 +417,36 @@ ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* 
 /* A whole FP8 layer (model.py:889-904).  Expert e's canonical tensors: wg[e], wu[e] e4m3 [I][H] with scales
  * sg[e], su[e] f32 [I/128][H/128]; wd[e] [H][I], sd[e] [H/128][I/128].  Index E is the shared expert (pointers may be
  * NULL: no shared expert).  Only experts in [e_lo, e_hi) are computed (an expert-parallel rank's share); the shared
- * expert is added when with_shared.  acc [T][H] f32 (before the final rounding), out [T][H] bf16 (may be NULL). */
+ * expert is added when with_shared.  acc [T][H] f32 (before the final rounding), out [T][H] bf16 (may be NULL).
+ * limit: the SwiGLU clamp of orc_fp8_expert_row (0: none).  pickmax [T][H] (may be NULL): per element the largest
+ * magnitude among the outputs that were added there (what one bf16 rounding flip of one of them can change). */
 ORC_API int orc_moe_fp8_layer(const uint16_t* x, const int32_t* idx, const float* w, int T, int H, int I, int E,
                               int topk, const uint8_t* const* wg, const float* const* sg, const uint8_t* const* wu,
                               const float* const* su, const uint8_t* const* wd, const float* const* sd, int e_lo,
-                              int e_hi, int with_shared, float* acc, uint16_t* out) {
+                              int e_hi, int with_shared, float limit, float* acc, uint16_t* out, float* pickmax) {
   if (H % 128 || I % 128) return -1;
   lut_init();
   float* y = (float*)malloc(sizeof(float) * H);
   memset(acc, 0, sizeof(float) * (size_t)T * H);
+  if (pickmax) memset(pickmax, 0, sizeof(float) * (size_t)T * H);
   for (int e = e_lo; e < e_hi; ++e) /* ascending expert id: each row's adds happen in that order */
     for (int t = 0; t < T; ++t)
       for (int j = 0; j < topk; ++j)
         if (idx[(size_t)t * topk + j] == e) {
           orc_fp8_expert_row(x + (size_t)t * H, H, I, wg[e], sg[e], wu[e], su[e], wd[e], sd[e], w[(size_t)t * topk + j],
-                             y, NULL);
+                             limit, y, NULL);
           float* a = acc + (size_t)t * H;
           for (int n = 0; n < H; ++n) a[n] += y[n];
+          if (pickmax)
+            for (int n = 0; n < H; ++n) pickmax[(size_t)t * H + n] = fmaxf(pickmax[(size_t)t * H + n], fabsf(y[n]));
         }
   if (with_shared && wg[E])
     for (int t = 0; t < T; ++t) {
-      orc_fp8_expert_row(x + (size_t)t * H, H, I, wg[E], sg[E], wu[E], su[E], wd[E], sd[E], -1.f, y, NULL);
+      orc_fp8_expert_row(x + (size_t)t * H, H, I, wg[E], sg[E], wu[E], su[E], wd[E], sd[E], -1.f, limit, y, NULL);
       float* a = acc + (size_t)t * H;
       for (int n = 0; n < H; ++n) a[n] += y[n];
+      if (pickmax)
+        for (int n = 0; n < H; ++n) pickmax[(size_t)t * H + n] = fmaxf(pickmax[(size_t)t * H + n], fabsf(y[n]));
     }
   if (out)
     for (size_t i = 0; i < (size_t)T * H; ++i) out[i] = orc_f32_to_bf16(acc[i]);
@@ -545,6 +599,15 @@ ORC_API void orc_pack_bf16_tile(const uint16_t* w, int N, int K, uint8_t* out) {
           memcpy(blk + 512 * p + 16 * l, w + (size_t)n * K + 128 * b + 64 * (p >> 1) + 16 * t + 8 * (p & 1), 16);
       }
     }
+}
+
+/* the thread count of the parallel loops (a launcher may have exported OMP_NUM_THREADS=1) */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
 }
 
 ORC_API int orc_num_threads(void) {

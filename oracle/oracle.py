@@ -40,6 +40,8 @@ def lib():
         L.orc_f32_to_e4m3.argtypes = [C.c_float]
         L.orc_route_sigmoid.restype = C.c_float
         L.orc_route_sigmoid.argtypes = [C.c_float]
+        L.orc_route_sqrtsoftplus.restype = C.c_float
+        L.orc_route_sqrtsoftplus.argtypes = [C.c_float]
         L.orc_read_int4_block.restype = C.c_uint16
         L.orc_num_threads.restype = C.c_int
         _LIB = L
@@ -171,20 +173,22 @@ def _ptr_array(arrs):
     return a
 
 
-def fp8_expert_row(x_bf16, wg, sg, wu, su, wd, sd, wroute=None):
+def fp8_expert_row(x_bf16, wg, sg, wu, su, wd, sd, wroute=None, swiglu_limit=0.0):
     """One expert on one row.  Returns (y [H] f32 (bf16-rounded values), h [I] f32 (bf16-rounded values))."""
     I, H = wg.shape
     y = np.empty(H, np.float32)
     h = np.empty(I, np.float32)
     x_bf16 = _c(x_bf16, np.uint16)
     lib().orc_fp8_expert_row(_p(x_bf16), H, I, _p(wg), _p(sg), _p(wu), _p(su), _p(wd), _p(sd),
-                             C.c_float(-1.0 if wroute is None else wroute), _p(y), _p(h))
+                             C.c_float(-1.0 if wroute is None else wroute), C.c_float(swiglu_limit), _p(y), _p(h))
     return y, h
 
 
-def moe_fp8_layer(x_bf16, idx, w, experts, shared, e_lo=0, e_hi=None, with_shared=True):
+def moe_fp8_layer(x_bf16, idx, w, experts, shared, e_lo=0, e_hi=None, with_shared=True, swiglu_limit=0.0,
+                  pickmax=False):
     """experts: dict e -> (wg, sg, wu, su, wd, sd) canonical numpy arrays (only the picked experts need be present);
-    shared: the same tuple or None.  Returns (acc f32 [T][H], out bf16 bits [T][H])."""
+    shared: the same tuple or None.  Returns (acc f32 [T][H], out bf16 bits [T][H]) and, with pickmax, a third array
+    f32 [T][H]: per element the largest magnitude among the bf16 outputs that were added there."""
     x_bf16, idx, w = _c(x_bf16, np.uint16), _c(idx, np.int32), _c(w, np.float32)
     T, H = x_bf16.shape
     k = idx.shape[1]
@@ -199,10 +203,11 @@ def moe_fp8_layer(x_bf16, idx, w, experts, shared, e_lo=0, e_hi=None, with_share
     acc = np.empty((T, H), np.float32)
     out = np.empty((T, H), np.uint16)
     pa = [_ptr_array(c) for c in cols]
+    pm = np.empty((T, H), np.float32) if pickmax else None
     rc = lib().orc_moe_fp8_layer(_p(x_bf16), _p(idx), _p(w), T, H, I, E, k, pa[0], pa[1], pa[2], pa[3], pa[4], pa[5],
-                                 e_lo, e_hi, int(with_shared), _p(acc), _p(out))
+                                 e_lo, e_hi, int(with_shared), C.c_float(swiglu_limit), _p(acc), _p(out), _p(pm))
     assert rc == 0
-    return acc, out
+    return (acc, out, pm) if pickmax else (acc, out)
 
 
 def pack_fp8_tile(w):
@@ -280,3 +285,11 @@ def pack_bf16_tile(w):
 
 def num_threads():
     return lib().orc_num_threads()
+
+
+def set_threads(n=None):
+    """Use n host threads (default: every core this process may run on), whatever OMP_NUM_THREADS a launcher exported."""
+    if n is None:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(int(n))
+    return num_threads()
