@@ -8,7 +8,7 @@ LIB_PATH = os.path.join(HERE, "libdsgx_moe.so")
 
 OK, ERR_ARG, ERR_FORMAT, ERR_SHAPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED, ERR_LIMIT = range(8)
 FMT_NVFP4, FMT_RETIRED, FMT_INT4, FMT_BF16, FMT_FP8 = range(5)
-SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
+SCORE_SIGMOID, SCORE_SOFTMAX, SCORE_SQRTSOFTPLUS = 0, 1, 2
 MAX_ROWS = 8
 
 
@@ -27,7 +27,8 @@ class LayerW(C.Structure):
 class MoeShape(C.Structure):
     _fields_ = [("H", C.c_int32), ("I", C.c_int32), ("E", C.c_int32), ("topk", C.c_int32), ("n_group", C.c_int32),
                 ("topk_group", C.c_int32), ("score_fn", C.c_int32), ("norm_topk", C.c_int32),
-                ("route_scale", C.c_float), ("fmt", C.c_uint32), ("e_lo", C.c_int32), ("e_hi", C.c_int32)]
+                ("route_scale", C.c_float), ("fmt", C.c_uint32), ("e_lo", C.c_int32), ("e_hi", C.c_int32),
+                ("sh_lo", C.c_int32), ("sh_hi", C.c_int32), ("swiglu_limit", C.c_float), ("reserved", C.c_int32)]
 
 
 class PeerSet(C.Structure):

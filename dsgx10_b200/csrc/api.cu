@@ -71,7 +71,8 @@ static int check_route_shape(const dsgx_moe_shape* s) {
   if (s->n_group < 1 || s->n_group > 32 || s->E % s->n_group || s->topk_group < 1 || s->topk_group > s->n_group)
     return DSGX_ERR_SHAPE;
   if (s->n_group > 1 && (s->E / s->n_group < 2 || s->topk > s->topk_group * (s->E / s->n_group))) return DSGX_ERR_SHAPE;
-  if (s->score_fn != DSGX_SCORE_SIGMOID && s->score_fn != DSGX_SCORE_SOFTMAX) return DSGX_ERR_SHAPE;
+  if (s->score_fn != DSGX_SCORE_SIGMOID && s->score_fn != DSGX_SCORE_SOFTMAX && s->score_fn != DSGX_SCORE_SQRTSOFTPLUS)
+    return DSGX_ERR_SHAPE;
   return DSGX_OK;
 }
 static int check_shape(const dsgx_moe_shape* s) {
@@ -84,6 +85,12 @@ static int check_shape(const dsgx_moe_shape* s) {
   if (s->e_lo < 0 || s->e_hi > s->E || s->e_lo > s->e_hi) return DSGX_ERR_SHAPE;
   if (s->fmt == DSGX_FMT_FP8 && (s->H > 4096 || s->I > 4096 || s->H % 256 || s->I % 256)) return DSGX_ERR_SHAPE;
   if (s->fmt == DSGX_FMT_INT4 && (s->H % 512 || s->I % 512)) return DSGX_ERR_SHAPE;
+  if (s->sh_lo || s->sh_hi) {  // a part of the shared expert: FP8 decode only, whole pieces of 512 channels
+    if (s->fmt != DSGX_FMT_FP8 || s->sh_lo < 0 || s->sh_hi > s->I || s->sh_lo >= s->sh_hi || s->sh_lo % 512 ||
+        (s->sh_hi % 512 && s->sh_hi != s->I))
+      return DSGX_ERR_SHAPE;
+  }
+  if (!(s->swiglu_limit >= 0.f) || (s->swiglu_limit > 0.f && s->fmt != DSGX_FMT_FP8)) return DSGX_ERR_SHAPE;
   return DSGX_OK;
 }
 
@@ -163,7 +170,8 @@ int dsgx_finalize_peers(const dsgx_peer_set* ps, int M, int H, void* out, int32_
   if (!ps || !ps->parts || !ps->flags || !ps->state || (!out && !ps->outs) || !status_word) return DSGX_ERR_ARG;
   if ((ps->outs != nullptr) != (ps->done != nullptr)) return DSGX_ERR_ARG;
   if (ps->outs && H % 8) return DSGX_ERR_SHAPE;
-  if (ps->world < 1 || ps->world > 32 || ps->rank < 0 || ps->rank >= ps->world || ps->shared_rank >= ps->world) return DSGX_ERR_ARG;
+  if (ps->world < 1 || ps->world > 32 || ps->rank < 0 || ps->rank >= ps->world || ps->shared_rank >= ps->world || ps->shared_rank < -2) return DSGX_ERR_ARG;
+  if (ps->shared_rank == -2 && ps->outs) return DSGX_ERR_UNSUPPORTED;  // (parts of the shared expert: the decode form only)
   if (M < 1 || M > ps->rows_cap || H < 4 || H % 4 || (size_t)M * H / 4 > (size_t)1 << 30) return DSGX_ERR_SHAPE;
   PeerParams p;
   p.parts = ps->parts, p.flags = ps->flags, p.state = ps->state, p.rank = ps->rank, p.world = ps->world;
@@ -202,7 +210,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.ws = decode_ws_carve(ws, s->H, s->I);
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr;
     p.up = cfg->up, p.down = cfg->down;
-    p.sh_lo = 0, p.sh_hi = s->I;
+    p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                       cfg->parts == 0 ? 3 : cfg->parts);
@@ -220,7 +228,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
-    p.sh_lo = 0, p.sh_hi = s->I;
+    p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                        cfg->parts == 0 ? 3 : cfg->parts);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
@@ -257,7 +265,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     p.idx = st->idx, p.w = st->w;
     p.ws = decode_ws_carve(st->ws, s->H, s->I);
     p.yr = st->yr, p.ys = st->ys, p.ysum = 0, p.up = 0, p.down = 0;
-    p.sh_lo = 0, p.sh_hi = s->I;
+    p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -265,7 +273,8 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     // Three rows and more: the whole step as one persistent kernel.  One or two rows: the four-kernel step is faster
     // (measured): the routing chain is too long to hide behind the little work that needs no routing.
     // flags: bit 0 never the one kernel; bit 2 always; bit 3: route with two small kernels, experts in the one kernel.
-    if (fp8 && !(st->flags & 1) && (M >= 3 || (st->flags & 12)) && step_fp8_fits(s->H, s->I, s->E, M)) {
+    const bool sh_part = p.sh_lo != 0 || p.sh_hi != s->I;  // (a part of the shared expert: the separate kernels)
+    if (fp8 && !sh_part && !(st->flags & 1) && (M >= 3 || (st->flags & 12)) && step_fp8_fits(s->H, s->I, s->E, M)) {
       StepParams sp;
       sp.pre_routed = (st->flags & 8) ? 1 : 0;
       if (sp.pre_routed) {
@@ -327,6 +336,7 @@ static int check_prefill_shape(const dsgx_moe_shape* s) {
   const int rc = check_shape(s);
   if (rc) return rc;
   if (s->fmt != DSGX_FMT_FP8) return DSGX_ERR_UNSUPPORTED;
+  if (s->sh_lo || (s->sh_hi && s->sh_hi != s->I)) return DSGX_ERR_UNSUPPORTED;  // (the prefill pass runs whole experts)
   if (s->H % 256 || s->I % 128) return DSGX_ERR_SHAPE;
   return DSGX_OK;
 }
@@ -394,7 +404,7 @@ int dsgx_moe_prefill(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void*
   if ((size_t)T * s->topk > (size_t)1 << 30) return DSGX_ERR_SHAPE;
   PrefillParams q;
   q.T = T, q.H = s->H, q.I = s->I, q.E = s->E, q.topk = s->topk, q.has_shared = sh, q.ysum = ysum & 1, q.parts = (ysum >> 8) & 3;
-  q.e_lo = s->e_lo, q.e_hi = s->e_hi;
+  q.e_lo = s->e_lo, q.e_hi = s->e_hi, q.limit = s->swiglu_limit;
   q.x = reinterpret_cast<const __nv_bfloat16*>(x), q.idx = idx, q.w = w;
   q.pw = prefill_weights_carve(const_cast<void*>(wbuf), s->H, s->I, s->E);
   q.ws = prefill_ws_carve(ws, T, s->H, s->I, s->E, s->topk);

@@ -137,6 +137,10 @@ DSGX_DEV uint32_t quant_e4m3(float v, float s) {
 // scale of a block of 128 values from its absolute maximum: max(amax, 1e-4) * (1/448)
 DSGX_DEV float act_scale(float amax) { return __fmul_rn(fmaxf(amax, 1e-4f), 1.0f / 448.0f); }
 DSGX_DEV float silu(float g) { return __fdiv_rn(g, 1.f + expf(-g)); }
+// The SwiGLU clamp on the bf16 gate and up values (ds41f ref/inference/model.py:845-847): up to +-lim, gate from above; lim 0: none.
+DSGX_DEV void swiglu_clamp(float& g, float& u, float lim) {
+  if (lim > 0.f) u = fminf(fmaxf(u, -lim), lim), g = fminf(g, lim);
+}
 
 DSGX_DEV float warp_max(float v) {
 #pragma unroll

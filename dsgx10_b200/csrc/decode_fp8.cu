@@ -101,8 +101,9 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   int pend = 0, pend_uidx = 0, pend_split = 0, pend_wslot = 0, pend_tslot = -1, pend_i8 = 0, pend_ticket = 0;
   auto write_h = [&](const float (&a)[4]) {  // a = gate r0, gate r1, up r0, up r1 of channel 8 i8 + g
     const int ch = pend_i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
-    float h0 = __fmul_rn(silu(bf16_round(a[0])), bf16_round(a[2]));
-    float h1 = __fmul_rn(silu(bf16_round(a[1])), bf16_round(a[3]));
+    float g0 = bf16_round(a[0]), g1 = bf16_round(a[1]), u0 = bf16_round(a[2]), u1 = bf16_round(a[3]);
+    swiglu_clamp(g0, u0, p.limit), swiglu_clamp(g1, u1, p.limit);
+    float h0 = __fmul_rn(silu(g0), u0), h1 = __fmul_rn(silu(g1), u1);
     if (pend_tslot >= 0) h0 = __fmul_rn(tab.ent[pend_tslot].w[r0], h0), h1 = __fmul_rn(tab.ent[pend_tslot].w[r1], h1);
     __nv_bfloat16* hrow = p.ws.h + (size_t)pend_wslot * 8 * p.I;
     if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);
@@ -350,10 +351,16 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   // what a finished run still owes: 1, 2 its ticket among the unit's runs (the last adds the pieces and parks the pick's
   // rounded output), 3, 4 the unit's ticket among the slots of its output tile (the last adds the tile's picks)
   int pend = 0, pend_uidx = 0, pend_wslot = 0, pend_n16 = 0, pend_p0 = 0, pend_p1 = 0, pend_ticket = 0;
-  auto park = [&](const float (&acc)[4]) {  // every pick's output is rounded to bf16 before the f32 adds
+  // every pick's output is rounded to bf16 before the f32 adds; a GPU that holds only a part of the shared expert's
+  // intermediate channels keeps its part of that output in f32: it is rounded once all parts are added (across the GPUs)
+  const bool sh_part = p.sh_lo != 0 || p.sh_hi != p.I;
+  auto park = [&](const float (&acc)[4]) {
     float* yt = p.ws.ypick + ((size_t)pend_wslot * NT + pend_n16) * 128;
-    *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
-    *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) = make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
+    const bool keep = sh_part && pend_wslot == kShSlot;
+    *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) =
+        keep ? make_float2(acc[0], acc[1]) : make_float2(bf16_round(acc[0]), bf16_round(acc[1]));
+    *reinterpret_cast<float2*>(yt + (g + 8) * 8 + 2 * t) =
+        keep ? make_float2(acc[2], acc[3]) : make_float2(bf16_round(acc[2]), bf16_round(acc[3]));
   };
   auto advance = [&]() {
     if (pend == 1) {

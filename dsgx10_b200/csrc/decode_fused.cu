@@ -265,8 +265,9 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       if (dead) break;
       while (pend) advance();
       const int ch = i8 * 8 + g, r0 = 2 * t, r1 = 2 * t + 1;
-      float h0 = __fmul_rn(silu(bf16_round(tot[0])), bf16_round(tot[2]));
-      float h1 = __fmul_rn(silu(bf16_round(tot[1])), bf16_round(tot[3]));
+      float g0 = bf16_round(tot[0]), g1 = bf16_round(tot[1]), u0 = bf16_round(tot[2]), u1 = bf16_round(tot[3]);
+      swiglu_clamp(g0, u0, p.limit), swiglu_clamp(g1, u1, p.limit);
+      float h0 = __fmul_rn(silu(g0), u0), h1 = __fmul_rn(silu(g1), u1);
       if (!shared) h0 = __fmul_rn(tab.ent[s].w[r0], h0), h1 = __fmul_rn(tab.ent[s].w[r1], h1);
       __nv_bfloat16* hrow = p.ws.h + (size_t)wslot * 8 * p.I;
       if (r0 < p.M) hrow[(size_t)r0 * p.I + ch] = __float2bfloat16_rn(h0);

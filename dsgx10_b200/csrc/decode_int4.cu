@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
 
   const int upp = p.I / 8;
   const int total = dead ? 0 : tab.ntot * upp;
-  const int GW = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
+  const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;  // consecutive units on different SMs
   const int cpu4 = p.H / 512, cpub = p.H / 128;  // chunks a unit: INT4 blocks, BF16 blocks
   int pu = gw, pc = 0;
   uint32_t issued = 0, consumed = 0;
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
   }
   bool dead = !mbar_wait(cbar, 0);
 
-  const int GW = gridDim.x * kWarps, gw = blockIdx.x * kWarps + warp;
+  const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;  // consecutive units on different SMs
   if (!dead && tab.ntot == 0) {
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kThreads) {
       p.yr[i] = 0.f;

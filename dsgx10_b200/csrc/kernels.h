@@ -73,6 +73,7 @@ struct DecodeParams {
   __nv_bfloat16* out;  // when set, k_down also writes bf16(yr + ys)
   int ysum;
   int up, down;  // kernel variants (same bits)
+  float limit;     // the SwiGLU clamp (0: none)
   int sh_lo, sh_hi;  // the shared expert's intermediate channels this GPU computes (multiples of 512; the whole: 0, I)
 };
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
@@ -146,6 +147,7 @@ PrefillWs prefill_ws_carve(void* ws, int T, int H, int I, int E, int topk);
 
 struct PrefillParams {
   int T, H, I, E, topk, has_shared, ysum, e_lo, e_hi;
+  float limit;  // the SwiGLU clamp (0: none)
   int parts;  // bench hook: 0 the whole pass, 1 the routed gate/up GEMM alone, 2 the routed down GEMM alone
   const __nv_bfloat16* x;
   const int* idx;

@@ -112,19 +112,28 @@ __global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f), sv = make_float4(0.f, 0.f, 0.f, 0.f);
       if (p.shared_rank >= 0) sv = ld_peer4(p.parts[p.shared_rank] + off + (size_t)(p.rows_cap + r) * p.H + c);
       for (int q0 = 0; q0 < p.world; q0 += 8) {
-        float4 v[8];
+        float4 v[8], u[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          if (q0 + j < p.world) v[j] = ld_peer4(p.parts[q0 + j] + off + (size_t)r * p.H + c);
+          if (q0 + j < p.world) {
+            v[j] = ld_peer4(p.parts[q0 + j] + off + (size_t)r * p.H + c);
+            if (p.shared_rank == -2) u[j] = ld_peer4(p.parts[q0 + j] + off + (size_t)(p.rows_cap + r) * p.H + c);
+          }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (q0 + j < p.world) {
             const bool first = q0 + j == 0;
             a.x = first ? v[j].x : __fadd_rn(a.x, v[j].x), a.y = first ? v[j].y : __fadd_rn(a.y, v[j].y);
             a.z = first ? v[j].z : __fadd_rn(a.z, v[j].z), a.w = first ? v[j].w : __fadd_rn(a.w, v[j].w);
+            if (p.shared_rank == -2) {  // every rank holds a part of the shared expert's output: added in rank order
+              sv.x = first ? u[j].x : __fadd_rn(sv.x, u[j].x), sv.y = first ? u[j].y : __fadd_rn(sv.y, u[j].y);
+              sv.z = first ? u[j].z : __fadd_rn(sv.z, u[j].z), sv.w = first ? u[j].w : __fadd_rn(sv.w, u[j].w);
+            }
           }
       }
-      if (p.shared_rank >= 0)
+      if (p.shared_rank == -2)  // ... and rounded to bf16 once, as a whole expert's output is
+        sv = make_float4(bf16_round(sv.x), bf16_round(sv.y), bf16_round(sv.z), bf16_round(sv.w));
+      if (p.shared_rank >= 0 || p.shared_rank == -2)
         a.x = __fadd_rn(a.x, sv.x), a.y = __fadd_rn(a.y, sv.y), a.z = __fadd_rn(a.z, sv.z), a.w = __fadd_rn(a.w, sv.w);
       const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
       uint2 o;

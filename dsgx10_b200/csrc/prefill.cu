@@ -207,6 +207,7 @@ struct GemmArgs {
   const float* sb0;    // UP: gate scales, DOWN: down scales; [.. experts][N / 128][K / 128]
   const float* sb1;    // UP: up scales
   const float* wrow;   // UP: routing weight of every row (null: none)
+  float limit;         // UP: the SwiGLU clamp (0: none)
   uint8_t* hq;         // UP out: e4m3 [rows][N]
   float* hs;           // UP out: [rows][N / 128]
   __nv_bfloat16* y;    // DOWN out: [rows][N]
@@ -453,7 +454,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         float am = 0.f;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const float2 g = bf16_round2(acc0[c]), u = bf16_round2(acc1[c]);
+          float2 g = bf16_round2(acc0[c]), u = bf16_round2(acc1[c]);
+          swiglu_clamp(g.x, u.x, a.limit), swiglu_clamp(g.y, u.y, a.limit);
           float2 h = make_float2(__fmul_rn(silu_fast(g.x), u.x), __fmul_rn(silu_fast(g.y), u.y));
           if (a.wrow) h = make_float2(__fmul_rn(wr, h.x), __fmul_rn(wr, h.y));
           h = bf16_round2(h);
@@ -769,6 +771,7 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
     return cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
   GemmArgs a;
+  a.limit = q.limit;
   a.status = w.status;
   if (!q.parts) {  // (bench hook otherwise: the workspace holds the order and the operands of an earlier whole pass)
   // order, quantise, gather

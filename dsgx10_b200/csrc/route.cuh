@@ -30,6 +30,44 @@ DSGX_DEV float route_sigmoid(float l) {
   return __fdiv_rn(1.f, __fadd_rn(1.f, exp_ieee(x)));
 }
 
+// ln(y) for y in [1, 2^31) with IEEE operations only (a CPU repeats the bits): y = 2^n m, m in [1/sqrt2, sqrt2),
+// s = (m - 1) / (m + 1), ln m = 2 s (1 + z/3 + z^2/5 + z^3/7 + z^4/9 + z^5/11), z = s^2; ln y = n ln2_hi + (n ln2_lo + ln m).
+DSGX_DEV float log_ieee(float y) {
+  uint32_t u = __float_as_uint(y);
+  int n = (int)(u >> 23) - 127;
+  float m = __uint_as_float((u & 0x007FFFFFu) | 0x3F800000u);
+  if (m > 1.41421356f) m = __fmul_rn(m, 0.5f), n += 1;
+  const float f = __fsub_rn(m, 1.f);
+  const float sv = __fdiv_rn(f, __fadd_rn(2.f, f));
+  const float z = __fmul_rn(sv, sv);
+  float p = 1.f / 11;
+  p = fmaf(p, z, 1.f / 9);
+  p = fmaf(p, z, 1.f / 7);
+  p = fmaf(p, z, 1.f / 5);
+  p = fmaf(p, z, 1.f / 3);
+  p = fmaf(p, z, 1.f);
+  const float lm = __fmul_rn(__fmul_rn(2.f, sv), p);
+  const float nf = (float)n;
+  return fmaf(nf, 0.693145751953125f, fmaf(nf, 1.428606765330187e-06f, lm));
+}
+// sqrt(softplus(l)), torch's softplus (l > 20 ? l : log1p(exp(l))): the score of ds41f's router
+// (engine/kernels/common.cuh:264-287).  log1p(t) = ln(y) t / (y - 1) with y = fl(1 + t), t itself when y == 1.
+DSGX_DEV float route_sqrtsoftplus(float l) {
+  float sp;
+  if (l > 20.f) {
+    sp = l;
+  } else if (l < -87.f) {
+    sp = 0.f;
+  } else {
+    const float t = exp_ieee(l);
+    const float y = __fadd_rn(1.f, t);
+    const float d = __fsub_rn(y, 1.f);
+    sp = d == 0.f ? t : __fdiv_rn(__fmul_rn(log_ieee(y), t), d);
+  }
+  return __fsqrt_rn(sp);
+}
+DSGX_DEV float route_score1(int score_fn, float l) { return score_fn == DSGX_SCORE_SIGMOID ? route_sigmoid(l) : route_sqrtsoftplus(l); }
+
 constexpr int kRJ = 16;  // experts a lane: E <= 512
 
 // One row.  Expert e = lane + 32 j.  The row's logit of expert e is the sum, in ascending s, of nsplit partial sums
@@ -57,9 +95,9 @@ DSGX_DEV void route_row(const RouteParams& p, const float* __restrict__ l, int n
     for (int j = 0; j < kRJ; ++j)
       if (lane + 32 * j < p.E) logits_out[lane + 32 * j] = s[j];
   }
-  if (p.score_fn == DSGX_SCORE_SIGMOID) {
+  if (p.score_fn != DSGX_SCORE_SOFTMAX) {
 #pragma unroll
-    for (int j = 0; j < kRJ; ++j) s[j] = lane + 32 * j < p.E ? route_sigmoid(s[j]) : 0.f;
+    for (int j = 0; j < kRJ; ++j) s[j] = lane + 32 * j < p.E ? route_score1(p.score_fn, s[j]) : 0.f;
   } else {  // softmax: t = exp(l - max), lane sums over j ascending, butterfly, one division each
     float m = -INFINITY;
 #pragma unroll
@@ -224,8 +262,8 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     if (logits_out) logits_out[e] = lg;
   }
   float s;
-  if (p.score_fn == DSGX_SCORE_SIGMOID) {
-    s = valid ? route_sigmoid(lg) : 0.f;
+  if (p.score_fn != DSGX_SCORE_SOFTMAX) {
+    s = valid ? route_score1(p.score_fn, lg) : 0.f;
   } else {
     float m = warp_max(lg);
     if (lane == 0) sm.red[warp] = m;

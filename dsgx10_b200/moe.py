@@ -14,9 +14,9 @@ from ._lib import MoeShape, check, lib
 
 
 def shape(H, I, E, topk, fmt=_lib.FMT_FP8, n_group=1, topk_group=1, score_fn=_lib.SCORE_SIGMOID, norm_topk=True,
-          route_scale=1.0, e_lo=0, e_hi=None):
+          route_scale=1.0, e_lo=0, e_hi=None, sh_lo=0, sh_hi=0, swiglu_limit=0.0):
     return MoeShape(H, I, E, topk, n_group, topk_group, score_fn, int(norm_topk), route_scale, fmt, e_lo,
-                    E if e_hi is None else e_hi)
+                    E if e_hi is None else e_hi, sh_lo, sh_hi, swiglu_limit, 0)
 
 
 def _stream():

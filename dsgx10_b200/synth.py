@@ -83,6 +83,13 @@ class Fp8Layer:
         self.desc = torch.frombuffer(bytearray(bytes(self.desc_host)), dtype=torch.uint8).to(self.device)
         self.shared = shared
 
+    def to(self, device):
+        """The same layer with its pool and descriptors on another device (built on the CPU, it reaches the GPU in two
+        copies instead of hundreds of small generation kernels)."""
+        self.device = torch.device(device)
+        self.pool, self.desc = self.pool.to(self.device), self.desc.to(self.device)
+        return self
+
     def layer_w(self):
         L = _lib.LayerW()
         L.pool, L.desc, L.fmt = self.pool.data_ptr(), self.desc.data_ptr(), _lib.FMT_FP8
@@ -166,17 +173,20 @@ def tile_bf16(w):
 class Int4Layer:
     """One INT4-g32 layer: `E` routed experts in the engine's block layout + (optionally) a bf16 shared expert."""
 
-    def __init__(self, H, I, E, seed, device="cpu", shared=True, e_range=None):
+    def __init__(self, H, I, E, seed, device="cpu", shared=True, e_range=None, experts=None):
+        """experts: the ids to generate (default: all of e_range); the other experts' descriptors stay empty, so a step
+        must not pick them (a test of a full-size layer generates only what its rows route to)."""
         self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_INT4
         self.device = torch.device(device)
         shapes = ((I, H), (I, H), (H, I))
         mat_b = (I // 8) * (H // 512) * 2368
         assert mat_b == (H // 8) * (I // 512) * 2368 and mat_b % 256 == 0
         lo, hi = e_range if e_range is not None else (0, E)
+        ids = [e for e in (range(lo, hi) if experts is None else sorted(set(experts))) if lo <= e < hi]
         self.raw = {}
-        pool = np.empty(max(hi - lo, 1) * 3 * mat_b, np.uint8)
+        pool = np.empty(max(len(ids), 1) * 3 * mat_b, np.uint8)
         self.desc_host = (_lib.MatDesc * (E * 3))()
-        for n, e in enumerate(range(lo, hi)):
+        for n, e in enumerate(ids):
             self.raw[e] = []
             for m, (N, K) in enumerate(shapes):
                 wp, s = int4_tensors(N, K, seed * 1000 + e * 3 + m)

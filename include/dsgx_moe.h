@@ -41,7 +41,9 @@ typedef enum dsgx_status {
  * routed FP8 format: the reference's "tile_fp8" lane order (experts.h:66-70, layout.h:108-119) for the e4m3 values and
  * f32 scales [N/128][K/128] row-major. */
 enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF16 = 3, DSGX_FMT_FP8 = 4 };
-enum { DSGX_SCORE_SIGMOID = 0, DSGX_SCORE_SOFTMAX = 1 };
+/* scores of the router: sigmoid and softmax (altar1 engine/experts/formats.cuh:142-163; ds41f ref/inference/model.py:812-818),
+ * sqrt(softplus(l)) (ds41f engine/kernels/common.cuh:264-287, the only score dsk::router_topk has) */
+enum { DSGX_SCORE_SIGMOID = 0, DSGX_SCORE_SOFTMAX = 1, DSGX_SCORE_SQRTSOFTPLUS = 2 };
 
 enum { DSGX_MAX_ROWS = 8 };  /* decode rows a step */
 
@@ -89,6 +91,15 @@ typedef struct dsgx_moe_shape {
   float route_scale;
   uint32_t fmt;         /* DSGX_FMT_FP8 or DSGX_FMT_INT4 */
   int32_t e_lo, e_hi;   /* this GPU's experts [e_lo, e_hi) (expert parallelism: ds41f ref/inference/model.py:863-870) */
+  int32_t sh_lo, sh_hi; /* FP8 decode: the shared expert's intermediate channels [sh_lo, sh_hi) this GPU computes
+                           (multiples of 512; both 0: all of them).  The ranks of an expert-parallel step split the shared
+                           expert this way instead of leaving it to one of them: a rank reads rows [sh_lo, sh_hi) of its
+                           gate and up matrices and those K columns of its down matrix (the pointers still address the
+                           whole matrices), and its ys is an unrounded f32 partial sum: the parts are added across the
+                           ranks and rounded to bf16 once (dsgx_finalize_peers with shared_rank = -2) */
+  float swiglu_limit;   /* > 0: gate is clamped from above to this and up to +- this before silu, on their bf16 values
+                           (ds41f ref/inference/model.py:845-847; engine/kernels/prefill.cu:153-158 fixes 10); 0: no clamp */
+  int32_t reserved;
 } dsgx_moe_shape;
 
 int dsgx_last_cuda_error(void);
@@ -161,8 +172,9 @@ int dsgx_finalize(const float* R, const float* S, int M, int H, void* out_bf16, 
  *   flags[r]  rank r's flag words, u32 [world], zeroed once before the first step
  *   state     this rank's own u32 [2] {step counter, ticket}, zeroed once
  *   parts, flags: device arrays of `world` pointers.
- * out (this rank's memory) = bf16((yr of rank 0 + yr of rank 1 + ...) + ys of rank `shared_rank`), shared_rank < 0: no
- * shared expert.  The same bits on every rank.  The kernels of one step on the different GPUs wait for one another (each
+ * out (this rank's memory) = bf16((yr of rank 0 + yr of rank 1 + ...) + ys of rank `shared_rank`); shared_rank = -1: no
+ * shared expert; shared_rank = -2: every rank holds a part of the shared expert (dsgx_moe_shape.sh_lo / sh_hi) and
+ * out = bf16(sum of yr + bf16(ys of rank 0 + ys of rank 1 + ...)).  The same bits on every rank.  The kernels of one step on the different GPUs wait for one another (each
  * wait bounded; on a run-out the status word, this rank's memory, gets DSGX_ERR_DEVICE_WAIT): launch nothing else that
  * waits across GPUs at the same time, and one step at a time. */
 typedef struct dsgx_peer_set {

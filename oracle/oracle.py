@@ -19,8 +19,13 @@ SCORE_SIGMOID, SCORE_SOFTMAX, SCORE_SQRTSOFTPLUS = 0, 1, 2
 
 
 def build(with_ref=True):
-    """Compile liboracle.so (and the reference shim when the reference tree is present)."""
-    subprocess.run(["make", "-s", "-C", HERE, "all" if with_ref else os.path.join(HERE, "liboracle.so")], check=True)
+    """Compile liboracle.so and, when the reference tree is there (environment variable DSGX_REFERENCE, else the
+    directory `reference` beside this repository), the shim over the reference's own host functions."""
+    ref = os.environ.get("DSGX_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    cmd = ["make", "-s", "-C", HERE, "all" if with_ref else os.path.join(HERE, "liboracle.so")]
+    if with_ref and os.path.isdir(ref):
+        cmd.append("REF=" + ref)
+    subprocess.run(cmd, check=True)
 
 
 def lib():

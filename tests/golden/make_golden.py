@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Generates tests/golden/*.npz by running the reference's own Python CPU modules on small seeded layers.
 
-Run in a container that has the reference tree (its location: DSGX_REFERENCE, default below); the fixtures it writes are committed, this
+Run in a container that has the reference tree (its location: the environment variable DSGX_REFERENCE); the fixtures it writes are committed, this
 script is how they were made.  Nothing of the reference is copied: its modules are imported from where they lie.
 
   FP8:  ds41f ref/inference/model.py (Gate, Expert, MoE) over ref/torchref/kernel.py, switched to the "g128" recipe the
@@ -22,7 +22,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("DSGX_REFERENCE", "/root/reference")
+REF = os.environ.get("DSGX_REFERENCE")
+if not REF:
+    raise SystemExit("set DSGX_REFERENCE to the reference project's directory")
 
 from dsgx10_b200 import synth  # noqa: E402
 
@@ -36,7 +38,7 @@ def crc(*arrays):
 
 # ------------------------------------------------------------------------------------------------------------- FP8
 
-def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0):
+def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0, swiglu_limit=0.0, x_scale=1.0):
     sys.path[:0] = [os.path.join(REF, "ds41f-4xgx10-switchless/ref/torchref"),
                     os.path.join(REF, "ds41f-4xgx10-switchless/ref/inference")]
     import model as M  # the reference's model.py; `kernel` resolves to torchref/kernel.py
@@ -46,13 +48,15 @@ def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0):
     torch.set_default_dtype(torch.bfloat16)
     try:
         args = M.ModelArgs(dim=H, moe_inter_dim=I, n_routed_experts=E, n_activated_experts=topk, score_func=score,
-                           route_scale=route_scale, expert_dtype=None, n_layers=1)
+                           route_scale=route_scale, expert_dtype=None, n_layers=1, swiglu_limit=swiglu_limit)
         moe = M.MoE(0, args)
     finally:
         torch.set_default_dtype(torch.float32)
     layer = synth.Fp8Layer(H, I, E, seed, device="cpu")
     wr = synth.router_weights(E, H, seed + 2000)
     x = synth.activations(T, H, seed + 1000)
+    if x_scale != 1.0:  # (large activations, so that the SwiGLU clamp has something to clamp)
+        x = (x.float() * x_scale).to(torch.bfloat16)
     sums = []
     with torch.no_grad():
         moe.gate.weight = torch.nn.Parameter(wr.clone(), requires_grad=False)
@@ -76,8 +80,8 @@ def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0):
         finally:
             torch.set_default_dtype(torch.float32)
     np.savez_compressed(os.path.join(HERE, name + ".npz"),
-                        meta=np.array([H, I, E, topk, T, {"sigmoid": 0, "softmax": 1}[score], seed], np.int64),
-                        route_scale=np.float32(route_scale), weights_crc=np.array(sums, np.uint32),
+                        meta=np.array([H, I, E, topk, T, {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[score], seed], np.int64),
+                        route_scale=np.float32(route_scale), swiglu_limit=np.float32(swiglu_limit), weights_crc=np.array(sums, np.uint32),
                         x=synth.bf16_bits(x), logits=logits.float().numpy(), idx=indices.numpy().astype(np.int32),
                         w=weights.float().numpy(), out=synth.bf16_bits(out), e0=np.int32(e0), y0=synth.bf16_bits(y0),
                         ysh=synth.bf16_bits(ysh))
@@ -135,4 +139,6 @@ if __name__ == "__main__":
     fp8_case("fp8_sigmoid_small", 512, 256, 8, 2, 6, "sigmoid", 3101)
     fp8_case("fp8_sigmoid_top6", 1024, 512, 32, 6, 5, "sigmoid", 3102, route_scale=1.5)
     fp8_case("fp8_softmax", 512, 512, 16, 4, 4, "softmax", 3103)
+    # ds41f's own router score and its SwiGLU clamp (ref/config.json: scoring_func sqrtsoftplus, swiglu_limit 10)
+    fp8_case("fp8_sqrtsoftplus_clamp", 512, 256, 16, 6, 5, "sqrtsoftplus", 3104, route_scale=1.5, swiglu_limit=10.0, x_scale=48.0)
     int4_case("int4_sigmoid", 1024, 512, 16, 8, 5, 3201)

@@ -29,13 +29,14 @@ def _check(orc, shp, layer, x, idx, w, yr, ys, out, shared=True, e_lo=0, e_hi=No
     rows = np.arange(x.shape[0]) if rows is None else np.asarray(rows)
     xb = synth.bf16_bits(x)[rows]
     oi, ow = idx.cpu().numpy()[rows], w.cpu().numpy()[rows]
-    acc_r, _ = oracle_fp8_layer(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=False)
-    acc_all, out_all = oracle_fp8_layer(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=shared)
+    acc_r, _, pm_r = oracle_fp8_layer(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=False, pickmax=True)
+    acc_all, out_all, pm_all = oracle_fp8_layer(orc, layer, xb, oi, ow, e_lo, e_hi, with_shared=shared, pickmax=True)
     yr, ys, out = yr.cpu().numpy()[rows], ys.cpu().numpy()[rows], synth.bf16_bits(out)[rows]
-    assert_rows_close(yr, acc_r, TOL, what="yr")
+    assert_rows_close(yr, acc_r, TOL, what="yr", pickmax=pm_r)
     if shared:
-        assert_rows_close(yr + ys, acc_all, TOL, what="yr + ys")
-    assert_rows_close(orc.bf16_to_f32(out), orc.bf16_to_f32(out_all), TOL, frac=0.99, what="out")
+        assert_rows_close(yr + ys, acc_all, TOL, what="yr + ys", pickmax=pm_all)
+    assert_rows_close(orc.bf16_to_f32(out), orc.bf16_to_f32(out_all), TOL, what="out", pickmax=pm_all, rounded=True)
+    return pm_r, pm_all
 
 
 @pytest.mark.parametrize("T", [1, 7, 130, 300])
@@ -65,15 +66,23 @@ def test_ragged_segments_config1_shapes(orc):
     assert moe.ws_status(pl.ws) == 0
     rows = np.random.default_rng(0).choice(T, 12, replace=False)
     _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=rows)
-    # decode path on chunks of 8 rows: same numerics contract, outputs within tolerance of each other
-    from tests.util import assert_rows_close
+    # decode path on chunks of 8 rows: same numerics contract.  Both sides may have flipped one bf16 rounding of one
+    # expert's output against the exact sums, so up to two ulps of the largest output added at an element are explained
+    # (bf16_ulp(2 m) = 2 bf16_ulp(m)).
+    from dsgx10_b200 import synth
+    from tests.util import assert_rows_close, oracle_fp8_layer
+    first = np.arange(64)
+    _, _, pm = oracle_fp8_layer(orc, layer, synth.bf16_bits(x)[first], idx.cpu().numpy()[first], w.cpu().numpy()[first],
+                                with_shared=False, pickmax=True)
     ws = moe.decode_ws(shp)
     for r0 in range(0, 64, 8):
         yd, sd = moe.moe_decode(shp, layer.layer_w(), x[r0:r0 + 8].contiguous(), idx[r0:r0 + 8].contiguous(),
                                 w[r0:r0 + 8].contiguous(), ws)
         torch.cuda.synchronize()
-        assert_rows_close(yr[r0:r0 + 8].cpu().numpy(), yd.cpu().numpy(), TOL, frac=0.995, what="prefill vs decode yr")
-        assert_rows_close(ys[r0:r0 + 8].cpu().numpy(), sd.cpu().numpy(), TOL, frac=0.995, what="prefill vs decode ys")
+        assert_rows_close(yr[r0:r0 + 8].cpu().numpy(), yd.cpu().numpy(), TOL, what="prefill vs decode yr",
+                          pickmax=2 * pm[r0:r0 + 8], max_outliers=5e-3)
+        assert_rows_close(ys[r0:r0 + 8].cpu().numpy(), sd.cpu().numpy(), TOL, what="prefill vs decode ys",
+                          pickmax=2 * np.abs(sd.cpu().numpy()), max_outliers=5e-3)
 
 
 def test_expert_parallel_and_no_shared(orc):
@@ -153,3 +162,55 @@ def test_full_size_16384_tokens_properties(orc):
     for e in (hot, rare):
         rows += torch.nonzero((idx == e).any(dim=1)).flatten()[:3].tolist()
     _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=sorted(set(rows)))
+
+
+def test_ragged_batch_config5(orc):
+    """The mixed batch of the fifth benchmark configuration in ONE pass over the config-1 layer: 40 one-token decode rows, 16
+    speculative-verify requests of 2-6 rows and 8 prefill chunks of 512-4096 rows (the seeded mix bench.py --workload ragged
+    runs).  Rows of every request class are checked against the oracle, and the one-token rows also against the decode
+    path (same contract: what differs is explained by rounding flips of single outputs)."""
+    from dsgx10_b200 import moe, synth
+    from tests.util import assert_rows_close, oracle_fp8_layer
+    H, I, E, topk = 2048, 1024, 64, 6
+    rng = np.random.default_rng(20261102 + 5)
+    reqs = [1] * 40 + [int(v) for v in rng.integers(2, 7, 16)] + [int(v) for v in rng.integers(512, 4097, 8)]
+    T = sum(reqs)
+    starts = np.concatenate([[0], np.cumsum(reqs)])
+    shp, layer, x, wr, bias, idx, w = _setup(H, I, E, topk, T, seed=20261105)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    pick = np.random.default_rng(1)
+    rows = list(pick.choice(40, 4, replace=False))                                   # decode rows
+    rows += [int(starts[40 + j]) for j in pick.choice(16, 3, replace=False)]         # first row of three verify requests
+    rows += [int(starts[40 + 16 - 1 + 1] - 1)]                                       # last row of the last verify request
+    for j in range(8):                                                               # a row inside every prefill chunk
+        rows.append(int(starts[56 + j] + pick.integers(0, reqs[56 + j])))
+    rows += [T - 1]
+    _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=sorted(set(rows)))
+    # the 40 one-token rows through the decode path, eight at a time
+    first = np.arange(40)
+    _, _, pm = oracle_fp8_layer(orc, layer, synth.bf16_bits(x)[first], idx.cpu().numpy()[first], w.cpu().numpy()[first],
+                                with_shared=False, pickmax=True)
+    ws = moe.decode_ws(shp)
+    for r0 in range(0, 40, 8):
+        yd, sd = moe.moe_decode(shp, layer.layer_w(), x[r0:r0 + 8].contiguous(), idx[r0:r0 + 8].contiguous(),
+                                w[r0:r0 + 8].contiguous(), ws)
+        torch.cuda.synchronize()
+        assert_rows_close(yr[r0:r0 + 8].cpu().numpy(), yd.cpu().numpy(), TOL, what="ragged batch vs decode yr",
+                          pickmax=2 * pm[r0:r0 + 8], max_outliers=5e-3)
+        assert_rows_close(ys[r0:r0 + 8].cpu().numpy(), sd.cpu().numpy(), TOL, what="ragged batch vs decode ys",
+                          pickmax=2 * np.abs(sd.cpu().numpy()), max_outliers=5e-3)
+
+
+def test_512_experts(orc):
+    """The largest expert count the interface accepts (the tile table has E + 1 entries: one more than threads build it)."""
+    from dsgx10_b200 import moe
+    T = 700
+    shp, layer, x, wr, bias, idx, w = _setup(256, 256, 512, 8, T, seed=290)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=np.arange(0, T, 23))

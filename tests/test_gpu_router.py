@@ -23,6 +23,9 @@ CASES = [
     (1280, 40, 3, 4, 2, 1, 1.0, 7),
     (1024, 512, 8, 16, 4, 0, 1.0, 2),     # the largest expert count, a CTA a row
     (1024, 512, 8, 8, 3, 1, 1.0, 33),     # the same through the warp-a-row kernel
+    (5120, 384, 6, 1, 1, 2, 1.5, 4),      # ds41f's router: sqrt(softplus) scores, top-6 of 384, a CTA a row
+    (5120, 384, 6, 1, 1, 2, 1.5, 40),     # the same through the warp-a-row kernel
+    (2048, 64, 6, 1, 1, 2, 1.0, 1),
 ]
 
 
@@ -89,3 +92,20 @@ def test_sort_pack_bit_exact(orc, T, E, topk):
     want = orc.sort_pack(idx, E)
     for k in want:
         assert (got[k].cpu().numpy().reshape(want[k].shape) == want[k]).all(), k
+
+
+def test_finalize_both_modes():
+    """dsgx_finalize: mode 0 rounds the f32 sum once (the CPU references' order); mode 1 is the engine's
+    bf16(bf16(R) + bf16(S)) (altar1 engine/experts/decode.cu:591-598).  Bit-exact against the same arithmetic in torch."""
+    from dsgx10_b200 import moe
+    g = torch.Generator().manual_seed(77)
+    R = (torch.randn(5, 1024, generator=g) * 3).cuda()
+    S = torch.randn(5, 1024, generator=g).cuda()
+    out0 = moe.finalize(R, S, mode=0)
+    out1 = moe.finalize(R, S, mode=1)
+    out_r = moe.finalize(R, None, mode=0)
+    torch.cuda.synchronize()
+    assert torch.equal(out0, (R + S).to(torch.bfloat16))
+    assert torch.equal(out1, (R.to(torch.bfloat16).float() + S.to(torch.bfloat16).float()).to(torch.bfloat16))
+    assert torch.equal(out_r, R.to(torch.bfloat16))
+    assert not torch.equal(out0, out1)   # (the two orders do differ on some elements of this input)
