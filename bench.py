@@ -22,7 +22,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-CFG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4, score_fn=0, fmt="fp8")
+CFG_BIG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4, score_fn=0, fmt="fp8")                  # config 2
+CFG = dict(CFG_BIG)
 CFG_INT4 = dict(H=6144, I=2048, E=168, topk=8, n_group=1, topk_group=1, score_fn=1, fmt="int4")   # config 3
 CFG_SMALL = dict(H=2048, I=1024, E=64, topk=6, n_group=1, topk_group=1, score_fn=0, fmt="fp8")      # config 1
 
@@ -96,11 +97,13 @@ def step_bytes(rows_union, rows):
     return (rows_union + 1) * expert + E * H * 4 + rows * H * 2 * 2
 
 
-def up_bytes(rows_union):
+def up_bytes(n_routed, shared_frac=1.0):
+    """Algorithmic bytes of a gate/up launch: n_routed picked experts and shared_frac of the shared expert (two matrices
+    and their scales each)."""
     H, I = CFG["H"], CFG["I"]
     if CFG["fmt"] == "int4":
-        return rows_union * 2 * I * H * 2368 // 4096 + 2 * I * H * 2
-    return (rows_union + 1) * (2 * I * H + 2 * (I // 128) * (H // 128) * 4)
+        return n_routed * (2 * I * H * 2368 // 4096) + shared_frac * 2 * I * H * 2
+    return (n_routed + shared_frac) * (2 * I * H + 2 * (I // 128) * (H // 128) * 4)
 
 
 # --------------------------------------------------------------------------------------------------------- CPU arm
@@ -167,11 +170,10 @@ def run_reference(args):
 
 # --------------------------------------------------------------------------------------------------------- GPU arm
 
-def run_gpu(args):
+def dist_setup():
+    """(world, rank, local rank, device); the process group is created once, on the first call."""
     import torch
     import torch.distributed as dist
-    from dsgx10_b200 import _lib, moe, synth
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -179,23 +181,63 @@ def run_gpu(args):
         raise SystemExit("bench.py: no CUDA device; this library has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
+    return world, rank, local, dev
+
+
+def shared_part(rank, world, I):
+    """The shared expert's intermediate channels of a rank: parts of whole 512-channel pieces, one a rank while they last."""
+    if world == 1:
+        return 0, I
+    n = max(512, (I // world + 511) // 512 * 512)
+    lo = rank * n
+    return (lo, min(I, lo + n)) if lo < I else None
+
+
+def parity_rule(got, want, pm):
+    """The tests' rule on one step's rounded rows: within 2e-3 of the row maximum; what is left beyond that must be one
+    bf16 rounding flip of one added output (pm) or of the final rounding.  Returns (ok, max error, elements beyond 2e-3)."""
+    import numpy as np
+    got, want, pm = (np.asarray(a, np.float64) for a in (got, want, pm))
+    den = np.abs(want).max(axis=1, keepdims=True)
+    den = np.where(den == 0, 1.0, den)
+    diff = np.abs(got - want)
+    ulp = lambda v: 2.0 ** (np.floor(np.log2(np.maximum(np.abs(v), 2.0 ** -126))) - 7)
+    allow = 2e-3 * den + ulp(pm) + ulp(want)
+    beyond = int((diff > 2e-3 * den).sum())
+    return bool((diff <= allow).all() and beyond <= max(1, int(0.02 * diff.size))), float((diff / den).max()), beyond
+
+
+def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
+    """One decode workload (the shapes in CFG) on this rank's GPU; returns rank 0's result line (None on other ranks)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from dsgx10_b200 import _lib, moe, synth
+
+    world, rank, local, dev = dist_setup()
     _lib.lib()
+    rows = args.rows if rows is None else rows
+    n_steps = args.steps if steps is None else steps
 
     H, I, E, topk = CFG["H"], CFG["I"], CFG["E"], CFG["topk"]
-    rows = args.rows
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     int4 = CFG["fmt"] == "int4"
+    # several GPUs: contiguous expert ranges; an FP8 layer's shared expert is cut into parts of its intermediate channels,
+    # one a rank (the INT4 layers' bf16 shared expert stays whole, on rank 0)
+    part = (0, I) if world == 1 else (shared_part(rank, world, I) if not int4 else ((0, I) if rank == 0 else None))
     shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4 if int4 else _lib.FMT_FP8, n_group=CFG["n_group"],
-                    topk_group=CFG["topk_group"], score_fn=CFG["score_fn"], e_lo=e_lo, e_hi=e_hi)
+                    topk_group=CFG["topk_group"], score_fn=CFG["score_fn"], e_lo=e_lo, e_hi=e_hi,
+                    sh_lo=part[0] if (part and world > 1 and not int4) else 0,
+                    sh_hi=part[1] if (part and world > 1 and not int4) else 0)
     NL, NX = args.layers, 16
     layers, steps_buf = [], []
     for l in range(NL):
         if int4:
-            lay = synth.Int4Layer.on_device(H, I, E, SEED + 7919 * l, dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+            lay = synth.Int4Layer.on_device(H, I, E, SEED + 7919 * l, dev, shared=part is not None, e_range=(e_lo, e_hi))
         else:
-            lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+            lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=part is not None, e_range=(e_lo, e_hi))
         wr = synth.router_weights(E, H, SEED + 2000 + l, device="cpu").to(dev)
         layers.append((lay, lay.layer_w()))
         steps_buf.append(moe.LayerStep(shp, wr, None, device=dev, fused=False if args.separate else True if args.fused else None))
@@ -208,8 +250,8 @@ def run_gpu(args):
     peer = None
     if world > 1 and not args.nccl:
         from dsgx10_b200 import ep
-        peer = ep.PeerReduce(H, shared_rank=0)
-        args.steps += args.steps & 1
+        peer = ep.PeerReduce(H, shared_rank=0 if int4 else -2)
+        n_steps += n_steps & 1
 
     def step(i, host=False):
         lay, lw = layers[i % NL]
@@ -217,9 +259,8 @@ def run_gpu(args):
         if world == 1:
             if host:
                 sb.run_host(lw, xs_host[i % NX], out_host)
-            else:
-                sb.run(lw, xs[i % NX])
-            return
+                return out_host
+            return sb.run(lw, xs[i % NX])
         x = xs[i % NX]
         if host and peer is None:
             sb.x_stage[:rows].copy_(xs_host[i % NX], non_blocking=True)
@@ -228,21 +269,20 @@ def run_gpu(args):
             yr_p, ys_p = peer.parts(peer.launched + 1)
             if host:  # host buffers in place: copy-in kernel, partial sums, then the reduction writes the pinned rows
                 sb.run_host(lw, xs_host[i % NX], None, yr=yr_p, ys=ys_p)
-                peer.finalize(rows, out=out_host)
-            else:
-                sb.run(lw, x, finalize=False, yr=yr_p, ys=ys_p)
-                peer.finalize(rows)
-            return
+                return peer.finalize(rows, out=out_host)
+            sb.run(lw, x, finalize=False, yr=yr_p, ys=ys_p)
+            return peer.finalize(rows)
         sb.run(lw, x, finalize=False)
         red[0].copy_(sb.yr)
-        if rank == 0:
+        if part is not None:
             red[1].copy_(sb.ys)
         else:
             red[1].zero_()
         dist.all_reduce(red)
-        out = moe.finalize(red[0, :rows], red[1, :rows])
+        out = moe.finalize(red[0, :rows], red[1, :rows].to(torch.bfloat16).float())
         if host:
             out_host.copy_(out, non_blocking=True)
+        return out
 
     def barrier():
         if world > 1:
@@ -286,11 +326,11 @@ def run_gpu(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = timed(lambda i: step(i), args.steps)
+    ms = timed(lambda i: step(i), n_steps)
     # end to end: host buffers in, host buffer out, copies inside the timed region
-    for i in range(3):
+    for i in range(4):
         step(i, host=True)
-    ms_e2e = timed(lambda i: step(i, host=True), args.steps)
+    ms_e2e = timed(lambda i: step(i, host=True), n_steps)
 
     # the dominant kernel (gate/up stream) alone, for the roofline: same cold-weight rotation
     union = []
@@ -304,63 +344,91 @@ def run_gpu(args):
         lay, lw = layers[i % NL]
         sb = steps_buf[i % NL]
         moe.moe_decode(shp, lw, xs[i % NX], sb.idx, sb.w, sb.ws, sb.yr, sb.ys, parts=parts)
-    for i in range(NL):
-        up_only(i, parts=1)
-    for i in range(3):
-        up_only(i)
-    ms_up = timed(up_only, args.steps)
+    ms_up = None
+    if with_kernel:
+        for i in range(NL):
+            up_only(i, parts=1)
+        for i in range(3):
+            up_only(i)
+        ms_up = timed(up_only, n_steps)
     clocks = sampler.stop() if rank == 0 else None
     status = max(moe.ws_status(sb.ws) for sb in steps_buf)
     if peer is not None:
         status = max(status, int(peer.status.item()))
 
-    if rank != 0:
+    # ---- one step's rounded rows against the CPU oracle (outside every timed region; the oracle is only the checker):
+    # every rank runs the oracle over its own experts, the partial sums are added across the ranks
+    parity = None
+    if not int4 and not args.no_parity:
+        from oracle import oracle as orc
+        got = step(0)
+        torch.cuda.synchronize()
+        got = got.float().cpu().numpy()
+        sb, lay = steps_buf[0], layers[0][0]
+        idx_np, w_np = sb.idx[:rows].cpu().numpy(), sb.w[:rows].cpu().numpy()
+        mine = {int(e): lay.canonical(int(e)) for e in np.unique(idx_np) if e_lo <= e < e_hi}
+        if not mine:
+            mine = {e_lo: lay.canonical(e_lo)}   # (an expert no row picked: it gives the shapes, nothing is computed)
+        sh = lay.canonical(E) if rank == 0 else None
+        acc, _, pm = orc.moe_fp8_layer(synth.bf16_bits(xs[0]), idx_np, w_np, mine, sh, e_lo=e_lo, e_hi=e_hi,
+                                       with_shared=rank == 0, pickmax=True)
+        acc_t, pm_t = torch.from_numpy(acc).to(dev), torch.from_numpy(pm).to(dev)
         if world > 1:
-            dist.destroy_process_group()
-        return
+            dist.all_reduce(acc_t)
+            dist.all_reduce(pm_t, op=dist.ReduceOp.MAX)
+        ok, err, beyond = parity_rule(got, acc_t.cpu().numpy(), pm_t.cpu().numpy())
+        parity = {"ok": ok, "max_err_of_row_max": err, "elements_beyond_2e-3": beyond, "rows": rows,
+                  "against": "the CPU oracle on the picked experts (every rank its own, partial sums added)"}
+
+    if rank != 0:
+        return None
     peaks, peak_kind = measured_peaks()
-    us = ms * 1e3 / args.steps
-    us_e2e = ms_e2e * 1e3 / args.steps
-    us_up = ms_up * 1e3 / args.steps
+    us = ms * 1e3 / n_steps
+    us_e2e = ms_e2e * 1e3 / n_steps
     # distinct experts a step touches (all ranks): from the routed ids of the last steps (all ranks route identically)
     tot_union = sum(len(set(sb.idx[:rows].flatten().tolist())) for sb in steps_buf) / NL
     sb_bytes = step_bytes(tot_union, rows)
-    upb = sum(up_bytes(u - (0 if rank == 0 else 1)) for u in union) / NL  # rank 0 also streams the shared expert
-    ach = upb / (us_up * 1e-6) / 1e9
     line = {
-        "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": world, "steps": args.steps,
+        "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": world, "steps": n_steps,
         "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "int4-g32 weights, bf16 activations (f32 accumulate)" if int4 else "fp8_e4m3 (f32 accumulate)",
         "data": "synthetic",
         "config": {"workload": workload_name(rows), "rows": rows,
                    "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
-                                                   " (partial sums reduced over peer memory by k_finalize_peers)"), "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
+                                                   " (partial sums reduced over peer memory by k_finalize_peers; the shared "
+                                                   "expert in parts across the ranks)"),
+                   "cold_weights": f"{NL} layers x 16 activations cycled; inputs larger than L2",
                    "launch": "eager" if args.eager else "one CUDA graph of the timed steps"},
         "tokens_per_s": rows / (us * 1e-6),
         "step_hbm_gbs": sb_bytes / (us * 1e-6) / 1e9,
         "step_frac_of_measured_hbm": sb_bytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
         "step_frac_of_8tbs": sb_bytes / (us * 1e-6) / 1e9 / 8000.0,
         "step_algorithmic_bytes": sb_bytes,
-        "roofline": {"bound": "hbm", "kernel": ("k_up_i4 (+ activation staging launch)" if int4 else "k_up_fp8"), "achieved": ach,
-                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": peak_kind,
-                     "us_per_launch": us_up, "algorithmic_bytes": upb,
-                     # one ncu capture of this kernel (its summary is among the committed profiles): 151.14 MB read +
-                     # 3.91 MB written for 151.03 MB algorithmic; the traffic grows with the experts a launch streams
-                     "traffic": None if int4 else upb * (151.142912 + 3.909120) / 151.031808,
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "
-                                       "this launch's algorithmic bytes"},
         "e2e": {"value": us_e2e, "unit": "us", "h2d_bytes_per_step": rows * H * 2, "d2h_bytes_per_step": rows * H * 2},
-        # this library's kernels a step: the one persistent kernel from three rows (or --fused), else front (logits, routing,
-        # slot table), gate/up, down; with several GPUs also the reduction kernel
-        "gpu_launches": args.steps * ((1 if (args.fused or (rows >= 3 and not args.separate and not int4)) else 3) + (1 if world > 1 else 0)),
+        # this library's kernels a step: the one persistent kernel from three rows (or --fused), else front, routing, gate/up,
+        # down; with several GPUs also the reduction kernel
+        "gpu_launches": n_steps * ((1 if (args.fused or (rows >= 3 and not args.separate and not int4 and world == 1)) else 4)
+                                   + (1 if world > 1 else 0)),
         "clocks": clocks,
         "device_status": status,
+        "parity": parity,
     }
-    if not args.no_cpu_baseline and world == 1 and not int4:
+    if ms_up is not None:
+        us_up = ms_up * 1e3 / n_steps
+        sh_frac = ((part[1] - part[0]) / I) if part else 0.0
+        upb = sum(up_bytes(u, sh_frac) for u in union) / NL  # this rank's picked experts + its part of the shared one
+        ach = upb / (us_up * 1e-6) / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": ("k_up_i4 (+ activation staging launch)" if int4 else "k_up_fp8"),
+                            "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                            "peak_kind": peak_kind, "us_per_launch": us_up, "algorithmic_bytes": upb,
+                            # one ncu capture of this kernel (its summary is among the committed profiles): 151.14 MB read +
+                            # 3.91 MB written for 151.03 MB algorithmic; the traffic grows with the experts a launch streams
+                            "traffic": None if int4 else upb * (151.142912 + 3.909120) / 151.031808,
+                            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "
+                                              "this launch's algorithmic bytes"}
+    if with_cpu and not args.no_cpu_baseline and world == 1 and not int4:
         line["cpu_baseline"] = cpu_baseline(rows, workload=args.workload)
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 # ------------------------------------------------------------------------------------------- prefill workload (GPU)
@@ -415,27 +483,22 @@ def run_prefill_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def run_prefill(args):
+def run_prefill(args, workload=None, steps=None, with_cpu=True):
     """Config 4: one layer's prefill over `--tokens` tokens whose expert popularity follows Zipf(1.1) (a router bias
-    calibrated so that the realised pick histogram matches), experts sharded over the ranks, partial sums all-reduced."""
+    calibrated so that the realised pick histogram matches), experts sharded over the ranks, partial sums reduced over
+    peer memory.  Config 5 (`ragged`): the mixed batch through the same pass.  Returns rank 0's result line."""
     import numpy as np
     import torch
     import torch.distributed as dist
     from dsgx10_b200 import _lib, moe, synth
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; this library has no CPU path (use --impl reference for the CPU arm)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, local, dev = dist_setup()
     _lib.lib()
+    workload = args.workload if workload is None else workload
+    n_steps = args.steps if steps is None else steps
     H, I, E, topk = PF["H"], PF["I"], PF["E"], PF["topk"]
     T = args.tokens
-    ragged = args.workload == "ragged"
+    ragged = workload == "ragged"
     if ragged:  # config 5: 64 requests packed into one token-sorted pass: 40 decode rows, 16 verify rows, 8 prefill chunks
         rng = np.random.default_rng(SEED + 5)
         reqs = [1] * 40 + [int(v) for v in rng.integers(2, 7, 16)] + [int(v) for v in rng.integers(512, 4097, 8)]
@@ -484,12 +547,13 @@ def run_prefill(args):
             yr_p, _ = peer.parts(peer.launched + 1)
             pl.run(xs[i % NX], idx, w, yr=yr_p, ys=False, out=False, ysum=True)
             peer.finalize(T, out=None if peer.sliced else out)   # (sliced: the rounded rows land in peer.out on every rank)
-            return
+            return peer.out if peer.sliced else out
         # one GPU: only the rounded rows; several: the f32 partial sums for the reduction
         pl.run(xs[i % NX], idx, w, yr=yr if world > 1 else False, ys=ys if world > 1 else False, out=out, ysum=world > 1)
         if world > 1:  # rank 0's partial sums hold the shared expert's output too: one buffer to reduce
             dist.all_reduce(yr)
             out.copy_(moe.finalize(yr))
+        return out
 
     # end to end: host activations in, router, experts, host bf16 out; the pass is cut into chunks of tokens that go
     # round two streams (each with its own workspace), so that the copies of one chunk overlap the kernels of another
@@ -546,23 +610,43 @@ def run_prefill(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms = timed(experts, args.steps)
+    ms = timed(experts, n_steps)
     for i in range(3):
         whole(i)
-    ms_e2e = timed(whole, args.steps)
+    ms_e2e = timed(whole, max(2, n_steps // 2))
     # the dominant kernel alone: the routed gate/up grouped GEMM over the operands the last pass left in the workspace
-    idx, w = routed[(args.steps - 1) % NX]
-    pl.run(xs[(args.steps - 1) % NX], idx, w, yr=yr, ys=ys, out=out)
+    idx, w = routed[(n_steps - 1) % NX]
+    pl.run(xs[(n_steps - 1) % NX], idx, w, yr=yr, ys=ys, out=out)
     up = lambda i: pl.run(xs[0], idx, w, yr=yr, ys=ys, out=out, parts=1)
     for i in range(3):
         up(i)
-    ms_up = timed(up, args.steps)
+    ms_up = timed(up, n_steps)
     clocks = sampler.stop() if rank == 0 else None
     status = moe.ws_status(pl.ws)
-    if rank != 0:
+    # ---- sampled rows of one pass against the CPU oracle (outside the timed regions; the oracle is only the checker)
+    parity = None
+    if not args.no_parity:
+        from oracle import oracle as orc
+        idx0, w0 = routed[0]
+        got = experts(0)
+        torch.cuda.synchronize()
+        rows_s = np.unique(np.concatenate([[0, T - 1], np.random.default_rng(3).integers(0, T, 14)]))
+        got = got[torch.from_numpy(rows_s).to(dev)].float().cpu().numpy()
+        idx_np, w_np = idx0.cpu().numpy()[rows_s], w0.cpu().numpy()[rows_s]
+        mine = {int(e): lay.canonical(int(e)) for e in np.unique(idx_np) if e_lo <= e < e_hi}
+        if not mine:
+            mine = {e_lo: lay.canonical(e_lo)}
+        acc, _, pm = orc.moe_fp8_layer(synth.bf16_bits(xs[0])[rows_s], idx_np, w_np, mine, lay.canonical(E) if rank == 0 else None,
+                                       e_lo=e_lo, e_hi=e_hi, with_shared=rank == 0, pickmax=True)
+        acc_t, pm_t = torch.from_numpy(acc).to(dev), torch.from_numpy(pm).to(dev)
         if world > 1:
-            dist.destroy_process_group()
-        return
+            dist.all_reduce(acc_t)
+            dist.all_reduce(pm_t, op=dist.ReduceOp.MAX)
+        ok, err, beyond = parity_rule(got, acc_t.cpu().numpy(), pm_t.cpu().numpy())
+        parity = {"ok": ok, "max_err_of_row_max": err, "elements_beyond_2e-3": beyond, "rows": int(len(rows_s)),
+                  "against": "the CPU oracle on sampled rows (every rank its own experts, partial sums added)"}
+    if rank != 0:
+        return None
     peaks, peak_kind = measured_peaks()
     local_picks = int(counts[e_lo:e_hi].sum())
     fl_up = local_picks * 2 * H * I * 2
@@ -572,7 +656,7 @@ def run_prefill(args):
     tf_e2e = prefill_flops(T) / (ms_e2e * 1e-3) / 1e12
     c = np.sort(counts)[::-1]
     line = {
-        "metric": "moe_prefill_grouped_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "metric": "moe_prefill_grouped_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": n_steps,
         "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3 (f32 accumulate)", "data": "synthetic",
         "config": {"workload": (f"config 5: ragged batch of 64 requests (40 x 1, 16 x 2-6, 8 x 512-4096 tokens) in one pass, "
@@ -593,15 +677,14 @@ def run_prefill(args):
                      "traffic": None},
         "e2e": {"value": tf_e2e, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": T * H * 2,
                 "d2h_bytes_per_step": T * H * 2},
-        "gpu_launches": args.steps * (11 + (1 if world > 1 else 0)),
+        "gpu_launches": n_steps * (11 + (1 if world > 1 else 0)),
         "clocks": clocks,
         "device_status": status,
+        "parity": parity,
     }
-    if not args.no_cpu_baseline and world == 1:
+    if with_cpu and not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(1, workload="prefill")
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 def cpu_baseline(rows, workload="decode"):
@@ -630,31 +713,90 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="prefill end to end: chunks of tokens the pass is cut into")
     ap.add_argument("--layers", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
-    ap.add_argument("--nccl", action="store_true", help="several GPUs: reduce with an NCCL all-reduce instead of the peer kernel")
-    ap.add_argument("--separate", action="store_true", help="always run the step as four kernels")
-    ap.add_argument("--fused", action="store_true", help="always run the step as the one persistent kernel")
-    ap.add_argument("--experts", type=int, default=0,
-                    help="profiling only: a layer with fewer routed experts (same matrices), to keep an ncu capture small")
+    dv = ap.add_argument_group("development switches (profiling and A/B runs; none belongs to the benchmark contract)")
+    dv.add_argument("--eager", action="store_true", help="no CUDA graph: launch every kernel from the host")
+    dv.add_argument("--nccl", action="store_true", help="several GPUs: reduce with an NCCL all-reduce instead of the peer kernel")
+    dv.add_argument("--separate", action="store_true", help="always run the step as four kernels")
+    dv.add_argument("--fused", action="store_true", help="always run the step as the one persistent kernel")
+    dv.add_argument("--experts", type=int, default=0,
+                    help="a layer with fewer routed experts (same matrices), to keep an ncu capture small")
+    ap.add_argument("--no-parity", action="store_true", help="skip the check of one step's rows against the CPU oracle")
+    ap.add_argument("--no-others", action="store_true",
+                    help="the headline workload only (default: the other configurations follow, briefly, as sub-records)")
     args = ap.parse_args()
-    if args.experts:
-        CFG["E"] = args.experts
-    if args.workload == "decode1":  # config 1: the same decode bench over the small FP8 layer
-        CFG.update(CFG_SMALL)
-        if args.layers == 3:
-            args.layers = 12  # 12 x 50 MB of picked experts between reuses: larger than L2
-    if args.workload == "int4":  # config 3: the same decode bench over an INT4-g32 layer
-        CFG.update(CFG_INT4)
-        if args.layers == 3:
-            args.layers = 2
-    if args.workload in ("prefill", "ragged"):
-        if args.steps == 200:
-            args.steps = 20
-        run_prefill_reference(args) if args.impl == "reference" else run_prefill(args)
-    elif args.impl == "reference":
-        run_reference(args)
-    else:
-        run_gpu(args)
+
+    def select(workload):
+        """CFG and the layer count of a decode workload."""
+        CFG.update(CFG_BIG)
+        layers = args.layers
+        if workload == "decode1":  # config 1: the same decode bench over the small FP8 layer
+            CFG.update(CFG_SMALL)
+            layers = 12 if args.layers == 3 else args.layers  # 12 x 50 MB of picked experts between reuses: larger than L2
+        if workload == "int4":  # config 3: the same decode bench over an INT4-g32 layer
+            CFG.update(CFG_INT4)
+            layers = 2 if args.layers == 3 else args.layers
+        if args.experts:
+            CFG["E"] = args.experts
+        return layers
+
+    if args.workload in ("prefill", "ragged") and args.steps == 200:
+        args.steps = 20
+    if args.impl == "reference":
+        args.layers = select(args.workload)
+        run_prefill_reference(args) if args.workload in ("prefill", "ragged") else run_reference(args)
+        return
+
+    import copy
+    import gc
+
+    def one(workload, rows, steps, brief):
+        """A workload's line; brief: a sub-record (fewer steps, no CPU leg), cut down to its figures."""
+        import torch
+        a = copy.copy(args)
+        a.workload = workload
+        if workload in ("prefill", "ragged"):
+            line = run_prefill(a, workload=workload, steps=steps, with_cpu=not brief)
+        else:
+            a.layers = select(workload)
+            line = run_gpu(a, rows=rows, steps=steps, with_kernel=True, with_cpu=not brief)
+        gc.collect()
+        torch.cuda.empty_cache()
+        if line is None or not brief:
+            return line
+        keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "tokens_per_s", "step_frac_of_measured_hbm",
+                                     "device_status", "parity") if k in line}
+        keep["workload"] = line["config"]["workload"]
+        keep["e2e"] = line["e2e"]["value"]
+        if "roofline" in line:
+            keep["roofline"] = {k: line["roofline"][k] for k in ("kernel", "achieved", "unit", "frac", "us_per_launch")}
+        keep["clocks"] = line["clocks"]
+        return keep
+
+    head = one(args.workload, args.rows, args.steps, brief=False)
+    others = {}
+    default_run = args.workload == "decode" and args.rows == 1 and not (args.no_others or args.eager or args.experts
+                                                                        or args.separate or args.fused or args.nccl)
+    if default_run:
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        plan = [("config2_rows8", "decode", 8, 30)]
+        if world == 1:
+            plan += [("config1_rows1", "decode1", 1, 60), ("config3_int4_rows1", "int4", 1, 30),
+                     ("config3_int4_rows4", "int4", 4, 20), ("config4_prefill_16384", "prefill", 1, 6),
+                     ("config5_ragged_batch", "ragged", 1, 6)]
+        else:
+            plan += [("config4_prefill_16384", "prefill", 1, 6)]
+        for name, wl, rows, steps in plan:
+            try:
+                others[name] = one(wl, rows, steps, brief=True)
+            except Exception as ex:  # a sub-record that fails is reported, the headline stands
+                others[name] = {"error": f"{type(ex).__name__}: {ex}"[:300]}
+    if head is not None:
+        if others:
+            head["others"] = others
+        print(json.dumps(head), flush=True)
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -75,6 +75,30 @@ def _worker(rank, world, port, q):
             dist.all_gather(both, got)
             peer_same = peer_same and bool(torch.equal(both[0], both[1]))
         res["peer_ok"], res["peer_same"], res["peer_status"] = peer_ok, peer_same, int(pr.status.item())
+        # the shared expert in parts: each rank computes half of its intermediate channels, its ys is an unrounded partial
+        # sum; the reduction adds the parts in rank order, rounds that sum to bf16 once and adds it to the sum of yr
+        I2 = 1024
+        full2 = synth.Fp8Layer(H, I2, E, 320, device=dev)
+        ref2 = moe.LayerStep(moe.shape(H, I2, E, topk), wr, device=dev)
+        st2 = moe.LayerStep(moe.shape(H, I2, E, topk, e_lo=lo, e_hi=hi, sh_lo=rank * 512, sh_hi=(rank + 1) * 512), wr, device=dev)
+        pr2 = ep.PeerReduce(H, shared_rank=-2)
+        parts_ok, parts_close = True, 0.0
+        for step_no in range(1, 4):
+            xs = synth.activations(2 + step_no, H, 330 + step_no).to(dev)
+            M = xs.shape[0]
+            want_one = ref2.run(full2.layer_w(), xs).clone()
+            yr_p, ys_p = pr2.parts(pr2.launched + 1)
+            st2.run(full2.layer_w(), xs, finalize=False, yr=yr_p, ys=ys_p)
+            mine_parts = torch.stack([yr_p[:M], ys_p[:M]]).clone()
+            got = pr2.finalize(M).clone()
+            gathered = [torch.empty_like(mine_parts) for _ in range(world)]
+            dist.all_gather(gathered, mine_parts)
+            want = moe.finalize(gathered[0][0] + gathered[1][0], (gathered[0][1] + gathered[1][1]).to(torch.bfloat16).float())
+            torch.cuda.synchronize()
+            parts_ok = parts_ok and bool(torch.equal(got, want))
+            den = want_one.float().abs().amax(dim=1, keepdim=True)
+            parts_close = max(parts_close, float(((got.float() - want_one.float()).abs() / den).max()))
+        res["parts_ok"], res["parts_close"], res["parts_status"] = parts_ok, parts_close, max(int(pr2.status.item()), moe.ws_status(st2.ws))
         # the same kernel over a prefill's rows (its many-CTA form): f32 partial sums of 600 rows, no shared-expert term
         prw = ep.PeerReduce(H, rows_cap=600, shared_rank=-1)
         wide_ok = True
@@ -143,5 +167,7 @@ def test_two_gpus_match_one():
         assert res["decode_yr"] <= 1e-6 and res["decode_ys"] == 0.0, res    # only the association of the f32 adds differs
         assert res["prefill"] <= 1e-6, res
         assert res["peer_ok"] and res["peer_same"] and res["peer_status"] == 0, res
+        assert res["parts_ok"] and res["parts_status"] == 0, res
+        assert res["parts_close"] <= 2e-3 + 2 ** -7, res     # against one GPU: a bf16 rounding flip of the output at most
         assert res["peer_wide_ok"] and res["peer_wide_status"] == 0, res
         assert res["peer_sliced_ok"] and res["peer_sliced_status"] == 0, res
