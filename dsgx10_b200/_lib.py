@@ -10,6 +10,7 @@ OK, ERR_ARG, ERR_FORMAT, ERR_SHAPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED, 
 FMT_NVFP4, FMT_RETIRED, FMT_INT4, FMT_BF16, FMT_FP8 = range(5)
 SCORE_SIGMOID, SCORE_SOFTMAX, SCORE_SQRTSOFTPLUS = 0, 1, 2
 MAX_ROWS = 8
+PH_BUCKET, PH_UP, PH_DOWN, PH_COMBINE, PH_SHARED, PH_ALL = 1, 2, 4, 8, 16, 31
 
 
 class MatDesc(C.Structure):
@@ -17,7 +18,7 @@ class MatDesc(C.Structure):
 
 
 class SharedW(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("g", "u", "d", "gs", "us", "ds", "bg", "bu", "bd")]
+    _fields_ = [(n, C.c_void_p) for n in ("g", "u", "d", "gs", "us", "ds", "bg", "bu", "bd", "bgu")]
 
 
 class LayerW(C.Structure):
@@ -37,9 +38,14 @@ class PeerSet(C.Structure):
                 ("outs", C.c_void_p), ("done", C.c_void_p)]
 
 
+class PrefillView(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("counts", "offsets", "perm_tok", "perm_slot", "pos_of", "row_order", "hq", "hs",
+                                          "hq_shared", "hs_shared")]
+
+
 class DecodeCfg(C.Structure):
     _fields_ = [("ysum", C.c_int32), ("pdl", C.c_int32), ("parts", C.c_int32), ("up", C.c_int32),
-                ("down", C.c_int32), ("reserved", C.c_int32 * 3)]
+                ("down", C.c_int32), ("reserved", C.c_int32 * 3), ("logits", C.c_void_p), ("bias", C.c_void_p)]
 
 
 class LayerStep(C.Structure):
@@ -68,6 +74,13 @@ SYMBOLS = {
     "dsgx_prefill_prepare": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V]),
     "dsgx_prefill_ws_bytes": (_Z, [C.POINTER(MoeShape), _I]),
     "dsgx_moe_prefill": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _V, _I, _V, _V, _V, _V, _I, _V]),
+    "dsgx_moe_prefill_phases": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _V, _I, _V, _V, _V, _V, _I, _I, _V]),
+    "dsgx_prefill_view_of": (_I, [C.POINTER(MoeShape), _V, _I, _V]),
+    "dsgx_decode_up_variants": (_I, []),
+    "dsgx_decode_down_variants": (_I, []),
+    "dsgx_decode_up_name": (C.c_char_p, [_I]),
+    "dsgx_decode_down_name": (C.c_char_p, [_I]),
+    "dsgx_sort_static_status": (_I, []),
     "dsgx_ws_status": (_I, [_V]),
 }
 

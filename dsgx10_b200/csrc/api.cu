@@ -43,6 +43,7 @@ size_t decode_ws_bytes(int H, int I) {
   n += al256(sizeof(StepSync));
   n += al256((size_t)kPartUnits * kMaxPieces * 128 * 4);
   n += al256((size_t)kPartUnits * 4);
+  n += 512;
   return n;
 }
 DecodeWs decode_ws_carve(void* ws, int H, int I) {
@@ -60,7 +61,8 @@ DecodeWs decode_ws_carve(void* ws, int H, int I) {
   w.lpart = reinterpret_cast<float*>(p), p += al256((size_t)((H + 1023) / 1024) * kMaxRows * 512 * 4);
   w.sync = reinterpret_cast<StepSync*>(p), p += al256(sizeof(StepSync));
   w.part = reinterpret_cast<float*>(p), p += al256((size_t)kPartUnits * kMaxPieces * 128 * 4);
-  w.cnt_u = reinterpret_cast<int*>(p);
+  w.cnt_u = reinterpret_cast<int*>(p), p += al256((size_t)kPartUnits * 4);
+  w.r_idx = reinterpret_cast<int*>(p), w.r_w = reinterpret_cast<float*>(p + 256);
   return w;
 }
 
@@ -191,46 +193,48 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
                     int M, void* ws, float* yr, float* ys, void* stream, const dsgx_decode_cfg* cfg) {
   const int rc = check_shape(s);
   if (rc) return rc;
-  if (!L || !x || !idx || !w || !ws || !yr) return DSGX_ERR_ARG;
+  const dsgx_decode_cfg dflt = {0, 1, 0, 0, 0, {0, 0, 0}, nullptr, nullptr};
+  if (!cfg) cfg = &dflt;
+  const bool own_route = cfg->logits != nullptr;  // the step routes on the caller's logits: idx / w are not read
+  if (!L || !x || (!own_route && (!idx || !w)) || !ws || !yr) return DSGX_ERR_ARG;
   if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
   if (L->fmt != s->fmt) return DSGX_ERR_FORMAT;
+  RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
   if (!L->pool || !L->desc) return DSGX_ERR_ARG;
   if (((uintptr_t)L->pool & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh8 = L->sh.g != nullptr;
   if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds)) return DSGX_ERR_ARG;
-  const dsgx_decode_cfg dflt = {0, 1, 0, 0, 0, {0, 0, 0}};
-  if (!cfg) cfg = &dflt;
   if (s->fmt == DSGX_FMT_FP8) {
-    if (L->sh.bg || L->sh.bu || L->sh.bd) return DSGX_ERR_FORMAT;  // an FP8 layer's shared expert is FP8
+    if (L->sh.bg || L->sh.bu || L->sh.bd || L->sh.bgu) return DSGX_ERR_FORMAT;  // an FP8 layer's shared expert is FP8
     if (sh8 && !ys && !cfg->ysum) return DSGX_ERR_ARG;
     DecodeParams p;
     p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
     p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
-    p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
+    p.idx = own_route ? p.ws.r_idx : idx, p.w = own_route ? p.ws.r_w : w;
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr;
     p.up = cfg->up, p.down = cfg->down;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
-                                      cfg->parts == 0 ? 3 : cfg->parts);
+                                      cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
   }
   if (s->fmt == DSGX_FMT_INT4) {
     if (L->sh.g || L->sh.u || L->sh.d) return DSGX_ERR_FORMAT;  // an INT4 layer's shared expert is bf16
-    const bool shb = L->sh.bg != nullptr;
-    if (shb && (!L->sh.bu || !L->sh.bd)) return DSGX_ERR_ARG;
+    const bool shb = L->sh.bg != nullptr || L->sh.bgu != nullptr;
+    if (shb && (!L->sh.bd || (L->sh.bgu ? (L->sh.bg || L->sh.bu) : !L->sh.bu))) return DSGX_ERR_ARG;  // one of the two forms
     if (shb && !ys && !cfg->ysum) return DSGX_ERR_ARG;
     if (!decode_int4_fits(s->H, M)) return DSGX_ERR_SHAPE;
     DecodeParams p;
     p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
     p.pool = L->pool, p.desc = L->desc, p.sh = L->sh;
-    p.idx = idx, p.w = w;
     p.ws = decode_ws_carve(ws, s->H, s->I);
+    p.idx = own_route ? p.ws.r_idx : idx, p.w = own_route ? p.ws.r_w : w;
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
-                                       cfg->parts == 0 ? 3 : cfg->parts);
+                                       cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
   }
   return DSGX_ERR_UNSUPPORTED;
@@ -254,10 +258,10 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     if (((uintptr_t)L->pool & 255) || ((uintptr_t)st->ws & 255) || ((uintptr_t)x & 15) || ((uintptr_t)st->wr & 15))
       return DSGX_ERR_ARG;
     const bool fp8 = s->fmt == DSGX_FMT_FP8;
-    const bool sh8 = L->sh.g != nullptr, shb = L->sh.bg != nullptr;
+    const bool sh8 = L->sh.g != nullptr, shb = L->sh.bg != nullptr || L->sh.bgu != nullptr;
     if (fp8 ? shb : sh8) return DSGX_ERR_FORMAT;
     if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds || !st->ys)) return DSGX_ERR_ARG;
-    if (shb && (!L->sh.bu || !L->sh.bd || !st->ys)) return DSGX_ERR_ARG;
+    if (shb && (!L->sh.bd || !st->ys || (L->sh.bgu ? (L->sh.bg || L->sh.bu) : !L->sh.bu))) return DSGX_ERR_ARG;
     if (!fp8 && !decode_int4_fits(s->H, M)) return DSGX_ERR_SHAPE;
     DecodeParams p;
     p.H = s->H, p.I = s->I, p.E = s->E, p.topk = s->topk, p.M = M, p.e_lo = s->e_lo, p.e_hi = s->e_hi;
@@ -274,9 +278,10 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     // (measured): the routing chain is too long to hide behind the little work that needs no routing.
     // flags: bit 0 never the one kernel; bit 2 always; bit 3: route with two small kernels, experts in the one kernel.
     const bool sh_part = p.sh_lo != 0 || p.sh_hi != s->I;  // (a part of the shared expert: the separate kernels)
-    if (fp8 && !sh_part && !(st->flags & 1) && (M >= 3 || (st->flags & 12)) && step_fp8_fits(s->H, s->I, s->E, M)) {
+    if (fp8 && !sh_part && !(st->flags & 1) && (M >= 3 || (st->flags & 28)) && step_fp8_fits(s->H, s->I, s->E, M)) {
       StepParams sp;
       sp.pre_routed = (st->flags & 8) ? 1 : 0;
+      sp.test_no_table = (st->flags & 16) && !sp.pre_routed ? 1 : 0;
       if (sp.pre_routed) {
         cudaError_t e0 = launch_front_route_only(p, rp, xb, st->wr, st->bias, st->logits, st->idx, st->w, (cudaStream_t)stream, true);
         if (e0 != cudaSuccess) return cuda_fail(e0);
@@ -393,25 +398,55 @@ size_t dsgx_prefill_ws_bytes(const dsgx_moe_shape* s, int T) {
   return prefill_ws_bytes(T, s->H, s->I, s->E, s->topk);
 }
 
-int dsgx_moe_prefill(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* wbuf, const void* x, const int32_t* idx,
-                     const float* w, int T, void* ws, float* yr, float* ys, void* out, int ysum, void* stream) {
+int dsgx_moe_prefill_phases(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* wbuf, const void* x, const int32_t* idx,
+                            const float* w, int T, void* ws, float* yr, float* ys, void* out, int ysum, int phases,
+                            void* stream) {
   const int rc = check_prefill_shape(s);
   if (rc) return rc;
   if (!L || !wbuf || !x || !idx || !w || !ws || (!yr && !out) || T < 1) return DSGX_ERR_ARG;
+  if (phases < 1 || phases > DSGX_PH_ALL) return DSGX_ERR_ARG;
   if (((uintptr_t)wbuf & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh = L->sh.g != nullptr;
   if (sh && !ys && !(ysum & 1) && !out) return DSGX_ERR_ARG;
   if ((size_t)T * s->topk > (size_t)1 << 30) return DSGX_ERR_SHAPE;
   PrefillParams q;
-  q.T = T, q.H = s->H, q.I = s->I, q.E = s->E, q.topk = s->topk, q.has_shared = sh, q.ysum = ysum & 1, q.parts = (ysum >> 8) & 3;
+  q.T = T, q.H = s->H, q.I = s->I, q.E = s->E, q.topk = s->topk, q.has_shared = sh, q.ysum = ysum & 1, q.phases = phases;
   q.e_lo = s->e_lo, q.e_hi = s->e_hi, q.limit = s->swiglu_limit;
   q.x = reinterpret_cast<const __nv_bfloat16*>(x), q.idx = idx, q.w = w;
   q.pw = prefill_weights_carve(const_cast<void*>(wbuf), s->H, s->I, s->E);
   q.ws = prefill_ws_carve(ws, T, s->H, s->I, s->E, s->topk);
   q.yr = yr, q.ys = ys, q.out = reinterpret_cast<__nv_bfloat16*>(out);
-  cudaError_t e = cudaMemsetAsync(q.ws.status, 0, 4, (cudaStream_t)stream);
+  cudaError_t e = cudaSuccess;
+  if (phases & DSGX_PH_BUCKET) e = cudaMemsetAsync(q.ws.status, 0, 4, (cudaStream_t)stream);
   if (e == cudaSuccess) e = launch_prefill_fp8(q, (cudaStream_t)stream);
   return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+int dsgx_moe_prefill(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* wbuf, const void* x, const int32_t* idx,
+                     const float* w, int T, void* ws, float* yr, float* ys, void* out, int ysum, void* stream) {
+  return dsgx_moe_prefill_phases(s, L, wbuf, x, idx, w, T, ws, yr, ys, out, ysum, DSGX_PH_ALL, stream);
+}
+
+int dsgx_prefill_view_of(const dsgx_moe_shape* s, void* ws, int T, dsgx_prefill_view* v) {
+  const int rc = check_prefill_shape(s);
+  if (rc) return rc;
+  if (!ws || !v || T < 1) return DSGX_ERR_ARG;
+  const PrefillWs w = prefill_ws_carve(ws, T, s->H, s->I, s->E, s->topk);
+  v->counts = w.counts, v->offsets = w.offsets, v->perm_tok = w.perm_tok, v->perm_slot = w.perm_slot;
+  v->pos_of = w.pos_of, v->row_order = w.row_order, v->hq = w.hq, v->hs = w.hs, v->hq_shared = w.hq_sh, v->hs_shared = w.hs_sh;
+  return DSGX_OK;
+}
+
+int dsgx_decode_up_variants(void) { return decode_fp8_up_variants(); }
+int dsgx_decode_down_variants(void) { return decode_fp8_down_variants(); }
+const char* dsgx_decode_up_name(int v) { return decode_fp8_variant_name(0, v); }
+const char* dsgx_decode_down_name(int v) { return decode_fp8_variant_name(1, v); }
+
+int dsgx_sort_static_status(void) {
+  int word = 0;
+  cudaError_t e = sort_static_status(&word);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return word ? DSGX_ERR_ARG : DSGX_OK;
 }
 
 int dsgx_ws_status(const void* ws) {

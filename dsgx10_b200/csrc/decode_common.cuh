@@ -20,7 +20,7 @@ struct alignas(16) SlotTab {
   int nslots;  // routed slots
   int ntot;    // + the shared expert's
   int bad;     // a dsgx_status when the picks or descriptors were refused (the routed work is then dropped)
-  int pad;
+  int bgu;     // 1: the bf16 shared expert's gate and up rows are interleaved in one matrix (ent.g; ent.u one tile on)
   SlotEnt ent[kMaxSlots + 1];
 };
 static_assert(sizeof(SlotEnt) == 96 && sizeof(SlotTab) % 16 == 0, "SlotTab is copied in 16-byte pieces");
@@ -66,7 +66,7 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
   if (cp.nt == 0) cp = whole_cta();
   const int tid = threadIdx.x, nt = cp.nt;
   if (tid < 16) bm[tid] = 0;
-  if (tid == 0) tab.bad = 0, tab.pad = 0;
+  if (tid == 0) tab.bad = 0, tab.bgu = 0;
   for (int i = tid; i < (kMaxSlots + 1) * 8; i += nt) tab.ent[i >> 3].w[i & 7] = 0.f;
   cp.sync();
   const int np = M * topk;
@@ -115,7 +115,7 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
     int n = 0;
     for (int k = 0; k < 16; ++k) n += __popc(bm[k]);
     if (tab.bad) n = 0;  // refuse the routed work, keep the kernels well-defined
-    const bool has_sh = fmt == DSGX_FMT_FP8 ? sh.g != nullptr : sh.bg != nullptr;
+    const bool has_sh = fmt == DSGX_FMT_FP8 ? sh.g != nullptr : (sh.bg != nullptr || sh.bgu != nullptr);
     tab.nslots = n, tab.ntot = n + (has_sh ? 1 : 0);
     if (has_sh) {
       SlotEnt& en = tab.ent[n];
@@ -125,7 +125,8 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
       if (fmt == DSGX_FMT_FP8) {
         en.g = sh.g, en.u = sh.u, en.d = sh.d, en.sg = sh.gs, en.su = sh.us, en.sd = sh.ds;
       } else {
-        en.g = sh.bg, en.u = sh.bu, en.d = sh.bd, en.sg = en.su = en.sd = nullptr;
+        en.g = sh.bg ? sh.bg : sh.bgu, en.u = sh.bu, en.d = sh.bd, en.sg = en.su = en.sd = nullptr;
+        tab.bgu = sh.bg ? 0 : 1;
       }
     }
   }

@@ -570,9 +570,11 @@ static cudaError_t launch_up_down(const DecodeParams& p, cudaStream_t st, bool p
 }
 
 // The expert step on the caller's idx / w: k_prep (slot table, quantised rows), k_up, k_down.
-cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts,
+                              const RouteParams* rp, const float* logits, const float* bias) {
   if ((parts & 1) && !(parts & 4)) {  // (bit 2: the table and the quantised rows of an earlier call are still in ws)
-    cudaError_t e = launch_prep(p, DSGX_FMT_FP8, x, st, pdl);
+    cudaError_t e = rp ? launch_stage_route(p, DSGX_FMT_FP8, *rp, x, logits, bias, const_cast<int*>(p.idx), const_cast<float*>(p.w), st, pdl)
+                       : launch_prep(p, DSGX_FMT_FP8, x, st, pdl);
     if (e != cudaSuccess) return e;
   }
   return launch_up_down(p, st, pdl, parts & 3);

@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(256) k_prep(TabArgs ta, const int* __restrict_
   pdl_launch_dependents();
   pdl_wait();
   if (blockIdx.x == 0) {
+    if (!idx) return;  // (the table comes from the routing kernel that follows: this launch only stages x)
     build_slot_tab(tab, bm, idx, w, ta.M, ta.topk, ta.E, ta.e_lo, ta.e_hi, ta.pool, ta.desc, ta.sh, ta.fmt);
     if (threadIdx.x == 0 && tab.bad) atomicCAS(status, 0, tab.bad);
     store_tab(tab, out);
@@ -141,6 +142,17 @@ cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteP
   if (e != cudaSuccess) return e;
   return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, fmt),
                   (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
+}
+
+// The expert step on the caller's logits (the fused routing of the reference's DecodeCfg::logits): x staged, then the rows
+// routed and the table built by the routing kernel; idx / w (the step's picks, an output here) go to the given buffers.
+cudaError_t launch_stage_route(const DecodeParams& p, uint32_t fmt, const RouteParams& rp, const __nv_bfloat16* x,
+                               const float* logits_in, const float* bias, int* idx, float* w, cudaStream_t st, bool pdl) {
+  cudaError_t e = launch_k(k_prep, dim3(1 + stage_ctas(p, fmt)), dim3(256), 0, st, pdl, tab_args(p, fmt), (const int*)nullptr,
+                           (const float*)nullptr, x, p.H, p.ws.xq, p.ws.tab, p.ws.status);
+  if (e != cudaSuccess) return e;
+  return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, fmt), logits_in, 1, bias,
+                  (float*)nullptr, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
 }
 
 // the same without staging x (the one-kernel step stages x itself)

@@ -18,6 +18,8 @@
 //
 // The per-unit arithmetic (block order, scale promotion, rounding points) is that of the separate kernels
 // (decode_fp8.cu), so both paths give the same bits.  Activation blocks here hold R = 1, 2, 4 or 8 rows (M rounded up).
+#include <atomic>
+
 #include "common.cuh"
 #include "decode_common.cuh"
 #include "kernels.h"
@@ -420,7 +422,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
         }
         __threadfence();
         __syncthreads();
-        if (threadIdx.x == 0) atomicExch(&sy->tab_ready, 1);
+        if (threadIdx.x == 0 && !sp.test_no_table) atomicExch(&sy->tab_ready, 1);
       }
     } else {
       dead = true;
@@ -498,15 +500,15 @@ size_t step_smem(int H, int R) {
 
 template <int KCH, int NST>
 cudaError_t launch_step(const StepParams& sp, cudaStream_t st) {
-  static bool done[64] = {false};
+  static std::atomic<bool> done[64];  // (per device; two host threads may both set the attribute: harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   const size_t smem = step_smem<KCH, NST>(sp.d.H, sp.R);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  if (!done[dev & 63]) {
+  if (!done[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(k_step_fp8<KCH, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
-    done[dev & 63] = true;
+    done[dev & 63].store(true, std::memory_order_release);
   }
   k_step_fp8<KCH, NST><<<sm_count(), kFThreads, smem, st>>>(sp);
   return cudaGetLastError();

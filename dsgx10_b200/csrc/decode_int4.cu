@@ -20,6 +20,8 @@
 //           into the bf16 tile the down kernel reads (no quantisation, so no tickets).
 //   k_down: unit = (slot, 16 output channels); each pick's f32 output is parked, the tile's last slot adds
 //           w_route * y in ascending expert id (a ticket) and the shared expert's output after them.
+#include <atomic>
+
 #include "common.cuh"
 #include "decode_common.cuh"
 #include "kernels.h"
@@ -164,8 +166,14 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
     uint8_t* st = myring + (issued % kNST) * kUpStage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, 2 * blk);
-    bulk_g2s_hint(st, tab.ent[slot].g + off, blk, bar, pol);
-    bulk_g2s_hint(st + kI4Blk, tab.ent[slot].u + off, blk, bar, pol);
+    if (sh && tab.bgu) {  // interleaved gate/up rows: the unit's 16 rows are two consecutive 8-row tiles of one matrix
+      const uint8_t* gu = tab.ent[slot].g + ((size_t)(2 * i8) * cpu + pc) * blk;
+      bulk_g2s_hint(st, gu, blk, bar, pol);
+      bulk_g2s_hint(st + kI4Blk, gu + (size_t)cpu * blk, blk, bar, pol);
+    } else {
+      bulk_g2s_hint(st, tab.ent[slot].g + off, blk, bar, pol);
+      bulk_g2s_hint(st + kI4Blk, tab.ent[slot].u + off, blk, bar, pol);
+    }
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
@@ -192,6 +200,30 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
       if (lane == 0 && pu < total) issue();
     }
     if (dead) break;
+    if (sh && tab.bgu) {
+      // interleaved rows: A row 2 j is gate and 2 j + 1 up of the unit's channel j (rows 0-7: channels 0-3, rows 8-15:
+      // channels 4-7), so the lanes of an odd row group hand their sums to the even group below them and the even groups
+      // end with (gate, up) of channel g / 2 and of channel 4 + g / 2
+      float o[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[c] = __shfl_down_sync(0xffffffffu, acc[c], 4);
+      if (!(g & 1)) {
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+          const int ch = i8 * 8 + 4 * hi + (g >> 1);
+          uint8_t* hgrp = reinterpret_cast<uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + ch / 16) * R * 32 + 2 * tile_pos(ch & 15);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int r = 2 * t + c;
+            if (r < R) {
+              const float h = __fmul_rn(bf16_round(silu(bf16_round(acc[2 * hi + c]))), bf16_round(o[2 * hi + c]));
+              *reinterpret_cast<__nv_bfloat16*>(hgrp + (size_t)r * 32) = __float2bfloat16_rn(h);
+            }
+          }
+        }
+      }
+      continue;
+    }
     // g, u rounded to bf16; h = bf16(bf16(silu(g)) * u), into the down kernel's tile
     const int ch = i8 * 8 + g;
     uint8_t* hgrp = reinterpret_cast<uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + ch / 16) * R * 32 + 2 * tile_pos(ch & 15);
@@ -352,25 +384,25 @@ constexpr size_t kSmemMax = 227 * 1024;
 
 template <class V>
 cudaError_t launch_up(const DecodeParams& p, cudaStream_t st, bool pdl) {
-  static bool done[64] = {false};
+  static std::atomic<bool> done[64];  // (per device; two host threads may both set the attribute: harmless)
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!done[dev & 63]) {
+  if (!done[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(k_up_i4<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);
     if (e != cudaSuccess) return e;
-    done[dev & 63] = true;
+    done[dev & 63].store(true, std::memory_order_release);
   }
   return launch_k(k_up_i4<V>, dim3(sm_count()), dim3(V::kThreads), up_smem<V>(p.H, rows_pow2(p.M)), st, pdl, p);
 }
 template <class V>
 cudaError_t launch_down(const DecodeParams& p, cudaStream_t st, bool pdl) {
-  static bool done[64] = {false};
+  static std::atomic<bool> done[64];  // (per device; two host threads may both set the attribute: harmless)
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!done[dev & 63]) {
+  if (!done[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(k_down_i4<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);
     if (e != cudaSuccess) return e;
-    done[dev & 63] = true;
+    done[dev & 63].store(true, std::memory_order_release);
   }
   return launch_k(k_down_i4<V>, dim3(sm_count()), dim3(V::kThreads), down_smem<V>(rows_pow2(p.M)), st, pdl, p);
 }
@@ -398,9 +430,11 @@ static cudaError_t launch_up_down(const DecodeParams& p, cudaStream_t st, bool p
 
 bool decode_int4_fits(int H, int M) { return up_smem<VarI<8, 2>>(H, rows_pow2(M)) <= kSmemMax; }
 
-cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts) {
+cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts,
+                               const RouteParams* rp, const float* logits, const float* bias) {
   if (parts & 1) {
-    cudaError_t e = launch_prep(p, DSGX_FMT_INT4, x, st, pdl);
+    cudaError_t e = rp ? launch_stage_route(p, DSGX_FMT_INT4, *rp, x, logits, bias, const_cast<int*>(p.idx), const_cast<float*>(p.w), st, pdl)
+                       : launch_prep(p, DSGX_FMT_INT4, x, st, pdl);
     if (e != cudaSuccess) return e;
   }
   return launch_up_down(p, st, pdl, parts);

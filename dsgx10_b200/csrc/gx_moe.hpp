@@ -35,10 +35,20 @@ inline void route(const MoeShape& s, const float* logits, const float* bias, int
 inline void router_logits(const __nv_bfloat16* x, const float* wr, int M, int H, int E, float* logits, cudaStream_t st) {
   check(dsgx_router_logits(x, wr, M, H, E, logits, st), "gx::router_logits");
 }
-// experts.h:139-141
+// the prefill path's bucket step on its own (experts.h: prefill.cu:94-150), deterministic
+inline size_t sort_ws_bytes(int T, int topk, int E) { return dsgx_sort_ws_bytes(T, topk, E); }
+inline void sort_pack(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok, int* perm_slot,
+                      int* pos_of, int* row_order, void* ws, cudaStream_t st) {
+  check(dsgx_sort_pack(idx, T, topk, E, counts, offsets, perm_tok, perm_slot, pos_of, row_order, ws, st), "gx::sort_pack");
+}
+// experts.h:139-145
 inline size_t decode_ws_bytes(const MoeShape& s) { return dsgx_decode_ws_bytes(&s); }
+inline int decode_up_variants() { return dsgx_decode_up_variants(); }
+inline int decode_down_variants() { return dsgx_decode_down_variants(); }
+inline const char* decode_up_name(int v) { return dsgx_decode_up_name(v); }
+inline const char* decode_down_name(int v) { return dsgx_decode_down_name(v); }
 inline void moe_decode(const MoeShape& s, const LayerW& L, const __nv_bfloat16* x, const int* idx, const float* w, int M,
-                       void* ws, float* yr, float* ys, cudaStream_t st, const DecodeCfg& cfg = DecodeCfg{0, 1, 0, 0, 0, {0, 0, 0}}) {
+                       void* ws, float* yr, float* ys, cudaStream_t st, const DecodeCfg& cfg = DecodeCfg{0, 1, 0, 0, 0, {0, 0, 0}, nullptr, nullptr}) {
   check(dsgx_moe_decode(&s, &L, x, idx, w, M, ws, yr, ys, st, &cfg), "gx::moe_decode");
 }
 // experts.h:146-147 (mode 1 is the reference's bf16(bf16(R) + bf16(S)); mode 0 rounds the f32 sum once)
@@ -55,6 +65,22 @@ inline void moe_prefill(const MoeShape& s, const LayerW& L, const void* wbuf, co
                         const float* w, int T, void* ws, float* yr, float* ys, cudaStream_t st, __nv_bfloat16* out = nullptr,
                         bool ysum = false) {
   check(dsgx_moe_prefill(&s, &L, wbuf, x, idx, w, T, ws, yr, ys, out, ysum ? 1 : 0, st), "gx::moe_prefill");
+}
+
+// experts.h:185-193: the pass in separate calls, and the workspace's intermediates
+enum PrefillPhase { kPhBucket = DSGX_PH_BUCKET, kPhUp = DSGX_PH_UP, kPhDown = DSGX_PH_DOWN, kPhCombine = DSGX_PH_COMBINE,
+                    kPhShared = DSGX_PH_SHARED, kPhAll = DSGX_PH_ALL };
+constexpr int kPrefillAll = DSGX_PH_ALL;
+inline void moe_prefill_phases(const MoeShape& s, const LayerW& L, const void* wbuf, const __nv_bfloat16* x, const int* idx,
+                               const float* w, int T, void* ws, float* yr, float* ys, cudaStream_t st, int phases,
+                               __nv_bfloat16* out = nullptr, bool ysum = false) {
+  check(dsgx_moe_prefill_phases(&s, &L, wbuf, x, idx, w, T, ws, yr, ys, out, ysum ? 1 : 0, phases, st), "gx::moe_prefill_phases");
+}
+using PrefillView = dsgx_prefill_view;
+inline PrefillView prefill_view(const MoeShape& s, void* ws, int T) {
+  PrefillView v{};
+  check(dsgx_prefill_view_of(&s, ws, T, &v), "gx::prefill_view");
+  return v;
 }
 
 // the all-reduce after the expert step and the rounding in one call over peer-mapped buffers (ds41f

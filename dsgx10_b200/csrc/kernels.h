@@ -28,6 +28,7 @@ size_t sort_ws_bytes(int T, int topk, int E);
 constexpr size_t kSortStaticBytes = DSGX_SORT_STATIC_MAX_BYTES;  // the fixed scratch of launch_sort_pack_static
 cudaError_t launch_sort_pack_static(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
                                     int* perm_slot, int* pos_of, int* row_order, cudaStream_t st);
+cudaError_t sort_static_status(int* word);
 cudaError_t launch_sort_pack(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
                              int* perm_slot, int* pos_of, int* row_order, void* ws, cudaStream_t st);
 cudaError_t launch_act_quant_tiled(const __nv_bfloat16* x, int M, int K, uint8_t* out, cudaStream_t st, bool pdl);
@@ -50,6 +51,8 @@ struct DecodeWs {
   float* lpart;     // [H/1024 slices][8][E] partial router logits of the layer step
   float* part;      // [kPartUnits][kMaxPieces][32 lanes][4] piece sums of the units whose K is split over several warps
   int* cnt_u;       // [kPartUnits] arrivals of a split unit's runs
+  int* r_idx;       // [kMaxRows][kMaxTopK] the picks of a step that routes on the caller's logits
+  float* r_w;
 };
 // A unit's K is summed in pieces of kPB 128-k blocks (decode_common.cuh); when a launch has fewer units than warps, the
 // pieces of a unit go to several warps (of different SMs) and meet in `part`, indexed by the unit's number in the launch.
@@ -80,8 +83,11 @@ cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const
                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
 int decode_fp8_up_variants();
 int decode_fp8_down_variants();
+const char* decode_fp8_variant_name(int down, int i);
 // parts: 1 = activation quantisation + gate/up, 2 = down + combine, 3 = both
-cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
+// rp: when not null, the step routes on the caller's logits (p.idx / p.w are outputs then)
+cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts,
+                              const RouteParams* rp = nullptr, const float* logits = nullptr, const float* bias = nullptr);
 
 // the one-kernel FP8 layer step (decode_fused.cu)
 struct StepSync {
@@ -105,19 +111,23 @@ struct StepParams {
   unsigned long long* stamps;  // optional [warps][8] phase timestamps (profiling aid), or null
   int R, sh_slot, has_sh;
   int pre_routed;  // 1: earlier kernels routed the rows and built the slot table; the step starts at the experts
+  int test_no_table;  // test hook: the table is never announced, so every wait for it runs out (bounded) and is reported
 };
 bool step_fp8_fits(int H, int I, int E, int M);
 cudaError_t launch_step_fp8(StepParams sp, cudaStream_t st);
 cudaError_t launch_front_route_only(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                                     const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
 
-cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts);
+cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts,
+                               const RouteParams* rp = nullptr, const float* logits = nullptr, const float* bias = nullptr);
 cudaError_t launch_layer_int4(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                               const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
 bool decode_int4_fits(int H, int M);
 
 // the front of a decode step (decode_front.cu); fmt selects how x is staged for the expert kernels
 cudaError_t launch_prep(const DecodeParams& p, uint32_t fmt, const __nv_bfloat16* x, cudaStream_t st, bool pdl);
+cudaError_t launch_stage_route(const DecodeParams& p, uint32_t fmt, const RouteParams& rp, const __nv_bfloat16* x,
+                               const float* logits_in, const float* bias, int* idx, float* w, cudaStream_t st, bool pdl);
 cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteParams& rp, const __nv_bfloat16* x,
                                const float* wr, const float* bias, float* logits, int* idx, float* w, cudaStream_t st,
                                bool pdl);
@@ -148,7 +158,7 @@ PrefillWs prefill_ws_carve(void* ws, int T, int H, int I, int E, int topk);
 struct PrefillParams {
   int T, H, I, E, topk, has_shared, ysum, e_lo, e_hi;
   float limit;  // the SwiGLU clamp (0: none)
-  int parts;  // bench hook: 0 the whole pass, 1 the routed gate/up GEMM alone, 2 the routed down GEMM alone
+  int phases;  // DSGX_PH_* bits: the parts of the pass to run
   const __nv_bfloat16* x;
   const int* idx;
   const float* w;

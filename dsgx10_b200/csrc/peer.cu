@@ -149,7 +149,10 @@ __global__ void __launch_bounds__(256) k_finalize_peers(PeerParams p) {
     if (p.outs) __threadfence_system();
     else __threadfence();
     if (atomicAdd(p.state + 1, 1u) == gridDim.x - 1) {
-      if (p.outs) {  // every CTA's stores to the peers are fenced (system scope) before its ticket
+      // every CTA's stores to the peers are fenced (system scope) before its ticket.  If a CTA of this launch gave up its
+      // wait (the status word is set before that CTA's ticket), the slice is incomplete: nothing is published, so that the
+      // peers' own bounded waits run out and report, instead of reading rows that never arrived.
+      if (p.outs && *reinterpret_cast<volatile int*>(p.status) == 0) {
         __threadfence_system();
         for (int q = 0; q < p.world; ++q) st_release_sys(p.done[q] + p.rank, e);
       }

@@ -773,7 +773,8 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   GemmArgs a;
   a.limit = q.limit;
   a.status = w.status;
-  if (!q.parts) {  // (bench hook otherwise: the workspace holds the order and the operands of an earlier whole pass)
+  const int ph = q.phases;
+  if (ph & DSGX_PH_BUCKET) {  // (without it the workspace holds the order and the operands of an earlier call)
   // order, quantise, gather
   e = launch_sort_pack(q.idx, T, topk, E, w.counts, w.offsets, w.perm_tok, w.perm_slot, w.pos_of, w.row_order, w.sort_ws, st);
   if (e != cudaSuccess) return e;
@@ -791,14 +792,14 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   // routed gate/up
   a.mode = 0, a.K = H, a.N = I, a.E = E, a.rows_total = P, a.wrow0 = 0, a.tile_off = w.tile_off, a.tile_info = w.tile_info;
   a.sa = w.xs_s, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = w.w_s, a.hq = w.hq, a.hs = w.hs, a.y = nullptr;
-  if (q.parts != 2) e = launch_gemm<0>(mXs, mG, mU, oHq, a, st);
-  if (e != cudaSuccess || q.parts == 1) return e;
+  if (ph & DSGX_PH_UP) e = launch_gemm<0>(mXs, mG, mU, oHq, a, st);
+  if (e != cudaSuccess) return e;
   // routed down
   a.mode = 1, a.K = I, a.N = H, a.sa = w.hs, a.sb0 = pw.sd, a.sb1 = nullptr, a.wrow = nullptr, a.hq = nullptr, a.hs = nullptr;
   a.y = w.y;
-  e = launch_gemm<1>(mHq, mD, mD, oY, a, st);
-  if (e != cudaSuccess || q.parts == 2) return e;
-  if (q.has_shared) {
+  if (ph & DSGX_PH_DOWN) e = launch_gemm<1>(mHq, mD, mD, oY, a, st);
+  if (e != cudaSuccess) return e;
+  if (q.has_shared && (ph & DSGX_PH_SHARED)) {
     a.mode = 0, a.K = H, a.N = I, a.E = 1, a.rows_total = T, a.wrow0 = E, a.tile_off = nullptr, a.tile_info = nullptr;
     a.sa = w.xs, a.sb0 = pw.sg, a.sb1 = pw.su, a.wrow = nullptr, a.hq = w.hq_sh, a.hs = w.hs_sh, a.y = nullptr;
     e = launch_gemm<0>(mX, mG, mU, oHsh, a, st);
@@ -807,6 +808,7 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
     e = launch_gemm<1>(mHsh, mD, mD, oYsh, a, st);
     if (e != cudaSuccess) return e;
   }
+  if (!(ph & DSGX_PH_COMBINE)) return cudaSuccess;
   const size_t n = (size_t)T * (H / 8);
   k_combine<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.y, q.has_shared ? w.y_sh : nullptr, q.idx, q.e_lo, q.e_hi, w.pos_of,
                                                          w.row_order, T, H,

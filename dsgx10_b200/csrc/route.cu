@@ -2,6 +2,8 @@
 // softmax, optional group-limited selection), the stable token -> expert sort, activation quantisation and the final
 // rounding.  Integer / f32 CUDA-core work, bound by latency (decode) or by HBM and issue rate (prefill); no tensor
 // cores on purpose: the selection must be reproducible bit for bit on a CPU.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "route.cuh"
@@ -245,21 +247,38 @@ cudaError_t launch_sort_pack(const int* idx, int T, int topk, int E, int* counts
 // by the call), and two calls that overlap on the device race on it.
 static __device__ __align__(256) unsigned char g_sort_scratch[kSortStaticBytes];
 
-cudaError_t launch_sort_pack_static(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
-                                    int* perm_slot, int* pos_of, int* row_order, cudaStream_t st) {
-  // set-up, once per device: the array's device address (this may load the module, so the first call is not the one to
-  // time, and it belongs before any stream capture)
-  static void* addr[64] = {nullptr};
+// set-up, once per device: the array's device address (this may load the module, so the first call is not the one to
+// time, and it belongs before any stream capture).  The cache is per device; two host threads that make the first call
+// together both look the address up and store the same value.
+static cudaError_t sort_scratch_addr(void** out) {
+  static std::atomic<void*> addr[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  void* p = dev >= 0 && dev < 64 ? addr[dev] : nullptr;
+  void* p = dev >= 0 && dev < 64 ? addr[dev].load(std::memory_order_acquire) : nullptr;
   if (!p) {
     e = cudaGetSymbolAddress(&p, g_sort_scratch);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) addr[dev] = p;
+    if (dev >= 0 && dev < 64) addr[dev].store(p, std::memory_order_release);
   }
+  *out = p;
+  return cudaSuccess;
+}
+
+cudaError_t launch_sort_pack_static(const int* idx, int T, int topk, int E, int* counts, int* offsets, int* perm_tok,
+                                    int* perm_slot, int* pos_of, int* row_order, cudaStream_t st) {
+  void* p = nullptr;
+  cudaError_t e = sort_scratch_addr(&p);
+  if (e != cudaSuccess) return e;
   return launch_sort_pack(idx, T, topk, E, counts, offsets, perm_tok, perm_slot, pos_of, row_order, p, st);
+}
+
+// the error word of the last static sort on this device (synchronous)
+cudaError_t sort_static_status(int* word) {
+  void* p = nullptr;
+  cudaError_t e = sort_scratch_addr(&p);
+  if (e != cudaSuccess) return e;
+  return cudaMemcpy(word, p, sizeof(int), cudaMemcpyDeviceToHost);
 }
 
 // ------------------------------------------------------------------------------------------ activation quantisation

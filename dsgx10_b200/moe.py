@@ -58,6 +58,13 @@ def sort_pack(idx, E):
     return out
 
 
+def decode_variants():
+    """The names of the decode kernels' variants: (gate/up, down)."""
+    L = lib()
+    return ([L.dsgx_decode_up_name(i).decode() for i in range(L.dsgx_decode_up_variants())],
+            [L.dsgx_decode_down_name(i).decode() for i in range(L.dsgx_decode_down_variants())])
+
+
 def sort_pack_static(idx, E):
     """sort_pack through the entry point that takes no workspace and allocates nothing (fixed scratch in the library)."""
     T, k = idx.shape
@@ -82,14 +89,16 @@ def decode_ws(shp, device="cuda"):
     return torch.zeros(decode_ws_bytes(shp), dtype=torch.uint8, device=device)
 
 
-def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True, parts=0, up=0, down=0):
-    """x bf16 [M][H]; idx, w from route(); returns (yr, ys) f32 [M][H]: this GPU's partial sums."""
+def moe_decode(shp, layer_w, x, idx, w, ws, yr=None, ys=None, ysum=False, pdl=True, parts=0, up=0, down=0, logits=None,
+               bias=None):
+    """x bf16 [M][H]; idx, w from route(); returns (yr, ys) f32 [M][H]: this GPU's partial sums.
+    logits (f32 [M][E], with an optional selection bias): the step routes the rows itself, idx and w may be None."""
     M, H = x.shape
     if yr is None:
         yr = torch.empty(M, H, dtype=torch.float32, device=x.device)
     if ys is None:
         ys = torch.empty(M, H, dtype=torch.float32, device=x.device)
-    cfg = _lib.DecodeCfg(int(ysum), int(pdl), int(parts), int(up), int(down))
+    cfg = _lib.DecodeCfg(int(ysum), int(pdl), int(parts), int(up), int(down), (C.c_int32 * 3)(0, 0, 0), _ptr(logits), _ptr(bias))
     check(lib().dsgx_moe_decode(C.byref(shp), C.byref(layer_w), _ptr(x), _ptr(idx), _ptr(w), M, _ptr(ws), _ptr(yr),
                                 _ptr(ys), _stream(), C.byref(cfg)), "dsgx_moe_decode")
     return yr, ys
@@ -150,6 +159,12 @@ class LayerStep:
         return out_host
 
 
+def prefill_view(shp, ws, T):
+    v = _lib.PrefillView()
+    check(lib().dsgx_prefill_view_of(C.byref(shp), _ptr(ws), T, C.byref(v)), "dsgx_prefill_view_of")
+    return v
+
+
 class PrefillLayer:
     """A layer prepared for the prefill path: the K-major weight copy (made once) and a workspace for up to T_max rows."""
 
@@ -167,14 +182,18 @@ class PrefillLayer:
             check(lib().dsgx_prefill_prepare(C.byref(shp), C.byref(layer_w), _ptr(self.wbuf), _stream()), "dsgx_prefill_prepare")
         self.ws = torch.empty(lib().dsgx_prefill_ws_bytes(C.byref(shp), T_max), dtype=torch.uint8, device=device)
 
-    def run(self, x, idx, w, yr=None, ys=None, out=None, ysum=False, parts=0):
-        """x bf16 [T][H]; idx, w from route(); returns (yr, ys, out): f32 partial sums and bf16(yr + ys)."""
+    def run(self, x, idx, w, yr=None, ys=None, out=None, ysum=False, parts=0, phases=None):
+        """x bf16 [T][H]; idx, w from route(); returns (yr, ys, out): f32 partial sums and bf16(yr + ys).
+        phases: DSGX_PH_* bits (default: the whole pass); parts 1 / 2: the routed gate/up / down GEMM alone."""
         T, H = x.shape
         assert T <= self.T_max
         f32 = dict(dtype=torch.float32, device=x.device)
         yr = torch.empty(T, H, **f32) if yr is None else (None if yr is False else yr)   # False: rounded rows only
         ys = torch.empty(T, H, **f32) if ys is None else (None if ys is False else ys)
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if out is None else (None if out is False else out)
-        check(lib().dsgx_moe_prefill(C.byref(self.shp), C.byref(self.layer_w), _ptr(self.wbuf), _ptr(x), _ptr(idx), _ptr(w), T,
-                                     _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum) | parts << 8, _stream()), "dsgx_moe_prefill")
+        if phases is None:
+            phases = {0: _lib.PH_ALL, 1: _lib.PH_UP, 2: _lib.PH_DOWN}[parts]
+        check(lib().dsgx_moe_prefill_phases(C.byref(self.shp), C.byref(self.layer_w), _ptr(self.wbuf), _ptr(x), _ptr(idx),
+                                            _ptr(w), T, _ptr(self.ws), _ptr(yr), _ptr(ys), _ptr(out), int(ysum), phases,
+                                            _stream()), "dsgx_moe_prefill_phases")
         return yr, ys, out

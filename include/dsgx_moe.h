@@ -61,12 +61,15 @@ typedef struct dsgx_mat_desc {
 } dsgx_mat_desc;
 
 /* The shared expert: stands in for gx::SharedW (experts.h:66-87).  FP8: g, u [I][H] and d [H][I] in the tile_fp8
- * layout with f32 block scales gs, us, ds.  BF16 (INT4 layers): bg, bu [I][H] and bd [H][I] in the bf16 tile layout
- * (layout.h:96-107).  All null: the layer has no fused shared expert. */
+ * layout with f32 block scales gs, us, ds.  BF16 (INT4 layers), in the bf16 tile layout (layout.h:96-107), either as
+ * the reference's engine holds it: bgu, the interleaved gate/up [2 I][H] (row 2 i gate, 2 i + 1 up of channel i), and bd
+ * [H][I]; or as three matrices bg, bu [I][H] and bd.  The two forms give the same bits.  All null: the layer has no fused
+ * shared expert. */
 typedef struct dsgx_shared_w {
   const uint8_t *g, *u, *d;
   const float *gs, *us, *ds;
   const uint8_t *bg, *bu, *bd;
+  const uint8_t* bgu;
 } dsgx_shared_w;
 
 /* One layer's weights on one GPU: stands in for gx::LayerW (experts.h:92-97).  desc is [E][3] (gate, up, down) in
@@ -80,8 +83,8 @@ typedef struct dsgx_layer_w {
 
 /* The reference fixes its shapes at compile time (experts.h:18-26); here they are run-time parameters. */
 typedef struct dsgx_moe_shape {
-  int32_t H;            /* hidden: K of gate/up, N of down; a multiple of 128 (INT4: of 512) */
-  int32_t I;            /* intermediate: N of gate/up, K of down; a multiple of 128 (INT4: of 512) */
+  int32_t H;            /* hidden: K of gate/up, N of down; FP8: a multiple of 256, at most 4096; INT4: a multiple of 512 */
+  int32_t I;            /* intermediate: N of gate/up, K of down; the same limits */
   int32_t E;            /* routed experts of the layer, <= 512 */
   int32_t topk;         /* picks a row, <= 8 */
   int32_t n_group;      /* expert groups for group-limited selection (1: none) */
@@ -140,6 +143,11 @@ int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, 
 #define DSGX_SORT_STATIC_MAX_BYTES 131328 /* 256 + 2 x 32 chunks x 512 experts x 4 bytes */
 int dsgx_sort_pack_static(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
                           int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* stream);
+/* A pick whose expert id lies outside [0, E) is left out of the order (counts and offsets describe the picks that are in)
+ * and recorded: after dsgx_sort_pack, dsgx_ws_status(ws) gives DSGX_ERR_ARG instead of DSGX_OK; after
+ * dsgx_sort_pack_static, this call does, for the last static sort on the current device (it copies one word back and so
+ * waits for that sort; the cached address of the array does not survive a cudaDeviceReset). */
+int dsgx_sort_static_status(void);
 
 /* ---- decode (1..DSGX_MAX_ROWS rows) ------------------------------------------------------------------------------
  * Stands in for gx::decode_ws_bytes / gx::moe_decode (altar1 engine/experts/experts.h:104-141) and dsk::moe_routed
@@ -154,8 +162,20 @@ typedef struct dsgx_decode_cfg {
                           gate/up kernel alone, over the slot table and quantised rows an earlier call left in ws */
   int32_t up, down;    /* kernel variants (experts.h:114-118): 0 the default; every variant gives the same bits */
   int32_t reserved[3];
+  /* Fused routing (experts.h:123-127): with logits (the router GEMV's f32 [M][E]) set, the step routes the rows itself
+   * (dsgx_route's code, the same bits) and the idx / w arguments are not read (may be null): no dsgx_route launch between
+   * the router GEMV and the experts.  bias: the selection bias f32 [E], or null. */
+  const float* logits;
+  const float* bias;
 } dsgx_decode_cfg;
 size_t dsgx_decode_ws_bytes(const dsgx_moe_shape* shape);
+/* The kernel variants dsgx_decode_cfg.up / .down select (FP8 layers), and their names: stands in for
+ * gx::decode_up_variants / decode_down_variants / decode_up_name / decode_down_name (experts.h:142-145).  A name is a
+ * static string ("w16 k2 s2": warps a CTA, 128-k blocks a chunk, ring stages), null beyond the count. */
+int dsgx_decode_up_variants(void);
+int dsgx_decode_down_variants(void);
+const char* dsgx_decode_up_name(int v);
+const char* dsgx_decode_down_name(int v);
 int dsgx_moe_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, const int32_t* idx,
                     const float* w, int M, void* ws, float* yr, float* ys, void* stream, const dsgx_decode_cfg* cfg);
 
@@ -212,7 +232,15 @@ typedef struct dsgx_layer_step {
   int32_t flags;      /* FP8 layers run the step as four kernels (front, route, gate/up, down) at one or two rows and as
                          one persistent kernel from three rows up (the measured crossover); bit 0: always the four
                          kernels; bit 2: always the one kernel; bit 3: two small routing kernels, then the experts in the
-                         one kernel; every path gives the same bits */
+                         one kernel; every path gives the same bits.
+                         The one kernel's CTAs (one a SM) wait for one another through counters in ws, so all of them must
+                         be resident together: it wants the GPU to itself while it runs.  If other work holds SMs (another
+                         stream's kernels, another process), its bounded waits run out after about a second, the status
+                         word of ws gets DSGX_ERR_DEVICE_WAIT and the outputs are not written; the counters in ws are
+                         reset either way, so the next call on the workspace is clean once the status word is cleared.
+                         Callers that overlap the step with other kernels set bit 0.
+                         bit 4: a test of exactly that: the table is never announced inside the one kernel, every wait
+                         for it runs out and the step ends with the status word set */
   int32_t reserved;
   void* reserved_ptr; /* with flags bit 1: device memory for [warps][8] u64 phase timestamps of the one-kernel step
                          (a profiling aid; warps = 16 x SM count) */
@@ -239,14 +267,43 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* 
  * (ds41f engine/kernels/moe.cu:1332-1336); it reads the descriptors back to the host and synchronises, so it is a
  * load-time call.  Only the experts in [e_lo, e_hi) (and the shared expert, when the layer has one) are prepared and run.
  * ws: dsgx_prefill_ws_bytes(shape, T) bytes, T <= the value given there; no zeroing needed.
- * ysum: bit 0 as dsgx_decode_cfg.ysum; bits 8-9 a bench hook like dsgx_decode_cfg.parts (experts.h:121): 1 launches the
- * routed gate/up GEMM alone, 2 the routed down GEMM alone, over the operands a whole pass left in ws. */
+ * ysum: as dsgx_decode_cfg.ysum.
+ * dsgx_prefill_prepare allocates host memory, reads the descriptors back and synchronises: a load-time call.  The other
+ * calls of this header allocate nothing and do not synchronise (dsgx_ws_status and dsgx_sort_static_status copy one word
+ * back and so wait for the stream's work). */
 size_t dsgx_prefill_weights_bytes(const dsgx_moe_shape* shape);
 int dsgx_prefill_prepare(const dsgx_moe_shape* shape, const dsgx_layer_w* L, void* wbuf, void* stream);
 size_t dsgx_prefill_ws_bytes(const dsgx_moe_shape* shape, int T);
 int dsgx_moe_prefill(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* wbuf, const void* x_bf16,
                      const int32_t* idx, const float* w, int T, void* ws, float* yr, float* ys, void* out_bf16, int ysum,
                      void* stream);
+
+/* The same work in separate calls on one workspace, for per-phase timing: stands in for gx::moe_prefill_phases and its
+ * PrefillPhase bits (altar1 engine/experts/experts.h:191-193).  A phase reads what the phases before it left in ws. */
+enum {
+  DSGX_PH_BUCKET = 1,   /* the sort, the tile table, the quantisation of x and the gather of the sorted rows */
+  DSGX_PH_UP = 2,       /* the routed gate/up grouped GEMM (SwiGLU, h quantised) */
+  DSGX_PH_DOWN = 4,     /* the routed down grouped GEMM */
+  DSGX_PH_COMBINE = 8,  /* the per-row ordered sum, the shared expert's output added, the rounding */
+  DSGX_PH_SHARED = 16,  /* the shared expert's two dense GEMMs */
+  DSGX_PH_ALL = 31
+};
+int dsgx_moe_prefill_phases(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* wbuf, const void* x_bf16,
+                            const int32_t* idx, const float* w, int T, void* ws, float* yr, float* ys, void* out_bf16,
+                            int ysum, int phases, void* stream);
+
+/* The workspace's intermediates after a pass, for tests: stands in for gx::prefill_view (experts.h:185-190); the fields
+ * are this library's (h is kept quantised).  P = T * topk sorted picks. */
+typedef struct dsgx_prefill_view {
+  const int32_t *counts, *offsets;       /* [E], [E + 1]: picks an expert, their first sorted position */
+  const int32_t *perm_tok, *perm_slot;   /* [P]: the row and the pick number at a sorted position */
+  const int32_t *pos_of, *row_order;     /* [T][topk]: the sorted position of a pick; a row's picks in ascending expert id */
+  const uint8_t* hq;                     /* [P][I] e4m3: h of every sorted pick */
+  const float* hs;                       /* [P][I / 128]: its scales */
+  const uint8_t* hq_shared;              /* [T][I] e4m3, [T][I / 128]: the shared expert's h */
+  const float* hs_shared;
+} dsgx_prefill_view;
+int dsgx_prefill_view_of(const dsgx_moe_shape* shape, void* ws, int T, dsgx_prefill_view* view);
 
 /* Reads (synchronously) the device status word of a workspace: DSGX_OK or DSGX_ERR_DEVICE_WAIT. */
 int dsgx_ws_status(const void* ws);

@@ -224,6 +224,27 @@ def test_layer_step_equals_separate_calls(orc, H, I, E, topk, M, ng, tg):
     assert torch.equal(ws, snap) and moe.ws_status(ws) == 0
 
 
+def test_fused_routing_on_callers_logits():
+    """dsgx_decode_cfg.logits (the reference's DecodeCfg::logits, altar1 engine/experts/experts.h:123-127): the step routes
+    the rows itself and gives the bits of route + moe_decode; idx and w are not read."""
+    from dsgx10_b200 import moe, synth
+    H, I, E, topk, M = 1024, 512, 32, 6, 5
+    shp = moe.shape(H, I, E, topk, n_group=4, topk_group=2, route_scale=1.5)
+    layer = synth.Fp8Layer(H, I, E, 95, device="cuda")
+    x = synth.activations(M, H, 96).cuda()
+    wr = synth.router_weights(E, H, 97).cuda()
+    bias = (torch.randn(E, generator=torch.Generator().manual_seed(6)) * 0.01).float().cuda()
+    logits = moe.router_logits(x, wr)
+    idx, w = moe.route(shp, logits, bias)
+    yr, ys = moe.moe_decode(shp, layer.layer_w(), x, idx, w, moe.decode_ws(shp))
+    ws = moe.decode_ws(shp)
+    for _ in range(2):
+        yr2, ys2 = moe.moe_decode(shp, layer.layer_w(), x, None, None, ws, logits=logits, bias=bias)
+        torch.cuda.synchronize()
+        assert moe.ws_status(ws) == 0
+        assert torch.equal(yr2, yr) and torch.equal(ys2, ys)
+
+
 def test_kernel_variants_same_bits(orc):
     """Every up / down kernel variant (warps, chunking, ring depth) gives the same bits (cf. altar1
     engine/experts/tests/test_experts.cu:557-575)."""
@@ -236,8 +257,10 @@ def test_kernel_variants_same_bits(orc):
     idx, w = moe.route(shp, moe.router_logits(x, wr), None)
     ws = moe.decode_ws(shp)
     base = None
-    for up in range(7):
-        for down in range(5):
+    ups, downs = moe.decode_variants()
+    assert len(ups) == 7 and len(downs) == 5 and all(ups) and all(downs)
+    for up in range(len(ups)):
+        for down in range(len(downs)):
             if up and down:
                 continue
             yr, ys = moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws, up=up, down=down)
@@ -269,3 +292,31 @@ def test_one_kernel_step_equals_separate_kernels(orc, M):
         assert torch.equal(fused.idx[:M], sep.idx[:M]) and torch.equal(fused.w[:M], sep.w[:M])
         assert torch.equal(fused.yr[:M], sep.yr[:M]) and torch.equal(fused.ys[:M], sep.ys[:M])
         assert torch.equal(a, b)
+
+
+def test_one_kernel_step_reports_a_wait_that_runs_out():
+    """The one-kernel step's CTAs wait for one another through counters; when what they wait for never comes (here: the
+    table is never announced, a test switch of dsgx_layer_step.flags), the waits run out after about a second, the
+    status word says so, and the workspace's counters are reset: with the status word cleared the next step is right."""
+    import ctypes as C
+    from dsgx10_b200 import _lib, moe, synth
+    H, I, E, topk, M = 1024, 512, 32, 6, 4
+    shp = moe.shape(H, I, E, topk)
+    layer = synth.Fp8Layer(H, I, E, 700, device="cuda")
+    wr = synth.router_weights(E, H, 701).cuda()
+    x = synth.activations(M, H, 702).cuda()
+    good = moe.LayerStep(shp, wr, fused=True)
+    want = good.run(layer.layer_w(), x).clone()
+    step = moe.LayerStep(shp, wr, fused=True)
+    c = _lib.LayerStep.from_buffer_copy(step.c)
+    c.flags = 4 | 16
+    rc = _lib.lib().dsgx_moe_layer_decode(C.byref(shp), C.byref(layer.layer_w()), C.c_void_p(x.data_ptr()), M, C.byref(c), 1,
+                                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0                                   # the launch itself is fine
+    torch.cuda.synchronize()                         # (about a second: the bounded waits)
+    assert moe.ws_status(step.ws) == _lib.ERR_DEVICE_WAIT
+    step.ws[:4].zero_()                              # the caller clears the status word ...
+    got = step.run(layer.layer_w(), x)               # ... and the workspace is ready: its counters were reset
+    torch.cuda.synchronize()
+    assert moe.ws_status(step.ws) == 0
+    assert torch.equal(got, want)

@@ -81,6 +81,34 @@ def test_sigmoid_scaled_no_shared_and_expert_parallel(orc):
     _run(orc, 1024, 512, 16, 4, 6, seed=121, e_lo=0, e_hi=8)
 
 
+def test_interleaved_shared_expert_same_bits(orc):
+    """The bf16 shared expert as the reference's engine holds it (SharedW::bgu: gate and up rows interleaved in one
+    matrix, altar1 engine/experts/experts.h:72-87) gives the bits of the three-matrix form."""
+    import ctypes as C
+    from dsgx10_b200 import _lib, moe, synth
+    H, I, E, topk, M = 1024, 512, 16, 4, 5
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4, score_fn=1)
+    layer = synth.Int4Layer(H, I, E, 140, device="cuda")
+    x = synth.activations(M, H, 141).cuda()
+    wr = synth.router_weights(E, H, 142).cuda()
+    step = moe.LayerStep(shp, wr)
+    step.run(layer.layer_w(), x)
+    yr, ys = step.yr[:M].clone(), step.ys[:M].clone()
+    gu = np.empty((2 * I, H), np.uint16)
+    gu[0::2], gu[1::2] = layer.sh_bits[0], layer.sh_bits[1]
+    bgu = torch.from_numpy(synth.tile_bf16(gu)).cuda()
+    lw = layer.layer_w()
+    lw.sh.bg, lw.sh.bu, lw.sh.bgu = None, None, bgu.data_ptr()
+    step2 = moe.LayerStep(shp, wr)
+    step2.run(lw, x)
+    torch.cuda.synchronize()
+    assert moe.ws_status(step2.ws) == 0
+    assert torch.equal(step2.yr[:M], yr) and torch.equal(step2.ys[:M], ys)
+    lw.sh.bu = layer.sh_dev[1].data_ptr()          # both forms at once are refused
+    with pytest.raises(_lib.DsgxError):
+        step2.run(lw, x)
+
+
 def test_batch_invariance(orc):
     from dsgx10_b200 import _lib, moe, synth
     H, I, E, topk = 1024, 512, 16, 4

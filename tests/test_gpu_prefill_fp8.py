@@ -116,6 +116,28 @@ def test_rounded_rows_only_and_gemm_hooks(orc):
         assert torch.equal(pl.ws, snap) and moe.ws_status(pl.ws) == 0
 
 
+def test_phases_in_separate_calls(orc):
+    """dsgx_moe_prefill_phases (the reference's moe_prefill_phases, altar1 engine/experts/experts.h:191-193): the phases
+    run one call each on one workspace give the whole pass's bits; the view names the workspace's intermediates."""
+    from dsgx10_b200 import _lib, moe
+    T = 300
+    shp, layer, x, wr, bias, idx, w = _setup(1024, 512, 16, 4, T, seed=285)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = (t.clone() for t in pl.run(x, idx, w))
+    pl.ws.zero_()
+    f32 = dict(dtype=torch.float32, device="cuda")
+    yr2, ys2, out2 = torch.zeros(T, 1024, **f32), torch.zeros(T, 1024, **f32), torch.zeros(T, 1024, dtype=torch.bfloat16, device="cuda")
+    for ph in (_lib.PH_BUCKET, _lib.PH_UP, _lib.PH_DOWN, _lib.PH_SHARED, _lib.PH_COMBINE):
+        pl.run(x, idx, w, yr=yr2, ys=ys2, out=out2, phases=ph)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    assert torch.equal(yr2, yr) and torch.equal(ys2, ys) and torch.equal(out2, out)
+    v = moe.prefill_view(shp, pl.ws, T)
+    base = pl.ws.data_ptr()
+    counts = pl.ws[v.counts - base: v.counts - base + 16 * 4].view(torch.int32)
+    assert torch.equal(counts.long(), torch.bincount(idx.flatten().long(), minlength=16))
+
+
 def test_chunk_invariance(orc):
     """A row's bits do not depend on the other rows of the chunk (altar1 engine/experts/tests/test_prefill.inc:293-302)."""
     from dsgx10_b200 import moe
