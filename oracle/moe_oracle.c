@@ -205,6 +205,55 @@ ORC_API int orc_router_logits(const uint16_t* x, const float* wr, int R, int H, 
   return 0;
 }
 
+/* RMSNorm of bf16 rows (ds41f ref/inference/model.py:281-293; altar1 ref/glmref.py:225-228 and its engine's
+ * comm/glmcoll.cu:83-90): r = 1 / sqrt(mean(x^2) + eps), y = bf16(w * (x * r)) (mode 0, model.py: one rounding) or
+ * y = bf16(w * bf16(x * r)) (mode 1, altar-1: the normalised value is rounded before the weight).  The mean's sum is
+ * taken in the library's fixed order: the row in chunks of 8 values, chunk c to thread c mod 256 of 256, a thread adds
+ * its chunks in ascending order by fused multiply-adds from zero, the 32 threads of a warp go through the butterfly, the
+ * 8 warp sums are added in ascending order; then IEEE division, square root and reciprocal.  H a multiple of 8. */
+static float rms_rstd_row(const uint16_t* x, int H, float eps) {
+  float t[256];
+  for (int j = 0; j < 256; ++j) {
+    float a = 0.f;
+    for (int c = j; c < H / 8; c += 256)
+      for (int i = 0; i < 8; ++i) {
+        const float v = orc_bf16_to_f32(x[8 * c + i]);
+        a = fmaf(v, v, a);
+      }
+    t[j] = a;
+  }
+  float ss = 0.f;
+  for (int w = 0; w < 8; ++w) {
+    const float s = butterfly32(t + 32 * w);
+    ss = w ? ss + s : s;
+  }
+  return 1.f / sqrtf(ss / (float)H + eps);
+}
+static inline uint16_t rms_out(uint16_t x, float r, uint16_t w, int mode) {
+  const float xr = orc_bf16_to_f32(x) * r;
+  return orc_f32_to_bf16(orc_bf16_to_f32(w) * (mode == 1 ? bf16r(xr) : xr));
+}
+ORC_API int orc_rmsnorm(const uint16_t* x, const uint16_t* w, int R, int H, float eps, int mode, uint16_t* y) {
+  if (H % 8) return -1;
+  for (int r = 0; r < R; ++r) {
+    const float rs = rms_rstd_row(x + (size_t)r * H, H, eps);
+    for (int k = 0; k < H; ++k) y[(size_t)r * H + k] = rms_out(x[(size_t)r * H + k], rs, w[k], mode);
+  }
+  return 0;
+}
+/* The step that follows the experts in both engines (altar1 engine/comm/glmcoll.cu:225-330 allreduce_add_norm; ds41f
+ * model.py:  x = x + ffn(x), then the next norm): v = the layer's f32 sums (already reduced over ranks), out = bf16(v),
+ * h = bf16(res + out) (add_f32 = 0) or bf16(res + v) (add_f32 = 1), normed = RMSNorm(h).  res may be null (h = out). */
+ORC_API int orc_add_norm(const float* v, const uint16_t* res, const uint16_t* w, int R, int H, float eps, int mode,
+                         int add_f32, uint16_t* out, uint16_t* h, uint16_t* normed) {
+  if (H % 8) return -1;
+  for (size_t i = 0; i < (size_t)R * H; ++i) {
+    out[i] = orc_f32_to_bf16(v[i]);
+    h[i] = res ? orc_f32_to_bf16(orc_bf16_to_f32(res[i]) + (add_f32 ? v[i] : orc_bf16_to_f32(out[i]))) : out[i];
+  }
+  return orc_rmsnorm(h, w, R, H, eps, mode, normed);
+}
+
 enum { ORC_SCORE_SIGMOID = 0, ORC_SCORE_SOFTMAX = 1, ORC_SCORE_SQRTSOFTPLUS = 2 };
 
 /* Scores of one row.  softmax: t_e = exp(l_e - max), S = lane sums (lane j adds e = j, j + 32, ... ascending) through

@@ -126,6 +126,26 @@ def router_logits(x_bf16, wr):
     return out
 
 
+def rmsnorm(x_bf16, w_bf16, eps=1e-6, mode=0):
+    """RMSNorm of bf16 rows (bits in, bits out); mode 0: bf16(w (x r)), mode 1: bf16(w bf16(x r))."""
+    x_bf16, w_bf16 = _c(x_bf16, np.uint16), _c(w_bf16, np.uint16)
+    R, H = x_bf16.shape
+    y = np.empty((R, H), np.uint16)
+    assert lib().orc_rmsnorm(_p(x_bf16), _p(w_bf16), R, H, C.c_float(eps), mode, _p(y)) == 0
+    return y
+
+
+def add_norm(v, res_bf16, w_bf16, eps=1e-6, mode=0, add_f32=False):
+    """out = bf16(v); h = bf16(res + out) (or res + v); normed = RMSNorm(h).  Returns (out, h, normed) as bf16 bits."""
+    v, w_bf16 = _c(v, np.float32), _c(w_bf16, np.uint16)
+    R, H = v.shape
+    res = None if res_bf16 is None else _c(res_bf16, np.uint16)
+    out, h, normed = (np.empty((R, H), np.uint16) for _ in range(3))
+    assert lib().orc_add_norm(_p(v), _p(res) if res is not None else None, _p(w_bf16), R, H, C.c_float(eps), mode,
+                              int(add_f32), _p(out), _p(h), _p(normed)) == 0
+    return out, h, normed
+
+
 def route(logits, bias, topk, score_fn=SCORE_SIGMOID, n_group=1, topk_group=1, norm=True, route_scale=1.0):
     logits = _c(logits, np.float32)
     R, E = logits.shape
