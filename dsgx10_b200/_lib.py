@@ -50,7 +50,13 @@ class DecodeCfg(C.Structure):
 
 class LayerStep(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("wr", "bias", "logits", "idx", "w", "ws", "yr", "ys", "out_bf16", "x_stage")] + \
-               [("flags", C.c_int32), ("reserved", C.c_int32), ("reserved_ptr", C.c_void_p)]
+               [("flags", C.c_int32), ("reserved", C.c_int32), ("reserved_ptr", C.c_void_p),
+                ("norm_w", C.c_void_p), ("xn_out", C.c_void_p), ("norm_eps", C.c_float), ("norm_mode", C.c_int32)]
+
+
+class AddNorm(C.Structure):
+    _fields_ = [("res", C.c_void_p), ("res_out", C.c_void_p), ("norm_w", C.c_void_p), ("normed", C.c_void_p),
+                ("eps", C.c_float), ("norm_mode", C.c_int32), ("add_f32", C.c_int32), ("reserved", C.c_int32)]
 
 
 # every symbol include/dsgx_moe.h declares: name -> (restype, argtypes)
@@ -63,6 +69,8 @@ SYMBOLS = {
     "dsgx_sort_ws_bytes": (_Z, [_I, _I, _I]),
     "dsgx_sort_pack": (_I, [_V, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V, _V]),
     "dsgx_finalize_peers": (_I, [_V, _I, _I, _V, _V, _V]),
+    "dsgx_finalize_peers_norm": (_I, [_V, _I, _I, _V, C.POINTER(AddNorm), _V, _V]),
+    "dsgx_finalize_add_norm": (_I, [_V, _V, _I, _I, _I, _V, C.POINTER(AddNorm), _V]),
     "dsgx_sort_pack_static": (_I, [_V, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V]),
     "dsgx_decode_ws_bytes": (_Z, [C.POINTER(MoeShape)]),
     "dsgx_moe_decode": (_I, [C.POINTER(MoeShape), C.POINTER(LayerW), _V, _V, _V, _I, _V, _V, _V, _V,

@@ -184,6 +184,45 @@ int dsgx_finalize_peers(const dsgx_peer_set* ps, int M, int H, void* out, int32_
   return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
 }
 
+static int add_norm_args(const dsgx_add_norm* an, int H, AddNormParams& a) {
+  if (!an || !an->norm_w || (an->norm_mode != 0 && an->norm_mode != 1) || !(an->eps >= 0.f)) return DSGX_ERR_ARG;
+  if (H % 8 || H > 8192) return DSGX_ERR_SHAPE;
+  if (((uintptr_t)an->res | (uintptr_t)an->res_out | (uintptr_t)an->norm_w | (uintptr_t)an->normed) & 15) return DSGX_ERR_ARG;
+  a.res = reinterpret_cast<const __nv_bfloat16*>(an->res), a.res_out = reinterpret_cast<__nv_bfloat16*>(an->res_out);
+  a.w = reinterpret_cast<const __nv_bfloat16*>(an->norm_w), a.normed = reinterpret_cast<__nv_bfloat16*>(an->normed);
+  a.eps = an->eps, a.mode = an->norm_mode, a.add_f32 = an->add_f32 != 0, a.R = nullptr, a.S = nullptr, a.fin_mode = 0;
+  return DSGX_OK;
+}
+
+int dsgx_finalize_peers_norm(const dsgx_peer_set* ps, int M, int H, void* out, const dsgx_add_norm* an, int32_t* status_word,
+                             void* stream) {
+  if (!ps || !ps->parts || !ps->flags || !ps->state || !status_word || ps->outs || ps->done) return DSGX_ERR_ARG;
+  if (ps->world < 1 || ps->world > 32 || ps->rank < 0 || ps->rank >= ps->world || ps->shared_rank >= ps->world || ps->shared_rank < -2) return DSGX_ERR_ARG;
+  if (M < 1 || M > ps->rows_cap || ((uintptr_t)out & 15)) return DSGX_ERR_SHAPE;
+  AddNormParams a;
+  const int rc = add_norm_args(an, H, a);
+  if (rc) return rc;
+  PeerParams p;
+  p.parts = ps->parts, p.flags = ps->flags, p.state = ps->state, p.rank = ps->rank, p.world = ps->world;
+  p.rows_cap = ps->rows_cap, p.shared_rank = ps->shared_rank, p.M = M, p.H = H;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out), p.status = status_word, p.outs = nullptr, p.done = nullptr;
+  cudaError_t e = launch_add_norm(p, a, true, (cudaStream_t)stream, false);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
+int dsgx_finalize_add_norm(const float* R, const float* S, int M, int H, int mode, void* out, const dsgx_add_norm* an,
+                           void* stream) {
+  if (!R || M < 1 || (mode != 0 && mode != 1) || (((uintptr_t)R | (uintptr_t)S | (uintptr_t)out) & 15)) return DSGX_ERR_ARG;
+  AddNormParams a;
+  const int rc = add_norm_args(an, H, a);
+  if (rc) return rc;
+  a.R = R, a.S = S, a.fin_mode = mode;
+  PeerParams p{};
+  p.world = 1, p.rows_cap = M, p.shared_rank = -1, p.M = M, p.H = H, p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  cudaError_t e = launch_add_norm(p, a, false, (cudaStream_t)stream, true);
+  return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
+}
+
 size_t dsgx_decode_ws_bytes(const dsgx_moe_shape* s) {
   if (check_shape(s)) return 0;
   return decode_ws_bytes(s->H, s->I);
@@ -215,6 +254,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr;
     p.up = cfg->up, p.down = cfg->down;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
+    p.norm = FrontNorm{nullptr, nullptr, 0.f, 0};
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                       cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
@@ -233,6 +273,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.idx = own_route ? p.ws.r_idx : idx, p.w = own_route ? p.ws.r_w : w;
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
+    p.norm = FrontNorm{nullptr, nullptr, 0.f, 0};
     cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                        cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
@@ -270,6 +311,11 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     p.ws = decode_ws_carve(st->ws, s->H, s->I);
     p.yr = st->yr, p.ys = st->ys, p.ysum = 0, p.up = 0, p.down = 0;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
+    p.norm = FrontNorm{reinterpret_cast<const __nv_bfloat16*>(st->norm_w), reinterpret_cast<__nv_bfloat16*>(st->xn_out),
+                       st->norm_eps, st->norm_mode};
+    if (st->norm_w && ((st->norm_mode != 0 && st->norm_mode != 1) || !(st->norm_eps >= 0.f) || s->H % 8 ||
+                       (((uintptr_t)st->norm_w | (uintptr_t)st->xn_out) & 15)))
+      return DSGX_ERR_ARG;
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);

@@ -154,6 +154,17 @@ DSGX_DEV float warp_sum(float v) {
   return v;
 }
 
+// ---- RMSNorm pieces (IEEE operations only, so the CPU oracle repeats them bit for bit) ---------------------------------
+DSGX_DEV float rms_rstd(float ss, int H, float eps) {
+  return __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), eps)));
+}
+// mode 0: bf16(w (x r)); mode 1: bf16(w bf16(x r))
+DSGX_DEV float rms_apply(float x, float r, float w, int mode) {
+  float xr = __fmul_rn(x, r);
+  if (mode == 1) xr = bf16_round(xr);
+  return bf16_round(__fmul_rn(w, xr));
+}
+
 // ---- host-side launch helper ----------------------------------------------------------------------------------------
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>

@@ -253,12 +253,75 @@ DSGX_DEV void quant_row_to_block(uint8_t* blk, int r, int lane, bool valid, floa
   if (lane == 0) reinterpret_cast<float*>(blk + 1024)[r] = sc;
 }
 
-DSGX_DEV void quant_x_block(const __nv_bfloat16* __restrict__ x, int M, int K, uint8_t* out, int j, int r, int lane) {
+// The RMSNorm in front of a layer step.  rstd: the rows' 1 / rms in shared memory (rms_rows_rstd); w null: no norm.
+struct RowNorm {
+  const __nv_bfloat16* w;
+  const float* rstd;
+  int mode;
+};
+constexpr int kRmsRed = 8 * kMaxRows + kMaxRows;  // floats of shared memory rms_rows_rstd wants
+// Every row's 1 / rms into red[8 kMaxRows + r], by the first 256 threads of the CTA (all threads call; two CTA barriers).
+// The sum of squares in a fixed order: the row in chunks of 8 values, chunk c to thread c mod 256, a thread adds its chunks
+// in ascending order by fma from zero, the warps' butterflies, then the 8 warp sums in ascending order.
+DSGX_DEV void rms_rows_rstd(const __nv_bfloat16* __restrict__ x, int M, int H, float eps, float* red) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < 256) {
+    float ss[kMaxRows];
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) ss[r] = 0.f;
+    for (int c = tid; c < H / 8; c += 256) {
+      uint4 v[kMaxRows];
+#pragma unroll
+      for (int r = 0; r < kMaxRows; ++r)
+        if (r < M) v[r] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * H + 8 * c));
+#pragma unroll
+      for (int r = 0; r < kMaxRows; ++r)
+        if (r < M) {
+          const uint32_t* vv = &v[r].x;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float lo = bf16_bits_to_f(vv[j] & 0xffffu), hi = bf16_bits_to_f(vv[j] >> 16);
+            ss[r] = fmaf(lo, lo, ss[r]), ss[r] = fmaf(hi, hi, ss[r]);
+          }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r)
+      if (r < M) {
+        const float s = warp_sum(ss[r]);
+        if (lane == 0) red[warp * kMaxRows + r] = s;
+      }
+  }
+  __syncthreads();
+  if (tid < M) {
+    float s = red[tid];
+    for (int w = 1; w < 8; ++w) s = __fadd_rn(s, red[w * kMaxRows + tid]);
+    red[8 * kMaxRows + tid] = rms_rstd(s, H, eps);
+  }
+  __syncthreads();
+}
+// four consecutive values of row r at column k (a multiple of 4), normalised
+DSGX_DEV void norm4(const RowNorm& n, int r, int k, float& v0, float& v1, float& v2, float& v3) {
+  if (!n.w) return;
+  const uint2 wv = __ldg(reinterpret_cast<const uint2*>(n.w + k));
+  const float rs = n.rstd[r];
+  v0 = rms_apply(v0, rs, bf16_bits_to_f(wv.x & 0xffffu), n.mode), v1 = rms_apply(v1, rs, bf16_bits_to_f(wv.x >> 16), n.mode);
+  v2 = rms_apply(v2, rs, bf16_bits_to_f(wv.y & 0xffffu), n.mode), v3 = rms_apply(v3, rs, bf16_bits_to_f(wv.y >> 16), n.mode);
+}
+DSGX_DEV uint2 pack_bf16x4(float v0, float v1, float v2, float v3) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+DSGX_DEV void quant_x_block(const __nv_bfloat16* __restrict__ x, int M, int K, uint8_t* out, int j, int r, int lane,
+                            const RowNorm& nrm = RowNorm{nullptr, nullptr, 0}, __nv_bfloat16* xn_out = nullptr) {
   float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
   if (r < M) {
     const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)r * K + 128 * j + 4 * lane));
     v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
     v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+    norm4(nrm, r, 128 * j + 4 * lane, v0, v1, v2, v3);
+    if (xn_out) *reinterpret_cast<uint2*>(xn_out + (size_t)r * K + 128 * j + 4 * lane) = pack_bf16x4(v0, v1, v2, v3);
   }
   quant_row_to_block(out + (size_t)j * kActBlk, r, lane, r < M, v0, v1, v2, v3);
 }
@@ -273,12 +336,27 @@ inline __host__ __device__ int rows_pow2(int M) { return M <= 1 ? 1 : M <= 2 ? 2
 DSGX_DEV int tile_pos(int v) { return (v & 8) | ((v & 3) << 1) | ((v >> 2) & 1); }
 
 // x bf16 [M][K] -> tile [K/16 groups][R rows][16 values in tile_pos order]; rows M..R-1 are zero.  One thread a (group, row).
-DSGX_DEV void tile_x_group(const __nv_bfloat16* __restrict__ x, int M, int K, int R, uint8_t* out, int kg, int r) {
+DSGX_DEV void tile_x_group(const __nv_bfloat16* __restrict__ x, int M, int K, int R, uint8_t* out, int kg, int r,
+                           const RowNorm& nrm = RowNorm{nullptr, nullptr, 0}, __nv_bfloat16* xn_out = nullptr) {
   uint16_t v[16], o[16];
   if (r < M) {
     const uint4 a = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * K + 16 * kg));
     const uint4 b = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * K + 16 * kg + 8));
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    if (nrm.w) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v0 = bf16_bits_to_f(w[2 * i] & 0xffffu), v1 = bf16_bits_to_f(w[2 * i] >> 16);
+        float v2 = bf16_bits_to_f(w[2 * i + 1] & 0xffffu), v3 = bf16_bits_to_f(w[2 * i + 1] >> 16);
+        norm4(nrm, r, 16 * kg + 4 * i, v0, v1, v2, v3);
+        const uint2 pk = pack_bf16x4(v0, v1, v2, v3);
+        w[2 * i] = pk.x, w[2 * i + 1] = pk.y;
+      }
+      if (xn_out) {
+        uint4* d = reinterpret_cast<uint4*>(xn_out + (size_t)r * K + 16 * kg);
+        d[0] = make_uint4(w[0], w[1], w[2], w[3]), d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[2 * i] = (uint16_t)(w[i] & 0xffffu), v[2 * i + 1] = (uint16_t)(w[i] >> 16);
   } else {
@@ -306,7 +384,7 @@ DSGX_DEV void logit_slice_weights(const float* __restrict__ wr, int H, int e, in
                     : make_float4(0.f, 0.f, 0.f, 0.f);
 }
 DSGX_DEV void logit_slice_rows(const __nv_bfloat16* __restrict__ x, const float4 (&wv)[8], int M, int H, int E, int e, int sl,
-                               float* __restrict__ lpart, int lane) {
+                               float* __restrict__ lpart, int lane, const RowNorm& nrm = RowNorm{nullptr, nullptr, 0}) {
   const int base = sl * 1024, nit = min(1024, H - base) / 128;
   for (int r = 0; r < M; ++r) {
     uint2 xv[8];
@@ -317,20 +395,23 @@ DSGX_DEV void logit_slice_rows(const __nv_bfloat16* __restrict__ x, const float4
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (i < nit) {
-        a = fmaf(bf16_bits_to_f(xv[i].x & 0xffffu), wv[i].x, a);
-        a = fmaf(bf16_bits_to_f(xv[i].x >> 16), wv[i].y, a);
-        a = fmaf(bf16_bits_to_f(xv[i].y & 0xffffu), wv[i].z, a);
-        a = fmaf(bf16_bits_to_f(xv[i].y >> 16), wv[i].w, a);
+        float v0 = bf16_bits_to_f(xv[i].x & 0xffffu), v1 = bf16_bits_to_f(xv[i].x >> 16);
+        float v2 = bf16_bits_to_f(xv[i].y & 0xffffu), v3 = bf16_bits_to_f(xv[i].y >> 16);
+        norm4(nrm, r, base + 128 * i + 4 * lane, v0, v1, v2, v3);
+        a = fmaf(v0, wv[i].x, a);
+        a = fmaf(v1, wv[i].y, a);
+        a = fmaf(v2, wv[i].z, a);
+        a = fmaf(v3, wv[i].w, a);
       }
     a = warp_sum(a);
     if (lane == 0) lpart[((size_t)sl * kMaxRows + r) * E + e] = a;
   }
 }
 DSGX_DEV void logit_slice_task(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M, int H, int E, int e,
-                               int sl, float* __restrict__ lpart, int lane) {
+                               int sl, float* __restrict__ lpart, int lane, const RowNorm& nrm = RowNorm{nullptr, nullptr, 0}) {
   float4 wv[8];
   logit_slice_weights(wr, H, e, sl, lane, wv);
-  logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane);
+  logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane, nrm);
 }
 
 struct TabArgs {

@@ -17,15 +17,16 @@ namespace {
 
 // One CTA's share of staging x for the expert kernels.  FP8: one warp a (128-k block, row), quantised blocks.
 // Other formats: one thread a (16-value group, row) of the bf16 tile.
-DSGX_DEV void stage_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t* __restrict__ out, int fmt, int cta) {
+DSGX_DEV void stage_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t* __restrict__ out, int fmt, int cta,
+                      const RowNorm& nrm = RowNorm{nullptr, nullptr, 0}, __nv_bfloat16* xn_out = nullptr) {
   if (fmt == DSGX_FMT_FP8) {
     const int gw = cta * 8 + (threadIdx.x >> 5);
     const int j = gw >> 3, r = gw & 7;
-    if (j < H / 128) quant_x_block(x, M, H, out, j, r, threadIdx.x & 31);
+    if (j < H / 128) quant_x_block(x, M, H, out, j, r, threadIdx.x & 31, nrm, xn_out);
   } else {
     const int R = rows_pow2(M);
     const int i = cta * 256 + threadIdx.x;
-    if (i < H / 16 * R) tile_x_group(x, M, H, R, out, i / R, i % R);
+    if (i < H / 16 * R) tile_x_group(x, M, H, R, out, i / R, i % R, nrm, xn_out);
   }
 }
 
@@ -34,12 +35,15 @@ DSGX_DEV void stage_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t
 // summation order (lane j: k = base + 128 i + 4 j + c by fma, then the butterfly).  CTAs [nlog, ..): x -> blocks.
 __global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M,
                                                int H, int E, int nlog, float* __restrict__ lpart, uint8_t* __restrict__ xq,
-                                               int fmt) {
+                                               int fmt, FrontNorm fn) {
+  __shared__ float red[kRmsRed];
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const RowNorm nrm{fn.w, red + 8 * kMaxRows, fn.mode};
   if ((int)blockIdx.x >= nlog) {
     pdl_wait();
-    stage_x(x, M, H, xq, fmt, (int)blockIdx.x - nlog);
+    if (fn.w) rms_rows_rstd(x, M, H, fn.eps, red);
+    stage_x(x, M, H, xq, fmt, (int)blockIdx.x - nlog, nrm, fn.xn_out);
     return;
   }
   const int KS = (H + 1023) / 1024;
@@ -49,8 +53,9 @@ __global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__
   float4 wv[8];
   if (e < E) logit_slice_weights(wr, H, e, sl, lane, wv);
   pdl_wait();
+  if (fn.w) rms_rows_rstd(x, M, H, fn.eps, red);  // (every CTA sums the rows itself: 8 KB a row out of L2, no launch in front)
   if (e >= E) return;
-  logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane);
+  logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane, nrm);
 }
 
 // ----------------------------------------------------------------------------------------------------- k_route_union
@@ -138,7 +143,7 @@ cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteP
   const int KS = (p.H + 1023) / 1024;
   const int nlog = (p.E * KS + 7) / 8;
   cudaError_t e = launch_k(k_front, dim3(nlog + stage_ctas(p, fmt)), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog,
-                           p.ws.lpart, p.ws.xq, (int)fmt);
+                           p.ws.lpart, p.ws.xq, (int)fmt, p.norm);
   if (e != cudaSuccess) return e;
   return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, fmt),
                   (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
@@ -160,8 +165,10 @@ cudaError_t launch_front_route_only(const DecodeParams& p, const RouteParams& rp
                                     const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl) {
   const int KS = (p.H + 1023) / 1024;
   const int nlog = (p.E * KS + 7) / 8;
+  FrontNorm fn = p.norm;
+  fn.xn_out = nullptr;  // (the one kernel that follows writes the copy)
   cudaError_t e = launch_k(k_front, dim3(nlog), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq,
-                           (int)DSGX_FMT_FP8);
+                           (int)DSGX_FMT_FP8, fn);
   if (e != cudaSuccess) return e;
   return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, DSGX_FMT_FP8),
                   (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);

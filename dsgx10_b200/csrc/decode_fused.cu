@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   int* s_idx = reinterpret_cast<int*>(&rs + 1);
   float* s_w = reinterpret_cast<float*>(s_idx + kMaxRows * kMaxTopK);
   uint32_t* s_bm = reinterpret_cast<uint32_t*>(s_w + kMaxRows * kMaxTopK);
+  float* s_red = reinterpret_cast<float*>(s_bm + 16);  // the rows' 1 / rms when the step normalises its input
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   // Work is dealt to warps CTA-interleaved (consecutive work items go to different SMs): one SM pulls at most ~50 GB/s,
@@ -80,11 +81,15 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
   const int gwn = warp * nrc + blockIdx.x;       // this warp's index among them (valid when !router_cta)
   const int sh_units = sp.has_sh ? upp : 0, sh_down = sp.has_sh ? NT : 0;
 
+  // the RMSNorm in front of the step: every CTA sums the rows' squares itself (it quantises all of x anyway)
+  const RowNorm nrm{p.norm.w, s_red + 8 * kMaxRows, p.norm.mode};
+  if (p.norm.w) rms_rows_rstd(sp.x, p.M, p.H, p.norm.eps, s_red);
+
   // ---- the router's logit slices first: they head the longest chain of the step -------------------------------------------
   if (!router_cta && !sp.pre_routed) {
     int mine = 0;
     for (int task = gwn; task < ntask; task += GWn) {
-      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane);
+      logit_slice_task(sp.x, sp.wr, p.M, p.H, p.E, task / KS, task % KS, p.ws.lpart, lane, nrm);
       ++mine;
     }
     if (mine) {  // one global add a CTA: its last logit warp reports all of the CTA's slices
@@ -112,6 +117,9 @@ __global__ void __launch_bounds__(kFThreads, 1) k_step_fp8(const StepParams sp) 
       const uint2 xv = __ldg(reinterpret_cast<const uint2*>(sp.x + (size_t)r * p.H + 128 * j + 4 * lane));
       v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
       v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
+      norm4(nrm, r, 128 * j + 4 * lane, v0, v1, v2, v3);
+      if (p.norm.w && p.norm.xn_out && blockIdx.x == 0)
+        *reinterpret_cast<uint2*>(p.norm.xn_out + (size_t)r * p.H + 128 * j + 4 * lane) = pack_bf16x4(v0, v1, v2, v3);
     }
     cquant_row(xq + j * CB, R, r, lane, r < p.M, v0, v1, v2, v3);
   }
@@ -495,7 +503,7 @@ size_t step_smem(int H, int R) {
   const int CB = cblk_bytes(R);
   const size_t stage = 2 * KCH * 1024 + ((KCH * CB + 127) & ~127);
   return (size_t)(((H / 128) * CB + 127) & ~127) + kTabSmem + (size_t)kFW * NST * stage + (kFW * NST + 1) * 8 + 16 +
-         sizeof(RouteSmem) + kMaxRows * kMaxTopK * 8 + 64 + 128;
+         sizeof(RouteSmem) + kMaxRows * kMaxTopK * 8 + 64 + kRmsRed * 4 + 128;
 }
 
 template <int KCH, int NST>

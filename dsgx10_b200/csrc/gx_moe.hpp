@@ -89,6 +89,17 @@ using PeerSet = dsgx_peer_set;
 inline void finalize_peers(const PeerSet& ps, int M, int H, __nv_bfloat16* out, int* status_word, cudaStream_t st) {
   check(dsgx_finalize_peers(&ps, M, H, out, status_word, st), "gx::finalize_peers");
 }
+// the same with the residual add and the next block's RMSNorm fused in (altar1 engine/comm/glmcoll.cu:225-330
+// comm::glm::allreduce_add_norm), over peer memory or on one GPU
+using AddNorm = dsgx_add_norm;
+inline void finalize_peers_norm(const PeerSet& ps, int M, int H, __nv_bfloat16* out, const AddNorm& an, int* status_word,
+                                cudaStream_t st) {
+  check(dsgx_finalize_peers_norm(&ps, M, H, out, &an, status_word, st), "gx::finalize_peers_norm");
+}
+inline void finalize_add_norm(const float* R, const float* S, int M, int H, __nv_bfloat16* out, const AddNorm& an,
+                              cudaStream_t st, int mode = 0) {
+  check(dsgx_finalize_add_norm(R, S, M, H, mode, out, &an, st), "gx::finalize_add_norm");
+}
 // one layer step, router to rounded rows (the sequence of engine/model/model.cu:308-352)
 using LayerStep = dsgx_layer_step;
 inline void layer_decode(const MoeShape& s, const LayerW& L, const __nv_bfloat16* x, int M, const LayerStep& step,

@@ -63,6 +63,15 @@ constexpr size_t kSlotTabBytes = 8192;  // room reserved for a SlotTab
 size_t decode_ws_bytes(int H, int I);
 DecodeWs decode_ws_carve(void* ws, int H, int I);
 
+// RMSNorm of the step's input rows in front of the router (layer-step calls): x is the residual stream, the router and the
+// experts see xn = RMSNorm(x) (ds41f engine/kernels/dsk.h:130-135 gemv_bf16_norm; mode 0: bf16(w (x r)), the order of
+// ref/inference/model.py:288-293; mode 1: bf16(w bf16(x r)), altar-1's ref/glmref.py:225-228).  w null: x is used as is.
+struct FrontNorm {
+  const __nv_bfloat16* w;
+  __nv_bfloat16* xn_out;  // optional copy of the normalised rows [M][H]
+  float eps;
+  int mode;
+};
 struct DecodeParams {
   int H, I, E, topk, M, e_lo, e_hi;
   const uint8_t* pool;
@@ -78,6 +87,7 @@ struct DecodeParams {
   int up, down;  // kernel variants (same bits)
   float limit;     // the SwiGLU clamp (0: none)
   int sh_lo, sh_hi;  // the shared expert's intermediate channels this GPU computes (multiples of 512; the whole: 0, I)
+  FrontNorm norm;
 };
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);
@@ -185,5 +195,19 @@ struct PeerParams {
   uint32_t* const* done;       // sliced form: rank r's "slices landed" words, u32 [world]
 };
 cudaError_t launch_finalize_peers(const PeerParams& p, cudaStream_t st);
+// the reduction followed by the residual add and the RMSNorm for the next block, one kernel (peers: over peer memory;
+// else one GPU's own R / S)
+struct AddNormParams {
+  const __nv_bfloat16* res;  // residual stream in (null: h = out)
+  __nv_bfloat16* res_out;    // h (may alias res), or null
+  const __nv_bfloat16* w;    // norm weights [H]
+  __nv_bfloat16* normed;     // RMSNorm(h), or null
+  float eps;
+  int mode, add_f32;
+  const float* R;            // one GPU: the sums; S may be null
+  const float* S;
+  int fin_mode;
+};
+cudaError_t launch_add_norm(const PeerParams& p, const AddNormParams& an, bool peers, cudaStream_t st, bool pdl);
 
 }  // namespace dsgx

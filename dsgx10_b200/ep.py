@@ -156,3 +156,20 @@ class PeerReduce:
         if count:
             self.launched += 1
         return dst[:M]
+
+    def finalize_norm(self, M, norm_w, res=None, eps=1e-6, norm_mode=0, add_f32=False, count=True):
+        """The reduction with the residual add and the next block's RMSNorm in the same kernel:
+        returns (out, h, normed) = (bf16(v), bf16(res + out), RMSNorm(h)), each bf16 [M][H], the same bits on every rank."""
+        lib = self._lib.lib()
+        assert not self.sliced
+        dev = self.out.device
+        h, normed = (torch.empty(M, self.H, dtype=torch.bfloat16, device=dev) for _ in range(2))
+        an = self._lib.AddNorm(res.data_ptr() if res is not None else None, h.data_ptr(), norm_w.data_ptr(), normed.data_ptr(),
+                               eps, norm_mode, int(add_f32), 0)
+        rc = lib.dsgx_finalize_peers_norm(C.byref(self.set), M, self.H, C.c_void_p(self.out.data_ptr()), C.byref(an),
+                                          C.c_void_p(self.status.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc:
+            raise self._lib.DsgxError(rc, "dsgx_finalize_peers_norm")
+        if count:
+            self.launched += 1
+        return self.out[:M], h, normed

@@ -111,6 +111,20 @@ def finalize(R, S=None, mode=0):
     return out
 
 
+def add_norm_args(norm_w, res=None, eps=1e-6, norm_mode=0, add_f32=False, res_out=None, normed=None):
+    """The dsgx_add_norm struct over torch tensors (res_out / normed: given buffers, or made here when True)."""
+    return _lib.AddNorm(_ptr(res), _ptr(res_out), _ptr(norm_w), _ptr(normed), eps, norm_mode, int(add_f32), 0)
+
+
+def finalize_add_norm(R, S, norm_w, res=None, mode=0, eps=1e-6, norm_mode=0, add_f32=False):
+    """One GPU: out = bf16(R + S), h = bf16(res + out), normed = RMSNorm(h): returns (out, h, normed), bf16 [M][H]."""
+    M, H = R.shape
+    out, h, normed = (torch.empty(M, H, dtype=torch.bfloat16, device=R.device) for _ in range(3))
+    an = add_norm_args(norm_w, res, eps, norm_mode, add_f32, h, normed)
+    check(lib().dsgx_finalize_add_norm(_ptr(R), _ptr(S), M, H, mode, _ptr(out), C.byref(an), _stream()), "dsgx_finalize_add_norm")
+    return out, h, normed
+
+
 def ws_status(ws):
     return lib().dsgx_ws_status(_ptr(ws))
 
@@ -118,8 +132,9 @@ def ws_status(ws):
 class LayerStep:
     """The buffers of one layer step (router to rounded output) and the two step calls."""
 
-    def __init__(self, shp, wr, bias=None, device="cuda", fused=None, stamps=None):
-        """fused: None = the library's choice by row count, True = always the one-kernel step, False = never."""
+    def __init__(self, shp, wr, bias=None, device="cuda", fused=None, stamps=None, norm_w=None, norm_eps=1e-6, norm_mode=0):
+        """fused: None = the library's choice by row count, True = always the one-kernel step, False = never.
+        norm_w (bf16 [H]): the step normalises its input rows first (RMSNorm fused into the front); self.xn gets a copy."""
         f32 = dict(dtype=torch.float32, device=device)
         self.shp, self.wr, self.bias = shp, wr, bias
         self.logits = torch.empty(_lib.MAX_ROWS, shp.E, **f32)
@@ -133,6 +148,10 @@ class LayerStep:
         self.c = _lib.LayerStep(_ptr(wr), _ptr(bias), _ptr(self.logits), _ptr(self.idx), _ptr(self.w), _ptr(self.ws),
                                 _ptr(self.yr), _ptr(self.ys), _ptr(self.out), _ptr(self.x_stage),
                                 (0 if fused is None else 4 if fused else 1) | (2 if stamps is not None else 0), 0, _ptr(stamps))
+        self.norm_w = norm_w
+        if norm_w is not None:
+            self.xn = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
+            self.c.norm_w, self.c.xn_out, self.c.norm_eps, self.c.norm_mode = _ptr(norm_w), _ptr(self.xn), norm_eps, norm_mode
 
     def run(self, layer_w, x, finalize=True, yr=None, ys=None):
         """x bf16 [M][H] on the device -> self.out[:M] (bf16) when finalize, else self.yr / self.ys partial sums

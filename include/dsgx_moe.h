@@ -212,6 +212,31 @@ typedef struct dsgx_peer_set {
 } dsgx_peer_set;
 int dsgx_finalize_peers(const dsgx_peer_set* peers, int M, int H, void* out_bf16, int32_t* status_word, void* stream);
 
+/* What follows the experts in both engines, fused into the reduction: the residual add and the RMSNorm that feeds the next
+ * block.  Stands in for altar1's comm::glm::allreduce_add_norm (engine/comm/glmcoll.cu:225-330: the all-reduce's consumer
+ * adds the residual and normalises) and for ds41f's x = x + ffn(x) followed by the next norm (ref/inference/model.py).
+ * Per row: v = the reduced f32 sums (as dsgx_finalize_peers / dsgx_finalize), out = bf16(v),
+ *   h = bf16(res + out)  (add_f32 != 0: bf16(res + v), altar-1's f32 combine),  normed = RMSNorm(h; norm_w, eps):
+ *   r = 1 / sqrt(mean(h^2) + eps) in IEEE operations with the sum in a fixed order,
+ *   norm_mode 0: bf16(w (h r)) (model.py:288-293);  1: bf16(w bf16(h r)) (altar-1, glmref.py:225-228, glmcoll.cu:83-90).
+ * res (bf16 [M][H]) may be null (h = out); res_out (may alias res), normed and out_bf16 may each be null.  H a multiple of
+ * 8, at most 8192.  One CTA a row.  The peer form follows dsgx_finalize_peers' protocol (plain form only: outs null). */
+typedef struct dsgx_add_norm {
+  const void* res;
+  void* res_out;
+  const void* norm_w; /* bf16 [H] */
+  void* normed;
+  float eps;
+  int32_t norm_mode;
+  int32_t add_f32;
+  int32_t reserved;
+} dsgx_add_norm;
+int dsgx_finalize_peers_norm(const dsgx_peer_set* peers, int M, int H, void* out_bf16, const dsgx_add_norm* an,
+                             int32_t* status_word, void* stream);
+/* one GPU: v = R + S (mode as dsgx_finalize; S may be null) */
+int dsgx_finalize_add_norm(const float* R, const float* S, int M, int H, int mode, void* out_bf16, const dsgx_add_norm* an,
+                           void* stream);
+
 /* ---- one layer step, router to rounded output --------------------------------------------------------------------
  * The sequence the engines' layer runners issue around the operator (altar1 engine/model/model.cu:308-352: router
  * GEMV, route, moe_decode, then the reduction and the rounding): logits = x wr^T, route, the expert step, and
@@ -244,6 +269,14 @@ typedef struct dsgx_layer_step {
   int32_t reserved;
   void* reserved_ptr; /* with flags bit 1: device memory for [warps][8] u64 phase timestamps of the one-kernel step
                          (a profiling aid; warps = 16 x SM count) */
+  /* RMSNorm in front of the router, fused into the step's first kernel (ds41f engine/kernels/dsk.h:130-135 gemv_bf16_norm,
+     engine/model/model.cu:606-608: ffn_norm + the router's logits + the experts' quantised input in one launch): when
+     norm_w (bf16 [H]) is not null, x is the un-normalised residual stream and the router and the experts see
+     xn = RMSNorm(x; norm_w, norm_eps), norm_mode as dsgx_add_norm.norm_mode; xn_out (bf16 [8][H], optional) gets a copy. */
+  const void* norm_w;
+  void* xn_out;
+  float norm_eps;
+  int32_t norm_mode;
 } dsgx_layer_step;
 int dsgx_moe_layer_decode(const dsgx_moe_shape* shape, const dsgx_layer_w* L, const void* x_bf16, int M,
                           const dsgx_layer_step* step, int finalize, void* stream);

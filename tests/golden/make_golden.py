@@ -135,7 +135,38 @@ def int4_case(name, H, I, E, topk, T, seed, route_scale=2.5):
     print(name, "ok", out.shape)
 
 
+# --------------------------------------------------------------------------------------------------------- RMSNorm
+
+def norm_case(name, T, H, seed):
+    """Both references' RMSNorm on the same rows: ds41f model.py RMSNorm (one rounding) and altar1 glmref.rms_norm."""
+    sys.path[:0] = [os.path.join(REF, "ds41f-4xgx10-switchless/ref/torchref"),
+                    os.path.join(REF, "ds41f-4xgx10-switchless/ref/inference")]
+    import model as M
+    sys.path.insert(0, os.path.join(REF, "altar1-4xgx10-switchless/ref"))
+    import glmref as G
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(T, H, generator=g) * 3.0).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    res = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    with torch.no_grad():
+        torch.set_default_dtype(torch.bfloat16)
+        try:
+            norm = M.RMSNorm(H, 1e-6)
+            norm.weight = torch.nn.Parameter(w.clone(), requires_grad=False)
+            y_model = norm(x)
+            h = res + x                       # the residual add in bf16 (model.py: x = x + ffn(x))
+            y_model_h = norm(h)
+        finally:
+            torch.set_default_dtype(torch.float32)
+        y_glm = G.rms_norm(x, w, 1e-5)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), x=synth.bf16_bits(x), w=synth.bf16_bits(w), res=synth.bf16_bits(res),
+                        y_model=synth.bf16_bits(y_model), y_glm=synth.bf16_bits(y_glm), h=synth.bf16_bits(h),
+                        y_model_h=synth.bf16_bits(y_model_h))
+    print(name, "ok", y_model.shape)
+
+
 if __name__ == "__main__":
+    norm_case("rmsnorm", 6, 4096, 3301)
     fp8_case("fp8_sigmoid_small", 512, 256, 8, 2, 6, "sigmoid", 3101)
     fp8_case("fp8_sigmoid_top6", 1024, 512, 32, 6, 5, "sigmoid", 3102, route_scale=1.5)
     fp8_case("fp8_softmax", 512, 512, 16, 4, 4, "softmax", 3103)

@@ -75,6 +75,24 @@ def _worker(rank, world, port, q):
             dist.all_gather(both, got)
             peer_same = peer_same and bool(torch.equal(both[0], both[1]))
         res["peer_ok"], res["peer_same"], res["peer_status"] = peer_ok, peer_same, int(pr.status.item())
+        # the reduction with the residual add and the next block's RMSNorm in the same kernel: out as before, h and normed
+        # equal to the one-GPU entry point on the all-gathered sums, the same bits on both ranks
+        g = torch.Generator().manual_seed(77)
+        nw = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(dev)
+        resid = torch.randn(4, H, generator=g).to(torch.bfloat16).to(dev)
+        xs = synth.activations(4, H, 340).to(dev)
+        st.run(mine.layer_w(), xs, finalize=False)
+        if rank != 0:
+            st.ys.zero_()
+        mine_parts = torch.stack([st.yr[:4], st.ys[:4]]).clone()
+        gathered = [torch.empty_like(mine_parts) for _ in range(world)]
+        dist.all_gather(gathered, mine_parts)
+        want3 = moe.finalize_add_norm(gathered[0][0] + gathered[1][0], gathered[0][1], nw, resid)
+        yr_p, ys_p = pr.parts(pr.launched + 1)
+        st.run(mine.layer_w(), xs, finalize=False, yr=yr_p, ys=ys_p)
+        got3 = [t.clone() for t in pr.finalize_norm(4, nw, resid)]
+        torch.cuda.synchronize()
+        res["norm_ok"] = all(bool(torch.equal(a, b)) for a, b in zip(got3, want3)) and int(pr.status.item()) == 0
         # the shared expert in parts: each rank computes half of its intermediate channels, its ys is an unrounded partial
         # sum; the reduction adds the parts in rank order, rounds that sum to bf16 once and adds it to the sum of yr
         I2 = 1024
@@ -168,6 +186,7 @@ def test_two_gpus_match_one():
         assert res["prefill"] <= 1e-6, res
         assert res["peer_ok"] and res["peer_same"] and res["peer_status"] == 0, res
         assert res["parts_ok"] and res["parts_status"] == 0, res
+        assert res["norm_ok"], res
         assert res["parts_close"] <= 2e-3 + 2 ** -7, res     # against one GPU: a bf16 rounding flip of the output at most
         assert res["peer_wide_ok"] and res["peer_wide_status"] == 0, res
         assert res["peer_sliced_ok"] and res["peer_sliced_status"] == 0, res

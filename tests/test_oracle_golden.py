@@ -81,3 +81,21 @@ def test_int4_layer_matches_reference_glmref(orc):
     assert np.abs(w[safe] - g["w"][safe]).max() <= 1e-6
     acc, _ = orc.moe_bf16w_layer(g["x"], g["idx"], g["w"], deq, tuple(sh))
     assert rowmax_err(acc, g["out"]) <= 2e-3
+
+
+def test_rmsnorm_matches_both_references(orc):
+    """ds41f's model.py RMSNorm (one rounding) and altar1's glmref.rms_norm (the normalised value rounded first); the
+    references sum the squares in torch's order, so a row's 1/rms may differ in its last bit: bf16 bits equal on all but a
+    few elements, never more than one ulp apart.  Also the residual add in front (h = bf16(res + x))."""
+    g = np.load(os.path.join(GOLD, "rmsnorm.npz"))
+
+    def close(mine, theirs):
+        assert (mine == theirs).mean() > 0.995
+        a, b = mine.astype(np.int32), theirs.astype(np.int32)   # same sign (checked by the bound): bit patterns differ by one ulp
+        assert np.abs(a - b).max() <= 1
+
+    close(orc.rmsnorm(g["x"], g["w"], 1e-6, 0), g["y_model"])
+    close(orc.rmsnorm(g["x"], g["w"], 1e-5, 1), g["y_glm"])
+    out, h, normed = orc.add_norm(orc.bf16_to_f32(g["x"]), g["res"], g["w"], 1e-6, 0)
+    assert (out == g["x"]).all() and (h == g["h"]).all()
+    close(normed, g["y_model_h"])
