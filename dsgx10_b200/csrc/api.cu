@@ -80,19 +80,19 @@ static int check_route_shape(const dsgx_moe_shape* s) {
 static int check_shape(const dsgx_moe_shape* s) {
   if (!s) return DSGX_ERR_ARG;
   if (s->fmt == DSGX_FMT_NVFP4 || s->fmt == DSGX_FMT_RETIRED) return DSGX_ERR_FORMAT;
-  if (s->fmt != DSGX_FMT_FP8 && s->fmt != DSGX_FMT_INT4) return DSGX_ERR_FORMAT;
+  if (!fmt_fp8_family(s->fmt) && s->fmt != DSGX_FMT_INT4) return DSGX_ERR_FORMAT;
   const int rc = check_route_shape(s);
   if (rc) return rc;
   if (s->H < 128 || s->I < 128 || s->H % 128 || s->I % 128) return DSGX_ERR_SHAPE;
   if (s->e_lo < 0 || s->e_hi > s->E || s->e_lo > s->e_hi) return DSGX_ERR_SHAPE;
-  if (s->fmt == DSGX_FMT_FP8 && (s->H > 4096 || s->I > 4096 || s->H % 256 || s->I % 256)) return DSGX_ERR_SHAPE;
+  if (fmt_fp8_family(s->fmt) && (s->H > 4096 || s->I > 4096 || s->H % 256 || s->I % 256)) return DSGX_ERR_SHAPE;
   if (s->fmt == DSGX_FMT_INT4 && (s->H % 512 || s->I % 512)) return DSGX_ERR_SHAPE;
   if (s->sh_lo || s->sh_hi) {  // a part of the shared expert: FP8 decode only, whole pieces of 512 channels
-    if (s->fmt != DSGX_FMT_FP8 || s->sh_lo < 0 || s->sh_hi > s->I || s->sh_lo >= s->sh_hi || s->sh_lo % 512 ||
+    if (!fmt_fp8_family(s->fmt) || s->sh_lo < 0 || s->sh_hi > s->I || s->sh_lo >= s->sh_hi || s->sh_lo % 512 ||
         (s->sh_hi % 512 && s->sh_hi != s->I))
       return DSGX_ERR_SHAPE;
   }
-  if (!(s->swiglu_limit >= 0.f) || (s->swiglu_limit > 0.f && s->fmt != DSGX_FMT_FP8)) return DSGX_ERR_SHAPE;
+  if (!(s->swiglu_limit >= 0.f) || (s->swiglu_limit > 0.f && !fmt_fp8_family(s->fmt))) return DSGX_ERR_SHAPE;
   return DSGX_OK;
 }
 
@@ -243,7 +243,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
   if (((uintptr_t)L->pool & 255) || ((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return DSGX_ERR_ARG;
   const bool sh8 = L->sh.g != nullptr;
   if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds)) return DSGX_ERR_ARG;
-  if (s->fmt == DSGX_FMT_FP8) {
+  if (fmt_fp8_family(s->fmt)) {
     if (L->sh.bg || L->sh.bu || L->sh.bd || L->sh.bgu) return DSGX_ERR_FORMAT;  // an FP8 layer's shared expert is FP8
     if (sh8 && !ys && !cfg->ysum) return DSGX_ERR_ARG;
     DecodeParams p;
@@ -255,6 +255,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.up = cfg->up, p.down = cfg->down;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     p.norm = FrontNorm{nullptr, nullptr, 0.f, 0};
+    p.mx = s->fmt == DSGX_FMT_MXFP4;
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                       cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
@@ -274,6 +275,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     p.norm = FrontNorm{nullptr, nullptr, 0.f, 0};
+    p.mx = 0;
     cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                        cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
@@ -298,7 +300,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
     if (((uintptr_t)L->pool & 255) || ((uintptr_t)st->ws & 255) || ((uintptr_t)x & 15) || ((uintptr_t)st->wr & 15))
       return DSGX_ERR_ARG;
-    const bool fp8 = s->fmt == DSGX_FMT_FP8;
+    const bool fp8 = fmt_fp8_family(s->fmt), mx = s->fmt == DSGX_FMT_MXFP4;
     const bool sh8 = L->sh.g != nullptr, shb = L->sh.bg != nullptr || L->sh.bgu != nullptr;
     if (fp8 ? shb : sh8) return DSGX_ERR_FORMAT;
     if (sh8 && (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds || !st->ys)) return DSGX_ERR_ARG;
@@ -317,6 +319,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
                        (((uintptr_t)st->norm_w | (uintptr_t)st->xn_out) & 15)))
       return DSGX_ERR_ARG;
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
+    p.mx = mx;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
     // the whole step as one persistent kernel: measured faster from three rows up (flags bit 2 forces it, bit 0 forbids it)
@@ -324,7 +327,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
     // (measured): the routing chain is too long to hide behind the little work that needs no routing.
     // flags: bit 0 never the one kernel; bit 2 always; bit 3: route with two small kernels, experts in the one kernel.
     const bool sh_part = p.sh_lo != 0 || p.sh_hi != s->I;  // (a part of the shared expert: the separate kernels)
-    if (fp8 && !sh_part && !(st->flags & 1) && (M >= 3 || (st->flags & 28)) && step_fp8_fits(s->H, s->I, s->E, M)) {
+    if (fp8 && !mx && !sh_part && !(st->flags & 1) && (M >= 3 || (st->flags & 28)) && step_fp8_fits(s->H, s->I, s->E, M)) {
       StepParams sp;
       sp.pre_routed = (st->flags & 8) ? 1 : 0;
       sp.test_no_table = (st->flags & 16) && !sp.pre_routed ? 1 : 0;

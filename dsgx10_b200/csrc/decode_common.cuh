@@ -102,7 +102,7 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
     if (!fmt_ok) tab.bad = DSGX_ERR_FORMAT;
     en.e = e;
     en.g = pool + o[0], en.u = pool + o[1], en.d = pool + o[2];
-    if (fmt == DSGX_FMT_FP8) {
+    if (fmt == DSGX_FMT_FP8) {  // (MXFP4 blocks carry their scales)
       en.sg = reinterpret_cast<const float*>(pool + so[0]);
       en.su = reinterpret_cast<const float*>(pool + so[1]);
       en.sd = reinterpret_cast<const float*>(pool + so[2]);
@@ -115,14 +115,14 @@ DSGX_DEV void build_slot_tab(SlotTab& tab, uint32_t* bm, const int* idx, const f
     int n = 0;
     for (int k = 0; k < 16; ++k) n += __popc(bm[k]);
     if (tab.bad) n = 0;  // refuse the routed work, keep the kernels well-defined
-    const bool has_sh = fmt == DSGX_FMT_FP8 ? sh.g != nullptr : (sh.bg != nullptr || sh.bgu != nullptr);
+    const bool has_sh = fmt_fp8_family(fmt) ? sh.g != nullptr : (sh.bg != nullptr || sh.bgu != nullptr);
     tab.nslots = n, tab.ntot = n + (has_sh ? 1 : 0);
     if (has_sh) {
       SlotEnt& en = tab.ent[n];
       en.e = -1;
 #pragma unroll
       for (int r = 0; r < 8; ++r) en.w[r] = 0.f;
-      if (fmt == DSGX_FMT_FP8) {
+      if (fmt_fp8_family(fmt)) {
         en.g = sh.g, en.u = sh.u, en.d = sh.d, en.sg = sh.gs, en.su = sh.us, en.sd = sh.ds;
       } else {
         en.g = sh.bg ? sh.bg : sh.bgu, en.u = sh.bu, en.d = sh.bd, en.sg = en.su = en.sd = nullptr;
@@ -166,6 +166,50 @@ DSGX_DEV int ord_slot(const SlotTab& tab, int ord) {
 }
 
 DSGX_DEV uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// ---- MXFP4 (e2m1 values, a ue8m0 scale per 32 k) ---------------------------------------------------------------------
+DSGX_DEV uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// Eight e2m1 nibbles (value j at bits 4 j) -> the same eight values as e4m3 bytes (every e2m1 value is an e4m3 value):
+// lo = values 0..3, hi = values 4..7.  Magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 by a byte table, the sign bit by a second one.
+DSGX_DEV void e2m1x8_to_e4m3(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t m = w & 0x77777777u, s = (w >> 3) & 0x11111111u;
+  lo = prmt(0x3C383000u, 0x4C484440u, m) | prmt(0x00008000u, 0u, s);
+  hi = prmt(0x3C383000u, 0x4C484440u, m >> 16) | prmt(0x00008000u, 0u, s >> 16);
+}
+// byte G of four ue8m0 scale bytes as a float: 2^(e - 127) (e = 0: 2^-127, a subnormal)
+template <int G>
+DSGX_DEV float ue8m0_f(uint32_t s4) {
+  const uint32_t b = G == 3 ? (s4 >> 1) & 0x7f800000u : (s4 << (23 - 8 * G)) & 0x7f800000u;
+  return __uint_as_float(max(b, 0x00400000u));
+}
+// One 128-k block of two MXFP4 strips (A rows 0-7 from a, rows 8-15 from b) against an FP8 activation block: four MMAs of
+// 32 k (one scale group each, k = 32 G + 8 t + 0..7 in lane (g, t)), each promoted with its rows' scales:
+// d = ((d_0 s_0 + d_1 s_1) + d_2 s_2) + d_3 s_3 by fused multiply-adds from zero.
+DSGX_DEV void block_mma_mx(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint4 aw = lds128(a + 16 * lane), bw = lds128(b + 16 * lane);
+  const uint32_t sa = *reinterpret_cast<const uint32_t*>(a + 512 + 4 * g), sb = *reinterpret_cast<const uint32_t*>(b + 512 + 4 * g);
+  // the activations of row g at k = 32 G + 8 t .. + 7: block position (k / 64, row, (k / 16) % 4, k % 16)
+  const uint8_t* xr = act + (4 * g + (t >> 1)) * 16 + 8 * (t & 1);
+  const uint2 x0 = *reinterpret_cast<const uint2*>(xr), x1 = *reinterpret_cast<const uint2*>(xr + 32);
+  const uint2 x2 = *reinterpret_cast<const uint2*>(xr + 512), x3 = *reinterpret_cast<const uint2*>(xr + 544);
+  d[0] = d[1] = d[2] = d[3] = 0.f;
+  auto group = [&](uint32_t wa, uint32_t wb, const uint2& x, float fa, float fb) {
+    uint32_t al, ah, bl, bh;
+    e2m1x8_to_e4m3(wa, al, ah), e2m1x8_to_e4m3(wb, bl, bh);
+    float e[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_e4m3(e, al, bl, ah, bh, x.x, x.y);
+    d[0] = fmaf(e[0], fa, d[0]), d[1] = fmaf(e[1], fa, d[1]), d[2] = fmaf(e[2], fb, d[2]), d[3] = fmaf(e[3], fb, d[3]);
+  };
+  group(aw.x, bw.x, x0, ue8m0_f<0>(sa), ue8m0_f<0>(sb));
+  group(aw.y, bw.y, x1, ue8m0_f<1>(sa), ue8m0_f<1>(sb));
+  group(aw.z, bw.z, x2, ue8m0_f<2>(sa), ue8m0_f<2>(sb));
+  group(aw.w, bw.w, x3, ue8m0_f<3>(sa), ue8m0_f<3>(sb));
+}
 
 // ---- the summation order of a unit's K, and its split over warps --------------------------------------------------
 // A unit's sum over K is formed in pieces of kPB 128-k blocks: inside a piece the blocks' promoted partial sums are

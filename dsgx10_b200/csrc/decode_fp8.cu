@@ -90,7 +90,6 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   }
 
   const int upp = p.I / 8;  // units a slot
-  const size_t strip = (size_t)8 * p.H;
   const uint64_t pol = policy_evict_first();  // the weights are read once
   uint32_t issued = 0, consumed = 0;
   bool dead = false;
@@ -165,7 +164,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   // [r rp, (r + 1) rp) of the unit (rp = ceil(NP / split); a run past the last piece streams nothing and only reports).
   auto stream = [&](int first, int end, int split, int sh_units, int u0) {
     const int rp = (NP + split - 1) / split;
-    int pi = first, pc = 0, pnc = -1;  // the producer (lane 0): its item, chunks issued of it, chunks it has
+    int pi = first, pc = 0, pnc = -1, pblk = 1024;  // the producer (lane 0): its item, chunks issued of it, chunks it has
     const uint8_t *pg = nullptr, *pu = nullptr;
     auto issue = [&]() {
       while (pi < end) {
@@ -174,17 +173,18 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
           const int b0 = r * rp * kPB, b1 = min(HB, (r + 1) * rp * kPB);
           const bool shared = unit < sh_units;
           const int slot = shared ? 0 : (unit - sh_units) / upp, i8 = shared ? u0 + unit : (unit - sh_units) % upp;
-          const size_t off = (size_t)i8 * strip + (size_t)b0 * 1024;
+          pblk = !shared && p.mx ? kMxBlk : 1024;  // bytes of a (strip, 128-k block)
+          const size_t off = ((size_t)i8 * HB + b0) * pblk;
           pg = (shared ? p.sh.g : tab.ent[slot].g) + off, pu = (shared ? p.sh.u : tab.ent[slot].u) + off;
           pnc = b1 > b0 ? (b1 - b0) / kKCH : 0, pc = 0;
         }
         if (pc < pnc) {
           uint8_t* st = myring + (issued % kNST) * kUpStage;
           uint64_t* bar = mybar + issued % kNST;
-          mbar_expect_tx(bar, kUpStage);
-          bulk_g2s_hint(st, pg, kKCH * 1024, bar, pol);
-          bulk_g2s_hint(st + kKCH * 1024, pu, kKCH * 1024, bar, pol);
-          pg += kKCH * 1024, pu += kKCH * 1024;
+          mbar_expect_tx(bar, 2 * kKCH * pblk);
+          bulk_g2s_hint(st, pg, kKCH * pblk, bar, pol);
+          bulk_g2s_hint(st + kKCH * 1024, pu, kKCH * pblk, bar, pol);
+          pg += kKCH * pblk, pu += kKCH * pblk;
           ++issued;
           if (++pc == pnc) pi += GW, pnc = -1;
           return;
@@ -202,11 +202,12 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
       const int uidx = unit;
       float tot[4] = {0.f, 0.f, 0.f, 0.f}, pc4[4] = {0.f, 0.f, 0.f, 0.f};  // gate r0, gate r1, up r0, up r1
       if (b1 > b0) {
-        const int srow = (i8 * 8) / 128;
+        const bool mx = !shared && p.mx;
+        const int srow = (i8 * 8) / 128, blk = mx ? kMxBlk : 1024;
         const float* sgp = shared ? p.sh.gs : tab.ent[slot].sg;
         const float* sup = shared ? p.sh.us : tab.ent[slot].su;
-        const float sgl = lane < HB ? __ldg(sgp + (size_t)srow * HB + lane) : 0.f;
-        const float sul = lane < HB ? __ldg(sup + (size_t)srow * HB + lane) : 0.f;
+        const float sgl = mx ? 1.f : lane < HB ? __ldg(sgp + (size_t)srow * HB + lane) : 0.f;  // (MXFP4: scales in the block)
+        const float sul = mx ? 1.f : lane < HB ? __ldg(sup + (size_t)srow * HB + lane) : 0.f;
         const int nc = (b1 - b0) / kKCH;
         for (int c = 0; c < nc; ++c) {
           const uint32_t sidx = consumed % kNST;
@@ -220,7 +221,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
             const int kb = b0 + c * kKCH + b;
             const uint8_t* act = xq + kb * kActBlk;
             float d[4];
-            block_mma(d, st + b * 1024, st + kKCH * 1024 + b * 1024, act, lane);
+            if (mx) block_mma_mx(d, st + b * blk, st + kKCH * 1024 + b * blk, act, lane);
+            else block_mma(d, st + b * 1024, st + kKCH * 1024 + b * 1024, act, lane);
             const float2 xs = *reinterpret_cast<const float2*>(act + 1024 + 8 * t);
             const float sg = __shfl_sync(0xffffffffu, sgl, kb), su = __shfl_sync(0xffffffffu, sul, kb);
             pc4[0] = fmaf(d[0], sg * xs.x, pc4[0]), pc4[1] = fmaf(d[1], sg * xs.y, pc4[1]);
@@ -305,7 +307,6 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   const int split = pick_split(units, NP, GW, kPartUnits);
   const int rp = (NP + split - 1) / split;
   const int end = units * split;
-  const size_t strip = (size_t)8 * p.I;
   const bool sh_any = tab.ntot > tab.nslots;
   const int sh_b0 = p.sh_lo / 128, sh_b1 = p.sh_hi / 128;  // the shared expert's K blocks on this GPU
   uint32_t issued = 0, consumed = 0;
@@ -319,24 +320,25 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
     wslot = sh ? kShSlot : tslot;
     b0 = max(r * rp * kPB, sh ? sh_b0 : 0), b1 = min(min(IB, (r + 1) * rp * kPB), sh ? sh_b1 : IB);
   };
-  int pi = gw, pc = 0, pnc = -1, pwslot = 0, pb = 0;
+  int pi = gw, pc = 0, pnc = -1, pwslot = 0, pb = 0, pblk = 1024;
   const uint8_t* pd = nullptr;
   auto issue = [&]() {
     while (pi < end) {
       if (pnc < 0) {
         int tslot, n16, b0, b1;
         decode(pi, tslot, pwslot, n16, b0, b1);
-        pd = tab.ent[tslot].d + (size_t)(2 * n16) * strip + (size_t)b0 * 1024;
+        pblk = tslot < tab.nslots && p.mx ? kMxBlk : 1024;  // bytes of a (strip, 128-k block)
+        pd = tab.ent[tslot].d + ((size_t)(2 * n16) * IB + b0) * pblk;
         pb = b0, pnc = b1 > b0 ? (b1 - b0) / kKCH : 0, pc = 0;
       }
       if (pc < pnc) {
         uint8_t* st = myring + (issued % kNST) * kDownStage;
         uint64_t* bar = mybar + issued % kNST;
-        mbar_expect_tx(bar, kDownStage);
-        bulk_g2s_hint(st, pd, kKCH * 1024, bar, pol);
-        bulk_g2s_hint(st + kKCH * 1024, pd + strip, kKCH * 1024, bar, pol);
+        mbar_expect_tx(bar, 2 * kKCH * pblk + kKCH * kActBlk);
+        bulk_g2s_hint(st, pd, kKCH * pblk, bar, pol);
+        bulk_g2s_hint(st + kKCH * 1024, pd + (size_t)IB * pblk, kKCH * pblk, bar, pol);
         bulk_g2s(st + 2 * kKCH * 1024, p.ws.hq + ((size_t)pwslot * IB + pb) * kActBlk, kKCH * kActBlk, bar);
-        pd += kKCH * 1024, pb += kKCH;
+        pd += kKCH * pblk, pb += kKCH;
         ++issued;
         if (++pc == pnc) pi += GW, pnc = -1;
         return;
@@ -440,8 +442,9 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
     const int uidx = it / split;
     float tot[4] = {0.f, 0.f, 0.f, 0.f}, pc4[4] = {0.f, 0.f, 0.f, 0.f};
     if (b1 > b0) {
-      const int srow = (n16 * 16) / 128;
-      const float sdl = lane < IB ? __ldg(tab.ent[tslot].sd + (size_t)srow * IB + lane) : 0.f;
+      const bool mx = !sh && p.mx;
+      const int srow = (n16 * 16) / 128, blk = mx ? kMxBlk : 1024;
+      const float sdl = mx ? 1.f : lane < IB ? __ldg(tab.ent[tslot].sd + (size_t)srow * IB + lane) : 0.f;
       const int nc = (b1 - b0) / kKCH, kend = sh ? sh_b1 : IB;
       for (int c = 0; c < nc; ++c) {
         const uint32_t sidx = consumed % kNST;
@@ -455,7 +458,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
           const int kb = b0 + c * kKCH + b;
           const uint8_t* act = st + 2 * kKCH * 1024 + b * kActBlk;
           float d[4];
-          block_mma(d, st + b * 1024, st + kKCH * 1024 + b * 1024, act, lane);
+          if (mx) block_mma_mx(d, st + b * blk, st + kKCH * 1024 + b * blk, act, lane);
+          else block_mma(d, st + b * 1024, st + kKCH * 1024 + b * 1024, act, lane);
           const float2 hs = *reinterpret_cast<const float2*>(act + 1024 + 8 * t);
           const float sd = __shfl_sync(0xffffffffu, sdl, kb);
           pc4[0] = fmaf(d[0], sd * hs.x, pc4[0]), pc4[1] = fmaf(d[1], sd * hs.y, pc4[1]);
@@ -573,8 +577,8 @@ static cudaError_t launch_up_down(const DecodeParams& p, cudaStream_t st, bool p
 cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts,
                               const RouteParams* rp, const float* logits, const float* bias) {
   if ((parts & 1) && !(parts & 4)) {  // (bit 2: the table and the quantised rows of an earlier call are still in ws)
-    cudaError_t e = rp ? launch_stage_route(p, DSGX_FMT_FP8, *rp, x, logits, bias, const_cast<int*>(p.idx), const_cast<float*>(p.w), st, pdl)
-                       : launch_prep(p, DSGX_FMT_FP8, x, st, pdl);
+    cudaError_t e = rp ? launch_stage_route(p, p.mx ? DSGX_FMT_MXFP4 : DSGX_FMT_FP8, *rp, x, logits, bias, const_cast<int*>(p.idx), const_cast<float*>(p.w), st, pdl)
+                       : launch_prep(p, p.mx ? DSGX_FMT_MXFP4 : DSGX_FMT_FP8, x, st, pdl);
     if (e != cudaSuccess) return e;
   }
   return launch_up_down(p, st, pdl, parts & 3);
@@ -584,7 +588,7 @@ cudaError_t launch_decode_fp8(const DecodeParams& p, const __nv_bfloat16* x, cud
 // the routing).
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl) {
-  cudaError_t e = launch_front_route(p, DSGX_FMT_FP8, rp, x, wr, bias, logits, idx, w, st, pdl);
+  cudaError_t e = launch_front_route(p, p.mx ? DSGX_FMT_MXFP4 : DSGX_FMT_FP8, rp, x, wr, bias, logits, idx, w, st, pdl);
   if (e != cudaSuccess) return e;
   return launch_up_down(p, st, pdl, 3);
 }

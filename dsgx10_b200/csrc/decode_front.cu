@@ -19,7 +19,7 @@ namespace {
 // Other formats: one thread a (16-value group, row) of the bf16 tile.
 DSGX_DEV void stage_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t* __restrict__ out, int fmt, int cta,
                       const RowNorm& nrm = RowNorm{nullptr, nullptr, 0}, __nv_bfloat16* xn_out = nullptr) {
-  if (fmt == DSGX_FMT_FP8) {
+  if (fmt_fp8_family((uint32_t)fmt)) {
     const int gw = cta * 8 + (threadIdx.x >> 5);
     const int j = gw >> 3, r = gw & 7;
     if (j < H / 128) quant_x_block(x, M, H, out, j, r, threadIdx.x & 31, nrm, xn_out);
@@ -127,7 +127,7 @@ TabArgs tab_args(const DecodeParams& p, uint32_t fmt) {
 }
 
 int stage_ctas(const DecodeParams& p, uint32_t fmt) {
-  return fmt == DSGX_FMT_FP8 ? (p.H / 128 * 8 + 7) / 8 : (p.H / 16 * rows_pow2(p.M) + 255) / 256;
+  return fmt_fp8_family(fmt) ? (p.H / 128 * 8 + 7) / 8 : (p.H / 16 * rows_pow2(p.M) + 255) / 256;
 }
 
 }  // namespace

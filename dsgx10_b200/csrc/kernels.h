@@ -12,6 +12,9 @@ namespace dsgx {
 // A quantised activation block: 128 k of up to 8 rows as e4m3 in MMA operand order (1024 B) + the rows' f32 scales.
 constexpr int kActBlk = 1024 + 32;
 constexpr int kMaxRows = DSGX_MAX_ROWS;
+constexpr int kMxBlk = 544;  // bytes of an MXFP4 block: 8 rows x 128 k of e2m1 + 8 x 4 scale bytes
+// FP8 activations and FP8 shared expert: the FP8 kernels serve the layer
+inline __host__ __device__ bool fmt_fp8_family(uint32_t fmt) { return fmt == DSGX_FMT_FP8 || fmt == DSGX_FMT_MXFP4; }
 constexpr int kMaxTopK = 8;
 constexpr int kMaxSlots = kMaxRows * kMaxTopK + 1;  // the union of a step's picks + the shared expert
 
@@ -88,6 +91,7 @@ struct DecodeParams {
   float limit;     // the SwiGLU clamp (0: none)
   int sh_lo, sh_hi;  // the shared expert's intermediate channels this GPU computes (multiples of 512; the whole: 0, I)
   FrontNorm norm;
+  int mx;  // 1: the routed experts are DSGX_FMT_MXFP4 (the shared expert, the activations and the sums as FP8's)
 };
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                              const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl);

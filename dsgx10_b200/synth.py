@@ -116,6 +116,115 @@ class Fp8Layer:
         return 3 * self.I * self.H + 3 * (self.I // 128) * (self.H // 128) * 4
 
 
+# ---------------------------------------------------------------------------------------------------- MXFP4 tensors
+
+def quant_mx4(w):
+    """f32 [N][K] -> (e2m1 nibbles uint8 [N][K/2], the lower k in the low nibble; ue8m0 scale bytes uint8 [N][K/32]):
+    scale = 2^ceil(log2(amax / 6)) per 32 along K, values rounded to nearest, ties to the even mantissa (ds41f
+    ref/torchref/kernel.py:20-50, 86-100: the quantiser of its fp4 tensors)."""
+    N, K = w.shape
+    blk = w.float().view(N, K // 32, 32)
+    v = blk.abs().amax(-1).clamp_min(6 * 2.0 ** -126) * torch.tensor(1.0 / 6.0, dtype=torch.float32, device=w.device)
+    bits = v.view(torch.int32)
+    e = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).to(torch.int32)          # the biased exponent of 2^ceil(log2 v)
+    s = torch.ldexp(torch.ones_like(v), (e - 127).float())
+    a = (blk / s[..., None]).clamp(-6.0, 6.0)
+    mag = a.abs()
+    code = torch.zeros_like(mag, dtype=torch.uint8)
+    for thr, incl in ((0.25, False), (0.75, True), (1.25, False), (1.75, True), (2.5, False), (3.5, True), (5.0, False)):
+        code += ((mag >= thr) if incl else (mag > thr)).to(torch.uint8)
+    code |= ((a < 0) | ((a == 0) & torch.signbit(a))).to(torch.uint8) << 3
+    code = code.view(N, K // 2, 2)
+    return (code[..., 0] | code[..., 1] << 4).contiguous(), e.to(torch.uint8).contiguous()
+
+
+def tile_mx4(q, s):
+    """canonical MXFP4 (nibble bytes [N][K/2], ue8m0 [N][K/32]) -> blocks of 8 rows x 128 k, 544 B, [N/8][K/128]:
+    [32 lanes 4 g + t][4 groups G][4 bytes: k = 128 b + 32 G + 8 t + 0..7 of row 8 n8 + g], then [8 g][4 G] scales."""
+    N, K = q.shape[0], q.shape[1] * 2
+    v = q.view(N // 8, 8, K // 128, 4, 4, 4)                 # n8, g, b, G, t, 4 bytes
+    vals = v.permute(0, 2, 1, 4, 3, 5).contiguous().view(N // 8, K // 128, 512)   # n8, b, g, t, G, bytes
+    sc = s.view(N // 8, 8, K // 128, 4).permute(0, 2, 1, 3).contiguous().view(N // 8, K // 128, 32)
+    return torch.cat([vals, sc], dim=-1).contiguous().view(-1)
+
+
+def untile_mx4(m, N, K):
+    blk = m.view(N // 8, K // 128, 544)
+    vals = blk[..., :512].reshape(N // 8, K // 128, 8, 4, 4, 4).permute(0, 2, 1, 4, 3, 5).contiguous().view(N, K // 2)
+    sc = blk[..., 512:].reshape(N // 8, K // 128, 8, 4).permute(0, 2, 1, 3).contiguous().view(N, K // 32)
+    return vals, sc
+
+
+def mx4_mat_bytes(N, K):
+    return (N // 8) * (K // 128) * 544
+
+
+class Mx4Layer(Fp8Layer):
+    """One MXFP4 layer as ds41f stores it: `E` routed experts in e2m1 with a ue8m0 scale per 32 along K, and an FP8
+    (128x128 block-scaled) shared expert, in one device pool."""
+
+    def __init__(self, H, I, E, seed, device="cpu", shared=True, std=0.02, e_range=None, experts=None):
+        """experts: the routed ids to generate (default: all of e_range); the others' descriptors stay empty."""
+        self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_MXFP4
+        self.device = torch.device(device)
+        mat8, sc8 = I * H, al256((I // 128) * (H // 128) * 4)
+        mat4 = al256(mx4_mat_bytes(I, H))           # (gate, up and down have the same number of bytes)
+        lo, hi = e_range if e_range is not None else (0, E)
+        ids = list(range(lo, hi)) if experts is None else sorted(experts)
+        self.pool = torch.empty(max(len(ids) * 3 * mat4 + (3 * mat8 + 3 * sc8 if shared else 0), 256), dtype=torch.uint8,
+                                device=self.device)
+        self.desc_host = (_lib.MatDesc * (E * 3))()
+        self._off = {}
+        for n, e in enumerate(ids):
+            for m in range(3):
+                N, K = (H, I) if m == 2 else (I, H)
+                g = _gen(self.device, seed * 1000003 + e * 3 + m)
+                w = torch.randn(N, K, generator=g, device=self.device, dtype=torch.float32) * std
+                off = (n * 3 + m) * mat4
+                self.pool[off:off + mx4_mat_bytes(N, K)] = tile_mx4(*quant_mx4(w))
+                self._off[(e, m)] = (off, 0)
+                d = self.desc_host[e * 3 + m]
+                d.off, d.s2, d.fmt = off, 1.0, _lib.FMT_MXFP4
+        if shared:
+            base = len(ids) * 3 * mat4
+            for m in range(3):
+                N, K = (H, I) if m == 2 else (I, H)
+                g = _gen(self.device, seed * 1000003 + E * 3 + m)
+                w = torch.randn(N, K, generator=g, device=self.device, dtype=torch.float32) * std
+                q, sc = quant_fp8_128(w)
+                off, soff = base + m * mat8, base + 3 * mat8 + m * sc8
+                self.pool[off:off + mat8] = tile_fp8(q)
+                self.pool[soff:soff + sc.numel() * 4] = sc.view(-1).view(torch.uint8)
+                self._off[(E, m)] = (off, soff)
+        self.desc = torch.frombuffer(bytearray(bytes(self.desc_host)), dtype=torch.uint8).to(self.device)
+        self.shared = shared
+
+    def layer_w(self):
+        L = super().layer_w()
+        L.fmt = _lib.FMT_MXFP4
+        return L
+
+    def canonical(self, e):
+        """Routed expert e: (wg, sg, wu, su, wd, sd) = nibble bytes [N][K/2] and ue8m0 bytes [N][K/32]; e == E: the FP8
+        shared expert's tuple (Fp8Layer.canonical)."""
+        if e == self.E:
+            return super().canonical(e)
+        out = []
+        for m in range(3):
+            N, K = (self.H, self.I) if m == 2 else (self.I, self.H)
+            off, _ = self._off[(e, m)]
+            q, sc = untile_mx4(self.pool[off:off + mx4_mat_bytes(N, K)], N, K)
+            out += [q.cpu().numpy(), sc.cpu().numpy()]
+        return tuple(out)
+
+    def expert_bytes(self):
+        """Algorithmic bytes of one routed expert: three matrices of e2m1 values with their scale bytes."""
+        return 3 * mx4_mat_bytes(self.I, self.H)
+
+    def shared_bytes(self):
+        return 3 * self.I * self.H + 3 * (self.I // 128) * (self.H // 128) * 4
+
+
 # ---------------------------------------------------------------------------------------------- router / activations
 
 def router_weights(E, H, seed, device="cpu", std=0.02):

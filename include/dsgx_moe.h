@@ -40,7 +40,15 @@ typedef enum dsgx_status {
 /* Expert formats.  Tags 2 and 3 are the reference's (altar1 engine/experts/experts.h:39); tag 4 is this library's
  * routed FP8 format: the reference's "tile_fp8" lane order (experts.h:66-70, layout.h:108-119) for the e4m3 values and
  * f32 scales [N/128][K/128] row-major. */
-enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF16 = 3, DSGX_FMT_FP8 = 4 };
+enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF16 = 3, DSGX_FMT_FP8 = 4, DSGX_FMT_MXFP4 = 5 };
+/* Tag 5, DSGX_FMT_MXFP4: ds41f's routed expert format (ref/inference/model.py expert_dtype "fp4" over
+ * ref/torchref/kernel.py:111-138: e2m1 values with one ue8m0 scale per 32 along K; engine/kernels/dsk.h:176-210), "W4A8":
+ * the activations are quantised as for DSGX_FMT_FP8 (e4m3 per 128 with an f32 scale), W = e2m1 * 2^(scale - 127), the
+ * rest of the contract is DSGX_FMT_FP8's; the layer's shared expert is FP8 (dsgx_shared_w.g/u/d), as ds41f's.  Decode
+ * only.  Layout of a matrix [N][K] (N a multiple of 8, K of 128), made by dsgx10_b200/weights.py pack_mx4:
+ *   [N/8 strips][K/128 blocks] of 544 bytes: [32 lanes (g = lane / 4, t = lane % 4)][4 groups G][4 bytes] = the 8
+ *   values of row 8 strip + g at k = 128 block + 32 G + 8 t + 0..7, two a byte, the lower k in the low nibble (the
+ *   checkpoint's own nibble order), then [8 rows g][4 groups G] the ue8m0 scale bytes.  rsv is zero. */
 /* scores of the router: sigmoid and softmax (altar1 engine/experts/formats.cuh:142-163; ds41f ref/inference/model.py:812-818),
  * sqrt(softplus(l)) (ds41f engine/kernels/common.cuh:264-287, the only score dsk::router_topk has) */
 enum { DSGX_SCORE_SIGMOID = 0, DSGX_SCORE_SOFTMAX = 1, DSGX_SCORE_SQRTSOFTPLUS = 2 };
@@ -92,7 +100,7 @@ typedef struct dsgx_moe_shape {
   int32_t score_fn;     /* DSGX_SCORE_* */
   int32_t norm_topk;    /* 1: weights = s / (sum + 1e-20) * route_scale; 0: s * route_scale */
   float route_scale;
-  uint32_t fmt;         /* DSGX_FMT_FP8 or DSGX_FMT_INT4 */
+  uint32_t fmt;         /* DSGX_FMT_FP8, DSGX_FMT_INT4 or DSGX_FMT_MXFP4 */
   int32_t e_lo, e_hi;   /* this GPU's experts [e_lo, e_hi) (expert parallelism: ds41f ref/inference/model.py:863-870) */
   int32_t sh_lo, sh_hi; /* FP8 decode: the shared expert's intermediate channels [sh_lo, sh_hi) this GPU computes
                            (multiples of 512; both 0: all of them).  The ranks of an expert-parallel step split the shared

@@ -430,13 +430,49 @@ static void fp8_gemv(const uint8_t* qx, const float* sx, const uint8_t* qw, cons
 
 static inline float silu_f(float g) { return g / (1.f + expf(-g)); }
 
-/* One FP8 expert on one row (model.py:841-851): x bf16 [H] -> y [H] as bf16-rounded floats.
+/* MXFP4 weights (ds41f ref/torchref/kernel.py:16, 111-118 dequant_fp4_weight): e2m1 nibbles [N][K/2], value k of row n in
+ * byte k/2, the even k in the low nibble; one ue8m0 scale byte per 32 along K, W = value * 2^(byte - 127).
+ * y[n] = bf16(sum_k (f32(qx[k]) sx[k/128]) * W[n][k]) (kernel.py:135-138 fp4_gemm over the fp8 activations of
+ * model.py:187-196), summed in double like fp8_gemv. */
+static const float g_e2m1[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+static void mx4_gemv(const uint8_t* qx, const float* sx, const uint8_t* qw, const uint8_t* sw, int N, int K, float* y,
+                     int round_bf16) {
+  float* xd = (float*)malloc(sizeof(float) * K);
+  for (int k = 0; k < K; ++k) xd[k] = g_e4m3_lut[qx[k]] * sx[k / 128];
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    const uint8_t* wr = qw + (size_t)n * (K / 2);
+    const uint8_t* swr = sw + (size_t)n * (K / 32);
+    double acc = 0.0;
+    for (int gq = 0; gq < K / 32; ++gq) {
+      const float s = ldexpf(1.f, (int)swr[gq] - 127);
+      double a = 0.0;
+      for (int i = 0; i < 32; ++i) {
+        const int k = 32 * gq + i;
+        const float wv = g_e2m1[(wr[k / 2] >> (4 * (k & 1))) & 15] * s;
+        a += (double)xd[k] * (double)wv;
+      }
+      acc += a;
+    }
+    y[n] = round_bf16 ? bf16r((float)acc) : (float)acc;
+  }
+  free(xd);
+}
+ORC_API void orc_mx4_dequant(const uint8_t* qw, const uint8_t* sw, int N, int K, float* out) {
+  for (int n = 0; n < N; ++n)
+    for (int k = 0; k < K; ++k)
+      out[(size_t)n * K + k] = g_e2m1[(qw[(size_t)n * (K / 2) + k / 2] >> (4 * (k & 1))) & 15] *
+                               ldexpf(1.f, (int)sw[(size_t)n * (K / 32) + k / 32] - 127);
+}
+
+/* One expert on one row (model.py:841-851): x bf16 [H] -> y [H] as bf16-rounded floats.  mx = 0: FP8 weights (e4m3
+ * [N][K], f32 scales [N/128][K/128]); mx = 1: MXFP4 weights (nibbles, ue8m0 bytes); the activations, the roundings and
+ * the SwiGLU are the same.
  * wroute: the routing weight applied to h in f32 before its rounding, or a negative number for "none" (shared expert).
  * limit > 0: the bf16 gate is clamped from above to limit and the bf16 up to +-limit before silu (model.py:845-847;
  * ds41f engine/kernels/prefill.cu:153-158 fixes limit = 10).  h_out (optional): the bf16-rounded h [I] as floats. */
-ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* wg, const float* sg, const uint8_t* wu,
-                                const float* su, const uint8_t* wd, const float* sd, float wroute, float limit, float* y,
-                                float* h_out) {
+static void expert_row(int mx, const uint16_t* x, int H, int I, const uint8_t* wg, const void* sg, const uint8_t* wu,
+                       const void* su, const uint8_t* wd, const void* sd, float wroute, float limit, float* y, float* h_out) {
   lut_init();
   float* xf = (float*)malloc(sizeof(float) * (H > I ? H : I));
   uint8_t* q = (uint8_t*)malloc(H > I ? H : I);
@@ -445,8 +481,8 @@ ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* 
   float* u = (float*)malloc(sizeof(float) * I);
   for (int k = 0; k < H; ++k) xf[k] = orc_bf16_to_f32(x[k]);
   orc_act_quant(xf, H, q, s);
-  fp8_gemv(q, s, wg, sg, I, H, g, 1);
-  fp8_gemv(q, s, wu, su, I, H, u, 1);
+  if (mx) mx4_gemv(q, s, wg, (const uint8_t*)sg, I, H, g, 1), mx4_gemv(q, s, wu, (const uint8_t*)su, I, H, u, 1);
+  else fp8_gemv(q, s, wg, (const float*)sg, I, H, g, 1), fp8_gemv(q, s, wu, (const float*)su, I, H, u, 1);
   for (int i = 0; i < I; ++i) {
     float gv = g[i], uv = u[i];
     if (limit > 0.f) {
@@ -459,8 +495,19 @@ ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* 
     if (h_out) h_out[i] = xf[i];
   }
   orc_act_quant(xf, I, q, s);
-  fp8_gemv(q, s, wd, sd, H, I, y, 1);
+  if (mx) mx4_gemv(q, s, wd, (const uint8_t*)sd, H, I, y, 1);
+  else fp8_gemv(q, s, wd, (const float*)sd, H, I, y, 1);
   free(xf), free(q), free(s), free(g), free(u);
+}
+ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* wg, const float* sg, const uint8_t* wu,
+                                const float* su, const uint8_t* wd, const float* sd, float wroute, float limit, float* y,
+                                float* h_out) {
+  expert_row(0, x, H, I, wg, sg, wu, su, wd, sd, wroute, limit, y, h_out);
+}
+ORC_API void orc_mx4_expert_row(const uint16_t* x, int H, int I, const uint8_t* wg, const uint8_t* sg, const uint8_t* wu,
+                                const uint8_t* su, const uint8_t* wd, const uint8_t* sd, float wroute, float limit, float* y,
+                                float* h_out) {
+  expert_row(1, x, H, I, wg, sg, wu, su, wd, sd, wroute, limit, y, h_out);
 }
 
 /* A whole FP8 layer (model.py:889-904).  Expert e's canonical tensors: wg[e], wu[e] e4m3 [I][H] with scales
@@ -469,10 +516,10 @@ ORC_API void orc_fp8_expert_row(const uint16_t* x, int H, int I, const uint8_t* 
  * expert is added when with_shared.  acc [T][H] f32 (before the final rounding), out [T][H] bf16 (may be NULL).
  * limit: the SwiGLU clamp of orc_fp8_expert_row (0: none).  pickmax [T][H] (may be NULL): per element the largest
  * magnitude among the outputs that were added there (what one bf16 rounding flip of one of them can change). */
-ORC_API int orc_moe_fp8_layer(const uint16_t* x, const int32_t* idx, const float* w, int T, int H, int I, int E,
-                              int topk, const uint8_t* const* wg, const float* const* sg, const uint8_t* const* wu,
-                              const float* const* su, const uint8_t* const* wd, const float* const* sd, int e_lo,
-                              int e_hi, int with_shared, float limit, float* acc, uint16_t* out, float* pickmax) {
+static int moe_layer(int mx, const uint16_t* x, const int32_t* idx, const float* w, int T, int H, int I, int E, int topk,
+                     const uint8_t* const* wg, const void* const* sg, const uint8_t* const* wu, const void* const* su,
+                     const uint8_t* const* wd, const void* const* sd, int e_lo, int e_hi, int with_shared, float limit,
+                     float* acc, uint16_t* out, float* pickmax) {
   if (H % 128 || I % 128) return -1;
   lut_init();
   float* y = (float*)malloc(sizeof(float) * H);
@@ -482,8 +529,8 @@ ORC_API int orc_moe_fp8_layer(const uint16_t* x, const int32_t* idx, const float
     for (int t = 0; t < T; ++t)
       for (int j = 0; j < topk; ++j)
         if (idx[(size_t)t * topk + j] == e) {
-          orc_fp8_expert_row(x + (size_t)t * H, H, I, wg[e], sg[e], wu[e], su[e], wd[e], sd[e], w[(size_t)t * topk + j],
-                             limit, y, NULL);
+          expert_row(mx, x + (size_t)t * H, H, I, wg[e], sg[e], wu[e], su[e], wd[e], sd[e], w[(size_t)t * topk + j], limit,
+                     y, NULL);
           float* a = acc + (size_t)t * H;
           for (int n = 0; n < H; ++n) a[n] += y[n];
           if (pickmax)
@@ -491,7 +538,7 @@ ORC_API int orc_moe_fp8_layer(const uint16_t* x, const int32_t* idx, const float
         }
   if (with_shared && wg[E])
     for (int t = 0; t < T; ++t) {
-      orc_fp8_expert_row(x + (size_t)t * H, H, I, wg[E], sg[E], wu[E], su[E], wd[E], sd[E], -1.f, limit, y, NULL);
+      expert_row(0, x + (size_t)t * H, H, I, wg[E], sg[E], wu[E], su[E], wd[E], sd[E], -1.f, limit, y, NULL); /* FP8 */
       float* a = acc + (size_t)t * H;
       for (int n = 0; n < H; ++n) a[n] += y[n];
       if (pickmax)
@@ -501,6 +548,22 @@ ORC_API int orc_moe_fp8_layer(const uint16_t* x, const int32_t* idx, const float
     for (size_t i = 0; i < (size_t)T * H; ++i) out[i] = orc_f32_to_bf16(acc[i]);
   free(y);
   return 0;
+}
+
+ORC_API int orc_moe_fp8_layer(const uint16_t* x, const int32_t* idx, const float* w, int T, int H, int I, int E,
+                              int topk, const uint8_t* const* wg, const float* const* sg, const uint8_t* const* wu,
+                              const float* const* su, const uint8_t* const* wd, const float* const* sd, int e_lo,
+                              int e_hi, int with_shared, float limit, float* acc, uint16_t* out, float* pickmax) {
+  return moe_layer(0, x, idx, w, T, H, I, E, topk, wg, (const void* const*)sg, wu, (const void* const*)su, wd,
+                   (const void* const*)sd, e_lo, e_hi, with_shared, limit, acc, out, pickmax);
+}
+/* The same with MXFP4 routed experts (scale pointers: ue8m0 bytes) and an FP8 shared expert at index E (f32 scales): a
+ * ds41f layer (model.py:872-887: routed experts in fp4, the shared expert in the default fp8). */
+ORC_API int orc_moe_mx4_layer(const uint16_t* x, const int32_t* idx, const float* w, int T, int H, int I, int E,
+                              int topk, const uint8_t* const* wg, const void* const* sg, const uint8_t* const* wu,
+                              const void* const* su, const uint8_t* const* wd, const void* const* sd, int e_lo, int e_hi,
+                              int with_shared, float limit, float* acc, uint16_t* out, float* pickmax) {
+  return moe_layer(1, x, idx, w, T, H, I, E, topk, wg, sg, wu, su, wd, sd, e_lo, e_hi, with_shared, limit, acc, out, pickmax);
 }
 
 /* ------------------------------------------------------------------------------------------------- INT4-g32 FFN */

@@ -209,10 +209,29 @@ def fp8_expert_row(x_bf16, wg, sg, wu, su, wd, sd, wroute=None, swiglu_limit=0.0
     return y, h
 
 
+def mx4_expert_row(x_bf16, wg, sg, wu, su, wd, sd, wroute=None, swiglu_limit=0.0):
+    """One MXFP4 expert (nibble bytes [N][K/2], ue8m0 bytes [N][K/32]) on one row: (y [H], h [I]) as bf16-rounded f32."""
+    I, H = wg.shape[0], wg.shape[1] * 2
+    y, h = np.empty(H, np.float32), np.empty(I, np.float32)
+    x_bf16 = _c(x_bf16, np.uint16)
+    lib().orc_mx4_expert_row(_p(x_bf16), H, I, _p(wg), _p(sg), _p(wu), _p(su), _p(wd), _p(sd),
+                             C.c_float(-1.0 if wroute is None else wroute), C.c_float(swiglu_limit), _p(y), _p(h))
+    return y, h
+
+
+def mx4_dequant(q, s):
+    q, s = _c(q, np.uint8), _c(s, np.uint8)
+    N, K = q.shape[0], q.shape[1] * 2
+    out = np.empty((N, K), np.float32)
+    lib().orc_mx4_dequant(_p(q), _p(s), N, K, _p(out))
+    return out
+
+
 def moe_fp8_layer(x_bf16, idx, w, experts, shared, e_lo=0, e_hi=None, with_shared=True, swiglu_limit=0.0,
-                  pickmax=False):
+                  pickmax=False, mx4=False):
     """experts: dict e -> (wg, sg, wu, su, wd, sd) canonical numpy arrays (only the picked experts need be present);
-    shared: the same tuple or None.  Returns (acc f32 [T][H], out bf16 bits [T][H]) and, with pickmax, a third array
+    shared: the same tuple or None.  mx4: the routed experts are MXFP4 (nibble bytes, ue8m0 bytes), the shared one FP8.
+    Returns (acc f32 [T][H], out bf16 bits [T][H]) and, with pickmax, a third array
     f32 [T][H]: per element the largest magnitude among the bf16 outputs that were added there."""
     x_bf16, idx, w = _c(x_bf16, np.uint16), _c(idx, np.int32), _c(w, np.float32)
     T, H = x_bf16.shape
@@ -229,8 +248,9 @@ def moe_fp8_layer(x_bf16, idx, w, experts, shared, e_lo=0, e_hi=None, with_share
     out = np.empty((T, H), np.uint16)
     pa = [_ptr_array(c) for c in cols]
     pm = np.empty((T, H), np.float32) if pickmax else None
-    rc = lib().orc_moe_fp8_layer(_p(x_bf16), _p(idx), _p(w), T, H, I, E, k, pa[0], pa[1], pa[2], pa[3], pa[4], pa[5],
-                                 e_lo, e_hi, int(with_shared), C.c_float(swiglu_limit), _p(acc), _p(out), _p(pm))
+    fn = lib().orc_moe_mx4_layer if mx4 else lib().orc_moe_fp8_layer
+    rc = fn(_p(x_bf16), _p(idx), _p(w), T, H, I, E, k, pa[0], pa[1], pa[2], pa[3], pa[4], pa[5], e_lo, e_hi,
+            int(with_shared), C.c_float(swiglu_limit), _p(acc), _p(out), _p(pm))
     assert rc == 0
     return (acc, out, pm) if pickmax else (acc, out)
 

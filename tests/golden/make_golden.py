@@ -38,7 +38,9 @@ def crc(*arrays):
 
 # ------------------------------------------------------------------------------------------------------------- FP8
 
-def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0, swiglu_limit=0.0, x_scale=1.0):
+def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0, swiglu_limit=0.0, x_scale=1.0, mx4=False):
+    """mx4: the routed experts in ds41f's own format (expert_dtype "fp4": e2m1 with a ue8m0 scale per 32), the shared
+    expert FP8."""
     sys.path[:0] = [os.path.join(REF, "ds41f-4xgx10-switchless/ref/torchref"),
                     os.path.join(REF, "ds41f-4xgx10-switchless/ref/inference")]
     import model as M  # the reference's model.py; `kernel` resolves to torchref/kernel.py
@@ -48,11 +50,12 @@ def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0, swiglu_limit=
     torch.set_default_dtype(torch.bfloat16)
     try:
         args = M.ModelArgs(dim=H, moe_inter_dim=I, n_routed_experts=E, n_activated_experts=topk, score_func=score,
-                           route_scale=route_scale, expert_dtype=None, n_layers=1, swiglu_limit=swiglu_limit)
+                           route_scale=route_scale, expert_dtype="fp4" if mx4 else None, n_layers=1,
+                           swiglu_limit=swiglu_limit)
         moe = M.MoE(0, args)
     finally:
         torch.set_default_dtype(torch.float32)
-    layer = synth.Fp8Layer(H, I, E, seed, device="cpu")
+    layer = (synth.Mx4Layer if mx4 else synth.Fp8Layer)(H, I, E, seed, device="cpu")
     wr = synth.router_weights(E, H, seed + 2000)
     x = synth.activations(T, H, seed + 1000)
     if x_scale != 1.0:  # (large activations, so that the SwiGLU clamp has something to clamp)
@@ -66,6 +69,11 @@ def fp8_case(name, H, I, E, topk, T, score, seed, route_scale=1.0, swiglu_limit=
             wg, sg, wu, su, wd, sd = layer.canonical(e)
             sums.append(crc(wg, sg, wu, su, wd, sd))
             for lin, q, s in ((ex.w1, wg, sg), (ex.w3, wu, su), (ex.w2, wd, sd)):
+                if mx4 and e < E:
+                    lin.weight = torch.nn.Parameter(torch.from_numpy(q.copy()).view(torch.float4_e2m1fn_x2), requires_grad=False)
+                    lin.weight.scale = lin.scale = torch.nn.Parameter(torch.from_numpy(s.copy()).view(torch.float8_e8m0fnu),
+                                                                      requires_grad=False)
+                    continue
                 lin.weight = torch.nn.Parameter(torch.from_numpy(q.copy()).view(torch.float8_e4m3fn), requires_grad=False)
                 lin.weight.scale = lin.scale = torch.nn.Parameter(torch.from_numpy(s.copy()), requires_grad=False)
         torch.set_default_dtype(torch.bfloat16)
@@ -172,4 +180,7 @@ if __name__ == "__main__":
     fp8_case("fp8_softmax", 512, 512, 16, 4, 4, "softmax", 3103)
     # ds41f's own router score and its SwiGLU clamp (ref/config.json: scoring_func sqrtsoftplus, swiglu_limit 10)
     fp8_case("fp8_sqrtsoftplus_clamp", 512, 256, 16, 6, 5, "sqrtsoftplus", 3104, route_scale=1.5, swiglu_limit=10.0, x_scale=48.0)
+    # ds41f's routed format: MXFP4 experts, FP8 shared expert, its score and clamp
+    fp8_case("mx4_sqrtsoftplus_clamp", 512, 256, 16, 6, 5, "sqrtsoftplus", 3105, route_scale=1.5, swiglu_limit=10.0, x_scale=32.0,
+             mx4=True)
     int4_case("int4_sigmoid", 1024, 512, 16, 8, 5, 3201)

@@ -18,13 +18,15 @@ def _crc(*arrays):
     return np.uint32(c)
 
 
-@pytest.mark.parametrize("name", ["fp8_sigmoid_small", "fp8_sigmoid_top6", "fp8_softmax", "fp8_sqrtsoftplus_clamp"])
+@pytest.mark.parametrize("name", ["fp8_sigmoid_small", "fp8_sigmoid_top6", "fp8_softmax", "fp8_sqrtsoftplus_clamp",
+                                  "mx4_sqrtsoftplus_clamp"])
 def test_fp8_layer_matches_reference_model_py(orc, name):
     from dsgx10_b200 import synth
     g = np.load(os.path.join(GOLD, name + ".npz"))
     H, I, E, topk, T, score, seed = (int(v) for v in g["meta"])
     limit = float(g["swiglu_limit"])   # (the last fixture: ds41f's sqrt(softplus) score and its SwiGLU clamp at 10)
-    layer = synth.Fp8Layer(H, I, E, seed, device="cpu")
+    mx4 = name.startswith("mx4")   # (ds41f's layer: MXFP4 routed experts, FP8 shared expert)
+    layer = (synth.Mx4Layer if mx4 else synth.Fp8Layer)(H, I, E, seed, device="cpu")
     experts = {e: layer.canonical(e) for e in range(E + 1)}
     if not all(_crc(*experts[e]) == g["weights_crc"][e] for e in range(E + 1)):
         pytest.skip("this torch build's CPU generator gives other weights than the fixture's (checksum)")
@@ -42,7 +44,8 @@ def test_fp8_layer_matches_reference_model_py(orc, name):
     assert (idx2 == g["idx"]).all()
     # one routed expert and the shared expert on row 0 (bf16 outputs): a rounding flip at most
     e0 = int(g["e0"])
-    y0, _ = orc.fp8_expert_row(x[0], *experts[e0], wroute=float(g["w"][0, 0]), swiglu_limit=limit)
+    row = orc.mx4_expert_row if mx4 else orc.fp8_expert_row
+    y0, _ = row(x[0], *experts[e0], wroute=float(g["w"][0, 0]), swiglu_limit=limit)
     ysh, _ = orc.fp8_expert_row(x[0], *experts[E], swiglu_limit=limit)
     if limit:  # the clamp is at work in this fixture: without it the outputs are far off
         y_free, _ = orc.fp8_expert_row(x[0], *experts[E])
@@ -53,7 +56,7 @@ def test_fp8_layer_matches_reference_model_py(orc, name):
         assert (orc.f32_to_bf16(mine) == orc.f32_to_bf16(theirs)).mean() > 0.98
     # the whole layer with the reference's routing
     shared = experts.pop(E)
-    acc, out = orc.moe_fp8_layer(x, g["idx"], g["w"], experts, shared, swiglu_limit=limit)
+    acc, out = orc.moe_fp8_layer(x, g["idx"], g["w"], experts, shared, swiglu_limit=limit, mx4=mx4)
     want = orc.bf16_to_f32(g["out"])
     assert rowmax_err(orc.bf16_to_f32(out), want) <= 2e-3 + 2 ** -8
     assert (out == g["out"]).mean() > 0.97

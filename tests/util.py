@@ -19,7 +19,8 @@ def oracle_fp8_layer(orc, layer, x_bits, idx, w, e_lo=0, e_hi=None, with_shared=
         experts = {picked[0]: layer.canonical(picked[0])}
     shared = layer.canonical(layer.E) if (layer.shared and with_shared) else None
     return orc.moe_fp8_layer(x_bits, idx, w, experts, shared, e_lo=e_lo, e_hi=e_hi if e_hi is not None else layer.E,
-                             with_shared=with_shared, pickmax=pickmax, swiglu_limit=swiglu_limit)
+                             with_shared=with_shared, pickmax=pickmax, swiglu_limit=swiglu_limit,
+                             mx4=getattr(layer, "fmt", None) == 5)   # (an MXFP4 layer: routed nibbles, FP8 shared expert)
 
 
 def rowmax_err(got, want):
