@@ -26,12 +26,17 @@ CFG_BIG = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4, score_fn=
 CFG = dict(CFG_BIG)
 CFG_INT4 = dict(H=6144, I=2048, E=168, topk=8, n_group=1, topk_group=1, score_fn=1, fmt="int4")   # config 3
 CFG_SMALL = dict(H=2048, I=1024, E=64, topk=6, n_group=1, topk_group=1, score_fn=0, fmt="fp8")      # config 1
+# config 2's shapes with the routed experts in ds41f's own format (MXFP4: e2m1, a ue8m0 scale per 32) and the FP8 shared expert
+CFG_MX4 = dict(H=4096, I=2048, E=256, topk=8, n_group=8, topk_group=4, score_fn=0, fmt="mx4")
 
 
 def workload_name(rows):
     if CFG["fmt"] == "int4":
         return (f"config 3: INT4-g32 MoE decode layer-step, hidden 6144, 168 experts x 2048, top-8 softmax, "
                 f"+ bf16 shared expert, rows {rows}")
+    if CFG["fmt"] == "mx4":
+        return (f"config 2 shapes, MXFP4 routed experts: MoE decode layer-step, hidden 4096, 256 experts x 2048 (e2m1, ue8m0 "
+                f"scale per 32), top-8 grouped (8 groups / 4), + FP8 shared expert, rows {rows}")
     if CFG["H"] == 2048:
         return (f"config 1: FP8 MoE decode layer-step, hidden 2048, 64 experts x 1024, top-6 sigmoid, + shared expert, "
                 f"rows {rows}")
@@ -94,6 +99,8 @@ def step_bytes(rows_union, rows):
     if CFG["fmt"] == "int4":  # routed experts in 2368-byte blocks of 8 x 512 values, the shared expert bf16
         return rows_union * 3 * I * H * 2368 // 4096 + 3 * I * H * 2 + E * H * 4 + rows * H * 2 * 2
     expert = 3 * I * H + 3 * (I // 128) * (H // 128) * 4
+    if CFG["fmt"] == "mx4":  # routed experts in 544-byte blocks of 8 x 128 values, the shared expert FP8
+        return rows_union * 3 * (I // 8) * (H // 128) * 544 + expert + E * H * 4 + rows * H * 2 * 2
     return (rows_union + 1) * expert + E * H * 4 + rows * H * 2 * 2
 
 
@@ -103,6 +110,8 @@ def up_bytes(n_routed, shared_frac=1.0):
     H, I = CFG["H"], CFG["I"]
     if CFG["fmt"] == "int4":
         return n_routed * (2 * I * H * 2368 // 4096) + shared_frac * 2 * I * H * 2
+    if CFG["fmt"] == "mx4":
+        return n_routed * 2 * (I // 8) * (H // 128) * 544 + shared_frac * (2 * I * H + 2 * (I // 128) * (H // 128) * 4)
     return (n_routed + shared_frac) * (2 * I * H + 2 * (I // 128) * (H // 128) * 4)
 
 
@@ -223,11 +232,11 @@ def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
 
     H, I, E, topk = CFG["H"], CFG["I"], CFG["E"], CFG["topk"]
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
-    int4 = CFG["fmt"] == "int4"
+    int4, mx4 = CFG["fmt"] == "int4", CFG["fmt"] == "mx4"
     # several GPUs: contiguous expert ranges; an FP8 layer's shared expert is cut into parts of its intermediate channels,
     # one a rank (the INT4 layers' bf16 shared expert stays whole, on rank 0)
     part = (0, I) if world == 1 else (shared_part(rank, world, I) if not int4 else ((0, I) if rank == 0 else None))
-    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4 if int4 else _lib.FMT_FP8, n_group=CFG["n_group"],
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4 if int4 else _lib.FMT_MXFP4 if mx4 else _lib.FMT_FP8, n_group=CFG["n_group"],
                     topk_group=CFG["topk_group"], score_fn=CFG["score_fn"], e_lo=e_lo, e_hi=e_hi,
                     sh_lo=part[0] if (part and world > 1 and not int4) else 0,
                     sh_hi=part[1] if (part and world > 1 and not int4) else 0)
@@ -237,7 +246,8 @@ def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
         if int4:
             lay = synth.Int4Layer.on_device(H, I, E, SEED + 7919 * l, dev, shared=part is not None, e_range=(e_lo, e_hi))
         else:
-            lay = synth.Fp8Layer(H, I, E, SEED + 7919 * l, device=dev, shared=part is not None, e_range=(e_lo, e_hi))
+            lay = (synth.Mx4Layer if mx4 else synth.Fp8Layer)(H, I, E, SEED + 7919 * l, device=dev, shared=part is not None,
+                                                              e_range=(e_lo, e_hi))
         wr = synth.router_weights(E, H, SEED + 2000 + l, device="cpu").to(dev)
         layers.append((lay, lay.layer_w()))
         steps_buf.append(moe.LayerStep(shp, wr, None, device=dev, fused=False if args.separate else True if args.fused else None))
@@ -371,7 +381,7 @@ def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
             mine = {e_lo: lay.canonical(e_lo)}   # (an expert no row picked: it gives the shapes, nothing is computed)
         sh = lay.canonical(E) if rank == 0 else None
         acc, _, pm = orc.moe_fp8_layer(synth.bf16_bits(xs[0]), idx_np, w_np, mine, sh, e_lo=e_lo, e_hi=e_hi,
-                                       with_shared=rank == 0, pickmax=True)
+                                       with_shared=rank == 0, pickmax=True, mx4=mx4)
         acc_t, pm_t = torch.from_numpy(acc).to(dev), torch.from_numpy(pm).to(dev)
         if world > 1:
             dist.all_reduce(acc_t)
@@ -391,7 +401,8 @@ def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
     line = {
         "metric": "moe_decode_layer_step_us", "value": us, "unit": "us", "n_gpus": world, "steps": n_steps,
         "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "int4-g32 weights, bf16 activations (f32 accumulate)" if int4 else "fp8_e4m3 (f32 accumulate)",
+        "vs_baseline": None, "dtype": "int4-g32 weights, bf16 activations (f32 accumulate)" if int4 else
+                                      "mxfp4 weights, fp8_e4m3 activations (f32 accumulate)" if mx4 else "fp8_e4m3 (f32 accumulate)",
         "data": "synthetic",
         "config": {"workload": workload_name(rows), "rows": rows,
                    "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
@@ -423,10 +434,10 @@ def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
                             "peak_kind": peak_kind, "us_per_launch": us_up, "algorithmic_bytes": upb,
                             # one ncu capture of this kernel (its summary is among the committed profiles): 151.14 MB read +
                             # 3.91 MB written for 151.03 MB algorithmic; the traffic grows with the experts a launch streams
-                            "traffic": None if int4 else upb * (151.142912 + 3.909120) / 151.031808,
+                            "traffic": None if (int4 or mx4) else upb * (151.142912 + 3.909120) / 151.031808,
                             "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 9-expert launch, scaled by "
                                               "this launch's algorithmic bytes"}
-    if with_cpu and not args.no_cpu_baseline and world == 1 and not int4:
+    if with_cpu and not args.no_cpu_baseline and world == 1 and not int4 and not mx4:
         line["cpu_baseline"] = cpu_baseline(rows, workload=args.workload)
     return line
 
@@ -705,9 +716,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--workload", default="decode", choices=["decode", "decode1", "int4", "prefill", "ragged"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode1", "int4", "mx4", "prefill", "ragged"],
                     help="decode: the headline layer-step (config 2); decode1: the small layer's step (config 1); int4: "
-                         "config 3; prefill: the grouped GEMM pass of config 4; ragged: the mixed batch of config 5 "
+                         "config 3; mx4: config 2's shapes with MXFP4 routed experts; prefill: the grouped GEMM pass of config 4; ragged: the mixed batch of config 5 "
                          "through the same pass")
     ap.add_argument("--tokens", type=int, default=16384, help="prefill: tokens a pass")
     ap.add_argument("--chunks", type=int, default=4, help="prefill end to end: chunks of tokens the pass is cut into")
@@ -735,6 +746,8 @@ def main():
         if workload == "int4":  # config 3: the same decode bench over an INT4-g32 layer
             CFG.update(CFG_INT4)
             layers = 2 if args.layers == 3 else args.layers
+        if workload == "mx4":
+            CFG.update(CFG_MX4)
         if args.experts:
             CFG["E"] = args.experts
         return layers
@@ -780,7 +793,8 @@ def main():
         world = int(os.environ.get("WORLD_SIZE", "1"))
         plan = [("config2_rows8", "decode", 8, 30)]
         if world == 1:
-            plan += [("config1_rows1", "decode1", 1, 60), ("config3_int4_rows1", "int4", 1, 30),
+            plan += [("config1_rows1", "decode1", 1, 60), ("mxfp4_rows1", "mx4", 1, 30), ("mxfp4_rows4", "mx4", 4, 20),
+                     ("config3_int4_rows1", "int4", 1, 30),
                      ("config3_int4_rows4", "int4", 4, 20), ("config4_prefill_16384", "prefill", 1, 6),
                      ("config5_ragged_batch", "ragged", 1, 6)]
         else:

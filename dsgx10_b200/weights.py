@@ -4,8 +4,8 @@ device pool + descriptors.
 It stands in for the part of the reference's converter / loader that feeds the expert kernels (altar1
 engine/weights/int4_pack.py:113-205: `rank_slice`, `pack`, `expert_entry`, `expert_descs`; the per-rank container of
 engine/weights/glw.h: header, table of contents, 4 KiB-aligned data, a checksum per entry) for the formats this library
-runs: routed FP8-128 experts (tag 4: `tile_fp8` values + f32 [N/128][K/128] scales), INT4-g32 experts (tag 2) and the
-shared expert (FP8, or BF16 as the interleaved gate/up matrix + down).  Nothing is quantised here: every stored code,
+runs: routed FP8-128 experts (tag 4: `tile_fp8` values + f32 [N/128][K/128] scales), INT4-g32 experts (tag 2), MXFP4
+experts (tag 5: e2m1 values + ue8m0 scales in 544-byte blocks) and the shared expert (FP8, or BF16 as the interleaved gate/up matrix + down).  Nothing is quantised here: every stored code,
 scale and zero point is the checkpoint's, only re-tiled.  numpy only on the packing side; torch carries the pool to the
 device.
 
@@ -27,14 +27,14 @@ import zlib
 
 import numpy as np
 
-FMT_INT4, FMT_BF16, FMT_FP8 = 2, 3, 4
+FMT_INT4, FMT_BF16, FMT_FP8, FMT_MXFP4 = 2, 3, 4, 5
 MAGIC = b"DSGXMOE1"
 VERSION = 1
 ALIGN = 4096
 HEADER = struct.Struct("<8sIIIIIIIIIIQQQ")   # magic, version, H, I, E, fmt, e_lo, e_hi, tp_rank, tp_world, n, toc, data, size
 ENTRY = struct.Struct("<IIQQ3Q3QI")           # id, fmt, offset, bytes, matrix offsets, scale offsets, crc32
 ENTRY_BYTES = 128
-I4_BLK, B16_BLK = 2368, 2048
+I4_BLK, B16_BLK, MX4_BLK = 2368, 2048, 544
 
 
 def _al(n, a=ALIGN):
@@ -56,6 +56,29 @@ def pack_fp8(q):
 def unpack_fp8(m, N, K):
     v = np.ascontiguousarray(m, np.uint8).reshape(N // 8, K // 128, 8, 4, 2, 16)
     return np.ascontiguousarray(v.transpose(0, 2, 1, 4, 3, 5)).reshape(N, K)
+
+
+def pack_mx4(q, s):
+    """canonical MXFP4 (e2m1 nibble bytes uint8 [N][K/2], the lower k in the low nibble; ue8m0 scale bytes uint8 [N][K/32];
+    ds41f ref/torchref/kernel.py:111-118) -> this library's blocks of 8 rows x 128 k, 544 B, [N/8][K/128]:
+    [32 lanes 4 g + t][4 groups G][4 bytes = k 128 b + 32 G + 8 t + 0..7 of row 8 n8 + g], then [8 g][4 G] scale bytes
+    (it stands in for ds41f's own re-tiling, engine/kernels/dsk.h:176-180 tile_fp4, for these kernels' operand order)."""
+    q, s = np.ascontiguousarray(q, np.uint8), np.ascontiguousarray(s, np.uint8)
+    N, K = q.shape[0], q.shape[1] * 2
+    assert N % 8 == 0 and K % 128 == 0 and s.shape == (N, K // 32)
+    vals = np.ascontiguousarray(q.reshape(N // 8, 8, K // 128, 4, 4, 4).transpose(0, 2, 1, 4, 3, 5))   # n8, b, g, t, G, byte
+    sc = np.ascontiguousarray(s.reshape(N // 8, 8, K // 128, 4).transpose(0, 2, 1, 3))                  # n8, b, g, G
+    out = np.empty((N // 8, K // 128, MX4_BLK), np.uint8)
+    out[..., :512] = vals.reshape(N // 8, K // 128, 512)
+    out[..., 512:] = sc.reshape(N // 8, K // 128, 32)
+    return out.reshape(-1)
+
+
+def unpack_mx4(m, N, K):
+    blk = np.ascontiguousarray(m, np.uint8).reshape(N // 8, K // 128, MX4_BLK)
+    q = np.ascontiguousarray(blk[..., :512].reshape(N // 8, K // 128, 8, 4, 4, 4).transpose(0, 2, 1, 4, 3, 5)).reshape(N, K // 2)
+    s = np.ascontiguousarray(blk[..., 512:].reshape(N // 8, K // 128, 8, 4).transpose(0, 2, 1, 3)).reshape(N, K // 32)
+    return q, s
 
 
 def pack_int4(wp, s, zp=None):
@@ -114,6 +137,17 @@ def rank_slice_fp8(tensors, rank, world):
     return (c(wg[lo:hi]), c(sg[b0:b1]), c(wu[lo:hi]), c(su[b0:b1]), c(wd[:, lo:hi]), c(sd[:, b0:b1]))
 
 
+def rank_slice_mx4(tensors, rank, world):
+    """The same for an MXFP4 expert (wg, sg, wu, su, wd, sd: nibble bytes and ue8m0 bytes): gate / up rows and down's input
+    columns; the cut falls on whole 128-k blocks of the down matrix."""
+    wg, sg, wu, su, wd, sd = tensors
+    I = wg.shape[0]
+    assert I % (128 * world) == 0
+    lo, hi = I * rank // world, I * (rank + 1) // world
+    c = np.ascontiguousarray
+    return (c(wg[lo:hi]), c(sg[lo:hi]), c(wu[lo:hi]), c(su[lo:hi]), c(wd[:, lo // 2:hi // 2]), c(sd[:, lo // 32:hi // 32]))
+
+
 def rank_slice_int4(tensors, rank, world):
     """The same for an INT4-g32 expert ((wp, s, zp) for gate, up, down; zp may be None): every cut is group- and
     word-aligned (int4_pack.py:113-140)."""
@@ -159,6 +193,10 @@ def expert_entry(fmt, tensors):
                                                               for s in (sg, su, sd)]
         buf, offs = _place(parts)
         return buf, offs[:3], offs[3:]
+    if fmt == FMT_MXFP4:
+        wg, sg, wu, su, wd, sd = tensors
+        buf, offs = _place([pack_mx4(wg, sg), pack_mx4(wu, su), pack_mx4(wd, sd)])
+        return buf, offs, [0, 0, 0]
     if fmt == FMT_INT4:
         buf, offs = _place([pack_int4(*t) for t in tensors])
         return buf, offs, [0, 0, 0]
@@ -166,7 +204,7 @@ def expert_entry(fmt, tensors):
         wg, wu, wd = tensors
         buf, offs = _place([pack_bf16(interleave_gate_up(wg, wu)), pack_bf16(wd)])
         return buf, [offs[0], 0, offs[1]], [0, 0, 0]
-    raise ValueError(f"expert format {fmt}: not INT4 (2), BF16 (3) or FP8 (4); NVFP4 (0) and the retired tag 1 are refused")
+    raise ValueError(f"expert format {fmt}: not INT4 (2), BF16 (3), FP8 (4) or MXFP4 (5); NVFP4 (0) and the retired tag 1 are refused")
 
 
 def write_layer_file(path, H, I, E, fmt, experts, shared=None, shared_fmt=None, tp=(0, 1), e_range=None):
@@ -189,10 +227,10 @@ def write_layer_file(path, H, I, E, fmt, experts, shared=None, shared_fmt=None, 
     for e in range(lo, hi):
         t = experts[e]
         if world > 1:
-            t = rank_slice_fp8(t, rank, world) if fmt == FMT_FP8 else rank_slice_int4(t, rank, world)
+            t = (rank_slice_fp8 if fmt == FMT_FP8 else rank_slice_mx4 if fmt == FMT_MXFP4 else rank_slice_int4)(t, rank, world)
         add(e, fmt, t)
     if shared is not None:
-        sf = shared_fmt if shared_fmt is not None else (FMT_FP8 if fmt == FMT_FP8 else FMT_BF16)
+        sf = shared_fmt if shared_fmt is not None else (FMT_FP8 if fmt in (FMT_FP8, FMT_MXFP4) else FMT_BF16)
         if world > 1:
             if sf == FMT_FP8:
                 shared = rank_slice_fp8(shared, rank, world)
@@ -233,8 +271,8 @@ def read_layer_file(path, verify=True):
         raise LayerFileError(f"layer file version {ver}, this reader knows {VERSION}")
     if size != raw.size or toc + n * ENTRY_BYTES > data or data > size:
         raise LayerFileError("layer file is truncated or its header is inconsistent")
-    if fmt not in (FMT_INT4, FMT_FP8):
-        raise LayerFileError(f"layer format {fmt}: this library runs INT4 (2) and FP8 (4) layers")
+    if fmt not in (FMT_INT4, FMT_FP8, FMT_MXFP4):
+        raise LayerFileError(f"layer format {fmt}: this library runs INT4 (2), FP8 (4) and MXFP4 (5) layers")
     entries = []
     for i in range(n):
         rec = ENTRY.unpack(raw[toc + i * ENTRY_BYTES: toc + i * ENTRY_BYTES + ENTRY.size].tobytes())

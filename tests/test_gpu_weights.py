@@ -52,3 +52,23 @@ def test_int4_layer_from_file_same_bits(tmp_path):
     torch.cuda.synchronize()
     assert moe.ws_status(a.ws) == 0 and moe.ws_status(b.ws) == 0
     assert torch.equal(a.yr[:M], b.yr[:M]) and torch.equal(a.ys[:M], b.ys[:M])
+
+
+def test_mx4_layer_from_file_same_bits(tmp_path):
+    from dsgx10_b200 import _lib, moe, synth, weights as W
+    H, I, E, topk, M = 1024, 512, 8, 4, 3
+    mem = synth.Mx4Layer(H, I, E, 820, device="cpu")
+    experts = {e: mem.canonical(e) for e in range(E)}
+    path = str(tmp_path / "mx4.dsgx")
+    W.write_layer_file(path, H, I, E, W.FMT_MXFP4, experts, shared=mem.canonical(E))
+    layer = W.load_layer_file(path, device="cuda")
+    mem.to("cuda")
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_MXFP4)
+    wr = synth.router_weights(E, H, 821).cuda()
+    x = synth.activations(M, H, 822).cuda()
+    a, b = moe.LayerStep(shp, wr), moe.LayerStep(shp, wr)
+    out_a = a.run(mem.layer_w(), x).clone()
+    out_b = b.run(layer.layer_w(), x).clone()
+    torch.cuda.synchronize()
+    assert moe.ws_status(a.ws) == 0 and moe.ws_status(b.ws) == 0
+    assert torch.equal(a.yr[:M], b.yr[:M]) and torch.equal(a.ys[:M], b.ys[:M]) and torch.equal(out_a, out_b)

@@ -115,3 +115,47 @@ def test_int4_layer_file_with_bf16_shared(tmp_path, orc):
     gu = W.interleave_gate_up(sh[0][I // 2:], sh[1][I // 2:])
     b = s_ent["offset"] - hdr["data"] + s_ent["moff"][0]
     assert (data[b: b + gu.size * 2] == orc.pack_bf16_tile(gu)).all()
+
+
+def test_mx4_packer_slices_and_file(tmp_path, orc):
+    """MXFP4 (tag 5): the packer is the synthetic layers' tiler (torch) byte for byte and round-trips; every value of a
+    packed block dequantises as the oracle dequantises the canonical tensor; rank slices; a layer file with an FP8 shared
+    expert."""
+    import torch
+    from dsgx10_b200 import synth
+    rng = np.random.default_rng(5)
+    N, K = 64, 512
+    q = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    s = rng.integers(100, 140, (N, K // 32), dtype=np.uint8)
+    packed = W.pack_mx4(q, s)
+    assert packed.size == (N // 8) * (K // 128) * 544
+    assert (packed == synth.tile_mx4(torch.from_numpy(q), torch.from_numpy(s)).numpy()).all()
+    q2, s2 = W.unpack_mx4(packed, N, K)
+    assert (q2 == q).all() and (s2 == s).all()
+    # the layout as the header states it, value by value: lane (g, t), group G, byte j of block b holds k = 128 b + 32 G + 8 t + 2 j
+    deq = orc.mx4_dequant(q, s)
+    vals = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    blk = packed.reshape(N // 8, K // 128, 544)
+    for n8, b, g, t, G, j in ((0, 0, 0, 0, 0, 0), (3, 2, 5, 1, 2, 3), (7, 3, 7, 3, 3, 1)):
+        byte = blk[n8, b, (4 * g + t) * 16 + 4 * G + j]
+        e = blk[n8, b, 512 + 4 * g + G]
+        k = 128 * b + 32 * G + 8 * t + 2 * j
+        want = deq[8 * n8 + g, k:k + 2]
+        got = np.array([vals[byte & 15], vals[byte >> 4]]) * np.float32(2.0) ** (int(e) - 127)
+        assert (got == want).all()
+    H, I = 256, 512
+    t = []
+    for n, k in ((I, H), (I, H), (H, I)):
+        t += [rng.integers(0, 256, (n, k // 2), dtype=np.uint8), rng.integers(110, 130, (n, k // 32), dtype=np.uint8)]
+    parts = [W.rank_slice_mx4(tuple(t), r, 2) for r in range(2)]
+    assert (np.concatenate([p[0] for p in parts]) == t[0]).all() and (np.concatenate([p[1] for p in parts]) == t[1]).all()
+    assert (np.concatenate([p[4] for p in parts], axis=1) == t[4]).all()
+    assert (np.concatenate([p[5] for p in parts], axis=1) == t[5]).all()
+    path = str(tmp_path / "mx4.dsgx")
+    shared = _fp8_expert(rng, H, I)
+    W.write_layer_file(path, H, I, 2, W.FMT_MXFP4, {0: tuple(t), 1: tuple(t)}, shared=shared)
+    hdr, entries, data = W.read_layer_file(path)
+    assert hdr["fmt"] == W.FMT_MXFP4 and [e["fmt"] for e in entries] == [W.FMT_MXFP4, W.FMT_MXFP4, W.FMT_FP8]
+    e0 = entries[0]
+    got = data[e0["offset"] - hdr["data"] + e0["moff"][2]:][:W.pack_mx4(t[4], t[5]).size]
+    assert (got == W.pack_mx4(t[4], t[5])).all()
