@@ -173,26 +173,31 @@ DSGX_DEV uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
   return d;
 }
-// Eight e2m1 nibbles (value j at bits 4 j) -> the same eight values as e4m3 bytes (every e2m1 value is an e4m3 value):
-// lo = values 0..3, hi = values 4..7.  Magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 by a byte table, the sign bit by a second one.
+// Eight e2m1 values of one stored word -> the same values as e4m3 bytes (every e2m1 value is an e4m3 value): lo = values
+// 0..3, hi = values 4..7.  Stored word: value j's magnitude code (0, .5, 1, 1.5, 2, 3, 4, 6) in bits 4 j .. 4 j + 2; the
+// sign of value i < 4 in bit 8 i + 7, of value i >= 4 in bit 8 (i - 4) + 3 (the top bits of the odd and the even nibbles):
+// where the e4m3 sign bits of lo lie, and four bits below those of hi.  Magnitudes by a byte table (prmt).
 DSGX_DEV void e2m1x8_to_e4m3(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  const uint32_t m = w & 0x77777777u, s = (w >> 3) & 0x11111111u;
-  lo = prmt(0x3C383000u, 0x4C484440u, m) | prmt(0x00008000u, 0u, s);
-  hi = prmt(0x3C383000u, 0x4C484440u, m >> 16) | prmt(0x00008000u, 0u, s >> 16);
+  const uint32_t m = w & 0x77777777u;
+  lo = prmt(0x3C383000u, 0x4C484440u, m) | (w & 0x80808080u);
+  hi = prmt(0x3C383000u, 0x4C484440u, m >> 16) | ((w << 4) & 0x80808080u);
 }
-// byte G of four ue8m0 scale bytes as a float: 2^(e - 127) (e = 0: 2^-127, a subnormal)
-template <int G>
-DSGX_DEV float ue8m0_f(uint32_t s4) {
-  const uint32_t b = G == 3 ? (s4 >> 1) & 0x7f800000u : (s4 << (23 - 8 * G)) & 0x7f800000u;
-  return __uint_as_float(max(b, 0x00400000u));
+// D = A B with a zero C operand (no accumulator to clear)
+DSGX_DEV void mma_e4m3_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 // One 128-k block of two MXFP4 strips (A rows 0-7 from a, rows 8-15 from b) against an FP8 activation block: four MMAs of
-// 32 k (one scale group each, k = 32 G + 8 t + 0..7 in lane (g, t)), each promoted with its rows' scales:
-// d = ((d_0 s_0 + d_1 s_1) + d_2 s_2) + d_3 s_3 by fused multiply-adds from zero.
+// 32 k (one scale group each; k = 32 G + 8 t + 0..7 in lane (g, t)), each promoted with its rows' scales:
+// d = ((d_0 s_0 + d_1 s_1) + d_2 s_2) + d_3 s_3 by fused multiply-adds from zero.  The scales are stored as bf16 (2^(e-127)
+// exactly, e = 0 included), one shift or mask from a float.  (Measured on the way: the legacy mma.sync is the scarce
+// resource here, a second MMA a group for the negative values cost more than the sign handling it saved.)
 DSGX_DEV void block_mma_mx(float (&d)[4], const uint8_t* a, const uint8_t* b, const uint8_t* act, int lane) {
   const int g = lane >> 2, t = lane & 3;
   const uint4 aw = lds128(a + 16 * lane), bw = lds128(b + 16 * lane);
-  const uint32_t sa = *reinterpret_cast<const uint32_t*>(a + 512 + 4 * g), sb = *reinterpret_cast<const uint32_t*>(b + 512 + 4 * g);
+  const uint2 sa = *reinterpret_cast<const uint2*>(a + 512 + 8 * g), sb = *reinterpret_cast<const uint2*>(b + 512 + 8 * g);
   // the activations of row g at k = 32 G + 8 t .. + 7: block position (k / 64, row, (k / 16) % 4, k % 16)
   const uint8_t* xr = act + (4 * g + (t >> 1)) * 16 + 8 * (t & 1);
   const uint2 x0 = *reinterpret_cast<const uint2*>(xr), x1 = *reinterpret_cast<const uint2*>(xr + 32);
@@ -201,14 +206,14 @@ DSGX_DEV void block_mma_mx(float (&d)[4], const uint8_t* a, const uint8_t* b, co
   auto group = [&](uint32_t wa, uint32_t wb, const uint2& x, float fa, float fb) {
     uint32_t al, ah, bl, bh;
     e2m1x8_to_e4m3(wa, al, ah), e2m1x8_to_e4m3(wb, bl, bh);
-    float e[4] = {0.f, 0.f, 0.f, 0.f};
-    mma_e4m3(e, al, bl, ah, bh, x.x, x.y);
+    float e[4];
+    mma_e4m3_zero(e, al, bl, ah, bh, x.x, x.y);
     d[0] = fmaf(e[0], fa, d[0]), d[1] = fmaf(e[1], fa, d[1]), d[2] = fmaf(e[2], fb, d[2]), d[3] = fmaf(e[3], fb, d[3]);
   };
-  group(aw.x, bw.x, x0, ue8m0_f<0>(sa), ue8m0_f<0>(sb));
-  group(aw.y, bw.y, x1, ue8m0_f<1>(sa), ue8m0_f<1>(sb));
-  group(aw.z, bw.z, x2, ue8m0_f<2>(sa), ue8m0_f<2>(sb));
-  group(aw.w, bw.w, x3, ue8m0_f<3>(sa), ue8m0_f<3>(sb));
+  group(aw.x, bw.x, x0, __uint_as_float(sa.x << 16), __uint_as_float(sb.x << 16));
+  group(aw.y, bw.y, x1, __uint_as_float(sa.x & 0xffff0000u), __uint_as_float(sb.x & 0xffff0000u));
+  group(aw.z, bw.z, x2, __uint_as_float(sa.y << 16), __uint_as_float(sb.y << 16));
+  group(aw.w, bw.w, x3, __uint_as_float(sa.y & 0xffff0000u), __uint_as_float(sb.y & 0xffff0000u));
 }
 
 // ---- the summation order of a unit's K, and its split over warps --------------------------------------------------

@@ -12,7 +12,7 @@ namespace dsgx {
 // A quantised activation block: 128 k of up to 8 rows as e4m3 in MMA operand order (1024 B) + the rows' f32 scales.
 constexpr int kActBlk = 1024 + 32;
 constexpr int kMaxRows = DSGX_MAX_ROWS;
-constexpr int kMxBlk = 544;  // bytes of an MXFP4 block: 8 rows x 128 k of e2m1 + 8 x 4 scale bytes
+constexpr int kMxBlk = 576;  // bytes of an MXFP4 block: 8 rows x 128 k of e2m1 + 8 x 4 scales as bf16
 // FP8 activations and FP8 shared expert: the FP8 kernels serve the layer
 inline __host__ __device__ bool fmt_fp8_family(uint32_t fmt) { return fmt == DSGX_FMT_FP8 || fmt == DSGX_FMT_MXFP4; }
 constexpr int kMaxTopK = 8;

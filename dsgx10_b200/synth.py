@@ -138,25 +138,61 @@ def quant_mx4(w):
     return (code[..., 0] | code[..., 1] << 4).contiguous(), e.to(torch.uint8).contiguous()
 
 
+def ue8m0_to_bf16_bits(s):
+    """ue8m0 bytes -> the bf16 bit patterns of 2^(byte - 127): byte << 7, and 0x0040 (a subnormal) for byte 0."""
+    s = s.to(torch.int32)
+    return torch.where(s == 0, torch.full_like(s, 0x40), s << 7).to(torch.int16)
+
+
+def _u32_bytes(v):
+    """int64 values in [0, 2^32) -> their little-endian bytes (uint8, four a value)."""
+    return torch.where(v >= 2 ** 31, v - 2 ** 32, v).to(torch.int32).view(torch.uint8)
+
+
+def mx4_words(q):
+    """canonical nibble bytes [N][K/2] -> the stored 32-bit words, as bytes [N][K/2]: the eight magnitude codes of
+    k = 8 j .. 8 j + 7 stay in their nibbles; the sign of value i < 4 goes to bit 8 i + 7, of value i >= 4 to bit
+    8 (i - 4) + 3 (where the kernels' e4m3 operands want them)."""
+    w = q.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    out = w & 0x77777777
+    for i in range(8):
+        out |= ((w >> (4 * i + 3)) & 1) << (8 * i + 7 if i < 4 else 8 * (i - 4) + 3)
+    return _u32_bytes(out)
+
+
+def mx4_unwords(b):
+    w = b.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    out = w & 0x77777777
+    for i in range(8):
+        out |= ((w >> (8 * i + 7 if i < 4 else 8 * (i - 4) + 3)) & 1) << (4 * i + 3)
+    return _u32_bytes(out)
+
+
 def tile_mx4(q, s):
-    """canonical MXFP4 (nibble bytes [N][K/2], ue8m0 [N][K/32]) -> blocks of 8 rows x 128 k, 544 B, [N/8][K/128]:
-    [32 lanes 4 g + t][4 groups G][4 bytes: k = 128 b + 32 G + 8 t + 0..7 of row 8 n8 + g], then [8 g][4 G] scales."""
+    """canonical MXFP4 (nibble bytes [N][K/2], ue8m0 [N][K/32]) -> blocks of 8 rows x 128 k, 576 B, [N/8][K/128]:
+    [32 lanes 4 g + t][4 groups G][one word (mx4_words): k = 128 b + 32 G + 8 t + 0..7 of row 8 n8 + g], then [8 g][4 G] the
+    scales 2^(byte - 127) as bf16."""
     N, K = q.shape[0], q.shape[1] * 2
-    v = q.view(N // 8, 8, K // 128, 4, 4, 4)                 # n8, g, b, G, t, 4 bytes
+    v = mx4_words(q).view(N // 8, 8, K // 128, 4, 4, 4)      # n8, g, b, G, t, 4 bytes
     vals = v.permute(0, 2, 1, 4, 3, 5).contiguous().view(N // 8, K // 128, 512)   # n8, b, g, t, G, bytes
-    sc = s.view(N // 8, 8, K // 128, 4).permute(0, 2, 1, 3).contiguous().view(N // 8, K // 128, 32)
-    return torch.cat([vals, sc], dim=-1).contiguous().view(-1)
+    sc = ue8m0_to_bf16_bits(s).view(N // 8, 8, K // 128, 4).permute(0, 2, 1, 3).contiguous().view(torch.uint8)
+    return torch.cat([vals, sc.view(N // 8, K // 128, 64)], dim=-1).contiguous().view(-1)
 
 
 def untile_mx4(m, N, K):
-    blk = m.view(N // 8, K // 128, 544)
-    vals = blk[..., :512].reshape(N // 8, K // 128, 8, 4, 4, 4).permute(0, 2, 1, 4, 3, 5).contiguous().view(N, K // 2)
-    sc = blk[..., 512:].reshape(N // 8, K // 128, 8, 4).permute(0, 2, 1, 3).contiguous().view(N, K // 32)
+    blk = m.view(N // 8, K // 128, MX4_BLK)
+    vals = mx4_unwords(blk[..., :512].reshape(N // 8, K // 128, 8, 4, 4, 4).permute(0, 2, 1, 4, 3, 5).contiguous().view(N, K // 2))
+    sb = blk[..., 512:].contiguous().view(torch.int16).to(torch.int32) & 0xFFFF       # n8, b, g * 4 + G
+    sc = torch.where(sb == 0x40, torch.zeros_like(sb), sb >> 7).to(torch.uint8)
+    sc = sc.view(N // 8, K // 128, 8, 4).permute(0, 2, 1, 3).contiguous().view(N, K // 32)
     return vals, sc
 
 
+MX4_BLK = 576
+
+
 def mx4_mat_bytes(N, K):
-    return (N // 8) * (K // 128) * 544
+    return (N // 8) * (K // 128) * MX4_BLK
 
 
 class Mx4Layer(Fp8Layer):
@@ -218,8 +254,9 @@ class Mx4Layer(Fp8Layer):
         return tuple(out)
 
     def expert_bytes(self):
-        """Algorithmic bytes of one routed expert: three matrices of e2m1 values with their scale bytes."""
-        return 3 * mx4_mat_bytes(self.I, self.H)
+        """Algorithmic bytes of one routed expert: three matrices of e2m1 values with one scale byte per 32 (the stored
+        blocks spend two bytes a scale: 576 instead of 544 bytes)."""
+        return 3 * (self.I // 8) * (self.H // 128) * 544
 
     def shared_bytes(self):
         return 3 * self.I * self.H + 3 * (self.I // 128) * (self.H // 128) * 4

@@ -5,7 +5,7 @@ It stands in for the part of the reference's converter / loader that feeds the e
 engine/weights/int4_pack.py:113-205: `rank_slice`, `pack`, `expert_entry`, `expert_descs`; the per-rank container of
 engine/weights/glw.h: header, table of contents, 4 KiB-aligned data, a checksum per entry) for the formats this library
 runs: routed FP8-128 experts (tag 4: `tile_fp8` values + f32 [N/128][K/128] scales), INT4-g32 experts (tag 2), MXFP4
-experts (tag 5: e2m1 values + ue8m0 scales in 544-byte blocks) and the shared expert (FP8, or BF16 as the interleaved gate/up matrix + down).  Nothing is quantised here: every stored code,
+experts (tag 5: e2m1 values + their power-of-two scales in 576-byte blocks) and the shared expert (FP8, or BF16 as the interleaved gate/up matrix + down).  Nothing is quantised here: every stored code,
 scale and zero point is the checkpoint's, only re-tiled.  numpy only on the packing side; torch carries the pool to the
 device.
 
@@ -34,7 +34,7 @@ ALIGN = 4096
 HEADER = struct.Struct("<8sIIIIIIIIIIQQQ")   # magic, version, H, I, E, fmt, e_lo, e_hi, tp_rank, tp_world, n, toc, data, size
 ENTRY = struct.Struct("<IIQQ3Q3QI")           # id, fmt, offset, bytes, matrix offsets, scale offsets, crc32
 ENTRY_BYTES = 128
-I4_BLK, B16_BLK, MX4_BLK = 2368, 2048, 544
+I4_BLK, B16_BLK, MX4_BLK = 2368, 2048, 576
 
 
 def _al(n, a=ALIGN):
@@ -58,27 +58,51 @@ def unpack_fp8(m, N, K):
     return np.ascontiguousarray(v.transpose(0, 2, 1, 4, 3, 5)).reshape(N, K)
 
 
+def mx4_words(q):
+    """canonical nibble bytes uint8 [N][K/2] -> the stored words uint32 [N][K/8]: magnitudes in place, the sign of value
+    i < 4 of a word at bit 8 i + 7, of value i >= 4 at bit 8 (i - 4) + 3."""
+    w = np.ascontiguousarray(q, np.uint8).view(np.uint32)
+    out = w & np.uint32(0x77777777)
+    for i in range(8):
+        out |= ((w >> np.uint32(4 * i + 3)) & np.uint32(1)) << np.uint32(8 * i + 7 if i < 4 else 8 * (i - 4) + 3)
+    return out
+
+
+def mx4_unwords(w):
+    w = np.ascontiguousarray(w, np.uint32)
+    out = w & np.uint32(0x77777777)
+    for i in range(8):
+        out |= ((w >> np.uint32(8 * i + 7 if i < 4 else 8 * (i - 4) + 3)) & np.uint32(1)) << np.uint32(4 * i + 3)
+    return out.view(np.uint8)
+
+
 def pack_mx4(q, s):
     """canonical MXFP4 (e2m1 nibble bytes uint8 [N][K/2], the lower k in the low nibble; ue8m0 scale bytes uint8 [N][K/32];
-    ds41f ref/torchref/kernel.py:111-118) -> this library's blocks of 8 rows x 128 k, 544 B, [N/8][K/128]:
-    [32 lanes 4 g + t][4 groups G][4 bytes = k 128 b + 32 G + 8 t + 0..7 of row 8 n8 + g], then [8 g][4 G] scale bytes
+    ds41f ref/torchref/kernel.py:111-118) -> this library's blocks of 8 rows x 128 k, 576 B, [N/8][K/128]:
+    [32 lanes 4 g + t][4 groups G][one word = k 128 b + 32 G + 8 t + 0..7 of row 8 n8 + g, the sign bits moved inside the
+    word (mx4_words)], then [8 g][4 G] the scales 2^(byte - 127) written as bf16 (byte << 7; 0x0040 for byte 0): the same
+    numbers, one shift from a float on the device
     (it stands in for ds41f's own re-tiling, engine/kernels/dsk.h:176-180 tile_fp4, for these kernels' operand order)."""
     q, s = np.ascontiguousarray(q, np.uint8), np.ascontiguousarray(s, np.uint8)
     N, K = q.shape[0], q.shape[1] * 2
     assert N % 8 == 0 and K % 128 == 0 and s.shape == (N, K // 32)
-    vals = np.ascontiguousarray(q.reshape(N // 8, 8, K // 128, 4, 4, 4).transpose(0, 2, 1, 4, 3, 5))   # n8, b, g, t, G, byte
-    sc = np.ascontiguousarray(s.reshape(N // 8, 8, K // 128, 4).transpose(0, 2, 1, 3))                  # n8, b, g, G
+    qw = mx4_words(q).view(np.uint8).reshape(N, K // 2)
+    vals = np.ascontiguousarray(qw.reshape(N // 8, 8, K // 128, 4, 4, 4).transpose(0, 2, 1, 4, 3, 5))  # n8, b, g, t, G, byte
+    sb = np.where(s == 0, 0x40, s.astype(np.uint16) << 7).astype(np.uint16)
+    sc = np.ascontiguousarray(sb.reshape(N // 8, 8, K // 128, 4).transpose(0, 2, 1, 3))                 # n8, b, g, G
     out = np.empty((N // 8, K // 128, MX4_BLK), np.uint8)
     out[..., :512] = vals.reshape(N // 8, K // 128, 512)
-    out[..., 512:] = sc.reshape(N // 8, K // 128, 32)
+    out[..., 512:] = sc.view(np.uint8).reshape(N // 8, K // 128, 64)
     return out.reshape(-1)
 
 
 def unpack_mx4(m, N, K):
     blk = np.ascontiguousarray(m, np.uint8).reshape(N // 8, K // 128, MX4_BLK)
     q = np.ascontiguousarray(blk[..., :512].reshape(N // 8, K // 128, 8, 4, 4, 4).transpose(0, 2, 1, 4, 3, 5)).reshape(N, K // 2)
-    s = np.ascontiguousarray(blk[..., 512:].reshape(N // 8, K // 128, 8, 4).transpose(0, 2, 1, 3)).reshape(N, K // 32)
-    return q, s
+    q = mx4_unwords(q.view(np.uint32)).reshape(N, K // 2)
+    sb = np.ascontiguousarray(blk[..., 512:]).view(np.uint16).reshape(N // 8, K // 128, 8, 4)
+    s = np.where(sb == 0x40, 0, sb >> 7).astype(np.uint8)
+    return q, np.ascontiguousarray(s.transpose(0, 2, 1, 3)).reshape(N, K // 32)
 
 
 def pack_int4(wp, s, zp=None):

@@ -46,9 +46,11 @@ enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF1
  * the activations are quantised as for DSGX_FMT_FP8 (e4m3 per 128 with an f32 scale), W = e2m1 * 2^(scale - 127), the
  * rest of the contract is DSGX_FMT_FP8's; the layer's shared expert is FP8 (dsgx_shared_w.g/u/d), as ds41f's.  Decode
  * only.  Layout of a matrix [N][K] (N a multiple of 8, K of 128), made by dsgx10_b200/weights.py pack_mx4:
- *   [N/8 strips][K/128 blocks] of 544 bytes: [32 lanes (g = lane / 4, t = lane % 4)][4 groups G][4 bytes] = the 8
- *   values of row 8 strip + g at k = 128 block + 32 G + 8 t + 0..7, two a byte, the lower k in the low nibble (the
- *   checkpoint's own nibble order), then [8 rows g][4 groups G] the ue8m0 scale bytes.  rsv is zero. */
+ *   [N/8 strips][K/128 blocks] of 576 bytes: [32 lanes (g = lane / 4, t = lane % 4)][4 groups G][one 32-bit word] = the
+ *   8 values v0..v7 of row 8 strip + g at k = 128 block + 32 G + 8 t + 0..7: v_j's magnitude code (its e2m1 nibble
+ *   without the sign) in bits 4 j .. 4 j + 2, the sign of v_i in bit 8 i + 7 for i < 4 and in bit 8 (i - 4) + 3 for
+ *   i >= 4; then [8 rows g][4 groups G] the scales 2^(byte - 127) as bf16 (byte << 7; 0x0040 for byte 0).  A lossless
+ *   re-tiling of the checkpoint's nibbles and scale bytes.  rsv is zero. */
 /* scores of the router: sigmoid and softmax (altar1 engine/experts/formats.cuh:142-163; ds41f ref/inference/model.py:812-818),
  * sqrt(softplus(l)) (ds41f engine/kernels/common.cuh:264-287, the only score dsk::router_topk has) */
 enum { DSGX_SCORE_SIGMOID = 0, DSGX_SCORE_SOFTMAX = 1, DSGX_SCORE_SQRTSOFTPLUS = 2 };

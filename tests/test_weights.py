@@ -128,21 +128,21 @@ def test_mx4_packer_slices_and_file(tmp_path, orc):
     q = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
     s = rng.integers(100, 140, (N, K // 32), dtype=np.uint8)
     packed = W.pack_mx4(q, s)
-    assert packed.size == (N // 8) * (K // 128) * 544
+    assert packed.size == (N // 8) * (K // 128) * 576
     assert (packed == synth.tile_mx4(torch.from_numpy(q), torch.from_numpy(s)).numpy()).all()
     q2, s2 = W.unpack_mx4(packed, N, K)
     assert (q2 == q).all() and (s2 == s).all()
-    # the layout as the header states it, value by value: lane (g, t), group G, byte j of block b holds k = 128 b + 32 G + 8 t + 2 j
+    # the layout as the header states it, value by value: lane (g, t), group G of block b holds k = 128 b + 32 G + 8 t + 0..7
     deq = orc.mx4_dequant(q, s)
-    vals = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
-    blk = packed.reshape(N // 8, K // 128, 544)
-    for n8, b, g, t, G, j in ((0, 0, 0, 0, 0, 0), (3, 2, 5, 1, 2, 3), (7, 3, 7, 3, 3, 1)):
-        byte = blk[n8, b, (4 * g + t) * 16 + 4 * G + j]
-        e = blk[n8, b, 512 + 4 * g + G]
-        k = 128 * b + 32 * G + 8 * t + 2 * j
-        want = deq[8 * n8 + g, k:k + 2]
-        got = np.array([vals[byte & 15], vals[byte >> 4]]) * np.float32(2.0) ** (int(e) - 127)
-        assert (got == want).all()
+    mags = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float32)
+    blk = packed.reshape(N // 8, K // 128, 576)
+    for n8, b, g, t, G in ((0, 0, 0, 0, 0), (3, 2, 5, 1, 2), (7, 3, 7, 3, 3)):
+        word = int(blk[n8, b, (4 * g + t) * 16 + 4 * G:][:4].view(np.uint32)[0])
+        e = int(blk[n8, b, 512 + 8 * g + 2 * G:][:2].view(np.uint16)[0]) >> 7     # the scale as bf16: byte << 7
+        k = 128 * b + 32 * G + 8 * t
+        got = np.array([(-1.0 if (word >> (8 * i + 7 if i < 4 else 8 * (i - 4) + 3)) & 1 else 1.0) * mags[(word >> (4 * i)) & 7]
+                        for i in range(8)], np.float32) * np.float32(2.0) ** (e - 127)
+        assert (got == deq[8 * n8 + g, k:k + 8]).all()
     H, I = 256, 512
     t = []
     for n, k in ((I, H), (I, H), (H, I)):
