@@ -164,31 +164,38 @@ DSGX_DEV void route_row(const RouteParams& p, const float* __restrict__ l, int n
     }
   }
 
+  // The picks.  The keys become order-preserving integers once (a NaN and a key that is out of the running rank as -inf,
+  // -0 as +0); every round each lane offers its largest, the warp takes the maximum, then the lowest expert id among the
+  // lanes that hold it (ties go to the lower id), and that expert leaves the running.
+  constexpr uint32_t kGone = 0x007FFFFFu;  // ord(-inf)
+  uint32_t ok[kRJ];
+#pragma unroll
+  for (int j = 0; j < kRJ; ++j) {
+    const float f = __fadd_rn(key[j], 0.f);
+    const uint32_t b = __float_as_uint(f);
+    ok[j] = f != f ? kGone : (b & 0x80000000u) ? ~b : b | 0x80000000u;
+  }
   float picked[8];
   int ids[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     picked[k] = 0.f, ids[k] = 0;
     if (k < p.topk) {
-      float bv = -INFINITY;
-      int bj = 0;
+      uint32_t mine = kGone;
 #pragma unroll
-      for (int j = 0; j < kRJ; ++j)
-        if (key[j] > bv) bv = key[j], bj = j;
-      int be = bv == -INFINITY ? 1 << 30 : lane + 32 * bj;
+      for (int j = 0; j < kRJ; ++j) mine = max(mine, ok[j]);
+      const uint32_t top = __reduce_max_sync(0xffffffffu, mine);
+      int cand = 1 << 30;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-        if (ov > bv || (ov == bv && oe < be)) bv = ov, be = oe;
-      }
-      if (be == 1 << 30) be = 0;
-      ids[k] = be;
+      for (int j = kRJ - 1; j >= 0; --j)
+        if (ok[j] == top) cand = lane + 32 * j;
+      int e = top == kGone ? 0 : (int)__reduce_min_sync(0xffffffffu, (unsigned)cand);  // (nothing left: expert 0)
+      ids[k] = e;
       float sv = 0.f;
 #pragma unroll
       for (int j = 0; j < kRJ; ++j)
-        if (lane + 32 * j == be) sv = s[j], key[j] = -INFINITY;
-      picked[k] = __shfl_sync(0xffffffffu, sv, be & 31);
+        if (lane + 32 * j == e) sv = s[j], ok[j] = kGone;
+      picked[k] = __shfl_sync(0xffffffffu, sv, e & 31);
     }
   }
   // the sum of the picked scores: four running sums at stride 4, then (t0 + t2) + (t1 + t3)
