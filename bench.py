@@ -494,10 +494,13 @@ def run_prefill_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def run_prefill(args, workload=None, steps=None, with_cpu=True):
+def run_prefill(args, workload=None, steps=None, with_cpu=True, a2a=False):
     """Config 4: one layer's prefill over `--tokens` tokens whose expert popularity follows Zipf(1.1) (a router bias
     calibrated so that the realised pick histogram matches), experts sharded over the ranks, partial sums reduced over
-    peer memory.  Config 5 (`ragged`): the mixed batch through the same pass.  Returns rank 0's result line."""
+    peer memory.  Config 5 (`ragged`): the mixed batch through the same pass.  a2a (several GPUs): the rows are partitioned
+    over the ranks instead, every rank routes its own rows, an all-to-all (NCCL) sends each row to the ranks that own one
+    of its picks, the f32 partial sums return by a second all-to-all and are added in rank order; the shared expert runs
+    on the rows' own rank.  Returns rank 0's result line."""
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -517,7 +520,8 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True):
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     shp_all = moe.shape(H, I, E, topk)
     shp = moe.shape(H, I, E, topk, e_lo=e_lo, e_hi=e_hi)
-    lay = synth.Fp8Layer(H, I, E, SEED, device=dev, shared=(rank == 0), e_range=(e_lo, e_hi))
+    a2a = a2a and world > 1
+    lay = synth.Fp8Layer(H, I, E, SEED, device=dev, shared=(rank == 0) and not a2a, e_range=(e_lo, e_hi))
     NX = 3  # distinct activation sets: 3 x 67 MB of inputs, and ~1.5 GB of intermediates a pass: nothing stays in L2
     xs = [synth.activations(T, H, SEED + 1000 + i, device="cpu").to(dev) for i in range(NX)]
     xs_host = [x.cpu().pin_memory() for x in xs]
@@ -552,8 +556,25 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True):
         # two GPUs: each reads the other's whole partial sums; more: each reduces 1 / N of the rows and stores them everywhere
         peer = ep.PeerReduce(H, rows_cap=T, shared_rank=-1, sliced=world > 2)
 
+    if a2a:  # the shared expert of this rank's own rows: a layer with no routed expert, only the shared one
+        from dsgx10_b200 import ep
+        peer = None
+        r_lo, r_hi = rank * T // world, (rank + 1) * T // world
+        lay_sh = synth.Fp8Layer(H, I, E, SEED, device=dev, shared=True, e_range=(0, 0))
+        pl_sh = moe.PrefillLayer(moe.shape(H, I, E, topk, e_lo=0, e_hi=0), lay_sh.layer_w(), r_hi - r_lo, device=dev)
+        out_all = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+        def local_routed(xr, ir, wr_):
+            y, _, _ = pl.run(xr, ir, wr_, ys=False, out=False)
+            return y
+
     def experts(i):
         idx, w = routed[i % NX]
+        if a2a:
+            x_loc, idx_loc, w_loc = xs[i % NX][r_lo:r_hi], idx[r_lo:r_hi].contiguous(), w[r_lo:r_hi].contiguous()
+            acc = ep.all_to_all_experts(x_loc, idx_loc, w_loc, E, local_routed)
+            _, ysh, _ = pl_sh.run(x_loc, idx_loc, w_loc, yr=False, out=False)
+            return moe.finalize(acc, ysh)     # this rank's rows
         if peer is not None:
             yr_p, _ = peer.parts(peer.launched + 1)
             pl.run(xs[i % NX], idx, w, yr=yr_p, ys=False, out=False, ysum=True)
@@ -622,9 +643,12 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True):
     if rank == 0:
         sampler.start()
     ms = timed(experts, n_steps)
-    for i in range(3):
-        whole(i)
-    ms_e2e = timed(whole, max(2, n_steps // 2))
+    if a2a:
+        ms_e2e = ms   # (no separate end-to-end leg for this scheme: the sub-record carries the device-timed pass)
+    else:
+        for i in range(3):
+            whole(i)
+        ms_e2e = timed(whole, max(2, n_steps // 2))
     # the dominant kernel alone: the routed gate/up grouped GEMM over the operands the last pass left in the workspace
     idx, w = routed[(n_steps - 1) % NX]
     pl.run(xs[(n_steps - 1) % NX], idx, w, yr=yr, ys=ys, out=out)
@@ -640,6 +664,10 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True):
         from oracle import oracle as orc
         idx0, w0 = routed[0]
         got = experts(0)
+        if a2a:  # every rank holds its own rows: gathered for the check
+            parts = [torch.empty((r + 1) * T // world - r * T // world, H, dtype=torch.bfloat16, device=dev) for r in range(world)]
+            dist.all_gather(parts, got.contiguous())
+            got = torch.cat(parts)
         torch.cuda.synchronize()
         rows_s = np.unique(np.concatenate([[0, T - 1], np.random.default_rng(3).integers(0, T, 14)]))
         got = got[torch.from_numpy(rows_s).to(dev)].float().cpu().numpy()
@@ -647,7 +675,8 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True):
         mine = {int(e): lay.canonical(int(e)) for e in np.unique(idx_np) if e_lo <= e < e_hi}
         if not mine:
             mine = {e_lo: lay.canonical(e_lo)}
-        acc, _, pm = orc.moe_fp8_layer(synth.bf16_bits(xs[0])[rows_s], idx_np, w_np, mine, lay.canonical(E) if rank == 0 else None,
+        sh_lay = lay_sh if a2a else lay
+        acc, _, pm = orc.moe_fp8_layer(synth.bf16_bits(xs[0])[rows_s], idx_np, w_np, mine, sh_lay.canonical(E) if rank == 0 else None,
                                        e_lo=e_lo, e_hi=e_hi, with_shared=rank == 0, pickmax=True)
         acc_t, pm_t = torch.from_numpy(acc).to(dev), torch.from_numpy(pm).to(dev)
         if world > 1:
@@ -675,7 +704,10 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True):
                                 f"config 4: prefill MoE, hidden 2048, 64 experts x 1024, top-6, + shared expert, {T} tokens, "
                                 f"Zipf(1.1) expert popularity (router bias scale {alpha})"), "tokens": T,
                    "segments": {"max": int(c[0]), "median": int(np.median(c)), "min": int(c[-1])},
-                   "parallelism": f"ep{world}" + ("" if world == 1 else " (NCCL all-reduce)" if peer is None else
+                   "parallelism": f"ep{world}" + ("" if world == 1 else
+                                                   " (rows partitioned; NCCL all-to-all dispatch of rows to the ranks that own "
+                                                   "a pick, all-to-all return of f32 partial sums)" if a2a else
+                                                   " (NCCL all-reduce)" if peer is None else
                                                    " (partial sums reduced over peer memory by k_finalize_peers)"),
                    "cold_inputs": f"{NX} activation sets cycled; inputs and intermediates larger than L2",
                    "step": "sort/permute + quantise + gate/up GEMM (SwiGLU) + down GEMM + shared expert + combine",
@@ -767,8 +799,9 @@ def main():
         import torch
         a = copy.copy(args)
         a.workload = workload
-        if workload in ("prefill", "ragged"):
-            line = run_prefill(a, workload=workload, steps=steps, with_cpu=not brief)
+        if workload in ("prefill", "ragged", "ragged_a2a"):
+            line = run_prefill(a, workload="ragged" if workload == "ragged_a2a" else workload, steps=steps, with_cpu=not brief,
+                               a2a=workload == "ragged_a2a")
         else:
             a.layers = select(workload)
             line = run_gpu(a, rows=rows, steps=steps, with_kernel=True, with_cpu=not brief)
@@ -798,7 +831,7 @@ def main():
                      ("config3_int4_rows4", "int4", 4, 20), ("config4_prefill_16384", "prefill", 1, 6),
                      ("config5_ragged_batch", "ragged", 1, 6)]
         else:
-            plan += [("config4_prefill_16384", "prefill", 1, 6)]
+            plan += [("config4_prefill_16384", "prefill", 1, 6), ("config5_ragged_batch_all_to_all", "ragged_a2a", 1, 6)]
         for name, wl, rows, steps in plan:
             try:
                 others[name] = one(wl, rows, steps, brief=True)

@@ -60,7 +60,8 @@ DSGX_DEV void block_mma(float (&d)[4], const uint8_t* a, const uint8_t* b, const
   d[0] += e[0], d[1] += e[1], d[2] += e[2], d[3] += e[3];
 }
 
-template <class V>
+// kMx: the routed experts are MXFP4 (a separate instantiation: an FP8 layer's kernels carry none of that code)
+template <class V, bool kMx>
 __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p) {
   constexpr int kWarps = V::kWarps, kKCH = V::kKCH, kNST = V::kNST, kUpStage = V::kUpStage;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
           const int b0 = r * rp * kPB, b1 = min(HB, (r + 1) * rp * kPB);
           const bool shared = unit < sh_units;
           const int slot = shared ? 0 : (unit - sh_units) / upp, i8 = shared ? u0 + unit : (unit - sh_units) % upp;
-          pblk = !shared && p.mx ? kMxBlk : 1024;  // bytes of a (strip, 128-k block)
+          pblk = kMx && !shared ? kMxBlk : 1024;  // bytes of a (strip, 128-k block)
           const size_t off = ((size_t)i8 * HB + b0) * pblk;
           pg = (shared ? p.sh.g : tab.ent[slot].g) + off, pu = (shared ? p.sh.u : tab.ent[slot].u) + off;
           pnc = b1 > b0 ? (b1 - b0) / kKCH : 0, pc = 0;
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
       const int uidx = unit;
       float tot[4] = {0.f, 0.f, 0.f, 0.f}, pc4[4] = {0.f, 0.f, 0.f, 0.f};  // gate r0, gate r1, up r0, up r1
       if (b1 > b0) {
-        const bool mx = !shared && p.mx;
+        const bool mx = kMx && !shared;
         const int srow = (i8 * 8) / 128, blk = mx ? kMxBlk : 1024;
         const float* sgp = shared ? p.sh.gs : tab.ent[slot].sg;
         const float* sup = shared ? p.sh.us : tab.ent[slot].su;
@@ -269,7 +270,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
 }
 
 // ------------------------------------------------------------------------------------------------------------ k_down
-template <class V>
+template <class V, bool kMx>
 __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams p) {
   constexpr int kWarps = V::kWarps, kThreads = V::kThreads, kKCH = V::kKCH, kNST = V::kNST, kDownStage = V::kDownStage;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
       if (pnc < 0) {
         int tslot, n16, b0, b1;
         decode(pi, tslot, pwslot, n16, b0, b1);
-        pblk = tslot < tab.nslots && p.mx ? kMxBlk : 1024;  // bytes of a (strip, 128-k block)
+        pblk = kMx && tslot < tab.nslots ? kMxBlk : 1024;  // bytes of a (strip, 128-k block)
         pd = tab.ent[tslot].d + ((size_t)(2 * n16) * IB + b0) * pblk;
         pb = b0, pnc = b1 > b0 ? (b1 - b0) / kKCH : 0, pc = 0;
       }
@@ -442,7 +443,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
     const int uidx = it / split;
     float tot[4] = {0.f, 0.f, 0.f, 0.f}, pc4[4] = {0.f, 0.f, 0.f, 0.f};
     if (b1 > b0) {
-      const bool mx = !sh && p.mx;
+      const bool mx = kMx && !sh;
       const int srow = (n16 * 16) / 128, blk = mx ? kMxBlk : 1024;
       const float sdl = mx ? 1.f : lane < IB ? __ldg(tab.ent[tslot].sd + (size_t)srow * IB + lane) : 0.f;
       const int nc = (b1 - b0) / kKCH, kend = sh ? sh_b1 : IB;
@@ -505,31 +506,39 @@ size_t down_smem() {
   return kTabSmem + (size_t)V::kWarps * V::kNST * V::kDownStage + (V::kWarps * V::kNST + 1) * 8 + 16;
 }
 
-template <class V>
-cudaError_t launch_up(const DecodeParams& p, cudaStream_t st, bool pdl) {
-  static std::atomic<bool> done[64];
+template <class V, bool kMx>
+cudaError_t launch_up_f(const DecodeParams& p, cudaStream_t st, bool pdl) {
+  static std::atomic<bool> done[64];  // (per device; two host threads may both set the attribute: harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!done[dev & 63].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(k_up_fp8<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(k_up_fp8<V, kMx>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     done[dev & 63].store(true, std::memory_order_release);
   }
   const size_t smem = up_smem<V>(p.H);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  return launch_k(k_up_fp8<V>, dim3(sm_count()), dim3(V::kThreads), smem, st, pdl, p);
+  return launch_k(k_up_fp8<V, kMx>, dim3(sm_count()), dim3(V::kThreads), smem, st, pdl, p);
 }
 template <class V>
-cudaError_t launch_down(const DecodeParams& p, cudaStream_t st, bool pdl) {
+cudaError_t launch_up(const DecodeParams& p, cudaStream_t st, bool pdl) {
+  return p.mx ? launch_up_f<V, true>(p, st, pdl) : launch_up_f<V, false>(p, st, pdl);
+}
+template <class V, bool kMx>
+cudaError_t launch_down_f(const DecodeParams& p, cudaStream_t st, bool pdl) {
   static std::atomic<bool> done[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (!done[dev & 63].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(k_down_fp8<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)down_smem<V>());
+    cudaError_t e = cudaFuncSetAttribute(k_down_fp8<V, kMx>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)down_smem<V>());
     if (e != cudaSuccess) return e;
     done[dev & 63].store(true, std::memory_order_release);
   }
-  return launch_k(k_down_fp8<V>, dim3(sm_count()), dim3(V::kThreads), down_smem<V>(), st, pdl, p);
+  return launch_k(k_down_fp8<V, kMx>, dim3(sm_count()), dim3(V::kThreads), down_smem<V>(), st, pdl, p);
+}
+template <class V>
+cudaError_t launch_down(const DecodeParams& p, cudaStream_t st, bool pdl) {
+  return p.mx ? launch_down_f<V, true>(p, st, pdl) : launch_down_f<V, false>(p, st, pdl);
 }
 
 }  // namespace

@@ -33,17 +33,19 @@ DSGX_DEV void stage_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t
 // ----------------------------------------------------------------------------------------------------------- k_front
 // CTAs [0, nlog): one warp per (expert, slice of 1024 k): the slice's partial logit of every row, in the router's
 // summation order (lane j: k = base + 128 i + 4 j + c by fma, then the butterfly).  CTAs [nlog, ..): x -> blocks.
+// kNorm: the rows are normalised first (a separate instantiation: the plain kernel keeps its registers and its start).
+template <bool kNorm>
 __global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, int M,
                                                int H, int E, int nlog, float* __restrict__ lpart, uint8_t* __restrict__ xq,
                                                int fmt, FrontNorm fn) {
-  __shared__ float red[kRmsRed];
+  __shared__ float red[kNorm ? kRmsRed : 1];
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const RowNorm nrm{fn.w, red + 8 * kMaxRows, fn.mode};
+  const RowNorm nrm{kNorm ? fn.w : nullptr, red + (kNorm ? 8 * kMaxRows : 0), fn.mode};
   if ((int)blockIdx.x >= nlog) {
     pdl_wait();
-    if (fn.w) rms_rows_rstd(x, M, H, fn.eps, red);
-    stage_x(x, M, H, xq, fmt, (int)blockIdx.x - nlog, nrm, fn.xn_out);
+    if (kNorm) rms_rows_rstd(x, M, H, fn.eps, red);
+    stage_x(x, M, H, xq, fmt, (int)blockIdx.x - nlog, nrm, kNorm ? fn.xn_out : nullptr);
     return;
   }
   const int KS = (H + 1023) / 1024;
@@ -53,7 +55,7 @@ __global__ void __launch_bounds__(256) k_front(const __nv_bfloat16* __restrict__
   float4 wv[8];
   if (e < E) logit_slice_weights(wr, H, e, sl, lane, wv);
   pdl_wait();
-  if (fn.w) rms_rows_rstd(x, M, H, fn.eps, red);  // (every CTA sums the rows itself: 8 KB a row out of L2, no launch in front)
+  if (kNorm) rms_rows_rstd(x, M, H, fn.eps, red);  // (every CTA sums the rows itself: 8 KB a row out of L2, no launch in front)
   if (e >= E) return;
   logit_slice_rows(x, wv, M, H, E, e, sl, lpart, lane, nrm);
 }
@@ -142,8 +144,8 @@ cudaError_t launch_front_route(const DecodeParams& p, uint32_t fmt, const RouteP
                                bool pdl) {
   const int KS = (p.H + 1023) / 1024;
   const int nlog = (p.E * KS + 7) / 8;
-  cudaError_t e = launch_k(k_front, dim3(nlog + stage_ctas(p, fmt)), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog,
-                           p.ws.lpart, p.ws.xq, (int)fmt, p.norm);
+  cudaError_t e = launch_k(p.norm.w ? k_front<true> : k_front<false>, dim3(nlog + stage_ctas(p, fmt)), dim3(256), 0, st, pdl, x,
+                           wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq, (int)fmt, p.norm);
   if (e != cudaSuccess) return e;
   return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, fmt),
                   (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
@@ -167,8 +169,8 @@ cudaError_t launch_front_route_only(const DecodeParams& p, const RouteParams& rp
   const int nlog = (p.E * KS + 7) / 8;
   FrontNorm fn = p.norm;
   fn.xn_out = nullptr;  // (the one kernel that follows writes the copy)
-  cudaError_t e = launch_k(k_front, dim3(nlog), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog, p.ws.lpart, p.ws.xq,
-                           (int)DSGX_FMT_FP8, fn);
+  cudaError_t e = launch_k(fn.w ? k_front<true> : k_front<false>, dim3(nlog), dim3(256), 0, st, pdl, x, wr, p.M, p.H, p.E, nlog,
+                           p.ws.lpart, p.ws.xq, (int)DSGX_FMT_FP8, fn);
   if (e != cudaSuccess) return e;
   return launch_k(k_route_union, dim3(p.M), dim3((p.E + 31) / 32 * 32), 0, st, pdl, rp, tab_args(p, DSGX_FMT_FP8),
                   (const float*)p.ws.lpart, KS, bias, logits, idx, w, p.ws.tab, p.ws.status, p.ws.status + 16);
