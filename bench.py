@@ -573,7 +573,7 @@ def run_prefill(args, workload=None, steps=None, with_cpu=True, a2a=False):
         if a2a:
             x_loc, idx_loc, w_loc = xs[i % NX][r_lo:r_hi], idx[r_lo:r_hi].contiguous(), w[r_lo:r_hi].contiguous()
             acc = ep.all_to_all_experts(x_loc, idx_loc, w_loc, E, local_routed)
-            _, ysh, _ = pl_sh.run(x_loc, idx_loc, w_loc, yr=False, out=False)
+            _, ysh, _ = pl_sh.run(x_loc, idx_loc, w_loc, out=False)   # (its routed partial sums are zero: no expert)
             return moe.finalize(acc, ysh)     # this rank's rows
         if peer is not None:
             yr_p, _ = peer.parts(peer.launched + 1)

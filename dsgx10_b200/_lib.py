@@ -9,7 +9,8 @@ LIB_PATH = os.path.join(HERE, "libdsgx_moe.so")
 OK, ERR_ARG, ERR_FORMAT, ERR_SHAPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED, ERR_LIMIT = range(8)
 FMT_NVFP4, FMT_RETIRED, FMT_INT4, FMT_BF16, FMT_FP8, FMT_MXFP4 = range(6)
 SCORE_SIGMOID, SCORE_SOFTMAX, SCORE_SQRTSOFTPLUS = 0, 1, 2
-MAX_ROWS = 8
+MAX_ROWS = 8         # rows one launch sequence takes
+MAX_STEP_ROWS = 16   # rows a decode call takes (9..16: two sequences)
 PH_BUCKET, PH_UP, PH_DOWN, PH_COMBINE, PH_SHARED, PH_ALL = 1, 2, 4, 8, 16, 31
 
 

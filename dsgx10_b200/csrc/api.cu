@@ -236,6 +236,16 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
   if (!cfg) cfg = &dflt;
   const bool own_route = cfg->logits != nullptr;  // the step routes on the caller's logits: idx / w are not read
   if (!L || !x || (!own_route && (!idx || !w)) || !ws || !yr) return DSGX_ERR_ARG;
+  if (M > kMaxRows && M <= DSGX_MAX_STEP_ROWS) {  // 9..16 rows: rows 0..7, then the rest, in stream order on the same workspace
+    if (cfg->parts != 0 && cfg->parts != 3) return DSGX_ERR_ARG;  // (the bench hooks address one launch sequence)
+    const int rc0 = dsgx_moe_decode(s, L, x, idx, w, kMaxRows, ws, yr, ys, stream, cfg);
+    if (rc0) return rc0;
+    const size_t r = kMaxRows;
+    dsgx_decode_cfg c2 = *cfg;
+    if (c2.logits) c2.logits += r * s->E;
+    return dsgx_moe_decode(s, L, reinterpret_cast<const uint8_t*>(x) + r * s->H * 2, idx ? idx + r * s->topk : nullptr,
+                           w ? w + r * s->topk : nullptr, M - kMaxRows, ws, yr + r * s->H, ys ? ys + r * s->H : nullptr, stream, &c2);
+  }
   if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
   if (L->fmt != s->fmt) return DSGX_ERR_FORMAT;
   RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
@@ -295,6 +305,17 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
   if (finalize && !st->out_bf16) return DSGX_ERR_ARG;
   int rc = check_shape(s);
   if (rc) return rc;
+  if (M > kMaxRows && M <= DSGX_MAX_STEP_ROWS) {  // 9..16 rows: two launch sequences, every buffer moved on by eight rows
+    rc = dsgx_moe_layer_decode(s, L, x, kMaxRows, st, finalize, stream);
+    if (rc) return rc;
+    const size_t r = kMaxRows;
+    dsgx_layer_step b = *st;
+    b.logits += r * s->E, b.idx += r * s->topk, b.w += r * s->topk, b.yr += r * s->H;
+    if (b.ys) b.ys += r * s->H;
+    if (b.out_bf16) b.out_bf16 = reinterpret_cast<uint8_t*>(b.out_bf16) + r * s->H * 2;
+    if (b.xn_out) b.xn_out = reinterpret_cast<uint8_t*>(b.xn_out) + r * s->H * 2;
+    return dsgx_moe_layer_decode(s, L, reinterpret_cast<const uint8_t*>(x) + r * s->H * 2, M - kMaxRows, &b, finalize, stream);
+  }
   {
     if (!L || !x || !L->pool || !L->desc || L->fmt != s->fmt) return DSGX_ERR_ARG;
     if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
@@ -361,7 +382,7 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* s, const dsgx_layer_w* L, c
                                const dsgx_layer_step* st, void* out_host, void* stream) {
   if (!st || !st->x_stage || !x_host || !s) return DSGX_ERR_ARG;
   if (out_host && !st->out_bf16) return DSGX_ERR_ARG;
-  if (M < 1 || M > kMaxRows) return DSGX_ERR_ARG;
+  if (M < 1 || M > DSGX_MAX_STEP_ROWS) return DSGX_ERR_ARG;
   const size_t bytes = (size_t)M * s->H * 2;
   // Host buffers the device can address (pinned, mapped memory) are used in place: a small kernel pulls x over PCIe
   // into the staging buffer, and the step's last kernel writes the rounded rows straight into out_host, instead of two

@@ -76,19 +76,29 @@ constexpr int kRJ = 16;  // experts a lane: E <= 512
 DSGX_DEV void route_row(const RouteParams& p, const float* __restrict__ l, int nsplit, size_t split_stride,
                         const float* __restrict__ bias, int lane, int& id_out, float& w_out, float* logits_out) {
   float s[kRJ], key[kRJ];
-  // every load before any math: one round trip
+  // every load before any math: one round trip (up to four slices of partial sums at a time, added in ascending order)
 #pragma unroll
   for (int j = 0; j < kRJ; ++j) {
     const int e = lane + 32 * j;
     s[j] = e < p.E ? (nsplit ? __ldcg(l + e) : l[e]) : -INFINITY;  // (nsplit 0: summed logits behind a plain pointer)
     key[j] = e < p.E && bias ? __ldg(bias + e) : 0.f;
   }
-  for (int sp = 1; sp < nsplit; ++sp) {
+  for (int sp0 = 1; sp0 < nsplit; sp0 += 3) {
+    float part[3][kRJ];
 #pragma unroll
-    for (int j = 0; j < kRJ; ++j) {
-      const int e = lane + 32 * j;
-      if (e < p.E) s[j] = __fadd_rn(s[j], __ldcg(l + sp * split_stride + e));
-    }
+    for (int q = 0; q < 3; ++q)
+#pragma unroll
+      for (int j = 0; j < kRJ; ++j) {
+        const int e = lane + 32 * j;
+        part[q][j] = sp0 + q < nsplit && e < p.E ? __ldcg(l + (sp0 + q) * split_stride + e) : 0.f;
+      }
+#pragma unroll
+    for (int q = 0; q < 3; ++q)
+      if (sp0 + q < nsplit) {
+#pragma unroll
+        for (int j = 0; j < kRJ; ++j)
+          if (lane + 32 * j < p.E) s[j] = __fadd_rn(s[j], part[q][j]);
+      }
   }
   if (logits_out) {
 #pragma unroll

@@ -137,20 +137,20 @@ class LayerStep:
         norm_w (bf16 [H]): the step normalises its input rows first (RMSNorm fused into the front); self.xn gets a copy."""
         f32 = dict(dtype=torch.float32, device=device)
         self.shp, self.wr, self.bias = shp, wr, bias
-        self.logits = torch.empty(_lib.MAX_ROWS, shp.E, **f32)
-        self.idx = torch.empty(_lib.MAX_ROWS, shp.topk, dtype=torch.int32, device=device)
-        self.w = torch.empty(_lib.MAX_ROWS, shp.topk, **f32)
+        self.logits = torch.empty(_lib.MAX_STEP_ROWS, shp.E, **f32)
+        self.idx = torch.empty(_lib.MAX_STEP_ROWS, shp.topk, dtype=torch.int32, device=device)
+        self.w = torch.empty(_lib.MAX_STEP_ROWS, shp.topk, **f32)
         self.ws = decode_ws(shp, device)
-        self.yr = torch.zeros(_lib.MAX_ROWS, shp.H, **f32)
-        self.ys = torch.zeros(_lib.MAX_ROWS, shp.H, **f32)
-        self.out = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
-        self.x_stage = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
+        self.yr = torch.zeros(_lib.MAX_STEP_ROWS, shp.H, **f32)
+        self.ys = torch.zeros(_lib.MAX_STEP_ROWS, shp.H, **f32)
+        self.out = torch.zeros(_lib.MAX_STEP_ROWS, shp.H, dtype=torch.bfloat16, device=device)
+        self.x_stage = torch.zeros(_lib.MAX_STEP_ROWS, shp.H, dtype=torch.bfloat16, device=device)
         self.c = _lib.LayerStep(_ptr(wr), _ptr(bias), _ptr(self.logits), _ptr(self.idx), _ptr(self.w), _ptr(self.ws),
                                 _ptr(self.yr), _ptr(self.ys), _ptr(self.out), _ptr(self.x_stage),
                                 (0 if fused is None else 4 if fused else 1) | (2 if stamps is not None else 0), 0, _ptr(stamps))
         self.norm_w = norm_w
         if norm_w is not None:
-            self.xn = torch.zeros(_lib.MAX_ROWS, shp.H, dtype=torch.bfloat16, device=device)
+            self.xn = torch.zeros(_lib.MAX_STEP_ROWS, shp.H, dtype=torch.bfloat16, device=device)
             self.c.norm_w, self.c.xn_out, self.c.norm_eps, self.c.norm_mode = _ptr(norm_w), _ptr(self.xn), norm_eps, norm_mode
 
     def run(self, layer_w, x, finalize=True, yr=None, ys=None):

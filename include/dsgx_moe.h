@@ -55,7 +55,11 @@ enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF1
  * sqrt(softplus(l)) (ds41f engine/kernels/common.cuh:264-287, the only score dsk::router_topk has) */
 enum { DSGX_SCORE_SIGMOID = 0, DSGX_SCORE_SOFTMAX = 1, DSGX_SCORE_SQRTSOFTPLUS = 2 };
 
-enum { DSGX_MAX_ROWS = 8 };  /* decode rows a step */
+enum { DSGX_MAX_ROWS = 8 };  /* decode rows one launch sequence of the expert kernels takes */
+/* Rows a decode call takes (the reference's kMaxRows, altar1 engine/experts/experts.h:24).  9..16 rows run as two launch
+ * sequences of at most 8 rows on the same stream and workspace (rows 0..7, then 8..M-1): every row's result is the one a
+ * smaller step gives it (the kernels are batch-invariant); an expert that both halves picked is streamed twice. */
+enum { DSGX_MAX_STEP_ROWS = 16 };
 
 /* One routed matrix of one expert: stands in for gx::MatDesc (altar1 engine/experts/experts.h:58-64), 64 bytes.
  *   off: byte offset of the matrix's blocks in the layer's pool, a multiple of 256
@@ -159,7 +163,7 @@ int dsgx_sort_pack_static(const int32_t* idx, int T, int topk, int E, int32_t* c
  * waits for that sort; the cached address of the array does not survive a cudaDeviceReset). */
 int dsgx_sort_static_status(void);
 
-/* ---- decode (1..DSGX_MAX_ROWS rows) ------------------------------------------------------------------------------
+/* ---- decode (1..DSGX_MAX_STEP_ROWS rows) ------------------------------------------------------------------------------
  * Stands in for gx::decode_ws_bytes / gx::moe_decode (altar1 engine/experts/experts.h:104-141) and dsk::moe_routed
  * (ds41f engine/kernels/dsk.h:212-236).  x bf16 [M][H]; idx, w from dsgx_route; ws: dsgx_decode_ws_bytes(shape) bytes,
  * zeroed once before the first call (its counters reset themselves).  Writes this GPU's f32 partial sums
@@ -250,8 +254,9 @@ int dsgx_finalize_add_norm(const float* R, const float* S, int M, int H, int mod
 /* ---- one layer step, router to rounded output --------------------------------------------------------------------
  * The sequence the engines' layer runners issue around the operator (altar1 engine/model/model.cu:308-352: router
  * GEMV, route, moe_decode, then the reduction and the rounding): logits = x wr^T, route, the expert step, and
- * out = bf16(yr + ys).  Every buffer is caller-owned device memory sized for DSGX_MAX_ROWS rows:
- * logits [8][E] f32, idx [8][topk] i32, w [8][topk] f32, yr, ys [8][H] f32, out [8][H] bf16, x_stage [8][H] bf16.
+ * out = bf16(yr + ys).  Every buffer is caller-owned device memory sized for the rows of the call (up to
+ * DSGX_MAX_STEP_ROWS): logits [M][E] f32, idx [M][topk] i32, w [M][topk] f32, yr, ys [M][H] f32, out [M][H] bf16,
+ * x_stage [M][H] bf16.
  * With n_ranks > 1 the caller reduces yr across GPUs between dsgx_moe_layer_decode(..., finalize = 0) and dsgx_finalize. */
 typedef struct dsgx_layer_step {
   const float* wr;    /* router weights f32 [E][H] */

@@ -320,3 +320,26 @@ def test_one_kernel_step_reports_a_wait_that_runs_out():
     torch.cuda.synchronize()
     assert moe.ws_status(step.ws) == 0
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("M", [9, 13, 16])
+def test_rows_9_to_16(orc, M):
+    """More than eight rows: two launch sequences of at most eight on one workspace; parity as any step, and the layer
+    step's rows (with the fused norm) equal the rows of two smaller steps bit for bit."""
+    _run(orc, 512, 256, 16, 4, M, seed=300 + M)
+    from dsgx10_b200 import moe, synth
+    H, I, E, topk = 1024, 512, 16, 4
+    shp = moe.shape(H, I, E, topk)
+    layer = synth.Fp8Layer(H, I, E, 310, device="cuda")
+    wr = synth.router_weights(E, H, 311, device="cpu").cuda()
+    x = synth.activations(M, H, 312, device="cpu").cuda()
+    nw = (1.0 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(313))).to(torch.bfloat16).cuda()
+    for kw in ({}, {"norm_w": nw}):
+        big, small = moe.LayerStep(shp, wr, **kw), moe.LayerStep(shp, wr, **kw)
+        out = big.run(layer.layer_w(), x).clone()
+        a = small.run(layer.layer_w(), x[:8]).clone()
+        b = small.run(layer.layer_w(), x[8:]).clone()
+        torch.cuda.synchronize()
+        assert moe.ws_status(big.ws) == 0
+        assert torch.equal(out, torch.cat([a, b]))
+        assert torch.equal(big.idx[8:M], small.idx[:M - 8])

@@ -123,3 +123,19 @@ def test_batch_invariance(orc):
         step.run(layer.layer_w(), x[r:r + 1].contiguous())
         torch.cuda.synchronize()
         assert torch.equal(step.yr[0], yr8[r]) and torch.equal(step.ys[0], ys8[r])
+
+
+def test_rows_9_to_16(orc):
+    """Twelve rows through an INT4 layer: the rows of an eight-row and a four-row step, bit for bit."""
+    from dsgx10_b200 import _lib, moe, synth
+    H, I, E, topk, M = 1024, 512, 8, 2, 12
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_INT4, score_fn=1)
+    layer = synth.Int4Layer(H, I, E, 950, device="cuda")
+    wr = synth.router_weights(E, H, 951, device="cpu").cuda()
+    x = synth.activations(M, H, 952, device="cpu").cuda()
+    big, small = moe.LayerStep(shp, wr), moe.LayerStep(shp, wr)
+    out = big.run(layer.layer_w(), x).clone()
+    a = small.run(layer.layer_w(), x[:8]).clone()
+    b = small.run(layer.layer_w(), x[8:]).clone()
+    torch.cuda.synchronize()
+    assert moe.ws_status(big.ws) == 0 and torch.equal(out, torch.cat([a, b]))
