@@ -81,24 +81,9 @@ __global__ void __launch_bounds__(512) k_route_union(RouteParams rp, TabArgs ta,
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
-#ifdef DSGX_ROUTE_WARP
-  // one warp routes the row with shuffles only (route.cuh: route_row, the same bits); the CTA's other warps join for the table
-  if (threadIdx.x < 32) {
-    int id;
-    float wv;
-    route_row(rp, lpart + (size_t)row * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, (int)threadIdx.x, id, wv,
-              logits ? logits + (size_t)row * rp.E : nullptr);
-    if ((int)threadIdx.x < rp.topk) {
-      idx[row * rp.topk + threadIdx.x] = id, w[row * rp.topk + threadIdx.x] = wv;
-      if (ta.M == 1) s_idx[threadIdx.x] = id, s_w[threadIdx.x] = wv;
-    }
-  }
-  (void)rs;
-#else
   route_row_cta(rp, lpart + (size_t)row * rp.E, nsplit, (size_t)kMaxRows * rp.E, bias, rs,
                 logits ? logits + (size_t)row * rp.E : nullptr, idx + row * rp.topk, w + row * rp.topk,
                 ta.M == 1 ? s_idx : nullptr, s_w);
-#endif
   if (ta.M > 1) {  // the last row to finish builds the slot table of the step (one row: its picks are in shared memory)
     __threadfence();
     __syncthreads();

@@ -162,12 +162,12 @@ def test_refusals():
     from dsgx10_b200 import _lib, moe, synth
     shp = moe.shape(512, 256, 16, 4)
     layer = synth.Fp8Layer(512, 256, 16, 1, device="cuda")
-    x = synth.activations(9, 512, 2).cuda()
-    idx = torch.zeros(9, 4, dtype=torch.int32, device="cuda")
-    w = torch.zeros(9, 4, device="cuda")
+    x = synth.activations(17, 512, 2).cuda()
+    idx = torch.zeros(17, 4, dtype=torch.int32, device="cuda")
+    w = torch.zeros(17, 4, device="cuda")
     ws = moe.decode_ws(shp)
     with pytest.raises(_lib.DsgxError) as e:
-        moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws)  # 9 rows
+        moe.moe_decode(shp, layer.layer_w(), x, idx, w, ws)  # 17 rows: more than a decode call takes
     assert e.value.status == _lib.ERR_ARG
     for fmt in (_lib.FMT_NVFP4, _lib.FMT_RETIRED, 7):
         bad = moe.shape(512, 256, 16, 4, fmt=fmt)
