@@ -80,13 +80,13 @@ static int check_route_shape(const dsgx_moe_shape* s) {
 static int check_shape(const dsgx_moe_shape* s) {
   if (!s) return DSGX_ERR_ARG;
   if (s->fmt == DSGX_FMT_NVFP4 || s->fmt == DSGX_FMT_RETIRED) return DSGX_ERR_FORMAT;
-  if (!fmt_fp8_family(s->fmt) && s->fmt != DSGX_FMT_INT4) return DSGX_ERR_FORMAT;
+  if (!fmt_fp8_family(s->fmt) && s->fmt != DSGX_FMT_INT4 && s->fmt != DSGX_FMT_BF16) return DSGX_ERR_FORMAT;
   const int rc = check_route_shape(s);
   if (rc) return rc;
   if (s->H < 128 || s->I < 128 || s->H % 128 || s->I % 128) return DSGX_ERR_SHAPE;
   if (s->e_lo < 0 || s->e_hi > s->E || s->e_lo > s->e_hi) return DSGX_ERR_SHAPE;
   if (fmt_fp8_family(s->fmt) && (s->H > 4096 || s->I > 4096 || s->H % 256 || s->I % 256)) return DSGX_ERR_SHAPE;
-  if (s->fmt == DSGX_FMT_INT4 && (s->H % 512 || s->I % 512)) return DSGX_ERR_SHAPE;
+  if ((s->fmt == DSGX_FMT_INT4 || s->fmt == DSGX_FMT_BF16) && (s->H % 512 || s->I % 512)) return DSGX_ERR_SHAPE;
   if (s->sh_lo || s->sh_hi) {  // a part of the shared expert: FP8 decode only, whole pieces of 512 channels
     if (!fmt_fp8_family(s->fmt) || s->sh_lo < 0 || s->sh_hi > s->I || s->sh_lo >= s->sh_hi || s->sh_lo % 512 ||
         (s->sh_hi % 512 && s->sh_hi != s->I))
@@ -265,14 +265,14 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.up = cfg->up, p.down = cfg->down;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     p.norm = FrontNorm{nullptr, nullptr, 0.f, 0};
-    p.mx = s->fmt == DSGX_FMT_MXFP4;
+    p.mx = s->fmt == DSGX_FMT_MXFP4, p.b16 = 0;
     if (p.up < 0 || p.up >= decode_fp8_up_variants() || p.down < 0 || p.down >= decode_fp8_down_variants()) return DSGX_ERR_ARG;
     cudaError_t e = launch_decode_fp8(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                       cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
   }
-  if (s->fmt == DSGX_FMT_INT4) {
-    if (L->sh.g || L->sh.u || L->sh.d) return DSGX_ERR_FORMAT;  // an INT4 layer's shared expert is bf16
+  if (s->fmt == DSGX_FMT_INT4 || s->fmt == DSGX_FMT_BF16) {
+    if (L->sh.g || L->sh.u || L->sh.d) return DSGX_ERR_FORMAT;  // an INT4 or BF16 layer's shared expert is bf16
     const bool shb = L->sh.bg != nullptr || L->sh.bgu != nullptr;
     if (shb && (!L->sh.bd || (L->sh.bgu ? (L->sh.bg || L->sh.bu) : !L->sh.bu))) return DSGX_ERR_ARG;  // one of the two forms
     if (shb && !ys && !cfg->ysum) return DSGX_ERR_ARG;
@@ -285,7 +285,7 @@ int dsgx_moe_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const void* 
     p.yr = yr, p.ys = ys, p.ysum = cfg->ysum, p.out = nullptr, p.up = 0, p.down = 0;
     p.sh_lo = s->sh_lo, p.sh_hi = s->sh_hi ? s->sh_hi : s->I, p.limit = s->swiglu_limit;
     p.norm = FrontNorm{nullptr, nullptr, 0.f, 0};
-    p.mx = 0;
+    p.mx = 0, p.b16 = s->fmt == DSGX_FMT_BF16;
     cudaError_t e = launch_decode_int4(p, reinterpret_cast<const __nv_bfloat16*>(x), (cudaStream_t)stream, cfg->pdl != 0,
                                        cfg->parts == 0 ? 3 : cfg->parts, own_route ? &rp : nullptr, cfg->logits, cfg->bias);
     return e == cudaSuccess ? DSGX_OK : cuda_fail(e);
@@ -340,7 +340,7 @@ int dsgx_moe_layer_decode(const dsgx_moe_shape* s, const dsgx_layer_w* L, const 
                        (((uintptr_t)st->norm_w | (uintptr_t)st->xn_out) & 15)))
       return DSGX_ERR_ARG;
     p.out = finalize ? reinterpret_cast<__nv_bfloat16*>(st->out_bf16) : nullptr;
-    p.mx = mx;
+    p.mx = mx, p.b16 = s->fmt == DSGX_FMT_BF16;
     RouteParams rp{s->E, s->topk, s->n_group, s->topk_group, s->score_fn, s->norm_topk, s->route_scale};
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
     // the whole step as one persistent kernel: measured faster from three rows up (flags bit 2 forces it, bit 0 forbids it)

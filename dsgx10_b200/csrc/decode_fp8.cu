@@ -77,13 +77,15 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   uint8_t* myring = ring + warp * kNST * kUpStage;
   uint64_t* mybar = bars + warp * kNST;
 
-  pdl_launch_dependents();
   if (lane == 0)
     for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
   if (threadIdx.x == 0) mbar_init(tabbar, 1);
   mbar_fence_init();
   __syncthreads();
   pdl_wait();
+  // (after the wait: the down kernel, launched on this trigger, reads the slot table before its own wait, and by now the
+  // kernel that wrote the table is complete)
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {  // the slot table and the quantised rows, made by the kernel ahead
     mbar_expect_tx(tabbar, (uint32_t)(sizeof(SlotTab) + HB * kActBlk));
     bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), tabbar);
@@ -289,7 +291,9 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   if (threadIdx.x == 0) mbar_init(cbar, 1);
   mbar_fence_init();
   __syncthreads();
-  pdl_wait();
+  // The slot table is older than the gate/up kernel (which needed it too, and triggered this launch only after its own
+  // wait): it is read, and the first stages' down weights are requested, BEFORE the wait for the gate/up kernel, whose
+  // last CTAs are still finishing then; only the quantised h, that kernel's output, is requested after the wait.
   if (threadIdx.x == 0) {
     mbar_expect_tx(cbar, (uint32_t)sizeof(SlotTab));
     bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), cbar);
@@ -298,6 +302,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
 
   const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;
   if (!dead && tab.ntot == 0) {  // nothing to add on this GPU: the partial sum is zero
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kThreads) {
       p.yr[i] = 0.f;
       if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
@@ -323,6 +328,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   };
   int pi = gw, pc = 0, pnc = -1, pwslot = 0, pb = 0, pblk = 1024;
   const uint8_t* pd = nullptr;
+  bool early = true;  // before the wait: the h blocks of the stages issued now are requested after it
+  const uint8_t* late_src[kNST];
   auto issue = [&]() {
     while (pi < end) {
       if (pnc < 0) {
@@ -338,7 +345,9 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
         mbar_expect_tx(bar, 2 * kKCH * pblk + kKCH * kActBlk);
         bulk_g2s_hint(st, pd, kKCH * pblk, bar, pol);
         bulk_g2s_hint(st + kKCH * 1024, pd + (size_t)IB * pblk, kKCH * pblk, bar, pol);
-        bulk_g2s(st + 2 * kKCH * 1024, p.ws.hq + ((size_t)pwslot * IB + pb) * kActBlk, kKCH * kActBlk, bar);
+        const uint8_t* hsrc = p.ws.hq + ((size_t)pwslot * IB + pb) * kActBlk;
+        if (early) late_src[issued % kNST] = hsrc;
+        else bulk_g2s(st + 2 * kKCH * 1024, hsrc, kKCH * kActBlk, bar);
         pd += kKCH * pblk, pb += kKCH;
         ++issued;
         if (++pc == pnc) pi += GW, pnc = -1;
@@ -349,6 +358,11 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_fp8(const DecodeParams 
   };
   if (lane == 0)
     while (pi < end && issued - consumed < (uint32_t)kNST) issue();
+  pdl_wait();
+  if (lane == 0)
+    for (uint32_t n = 0; n < issued; ++n)
+      bulk_g2s(myring + n * kDownStage + 2 * kKCH * 1024, late_src[n], kKCH * kActBlk, mybar + n);
+  early = false;
 
   const int g = lane >> 2, t = lane & 3;
   // what a finished run still owes: 1, 2 its ticket among the unit's runs (the last adds the pieces and parks the pick's

@@ -159,9 +159,9 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
   const uint64_t pol = policy_evict_first();
   auto issue = [&]() {
     const int slot = ord_slot(tab, pu / upp), i8 = pu % upp;
-    const bool sh = slot >= tab.nslots;
-    const uint32_t blk = sh ? kB16Blk : kI4Blk;
-    const int cpu = sh ? cpub : cpu4;
+    const bool sh = slot >= tab.nslots, b16 = sh || p.b16;  // (a BF16 layer's routed experts: the shared expert's block format)
+    const uint32_t blk = b16 ? kB16Blk : kI4Blk;
+    const int cpu = b16 ? cpub : cpu4;
     const size_t off = ((size_t)i8 * cpu + pc) * blk;
     uint8_t* st = myring + (issued % kNST) * kUpStage;
     uint64_t* bar = mybar + issued % kNST;
@@ -183,8 +183,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
   const int g = lane >> 2, t = lane & 3;
   for (int unit = gw; unit < total && !dead; unit += GW) {
     const int slot = ord_slot(tab, unit / upp), i8 = unit % upp;
-    const bool sh = slot >= tab.nslots;
-    const int cpu = sh ? cpub : cpu4;
+    const bool sh = slot >= tab.nslots, b16 = sh || p.b16;
+    const int cpu = b16 ? cpub : cpu4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 0; c < cpu; ++c) {
       const uint32_t sidx = consumed % kNST;
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
         break;
       }
       const uint8_t* st = myring + sidx * kUpStage;
-      if (sh) b16_block_mma(acc, st, st + kI4Blk, xt + (size_t)c * 8 * R * 32, R, lane);
+      if (b16) b16_block_mma(acc, st, st + kI4Blk, xt + (size_t)c * 8 * R * 32, R, lane);
       else i4_block_mma(acc, st, st + kI4Blk, xt + (size_t)c * 32 * R * 32, R, lane);
       ++consumed;
       __syncwarp();
@@ -282,17 +282,17 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
   const uint64_t pol = policy_evict_first();
   auto issue = [&]() {
     const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
-    const bool sh = slot >= tab.nslots;
-    const uint32_t blk = sh ? kB16Blk : kI4Blk;
-    const int cpu = sh ? cpub : cpu4;
-    const uint32_t hb = (sh ? 8 : 32) * R * 32;  // the chunk's h groups
+    const bool b16 = slot >= tab.nslots || p.b16;
+    const uint32_t blk = b16 ? kB16Blk : kI4Blk;
+    const int cpu = b16 ? cpub : cpu4;
+    const uint32_t hb = (b16 ? 8 : 32) * R * 32;  // the chunk's h groups
     const size_t off = ((size_t)(2 * n16) * cpu + pc) * blk;
     uint8_t* st = myring + (size_t)(issued % kNST) * stage;
     uint64_t* bar = mybar + issued % kNST;
     mbar_expect_tx(bar, 2 * blk + hb);
     bulk_g2s_hint(st, tab.ent[slot].d + off, blk, bar, pol);
     bulk_g2s_hint(st + kI4Blk, tab.ent[slot].d + off + (size_t)cpu * blk, blk, bar, pol);
-    bulk_g2s(st + kStageW, reinterpret_cast<const uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + (size_t)pc * (sh ? 8 : 32)) * R * 32, hb, bar);
+    bulk_g2s(st + kStageW, reinterpret_cast<const uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + (size_t)pc * (b16 ? 8 : 32)) * R * 32, hb, bar);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
@@ -341,8 +341,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
 
   for (int unit = gw; unit < total && !dead; unit += GW) {
     const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
-    const bool sh = slot >= tab.nslots;
-    const int cpu = sh ? cpub : cpu4;
+    const bool b16 = slot >= tab.nslots || p.b16;
+    const int cpu = b16 ? cpub : cpu4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 0; c < cpu; ++c) {
       const uint32_t sidx = consumed % kNST;
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
         break;
       }
       const uint8_t* st = myring + (size_t)sidx * stage;
-      if (sh) b16_block_mma(acc, st, st + kI4Blk, st + kStageW, R, lane);
+      if (b16) b16_block_mma(acc, st, st + kI4Blk, st + kStageW, R, lane);
       else i4_block_mma(acc, st, st + kI4Blk, st + kStageW, R, lane);
       ++consumed;
       __syncwarp();
@@ -433,8 +433,8 @@ bool decode_int4_fits(int H, int M) { return up_smem<VarI<8, 2>>(H, rows_pow2(M)
 cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cudaStream_t st, bool pdl, int parts,
                                const RouteParams* rp, const float* logits, const float* bias) {
   if (parts & 1) {
-    cudaError_t e = rp ? launch_stage_route(p, DSGX_FMT_INT4, *rp, x, logits, bias, const_cast<int*>(p.idx), const_cast<float*>(p.w), st, pdl)
-                       : launch_prep(p, DSGX_FMT_INT4, x, st, pdl);
+    cudaError_t e = rp ? launch_stage_route(p, p.b16 ? DSGX_FMT_BF16 : DSGX_FMT_INT4, *rp, x, logits, bias, const_cast<int*>(p.idx), const_cast<float*>(p.w), st, pdl)
+                       : launch_prep(p, p.b16 ? DSGX_FMT_BF16 : DSGX_FMT_INT4, x, st, pdl);
     if (e != cudaSuccess) return e;
   }
   return launch_up_down(p, st, pdl, parts);
@@ -442,7 +442,7 @@ cudaError_t launch_decode_int4(const DecodeParams& p, const __nv_bfloat16* x, cu
 
 cudaError_t launch_layer_int4(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,
                               const float* bias, float* logits, int* idx, float* w, cudaStream_t st, bool pdl) {
-  cudaError_t e = launch_front_route(p, DSGX_FMT_INT4, rp, x, wr, bias, logits, idx, w, st, pdl);
+  cudaError_t e = launch_front_route(p, p.b16 ? DSGX_FMT_BF16 : DSGX_FMT_INT4, rp, x, wr, bias, logits, idx, w, st, pdl);
   if (e != cudaSuccess) return e;
   return launch_up_down(p, st, pdl, 3);
 }

@@ -91,6 +91,7 @@ struct DecodeParams {
   float limit;     // the SwiGLU clamp (0: none)
   int sh_lo, sh_hi;  // the shared expert's intermediate channels this GPU computes (multiples of 512; the whole: 0, I)
   FrontNorm norm;
+  int b16;  // 1: the routed experts are DSGX_FMT_BF16 (the INT4 kernels stream them as they stream the bf16 shared expert)
   int mx;  // 1: the routed experts are DSGX_FMT_MXFP4 (the shared expert, the activations and the sums as FP8's)
 };
 cudaError_t launch_layer_fp8(const DecodeParams& p, const RouteParams& rp, const __nv_bfloat16* x, const float* wr,

@@ -1,8 +1,8 @@
 // Prefill / verify path of the FP8 (W8A8-g128) layer: the experts as grouped GEMMs over token-sorted ragged segments
 // on the 5th-generation tensor cores.
 //
-//   k_quant_rows   x bf16 [T][H] -> e4m3 [T][H] + f32 scales [T][H/128] (once per token)
-//   k_gather_rows  the quantised rows, scales and routing weights into the (expert id, token) order of the sort
+//   k_quant_scatter  x bf16 [T][H] -> e4m3 [T][H] + f32 scales [T][H/128] (once per token), written to the token's row
+//                    and to its picks' rows in the (expert id, token) order of the sort, with the routing weights
 //   k_tile_offsets prefix of the 128-row tiles per expert segment
 //   k_gemm_fp8     C = A B^T per 256-row tile on a pair of CTAs (a cluster of two, tcgen05 cta_group::2): each CTA stages its
 //                  128 rows of A and half of B by TMA (128-byte swizzle) through a 6-stage ring, so every byte of B
@@ -133,38 +133,36 @@ __global__ void __launch_bounds__(256) k_retile_fp8(const uint8_t* __restrict__ 
   *reinterpret_cast<uint4*>(out + (size_t)(8 * n8 + g) * K + 128 * j + 64 * q + 16 * t) = v;
 }
 
-__global__ void __launch_bounds__(256) k_quant_rows(const __nv_bfloat16* __restrict__ x, int T, int K, uint8_t* __restrict__ q,
-                                                    float* __restrict__ s) {
+// One warp a (token, 128-k block): the block quantised once (e4m3 + its f32 scale) and written to the token's row (the
+// shared expert's operand) and to the row of each of the token's picks in the (expert id, token) order of the sort
+// (pos_of), together with the picks' scales and routing weights: the routed GEMM's operand without a second pass over
+// the quantised rows.
+__global__ void __launch_bounds__(256) k_quant_scatter(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                       const int* __restrict__ pos_of, int T, int K, int topk,
+                                                       uint8_t* __restrict__ q, float* __restrict__ s,
+                                                       uint8_t* __restrict__ qs, float* __restrict__ ss, float* __restrict__ ws) {
   const int lane = threadIdx.x & 31;
   const size_t gw = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int KB = K / 128;
   if (gw >= (size_t)T * KB) return;
   const size_t r = gw / KB;
   const int j = (int)(gw % KB);
+  const int mypos = lane < topk ? __ldg(pos_of + r * topk + lane) : -1;  // (-1: a pick the sort refused)
   const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + r * K + 128 * j + 4 * lane));
   const float v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
   const float v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
   const float sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
-  *reinterpret_cast<uint32_t*>(q + r * K + 128 * j + 4 * lane) =
-      quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  const uint32_t word = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
+  *reinterpret_cast<uint32_t*>(q + r * K + 128 * j + 4 * lane) = word;
   if (lane == 0) s[r * KB + j] = sc;
-}
-
-// sorted position -> its token's quantised row, scales and routing weight
-__global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__ q, const float* __restrict__ s,
-                                                     const float* __restrict__ w, const int* __restrict__ perm_tok,
-                                                     const int* __restrict__ perm_slot, int P, int K, int topk,
-                                                     uint8_t* __restrict__ qs, float* __restrict__ ss, float* __restrict__ ws) {
-  const int per = K / 16;  // 16-byte pieces a row
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)P * per) return;
-  const size_t pos = i / per;
-  const int c = (int)(i % per);
-  const int t = perm_tok[pos];
-  reinterpret_cast<uint4*>(qs)[i] = __ldg(reinterpret_cast<const uint4*>(q + (size_t)t * K) + c);
-  const int KB = K / 128;
-  if (c < KB) ss[pos * KB + c] = s[(size_t)t * KB + c];
-  if (c == 0) ws[pos] = w[(size_t)t * topk + perm_slot[pos]];
+  for (int jj = 0; jj < topk; ++jj) {
+    const int pos = __shfl_sync(0xffffffffu, mypos, jj);
+    if (pos >= 0) *reinterpret_cast<uint32_t*>(qs + (size_t)pos * K + 128 * j + 4 * lane) = word;
+  }
+  if (lane < topk && mypos >= 0) {
+    ss[(size_t)mypos * KB + j] = sc;
+    if (j == 0) ws[mypos] = __ldg(w + r * topk + lane);
+  }
 }
 
 // The 256-row tiles (128 rows for each CTA of a pair) of the ragged segments: tile_off [E + 1] the prefix of the tiles per
@@ -781,10 +779,8 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   k_tile_offsets<<<1, 512, 0, st>>>(w.counts, w.offsets, E, q.e_lo, q.e_hi, w.tile_off, w.tile_info);
   {
     const size_t warps = (size_t)T * (H / 128);
-    k_quant_rows<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(q.x, T, H, w.xq, w.xs);
-    const size_t pieces = (size_t)P * (H / 16);
-    k_gather_rows<<<(unsigned)((pieces + 255) / 256), 256, 0, st>>>(w.xq, w.xs, q.w, w.perm_tok, w.perm_slot, P, H, topk,
-                                                                    w.xq_s, w.xs_s, w.w_s);
+    k_quant_scatter<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(q.x, q.w, w.pos_of, T, H, topk, w.xq, w.xs, w.xq_s,
+                                                                          w.xs_s, w.w_s);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;

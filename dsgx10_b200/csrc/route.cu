@@ -204,6 +204,8 @@ __global__ void __launch_bounds__(kSortTok) k_sort_scatter(const int* __restrict
       for (int w = 0; w < (lt >> 5); ++w) rank += __popc(m[w]);
       const int pos = base[(size_t)blockIdx.x * E + ex[j]] + rank;
       perm_tok[pos] = t, perm_slot[pos] = j, pos_of[(size_t)t * topk + j] = pos;
+    } else if (j < topk) {
+      pos_of[(size_t)t * topk + j] = -1;  // (an id outside [0, E): the pick has no place in the order)
     }
   // the row's picks in ascending expert id (insertion sort of at most 8)
   int o[8];

@@ -396,6 +396,45 @@ class Int4Layer:
         return 3 * self.I * self.H * 2
 
 
+class Bf16Layer(Int4Layer):
+    """One BF16 layer (altar-1 keeps a few layers' routed experts in BF16; altar1 engine/experts/experts.h:28-39, format tag
+    3): `E` routed experts and the shared expert in blocks of 8 rows x 128 k of bf16 (tile_bf16)."""
+
+    def __init__(self, H, I, E, seed, device="cpu", shared=True, e_range=None, std=0.02):
+        self.H, self.I, self.E, self.fmt = H, I, E, _lib.FMT_BF16
+        self.device = torch.device(device)
+        shapes = ((I, H), (I, H), (H, I))
+        mat_b = I * H * 2
+        lo, hi = e_range if e_range is not None else (0, E)
+        self.bits = {}
+        pool = np.empty(max(hi - lo, 1) * 3 * mat_b, np.uint8)
+        self.desc_host = (_lib.MatDesc * (E * 3))()
+        for n, e in enumerate(range(lo, hi)):
+            self.bits[e] = []
+            for m, (N, K) in enumerate(shapes):
+                w = bf16_bits((torch.randn(N, K, generator=_gen("cpu", seed * 1000 + e * 3 + m)) * std).to(torch.bfloat16))
+                self.bits[e].append(w)
+                off = (n * 3 + m) * mat_b
+                pool[off:off + mat_b] = tile_bf16(w)
+                d = self.desc_host[e * 3 + m]
+                d.off, d.s2, d.fmt = off, 1.0, _lib.FMT_BF16
+        self.pool = torch.from_numpy(pool).to(self.device)
+        self.desc = torch.frombuffer(bytearray(bytes(self.desc_host)), dtype=torch.uint8).to(self.device)
+        self.shared = shared
+        if shared:
+            self.sh_bits = [bf16_bits((torch.randn(n, k, generator=_gen("cpu", seed + 9 + i)) * std).to(torch.bfloat16))
+                            for i, (n, k) in enumerate(shapes)]
+            self.sh_dev = [torch.from_numpy(tile_bf16(b)).to(self.device) for b in self.sh_bits]
+
+    def layer_w(self):
+        L = super().layer_w()
+        L.fmt = _lib.FMT_BF16
+        return L
+
+    def expert_bytes(self):
+        return 3 * self.I * self.H * 2
+
+
 # ------------------------------------------------------------------------------------------- Zipf-skewed routing bias
 
 def zipf_target_shares(E, topk, s=1.1):

@@ -37,8 +37,10 @@ typedef enum dsgx_status {
   DSGX_ERR_LIMIT = 7        /* the request is beyond a fixed built-in size (dsgx_sort_pack_static) */
 } dsgx_status;
 
-/* Expert formats.  Tags 2 and 3 are the reference's (altar1 engine/experts/experts.h:39); tag 4 is this library's
- * routed FP8 format: the reference's "tile_fp8" lane order (experts.h:66-70, layout.h:108-119) for the e4m3 values and
+/* Expert formats.  Tags 2 and 3 are the reference's (altar1 engine/experts/experts.h:39): INT4-g32 blocks of 8 rows x 512 k
+ * (2368 B) and BF16 blocks of 8 rows x 128 k (2048 B), both consumed as the reference lays them out (layout.h:50-107); a
+ * BF16 layer's routed experts (decode only) run under the INT4 layers' contract with W given directly.  Tag 4 is this
+ * library's routed FP8 format: the reference's "tile_fp8" lane order (experts.h:66-70, layout.h:108-119) for the e4m3 values and
  * f32 scales [N/128][K/128] row-major. */
 enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF16 = 3, DSGX_FMT_FP8 = 4, DSGX_FMT_MXFP4 = 5 };
 /* Tag 5, DSGX_FMT_MXFP4: ds41f's routed expert format (ref/inference/model.py expert_dtype "fp4" over
@@ -106,7 +108,7 @@ typedef struct dsgx_moe_shape {
   int32_t score_fn;     /* DSGX_SCORE_* */
   int32_t norm_topk;    /* 1: weights = s / (sum + 1e-20) * route_scale; 0: s * route_scale */
   float route_scale;
-  uint32_t fmt;         /* DSGX_FMT_FP8, DSGX_FMT_INT4 or DSGX_FMT_MXFP4 */
+  uint32_t fmt;         /* DSGX_FMT_FP8, DSGX_FMT_INT4, DSGX_FMT_BF16 or DSGX_FMT_MXFP4 */
   int32_t e_lo, e_hi;   /* this GPU's experts [e_lo, e_hi) (expert parallelism: ds41f ref/inference/model.py:863-870) */
   int32_t sh_lo, sh_hi; /* FP8 decode: the shared expert's intermediate channels [sh_lo, sh_hi) this GPU computes
                            (multiples of 512; both 0: all of them).  The ranks of an expert-parallel step split the shared
@@ -137,7 +139,8 @@ int dsgx_route(const dsgx_moe_shape* shape, const float* logits, const float* bi
  * The stable (expert id, token) order of the T * topk picks: stands in for the bucket kernels of the prefill path
  * (altar1 engine/experts/prefill.cu:94-150; ds41f engine/kernels/prefill.cu:673-781), but deterministic.
  * counts [E], offsets [E+1], perm_tok [T*topk], perm_slot [T*topk], pos_of [T][topk], row_order [T][topk];
- * ws: dsgx_sort_ws_bytes(T, topk, E) bytes of scratch. */
+ * ws: dsgx_sort_ws_bytes(T, topk, E) bytes of scratch.  A pick whose id is outside [0, E) is left out of the order (its
+ * pos_of is -1) and recorded in the status word of ws. */
 size_t dsgx_sort_ws_bytes(int T, int topk, int E);
 int dsgx_sort_pack(const int32_t* idx, int T, int topk, int E, int32_t* counts, int32_t* offsets, int32_t* perm_tok,
                    int32_t* perm_slot, int32_t* pos_of, int32_t* row_order, void* ws, void* stream);

@@ -139,3 +139,38 @@ def test_rows_9_to_16(orc):
     b = small.run(layer.layer_w(), x[8:]).clone()
     torch.cuda.synchronize()
     assert moe.ws_status(big.ws) == 0 and torch.equal(out, torch.cat([a, b]))
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+def test_bf16_routed_experts(orc, M):
+    """A BF16 layer (format tag 3: altar-1's unquantised layers): the routed experts stream through the same kernels as the
+    bf16 shared expert; parity against the oracle on the bf16 weights, same bits run after run and for a row alone."""
+    from dsgx10_b200 import _lib, moe, synth
+    from tests.util import assert_rows_close, oracle_route
+    H, I, E, topk = 1024, 512, 8, 2
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_BF16, score_fn=1)
+    layer = synth.Bf16Layer(H, I, E, 970, device="cuda")
+    wr = synth.router_weights(E, H, 971).cuda()
+    x = synth.activations(M, H, 972 + M).cuda()
+    step = moe.LayerStep(shp, wr)
+    out = step.run(layer.layer_w(), x).clone()
+    torch.cuda.synchronize()
+    assert moe.ws_status(step.ws) == 0
+    xb = synth.bf16_bits(x)
+    _, oi, ow = oracle_route(orc, xb, wr.cpu().numpy(), None, shp)
+    assert (step.idx[:M].cpu().numpy() == oi).all()
+    experts = {int(e): tuple(layer.bits[int(e)]) for e in np.unique(oi)}
+    acc, out_o = orc.moe_bf16w_layer(xb, oi, ow, experts, tuple(layer.sh_bits))
+    assert_rows_close(step.yr[:M].cpu().numpy() + step.ys[:M].cpu().numpy(), acc, TOL, what="yr + ys")
+    out2 = step.run(layer.layer_w(), x).clone()
+    one = moe.LayerStep(shp, wr).run(layer.layer_w(), x[:1]).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2) and torch.equal(one[0], out[0])
+    # an INT4 layer's descriptors under the BF16 tag are refused on the device
+    i4 = synth.Int4Layer(H, I, E, 973, device="cuda")
+    L = i4.layer_w()
+    L.fmt = _lib.FMT_BF16
+    st2 = moe.LayerStep(shp, wr)
+    st2.run(L, x)
+    torch.cuda.synchronize()
+    assert moe.ws_status(st2.ws) == _lib.ERR_FORMAT
