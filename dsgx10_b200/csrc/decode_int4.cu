@@ -136,13 +136,13 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
   uint8_t* myring = ring + warp * kNST * kUpStage;
   uint64_t* mybar = bars + warp * kNST;
 
-  pdl_launch_dependents();
   if (lane == 0)
     for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
   if (threadIdx.x == 0) mbar_init(cbar, 1);
   mbar_fence_init();
   __syncthreads();
   pdl_wait();
+  pdl_launch_dependents();  // (after the wait: the down kernel reads the slot table before its own wait)
   if (threadIdx.x == 0) {
     mbar_expect_tx(cbar, (uint32_t)(sizeof(SlotTab) + xt_bytes));
     bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), cbar);
@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
   if (threadIdx.x == 0) mbar_init(cbar, 1);
   mbar_fence_init();
   __syncthreads();
-  pdl_wait();
+  // the slot table is older than the gate/up kernel: it is read, and the first stages' down weights are requested, before
+  // the wait for that kernel; only h, its output, is requested after the wait (as in the FP8 down kernel)
   if (threadIdx.x == 0) {
     mbar_expect_tx(cbar, (uint32_t)sizeof(SlotTab));
     bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), cbar);
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
 
   const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;  // consecutive units on different SMs
   if (!dead && tab.ntot == 0) {
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < (size_t)p.M * p.H; i += (size_t)gridDim.x * kThreads) {
       p.yr[i] = 0.f;
       if (p.out) p.out[i] = __float2bfloat16_rn(0.f);
@@ -280,6 +282,9 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
   int pu = gw, pc = 0;
   uint32_t issued = 0, consumed = 0;
   const uint64_t pol = policy_evict_first();
+  bool early = true;  // before the wait: the h groups of the stages issued now are requested after it
+  const uint8_t* late_src[kNST];
+  uint32_t late_bytes[kNST];
   auto issue = [&]() {
     const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
     const bool b16 = slot >= tab.nslots || p.b16;
@@ -292,12 +297,18 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
     mbar_expect_tx(bar, 2 * blk + hb);
     bulk_g2s_hint(st, tab.ent[slot].d + off, blk, bar, pol);
     bulk_g2s_hint(st + kI4Blk, tab.ent[slot].d + off + (size_t)cpu * blk, blk, bar, pol);
-    bulk_g2s(st + kStageW, reinterpret_cast<const uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + (size_t)pc * (b16 ? 8 : 32)) * R * 32, hb, bar);
+    const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.ws.h) + ((size_t)slot * (p.I / 16) + (size_t)pc * (b16 ? 8 : 32)) * R * 32;
+    if (early) late_src[issued % kNST] = hsrc, late_bytes[issued % kNST] = hb;
+    else bulk_g2s(st + kStageW, hsrc, hb, bar);
     ++issued;
     if (++pc == cpu) pc = 0, pu += GW;
   };
   if (lane == 0)
     for (int s = 0; s < kNST && pu < total; ++s) issue();
+  pdl_wait();
+  if (lane == 0)
+    for (uint32_t n = 0; n < issued; ++n) bulk_g2s(myring + (size_t)n * stage + kStageW, late_src[n], late_bytes[n], mybar + n);
+  early = false;
 
   const int g = lane >> 2, t = lane & 3;
   int pend = 0, pend_n16 = 0, pend_ticket = 0;
