@@ -390,6 +390,26 @@ def run_gpu(args, rows=None, steps=None, with_kernel=True, with_cpu=True):
         parity = {"ok": ok, "max_err_of_row_max": err, "elements_beyond_2e-3": beyond, "rows": rows,
                   "against": "the CPU oracle on the picked experts (every rank its own, partial sums added)"}
 
+    if int4 and not args.no_parity and world == 1:
+        # INT4: the timed layers are generated straight in the block layout on the device and keep no canonical tensors, so
+        # the check runs one step over a layer packed from canonical tensors (the experts these rows pick, the same router)
+        from oracle import oracle as orc
+        sb = steps_buf[0]
+        rc = min(rows, 2)  # (rows checked: packing an expert's canonical tensors on the host takes a second each)
+        picked = sorted(set(int(e) for e in moe.route(shp, moe.router_logits(xs[0][:rc], sb.wr), None)[0].flatten().tolist()))
+        chk = synth.Int4Layer(H, I, E, SEED + 99, device=dev, experts=picked)
+        st = moe.LayerStep(shp, sb.wr, None, device=dev)
+        got = st.run(chk.layer_w(), xs[0][:rc])
+        torch.cuda.synchronize()
+        idx_np, w_np = st.idx[:rc].cpu().numpy(), st.w[:rc].cpu().numpy()
+        deq = {e: tuple(orc.int4_dequant(wp, s_, None) for wp, s_ in chk.raw[e]) for e in picked}
+        acc, _ = orc.moe_bf16w_layer(synth.bf16_bits(xs[0][:rc]), idx_np, w_np, deq, tuple(chk.sh_bits))
+        ok, err, beyond = parity_rule(got.float().cpu().numpy(), acc, np.zeros_like(acc))
+        ok = ok and sorted(set(idx_np.ravel().tolist())) == picked and moe.ws_status(st.ws) == 0
+        parity = {"ok": ok, "max_err_of_row_max": err, "elements_beyond_2e-3": beyond, "rows": rc,
+                  "against": "the CPU oracle (dequantised INT4 experts, bf16 shared expert) on a layer packed from canonical "
+                             "tensors: the picked experts, the same router and rows"}
+
     if rank != 0:
         return None
     peaks, peak_kind = measured_peaks()
