@@ -410,7 +410,7 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* s, const dsgx_layer_w* L, c
 static int check_prefill_shape(const dsgx_moe_shape* s) {
   const int rc = check_shape(s);
   if (rc) return rc;
-  if (s->fmt != DSGX_FMT_FP8) return DSGX_ERR_UNSUPPORTED;
+  if (!fmt_fp8_family(s->fmt)) return DSGX_ERR_UNSUPPORTED;  // (MXFP4 layers: through an FP8 copy of the same weights)
   if (s->sh_lo || (s->sh_hi && s->sh_hi != s->I)) return DSGX_ERR_UNSUPPORTED;  // (the prefill pass runs whole experts)
   if (s->H % 256 || s->I % 128) return DSGX_ERR_SHAPE;
   return DSGX_OK;
@@ -434,25 +434,45 @@ int dsgx_prefill_prepare(const dsgx_moe_shape* s, const dsgx_layer_w* L, void* w
   if (nloc > 0) e = cudaMemcpy(hd, L->desc + (size_t)s->e_lo * 3, sizeof(dsgx_mat_desc) * nloc * 3, cudaMemcpyDeviceToHost);
   int bad = 0;
   const size_t mat = (size_t)I * H, sc = (size_t)(I / 128) * (H / 128);
+  // MXFP4 layers: the copy holds the same weights as e4m3 with a power-of-two scale per 128 x 128 block (exact while a
+  // block's scale bytes spread over at most 14; the flag word, first bytes of the copy's scale area until then, says
+  // otherwise); twice the MXFP4 bytes
+  const bool mx = s->fmt == DSGX_FMT_MXFP4;
+  int* flag = nullptr;
+  if (mx && e == cudaSuccess) {
+    e = cudaMalloc(&flag, 4);  // (load time)
+    if (e == cudaSuccess) e = cudaMemsetAsync(flag, 0, 4, st);
+  }
   for (int i = 0; e == cudaSuccess && i < nloc; ++i) {
     const int ex = s->e_lo + i;
     for (int m = 0; m < 3; ++m) {
       const dsgx_mat_desc& d = hd[i * 3 + m];
-      if (d.fmt != DSGX_FMT_FP8 || (d.off & 255)) {
+      if (d.fmt != s->fmt || (d.off & 255)) {
         bad = 1;
         break;
       }
       const uint8_t* src = L->pool + d.off;
-      const float* ssrc = reinterpret_cast<const float*>(L->pool + ((uint64_t)d.rsv[0] | (uint64_t)d.rsv[1] << 32));
       uint8_t* dst = (m == 0 ? pw.g : m == 1 ? pw.u : pw.d) + (size_t)ex * mat;
       float* sdst = (m == 0 ? pw.sg : m == 1 ? pw.su : pw.sd) + (size_t)ex * sc;
-      e = retile_matrix(src, ssrc, m == 2 ? H : I, m == 2 ? I : H, dst, sdst, st);
+      if (mx) {
+        e = convert_mx4_matrix(src, m == 2 ? H : I, m == 2 ? I : H, dst, sdst, flag, st);
+      } else {
+        const float* ssrc = reinterpret_cast<const float*>(L->pool + ((uint64_t)d.rsv[0] | (uint64_t)d.rsv[1] << 32));
+        e = retile_matrix(src, ssrc, m == 2 ? H : I, m == 2 ? I : H, dst, sdst, st);
+      }
       if (e != cudaSuccess) break;
     }
     if (bad) break;
   }
   delete[] hd;
+  int wide = 0;
+  if (flag) {
+    if (e == cudaSuccess && !bad) e = cudaMemcpyAsync(&wide, flag, 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(flag);
+  }
   if (bad) return DSGX_ERR_FORMAT;
+  if (wide) return DSGX_ERR_UNSUPPORTED;
   if (e == cudaSuccess && L->sh.g) {
     if (!L->sh.u || !L->sh.d || !L->sh.gs || !L->sh.us || !L->sh.ds) return DSGX_ERR_ARG;
     e = retile_matrix(L->sh.g, L->sh.gs, I, H, pw.g + (size_t)E * mat, pw.sg + (size_t)E * sc, st);

@@ -155,6 +155,9 @@ struct PrefillWeights {  // K-major row-major copies of the layer's matrices, [E
 size_t prefill_weights_bytes(int H, int I, int E);
 PrefillWeights prefill_weights_carve(void* buf, int H, int I, int E);
 cudaError_t retile_matrix(const uint8_t* tiled, const float* scales, int N, int K, uint8_t* out, float* sout, cudaStream_t st);
+// an MXFP4 matrix as the grouped GEMM's FP8 operand, W unchanged; *flag (device) is set when a 128 x 128 block's scales
+// spread over more than 14 octaves (not representable)
+cudaError_t convert_mx4_matrix(const uint8_t* blocks, int N, int K, uint8_t* out, float* sout, int* flag, cudaStream_t st);
 
 struct PrefillWs {
   int* status;

@@ -711,6 +711,56 @@ cudaError_t retile_matrix(const uint8_t* tiled, const float* scales, int N, int 
   return cudaMemcpyAsync(sout, scales, (size_t)(N / 128) * (K / 128) * 4, cudaMemcpyDeviceToDevice, st);
 }
 
+// An MXFP4 matrix (576-byte blocks of 8 rows x 128 k: kernels.h, dsgx_moe.h) as the FP8 operand the grouped GEMM reads:
+// K-major e4m3 values and one f32 scale per 128 x 128 block, W unchanged.  Every e2m1 value times a power of two is an
+// e4m3 value as long as the exponent stays in range: with S = 2^(emax - 6) for the block's largest scale exponent emax, a
+// group with exponent e holds v 2^(e - emax + 6), exact for emax - e <= 14 (6 x 2^6 = 384 <= 448; 0.5 x 2^-8 = 2^-9 and
+// 1.5 x 2^-8 = 3 x 2^-9 are e4m3 subnormals).  A block whose scales spread wider is reported in *flag and its small groups
+// are flushed; the caller refuses the layer.  One CTA a 128 x 128 block.
+__global__ void __launch_bounds__(256) k_mx4_to_fp8(const uint8_t* __restrict__ blocks, int N, int K, uint8_t* __restrict__ out,
+                                                    float* __restrict__ sout, int* __restrict__ flag) {
+  __shared__ int s_max, s_min;
+  const int KB = K / 128, nb = blockIdx.x / KB, kb = blockIdx.x % KB;
+  if (threadIdx.x == 0) s_max = 0, s_min = 255;
+  __syncthreads();
+  auto scale_exp = [&](int strip, int g, int G) {  // the group's ue8m0 byte back from its bf16 form
+    const uint8_t* b = blocks + ((size_t)(nb * 16 + strip) * KB + kb) * kMxBlk;
+    const uint32_t h = *reinterpret_cast<const uint16_t*>(b + 512 + 8 * g + 2 * G);
+    return h == 0x40u ? 0 : (int)(h >> 7);
+  };
+  for (int i = threadIdx.x; i < 512; i += 256) {  // 16 strips x 8 rows x 4 groups
+    const int e = scale_exp(i >> 5, (i >> 2) & 7, i & 3);
+    atomicMax(&s_max, e), atomicMin(&s_min, e);
+  }
+  __syncthreads();
+  const int emax = s_max;
+  if (threadIdx.x == 0) {
+    sout[(size_t)nb * KB + kb] = ldexpf(1.f, emax - 127 - 6);
+    if (emax - s_min > 14) atomicExch(flag, 1);
+  }
+  const float mags[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  for (int i = threadIdx.x; i < 2048; i += 256) {  // 16 strips x 32 lanes x 4 groups: one word of 8 values each
+    const int strip = i >> 7, lane = (i >> 2) & 31, G = i & 3, g = lane >> 2, t = lane & 3;
+    const uint8_t* b = blocks + ((size_t)(nb * 16 + strip) * KB + kb) * kMxBlk;
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(b + 16 * lane + 4 * G);
+    const float f = ldexpf(1.f, scale_exp(strip, g, G) - emax + 6);
+    uint32_t q[2] = {0, 0};
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const bool neg = (w >> (v < 4 ? 8 * v + 7 : 8 * (v - 4) + 3)) & 1;
+      const float val = mags[(w >> (4 * v)) & 7] * f;
+      const uint32_t byte = (uint32_t)__nv_cvt_float_to_fp8(neg ? -val : val, __NV_SATFINITE, __NV_E4M3);
+      q[v >> 2] |= byte << (8 * (v & 3));
+    }
+    *reinterpret_cast<uint2*>(out + (size_t)(nb * 128 + strip * 8 + g) * K + kb * 128 + 32 * G + 8 * t) = make_uint2(q[0], q[1]);
+  }
+}
+
+cudaError_t convert_mx4_matrix(const uint8_t* blocks, int N, int K, uint8_t* out, float* sout, int* flag, cudaStream_t st) {
+  k_mx4_to_fp8<<<(unsigned)((N / 128) * (K / 128)), 256, 0, st>>>(blocks, N, K, out, sout, flag);
+  return cudaGetLastError();
+}
+
 // ---- workspace ---------------------------------------------------------------------------------------------------------
 size_t prefill_ws_bytes(int T, int H, int I, int E, int topk) {
   const size_t P = (size_t)T * topk, HB = H / 128, IB = I / 128;

@@ -46,8 +46,11 @@ enum { DSGX_FMT_NVFP4 = 0, DSGX_FMT_RETIRED = 1, DSGX_FMT_INT4 = 2, DSGX_FMT_BF1
 /* Tag 5, DSGX_FMT_MXFP4: ds41f's routed expert format (ref/inference/model.py expert_dtype "fp4" over
  * ref/torchref/kernel.py:111-138: e2m1 values with one ue8m0 scale per 32 along K; engine/kernels/dsk.h:176-210), "W4A8":
  * the activations are quantised as for DSGX_FMT_FP8 (e4m3 per 128 with an f32 scale), W = e2m1 * 2^(scale - 127), the
- * rest of the contract is DSGX_FMT_FP8's; the layer's shared expert is FP8 (dsgx_shared_w.g/u/d), as ds41f's.  Decode
- * only.  Layout of a matrix [N][K] (N a multiple of 8, K of 128), made by dsgx10_b200/weights.py pack_mx4:
+ * rest of the contract is DSGX_FMT_FP8's; the layer's shared expert is FP8 (dsgx_shared_w.g/u/d), as ds41f's.  The
+ * decode kernels stream the format as it is; the prefill pass reads a copy dsgx_prefill_prepare makes: the same weights as
+ * e4m3 values with a power-of-two scale per 128 x 128 block (every e2m1 value times a power of two is an e4m3 value while
+ * a block's scale bytes differ by at most 14; a layer with a wider block is refused with DSGX_ERR_UNSUPPORTED), twice the
+ * MXFP4 bytes.  Layout of a matrix [N][K] (N a multiple of 8, K of 128), made by dsgx10_b200/weights.py pack_mx4:
  *   [N/8 strips][K/128 blocks] of 576 bytes: [32 lanes (g = lane / 4, t = lane % 4)][4 groups G][one 32-bit word] = the
  *   8 values v0..v7 of row 8 strip + g at k = 128 block + 32 G + 8 t + 0..7: v_j's magnitude code (its e2m1 nibble
  *   without the sign) in bits 4 j .. 4 j + 2, the sign of v_i in bit 8 i + 7 for i < 4 and in bit 8 (i - 4) + 3 for

@@ -126,3 +126,60 @@ def test_refusals():
     moe.moe_decode(shp, L, x, idx, w, ws)
     torch.cuda.synchronize()
     assert moe.ws_status(ws) == _lib.ERR_FORMAT
+
+
+@pytest.mark.parametrize("T", [7, 300])
+def test_prefill_through_the_fp8_copy(orc, T):
+    """An MXFP4 layer's prefill pass: dsgx_prefill_prepare turns the routed experts into the grouped GEMM's FP8 operand with
+    the weights unchanged (e4m3 values and a power-of-two scale per 128 x 128 block); parity as for an FP8 layer, and the
+    one-token rows agree with the decode path within the rule."""
+    from dsgx10_b200 import _lib, moe, synth
+    from tests.util import assert_rows_close, oracle_fp8_layer
+    H, I, E, topk = 512, 256, 8, 2
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_MXFP4)
+    layer = synth.Mx4Layer(H, I, E, 400 + T, device="cuda")
+    x = synth.activations(T, H, 401).cuda()
+    wr = synth.router_weights(E, H, 402).cuda()
+    idx, w = moe.route(shp, moe.router_logits(x, wr), None)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    xb = synth.bf16_bits(x)
+    oi, ow = idx.cpu().numpy(), w.cpu().numpy()
+    acc_r, _, pm_r = oracle_fp8_layer(orc, layer, xb, oi, ow, with_shared=False, pickmax=True)
+    acc_all, out_all, pm_all = oracle_fp8_layer(orc, layer, xb, oi, ow, with_shared=True, pickmax=True)
+    assert_rows_close(yr.cpu().numpy(), acc_r, TOL, what="yr", pickmax=pm_r)
+    assert_rows_close(orc.bf16_to_f32(synth.bf16_bits(out)), orc.bf16_to_f32(out_all), TOL, what="out", pickmax=pm_all, rounded=True)
+    # the decode path on the first rows: the same contract
+    M = min(T, 8)
+    yd, ysd = moe.moe_decode(shp, layer.layer_w(), x[:M].contiguous(), idx[:M].contiguous(), w[:M].contiguous(), moe.decode_ws(shp))
+    torch.cuda.synchronize()
+    assert_rows_close(yd.cpu().numpy(), yr[:M].cpu().numpy(), TOL, what="decode vs prefill", pickmax=pm_r[:M])
+
+
+def test_prefill_refuses_scales_that_spread_too_widely():
+    """A 128 x 128 block whose scale bytes differ by more than 14 has no exact FP8 form: the prepare call says so."""
+    from dsgx10_b200 import _lib, moe, synth
+    H, I, E, topk = 512, 256, 4, 2
+    layer = synth.Mx4Layer(H, I, E, 410, device="cpu")
+    off, _ = layer._off[(1, 0)]
+    nb = synth.mx4_mat_bytes(I, H)
+    q, sc = synth.untile_mx4(layer.pool[off:off + nb], I, H)
+    sc[3, 2] = int(sc[3, 3]) - 20            # one group 20 octaves below its neighbours
+    layer.pool[off:off + nb] = synth.tile_mx4(q, sc)
+    layer.to("cuda")
+    shp = moe.shape(H, I, E, topk, fmt=_lib.FMT_MXFP4)
+    with pytest.raises(_lib.DsgxError) as e:
+        moe.PrefillLayer(shp, layer.layer_w(), 16)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    # a spread of 14 is still exact
+    ok = synth.Mx4Layer(H, I, E, 411, device="cpu")
+    off, _ = ok._off[(0, 2)]
+    nb = synth.mx4_mat_bytes(H, I)
+    q, sc = synth.untile_mx4(ok.pool[off:off + nb], H, I)
+    blk = sc[:128, :4]
+    sc[5, 1] = int(blk.max()) - 14
+    ok.pool[off:off + nb] = synth.tile_mx4(q, sc)
+    ok.to("cuda")
+    moe.PrefillLayer(shp, ok.layer_w(), 16)
