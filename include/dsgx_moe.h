@@ -322,8 +322,8 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* 
  * load-time call.  Only the experts in [e_lo, e_hi) (and the shared expert, when the layer has one) are prepared and run.
  * ws: dsgx_prefill_ws_bytes(shape, T) bytes, T <= the value given there; no zeroing needed.
  * ysum: as dsgx_decode_cfg.ysum.
- * dsgx_prefill_prepare allocates host memory, reads the descriptors back and synchronises: a load-time call.  The other
- * calls of this header allocate nothing and do not synchronise (dsgx_ws_status and dsgx_sort_static_status copy one word
+ * dsgx_prefill_prepare allocates host memory (and, for MXFP4 layers, one device word), reads the descriptors back and
+ * synchronises: a load-time call.  The other calls of this header allocate nothing and do not synchronise (dsgx_ws_status and dsgx_sort_static_status copy one word
  * back and so wait for the stream's work). */
 size_t dsgx_prefill_weights_bytes(const dsgx_moe_shape* shape);
 int dsgx_prefill_prepare(const dsgx_moe_shape* shape, const dsgx_layer_w* L, void* wbuf, void* stream);
