@@ -120,6 +120,31 @@ DSGX_DEV void b16_block_mma(float (&acc)[4], const uint8_t* a, const uint8_t* b,
   }
 }
 
+// Pieces of a shared-expert unit (its K cut in kShSplit): a piece parks its four sums in the workspace and takes a ticket;
+// the piece that arrives last adds the parked sums in piece order (the same bits whichever piece that is) and goes on
+// with the unit's epilogue (returns true); the others are done (false).
+constexpr int kShSplit = 4;
+DSGX_DEV bool piece_join(float (&acc)[4], float* part, int* cnt, int unit, int piece, int S, int lane) {
+  float* pp = part + (size_t)unit * kMaxPieces * 128 + lane * 4;
+  *reinterpret_cast<float4*>(pp + piece * 128) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  __threadfence();
+  __syncwarp();
+  int ticket = 0;
+  if (lane == 0) ticket = atomicAdd(cnt + unit, 1);
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  if (ticket != S - 1) return false;
+  __threadfence();
+  float4 v[kShSplit];
+#pragma unroll
+  for (int j = 0; j < kShSplit; ++j) v[j] = j < S ? __ldcg(reinterpret_cast<const float4*>(pp + j * 128)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  acc[0] = v[0].x, acc[1] = v[0].y, acc[2] = v[0].z, acc[3] = v[0].w;
+#pragma unroll
+  for (int j = 1; j < kShSplit; ++j)
+    if (j < S) acc[0] = __fadd_rn(acc[0], v[j].x), acc[1] = __fadd_rn(acc[1], v[j].y), acc[2] = __fadd_rn(acc[2], v[j].z), acc[3] = __fadd_rn(acc[3], v[j].w);
+  if (lane == 0) cnt[unit] = 0;
+  return true;
+}
+
 // -------------------------------------------------------------------------------------------------------------- k_up
 template <class V>
 __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) {
@@ -151,14 +176,35 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
   bool dead = !mbar_wait(cbar, 0);
 
   const int upp = p.I / 8;
-  const int total = dead ? 0 : tab.ntot * upp;
-  const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;  // consecutive units on different SMs
+  const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;  // consecutive items on different SMs
   const int cpu4 = p.H / 512, cpub = p.H / 128;  // chunks a unit: INT4 blocks, BF16 blocks
-  int pu = gw, pc = 0;
+  // Items.  A unit of the bf16 shared expert is 3.5 times the bytes of an INT4 unit, and a warp streams at the rate its
+  // two ring stages allow: left whole, the 256 warps that hold a shared unit would set the kernel's time.  So the shared
+  // expert's units are cut into kShSplit pieces of their K (items 0 .. nshu S - 1, piece-major inside a unit), each summed
+  // by its own warp, the piece sums parked in the workspace and added in piece order by the piece that arrives last (a
+  // ticket); then the routed units, one item each.  A BF16 layer's units are all alike: no split.
+  const bool sh_any = !dead && tab.ntot > tab.nslots;
+  const int S = sh_any && !p.b16 && cpub % kShSplit == 0 ? kShSplit : 1;
+  const int nshi = sh_any ? upp * S : 0;
+  const int total = dead ? 0 : nshi + tab.nslots * upp;
+  auto decode = [&](int it, int& slot, int& i8, int& c0, int& c1, int& piece) {
+    if (it < nshi) {
+      slot = tab.nslots, i8 = it / S, piece = it % S;
+      c0 = piece * (cpub / S), c1 = c0 + cpub / S;
+    } else {
+      const int u = it - nshi;
+      slot = u / upp, i8 = u % upp, piece = 0, c0 = 0, c1 = p.b16 ? cpub : cpu4;
+    }
+  };
+  int pu = gw, pc = -1, pc1 = 0, pslot = 0, pi8 = 0;
   uint32_t issued = 0, consumed = 0;
   const uint64_t pol = policy_evict_first();
   auto issue = [&]() {
-    const int slot = ord_slot(tab, pu / upp), i8 = pu % upp;
+    if (pc < 0) {
+      int piece;
+      decode(pu, pslot, pi8, pc, pc1, piece);
+    }
+    const int slot = pslot, i8 = pi8;
     const bool sh = slot >= tab.nslots, b16 = sh || p.b16;  // (a BF16 layer's routed experts: the shared expert's block format)
     const uint32_t blk = b16 ? kB16Blk : kI4Blk;
     const int cpu = b16 ? cpub : cpu4;
@@ -175,18 +221,18 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
       bulk_g2s_hint(st + kI4Blk, tab.ent[slot].u + off, blk, bar, pol);
     }
     ++issued;
-    if (++pc == cpu) pc = 0, pu += GW;
+    if (++pc == pc1) pc = -1, pu += GW;
   };
   if (lane == 0)
     for (int s = 0; s < kNST && pu < total; ++s) issue();
 
   const int g = lane >> 2, t = lane & 3;
-  for (int unit = gw; unit < total && !dead; unit += GW) {
-    const int slot = ord_slot(tab, unit / upp), i8 = unit % upp;
+  for (int it = gw; it < total && !dead; it += GW) {
+    int slot, i8, c0, c1, piece;
+    decode(it, slot, i8, c0, c1, piece);
     const bool sh = slot >= tab.nslots, b16 = sh || p.b16;
-    const int cpu = b16 ? cpub : cpu4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = 0; c < cpu; ++c) {
+    for (int c = c0; c < c1; ++c) {
       const uint32_t sidx = consumed % kNST;
       if (!mbar_wait(mybar + sidx, (consumed / kNST) & 1)) {
         dead = true;
@@ -199,6 +245,8 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_i4(const DecodeParams p) 
       __syncwarp();
       if (lane == 0 && pu < total) issue();
     }
+    if (dead) break;
+    if (sh && S > 1 && !piece_join(acc, p.ws.part, p.ws.cnt_u, i8, piece, S, lane)) continue;  // (not the unit's last piece)
     if (dead) break;
     if (sh && tab.bgu) {
       // interleaved rows: A row 2 j is gate and 2 j + 1 up of the unit's channel j (rows 0-7: channels 0-3, rows 8-15:
@@ -277,16 +325,34 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
     }
     return;
   }
-  const int total = dead ? 0 : tab.ntot * NT;
   const int cpu4 = p.I / 512, cpub = p.I / 128;
-  int pu = gw, pc = 0;
+  // items as in the gate/up kernel: the shared expert's tiles cut into kShSplit pieces of their K first, then the routed
+  // slots' tiles
+  const bool sh_any = !dead && tab.ntot > tab.nslots;
+  const int S = sh_any && !p.b16 && cpub % kShSplit == 0 ? kShSplit : 1;
+  const int nshi = sh_any ? NT * S : 0;
+  const int total = dead ? 0 : nshi + tab.nslots * NT;
+  auto decode = [&](int it, int& slot, int& n16, int& c0, int& c1, int& piece) {
+    if (it < nshi) {
+      slot = tab.nslots, n16 = it / S, piece = it % S;
+      c0 = piece * (cpub / S), c1 = c0 + cpub / S;
+    } else {
+      const int u = it - nshi;
+      slot = u / NT, n16 = u % NT, piece = 0, c0 = 0, c1 = p.b16 ? cpub : cpu4;
+    }
+  };
+  int pu = gw, pc = -1, pc1 = 0, pslot = 0, pn16 = 0;
   uint32_t issued = 0, consumed = 0;
   const uint64_t pol = policy_evict_first();
   bool early = true;  // before the wait: the h groups of the stages issued now are requested after it
   const uint8_t* late_src[kNST];
   uint32_t late_bytes[kNST];
   auto issue = [&]() {
-    const int slot = ord_slot(tab, pu / NT), n16 = pu % NT;
+    if (pc < 0) {
+      int piece;
+      decode(pu, pslot, pn16, pc, pc1, piece);
+    }
+    const int slot = pslot, n16 = pn16;
     const bool b16 = slot >= tab.nslots || p.b16;
     const uint32_t blk = b16 ? kB16Blk : kI4Blk;
     const int cpu = b16 ? cpub : cpu4;
@@ -301,7 +367,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
     if (early) late_src[issued % kNST] = hsrc, late_bytes[issued % kNST] = hb;
     else bulk_g2s(st + kStageW, hsrc, hb, bar);
     ++issued;
-    if (++pc == cpu) pc = 0, pu += GW;
+    if (++pc == pc1) pc = -1, pu += GW;
   };
   if (lane == 0)
     for (int s = 0; s < kNST && pu < total; ++s) issue();
@@ -350,12 +416,12 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
     }
   };
 
-  for (int unit = gw; unit < total && !dead; unit += GW) {
-    const int slot = ord_slot(tab, unit / NT), n16 = unit % NT;
-    const bool b16 = slot >= tab.nslots || p.b16;
-    const int cpu = b16 ? cpub : cpu4;
+  for (int it = gw; it < total && !dead; it += GW) {
+    int slot, n16, c0, c1, piece;
+    decode(it, slot, n16, c0, c1, piece);
+    const bool sh = slot >= tab.nslots, b16 = sh || p.b16;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = 0; c < cpu; ++c) {
+    for (int c = c0; c < c1; ++c) {
       const uint32_t sidx = consumed % kNST;
       if (!mbar_wait(mybar + sidx, (consumed / kNST) & 1)) {
         dead = true;
@@ -371,6 +437,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_down_i4(const DecodeParams p
     }
     if (dead) break;
     while (pend) advance();
+    if (sh && S > 1 && !piece_join(acc, p.ws.part, p.ws.cnt_u, n16, piece, S, lane)) continue;  // (not the tile's last piece)
     // the pick's f32 output (not rounded: the contract's down product stays f32)
     float* yt = p.ws.ypick + ((size_t)slot * NT + n16) * 128;
     *reinterpret_cast<float2*>(yt + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
