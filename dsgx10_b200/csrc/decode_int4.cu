@@ -74,15 +74,19 @@ DSGX_DEV void i4_block_mma(float (&acc)[4], const uint8_t* a, const uint8_t* b, 
   i4_load(ra, a, lane);
   i4_load(rb, b, lane);
   const int t = lane & 3, row = (lane >> 2) & (R - 1);
+  // the eight zero-point nibbles of each strip as bytes (even groups, odd groups): 128 + u_z in both halves of a word is
+  // then one byte permutation a group
+  const uint32_t zae = ra.z & 0x0F0F0F0Fu, zao = (ra.z >> 4) & 0x0F0F0F0Fu;
+  const uint32_t zbe = rb.z & 0x0F0F0F0Fu, zbo = (rb.z >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
   for (int jj = 0; jj < 4; ++jj) {
     const uint32_t sa = sel4(ra.s, jj), sb = sel4(rb.s, jj);
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-      const int j = 2 * jj + q;
       const uint32_t ssa = __byte_perm(sa, 0, q ? 0x3232 : 0x1010), ssb = __byte_perm(sb, 0, q ? 0x3232 : 0x1010);
-      const uint32_t zza = ((ra.z >> (4 * j)) & 15u) * 0x00010001u | 0x43004300u;
-      const uint32_t zzb = ((rb.z >> (4 * j)) & 15u) * 0x00010001u | 0x43004300u;
+      const uint32_t zsel = 0x4040u + 0x0101u * jj;  // bytes (nibble byte jj, 0x43, nibble byte jj, 0x43)
+      const uint32_t zza = __byte_perm(q ? zao : zae, 0x43434343u, zsel);
+      const uint32_t zzb = __byte_perm(q ? zbo : zbe, 0x43434343u, zsel);
       const uint8_t* xp = act + ((size_t)(8 * jj + 4 * q + t) * R + row) * 32;
       const uint4 x0 = lds128(xp), x1 = lds128(xp + 16);
       const uint32_t alo = sel4(ra.v[jj], 2 * q), ahi = sel4(ra.v[jj], 2 * q + 1);
