@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   uint8_t* ring = smem + xq_bytes + kTabSmem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kWarps * kNST * kUpStage);
   uint64_t* tabbar = bars + kWarps * kNST;
+  uint64_t* xbar = tabbar + 1;  // the quantised rows: needed at the first MMA, not to request the first weights
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int GW = gridDim.x * kWarps, gw = warp * gridDim.x + blockIdx.x;
   uint8_t* myring = ring + warp * kNST * kUpStage;
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
 
   if (lane == 0)
     for (int s = 0; s < kNST; ++s) mbar_init(mybar + s, 1);
-  if (threadIdx.x == 0) mbar_init(tabbar, 1);
+  if (threadIdx.x == 0) mbar_init(tabbar, 1), mbar_init(xbar, 1);
   mbar_fence_init();
   __syncthreads();
   pdl_wait();
@@ -87,9 +88,10 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
   // kernel that wrote the table is complete)
   pdl_launch_dependents();
   if (threadIdx.x == 0) {  // the slot table and the quantised rows, made by the kernel ahead
-    mbar_expect_tx(tabbar, (uint32_t)(sizeof(SlotTab) + HB * kActBlk));
+    mbar_expect_tx(tabbar, (uint32_t)sizeof(SlotTab));
     bulk_g2s(&tab, p.ws.tab, sizeof(SlotTab), tabbar);
-    bulk_g2s(xq, p.ws.xq, HB * kActBlk, tabbar);
+    mbar_expect_tx(xbar, (uint32_t)(HB * kActBlk));
+    bulk_g2s(xq, p.ws.xq, HB * kActBlk, xbar);
   }
 
   const int upp = p.I / 8;  // units a slot
@@ -197,6 +199,7 @@ __global__ void __launch_bounds__(V::kThreads, 1) k_up_fp8(const DecodeParams p)
     };
     if (lane == 0)
       while (pi < end && issued - consumed < (uint32_t)kNST) issue();
+    if (!mbar_wait(xbar, 0)) dead = true;  // (the first weights are on their way)
     for (int it = first; it < end && !dead; it += GW) {
       const int unit = it / split, r = it % split;
       const int b0 = r * rp * kPB, b1 = min(HB, (r + 1) * rp * kPB);
