@@ -252,6 +252,9 @@ struct __align__(16) RouteSmem {
   float gsc[32];
   float S;
   uint32_t keep;
+  uint32_t pad[2];
+  uint32_t ck[128];  // the warps' best candidates: ordered keys ...
+  int ci[128];       // ... and their expert ids (8 a warp)
 };
 
 // nsplit 0: l is this thread's summed logit itself (l points at it); cp: the threads that take part (threadIdx.x < cp.nt).
@@ -351,27 +354,42 @@ DSGX_DEV void route_row_cta(const RouteParams& p, const float* __restrict__ l, i
     if (valid && !((sm.keep >> (e / gs)) & 1)) ku[e] = 0u;
     cp.sync();
   }
-  // rank of a candidate = keys above it + equal keys with a lower id; ranks 0 .. topk-1 are the picks in order
-  if (valid) {
-    const uint32_t mine = ku[e];
+  // The picks, in two levels.  Every warp takes the topk best of its 32 keys in order (a maximum over the warp, then the
+  // lowest lane that holds it: ties go to the lower id), which contain every global pick; then each of those candidates
+  // ranks itself among the candidates (keys above it + equal keys with a lower id): ranks 0 .. topk-1 are the picks in
+  // order.  A few hundred instructions on the critical path instead of every candidate against every key.
+  {
+    uint32_t k = valid ? ku[e] : 0u;
+    if (lane < 8) sm.ck[warp * 8 + lane] = 0u, sm.ci[warp * 8 + lane] = 0;
+    __syncwarp();
+#pragma unroll 1
+    for (int r = 0; r < p.topk; ++r) {
+      const uint32_t m = __reduce_max_sync(0xffffffffu, k);
+      if (m == 0u) break;  // (no candidate left in this warp)
+      const uint32_t holder = __reduce_min_sync(0xffffffffu, k == m ? (uint32_t)lane : 32u);
+      if (lane == 0) sm.ck[warp * 8 + r] = m, sm.ci[warp * 8 + r] = warp * 32 + (int)holder;
+      if ((uint32_t)lane == holder) k = 0u;
+    }
+  }
+  cp.sync();
+  const int nC = nW * 8;
+  if (e < nC) {
+    const uint32_t mine = sm.ck[e];
     if (mine) {
+      const int myid = sm.ci[e];
       int rank = 0;
-      const uint4* k4 = reinterpret_cast<const uint4*>(ku);  // four keys a load, eight loads in flight
-      const int n4 = p.E >> 2;
-#pragma unroll 8
-      for (int i = 0; i < n4; ++i) {
-        const uint4 v = k4[i];
-        const int b = 4 * i;
-        rank += (v.x > mine) || (v.x == mine && b < e);
-        rank += (v.y > mine) || (v.y == mine && b + 1 < e);
-        rank += (v.z > mine) || (v.z == mine && b + 2 < e);
-        rank += (v.w > mine) || (v.w == mine && b + 3 < e);
+      const uint4* k4 = reinterpret_cast<const uint4*>(sm.ck);
+      const int4* i4 = reinterpret_cast<const int4*>(sm.ci);
+#pragma unroll 4
+      for (int q = 0; q < (nC >> 2); ++q) {
+        const uint4 v = k4[q];
+        const int4 id = i4[q];
+        rank += (v.x > mine) || (v.x == mine && id.x < myid);
+        rank += (v.y > mine) || (v.y == mine && id.y < myid);
+        rank += (v.z > mine) || (v.z == mine && id.z < myid);
+        rank += (v.w > mine) || (v.w == mine && id.w < myid);
       }
-      for (int i = n4 << 2; i < p.E; ++i) {
-        const uint32_t v = ku[i];
-        rank += (v > mine) || (v == mine && i < e);
-      }
-      if (rank < p.topk) ids[rank] = e, picked[rank] = s;
+      if (rank < p.topk) ids[rank] = myid, picked[rank] = sm.s[myid];
     }
   }
   cp.sync();
