@@ -99,6 +99,11 @@ DSGX_DEV void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+DSGX_DEV void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+DSGX_DEV void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+DSGX_DEV void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 DSGX_DEV void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile with 128-byte rows and the 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart
@@ -263,7 +268,11 @@ DSGX_DEV void tc_mma_block(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32
 constexpr int kGCtl = 1024;
 constexpr int kGStageOut = 8 * 8192;
 
-template <int MODE>
+// kSS: the tile's scales (its rows' activation scales and the two weight-scale rows) are brought into shared memory one
+// tile ahead by the epilogue warps' own asynchronous 16-byte copies, so that a block reads them with three shared-memory
+// loads; without it every block fetches them from global memory a block ahead, and the epilogue warps (two a scheduler,
+// nothing to hide a global load behind) wait for them: 10 % of the gate/up launch.
+template <int MODE, bool kSS>
 __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant__ CUtensorMap mapA,
                                                           const __grid_constant__ CUtensorMap mapB0,
                                                           const __grid_constant__ CUtensorMap mapB1,
@@ -379,6 +388,14 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     // the scales of a block are fetched two blocks ahead of their use; those of a tile's first two blocks before the
     // tail of the tile before
     float pa[2], p0[2], p1[2];
+    // kSS: [2 buffers by tile parity][128 rows x (KB + 4) activation scales (the padding spreads the rows over the
+    // banks), then the KB + KB weight scales].  Rows are written by the two warps that own them and the weight scales by
+    // all eight, each warp all of what it reads: the copies of different warps carry the same bytes.  A warp requests tile
+    // i + 1's scales after block 2 of tile i, when every warp of the CTA is past tile i - 1 (the MMAs of block 2 waited for
+    // all their arrivals on block 0), whose buffer this is.
+    float* const scl = reinterpret_cast<float*>(outst + 8 * 2048 + 2048);
+    const int sstride = KB + 4, sbuf = 128 * sstride + 2 * KB;
+    uint32_t tcount = 0;
     auto scale_ptrs = [&](const int4& t, const float*& sap, const float*& sb0p, const float*& sb1p) {
       const int row = t.y + crow + trow;
       sap = a.sa + (size_t)(row < t.z ? row : t.y) * KB;  // (a safe row for the rows past the segment's end)
@@ -395,7 +412,21 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         pa[j] = __ldg(sap + k), p0[j] = __ldg(sb0p + k), p1[j] = __ldg(sb1p + k);
       }
     };
-    if (item < items) first_scales(ti);
+    auto stage_scales = [&](const int4& t, uint32_t buf) {
+      const float *sap, *sb0p, *sb1p;
+      scale_ptrs(t, sap, sb0p, sb1p);
+      float* dst = scl + buf * sbuf;
+      for (int c = 0; c < KB / 4; ++c) cp_async16(dst + trow * sstride + 4 * c, sap + 4 * c);
+      if (lane < KB / 2) {
+        const int which = lane >= KB / 4, c = lane - which * (KB / 4);
+        cp_async16(dst + 128 * sstride + which * KB + 4 * c, (which ? sb1p : sb0p) + 4 * c);
+      }
+      cp_async_commit();
+    };
+    if (item < items) {
+      if constexpr (kSS) stage_scales(ti, 0);
+      else first_scales(ti);
+    }
     while (item < items && !dead) {
       const int next = item + stride;
       int4 tn = make_int4(0, 0, 0, 0);
@@ -404,16 +435,27 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
       const int row = row0 + trow;
       const bool live = row < rend;
       const int srow = live ? row : ti.y;
-      const float *sap, *sb0p, *sb1p;
-      scale_ptrs(ti, sap, sb0p, sb1p);
+      const float *sap = nullptr, *sb0p = nullptr, *sb1p = nullptr;
+      if constexpr (!kSS) scale_ptrs(ti, sap, sb0p, sb1p);
+      const float* const scur = scl + (tcount & 1) * sbuf;
+      if constexpr (kSS) {  // this tile's scales, requested a tile ago, are there (this warp's copies; the others' are the same)
+        cp_async_wait_all();
+        __syncwarp();
+      }
       float2 acc0[32], acc1[32];  // columns [64 half, 64 half + 64) of the first and of the second 128, in pairs
       // one 128-k block; the tile's first block writes the accumulators (no zeroing pass)
       auto block = [&](auto first_tag, int kb) {
         constexpr bool kFirst = decltype(first_tag)::value;
         const uint32_t b = it & 1;
-        const float s0 = pa[0] * p0[0], s1 = pa[0] * p1[0];
-        pa[0] = pa[1], p0[0] = p0[1], p1[0] = p1[1];
-        if (kb + 2 < KB) pa[1] = __ldg(sap + kb + 2), p0[1] = __ldg(sb0p + kb + 2), p1[1] = __ldg(sb1p + kb + 2);
+        float s0, s1;
+        if constexpr (kSS) {
+          const float sa_k = scur[trow * sstride + kb];
+          s0 = sa_k * scur[128 * sstride + kb], s1 = sa_k * scur[128 * sstride + KB + kb];
+        } else {
+          s0 = pa[0] * p0[0], s1 = pa[0] * p1[0];
+          pa[0] = pa[1], p0[0] = p0[1], p1[0] = p1[1];
+          if (kb + 2 < KB) pa[1] = __ldg(sap + kb + 2), p0[1] = __ldg(sb0p + kb + 2), p1[1] = __ldg(sb1p + kb + 2);
+        }
         if (!mbar_wait(tfull + b, (it >> 1) & 1)) {
           dead = true;
           return;
@@ -440,9 +482,15 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         ++it;
       };
       block(std::true_type{}, 0);
-      for (int kb = 1; kb < KB && !dead; ++kb) block(std::false_type{}, kb);
+      for (int kb = 1; kb < KB && !dead; ++kb) {
+        block(std::false_type{}, kb);
+        if constexpr (kSS)
+          if (kb == 2 && next < items) stage_scales(tn, (tcount + 1) & 1);
+      }
       if (dead) break;
-      if (next < items) first_scales(tn);  // in flight during the tail
+      if constexpr (!kSS)
+        if (next < items) first_scales(tn);  // in flight during the tail
+      ++tcount;
       const bool warp_live = row0 + quarter * 32 + 31 < rend;  // all 32 rows of this warp: one TMA store; else row by row
       if (lane == 0) tma_store_wait_read();  // the staging is free of the stores of the tile before
       __syncwarp();
@@ -654,9 +702,9 @@ bool make_map_out(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols
 constexpr size_t kGemmSmem = (size_t)kGStages * kGStage + 1024 + kGCtl + kGStageOut;  // (UP uses 16 KB + 2 KB of the 64 KB)
 
 // CTA pairs (clusters of two), one pair for two SMs: as many pairs as the device keeps resident at once.
-template <int MODE>
-cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const CUtensorMap& mOut,
-                        const GemmArgs& a, cudaStream_t st) {
+template <int MODE, bool kSS>
+cudaError_t launch_gemm_ss(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const CUtensorMap& mOut,
+                           const GemmArgs& a, cudaStream_t st) {
   static int pairs[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -666,17 +714,28 @@ cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUt
   at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
   cfg.blockDim = dim3(kGThreads), cfg.dynamicSmemBytes = kGemmSmem, cfg.stream = st, cfg.attrs = at, cfg.numAttrs = 1;
   if (!pairs[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_fp8<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_fp8<MODE, kSS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
     if (e != cudaSuccess) return e;
     int n = 0;
     cfg.gridDim = dim3(sm_count() / 2 * 2);
-    e = cudaOccupancyMaxActiveClusters(&n, k_gemm_fp8<MODE>, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, k_gemm_fp8<MODE, kSS>, &cfg);
     if (e != cudaSuccess) return e;
     if (n < 1) return cudaErrorLaunchOutOfResources;
     pairs[dev & 63] = n < sm_count() / 2 ? n : sm_count() / 2;
   }
   cfg.gridDim = dim3(2 * pairs[dev & 63]);
-  return cudaLaunchKernelEx(&cfg, k_gemm_fp8<MODE>, mA, mB0, mB1, mOut, a);
+  return cudaLaunchKernelEx(&cfg, k_gemm_fp8<MODE, kSS>, mA, mB0, mB1, mOut, a);
+}
+// The scales in shared memory: gate/up launches whose K is a multiple of 512 (16-byte pieces of the scale rows) and whose
+// two buffers fit behind the 18 KB that this mode uses of the output staging; the down launch fills its staging.
+template <int MODE>
+cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const CUtensorMap& mOut,
+                        const GemmArgs& a, cudaStream_t st) {
+  const int KB = a.K / 128;
+  const size_t need = 2 * (size_t)(128 * (KB + 4) + 2 * KB) * sizeof(float);
+  if (MODE == 0 && KB % 4 == 0 && KB <= 64 && need <= (size_t)kGStageOut - 8 * 2048 - 2048)
+    return launch_gemm_ss<MODE, MODE == 0>(mA, mB0, mB1, mOut, a, st);
+  return launch_gemm_ss<MODE, false>(mA, mB0, mB1, mOut, a, st);
 }
 
 size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
