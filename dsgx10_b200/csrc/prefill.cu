@@ -288,6 +288,9 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
   uint8_t* outst = smem + kGStages * kGStage + kGCtl;          // per-warp output staging
   float* amax_x = reinterpret_cast<float*>(outst + 8 * 2048);  // UP: [2 buffers][2 halves][128 rows]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the down launch's staging fills its 64 KB: with the scales in shared memory its ring is one stage shorter and the
+  // scales take that stage's place
+  constexpr int kRing = MODE == 1 && kSS ? kGStages - 1 : kGStages;
 
   // The pair: CTA 0 (the leader) issues the MMAs of both; its `full` and `tempty` barriers collect the loads and the
   // epilogue warps of both CTAs; `empty`, `tfull` exist in both CTAs and are signalled by the leader's commits.
@@ -339,8 +342,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
         const int arow = ti.y + (int)rank * 128;
         const int brow = (a.wrow0 + ti.x) * a.N + ti.w * (MODE == 0 ? 128 : 256) + (MODE == 0 ? 0 : (int)rank * 128);
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % kGStages;
-          if (it >= kGStages && !mbar_wait(empty + s, ((it / kGStages) - 1) & 1)) {
+          const uint32_t s = it % kRing;
+          if (it >= kRing && !mbar_wait(empty + s, ((it / kRing) - 1) & 1)) {
             dead = true;
             break;
           }
@@ -362,8 +365,8 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
       int nblk = 0;
       for (int item = first; item < items; item += stride) nblk += KB;
       for (int it = 0; it < nblk; ++it) {
-        const uint32_t s = it % kGStages, b = it & 1;
-        if (!mbar_wait(full + s, (it / kGStages) & 1) || (it >= 2 && !mbar_wait(tempty + b, ((it >> 1) - 1) & 1))) {
+        const uint32_t s = it % kRing, b = it & 1;
+        if (!mbar_wait(full + s, (it / kRing) & 1) || (it >= 2 && !mbar_wait(tempty + b, ((it >> 1) - 1) & 1))) {
           dead = true;
           break;
         }
@@ -393,7 +396,7 @@ __global__ void __launch_bounds__(kGThreads, 1) k_gemm_fp8(const __grid_constant
     // all eight, each warp all of what it reads: the copies of different warps carry the same bytes.  A warp requests tile
     // i + 1's scales after block 2 of tile i, when every warp of the CTA is past tile i - 1 (the MMAs of block 2 waited for
     // all their arrivals on block 0), whose buffer this is.
-    float* const scl = reinterpret_cast<float*>(outst + 8 * 2048 + 2048);
+    float* const scl = reinterpret_cast<float*>(MODE == 0 ? outst + 8 * 2048 + 2048 : smem + (kGStages - 1) * kGStage);
     const int sstride = KB + 4, sbuf = 128 * sstride + 2 * KB;
     uint32_t tcount = 0;
     auto scale_ptrs = [&](const int4& t, const float*& sap, const float*& sb0p, const float*& sb1p) {
@@ -726,15 +729,15 @@ cudaError_t launch_gemm_ss(const CUtensorMap& mA, const CUtensorMap& mB0, const 
   cfg.gridDim = dim3(2 * pairs[dev & 63]);
   return cudaLaunchKernelEx(&cfg, k_gemm_fp8<MODE, kSS>, mA, mB0, mB1, mOut, a);
 }
-// The scales in shared memory: gate/up launches whose K is a multiple of 512 (16-byte pieces of the scale rows) and whose
-// two buffers fit behind the 18 KB that this mode uses of the output staging; the down launch fills its staging.
+// The scales in shared memory: launches whose K is a multiple of 512 (16-byte pieces of the scale rows) and whose two
+// buffers fit behind the 18 KB that the gate/up mode uses of the output staging, or in the ring stage the down mode gives up.
 template <int MODE>
 cudaError_t launch_gemm(const CUtensorMap& mA, const CUtensorMap& mB0, const CUtensorMap& mB1, const CUtensorMap& mOut,
                         const GemmArgs& a, cudaStream_t st) {
   const int KB = a.K / 128;
   const size_t need = 2 * (size_t)(128 * (KB + 4) + 2 * KB) * sizeof(float);
-  if (MODE == 0 && KB % 4 == 0 && KB <= 64 && need <= (size_t)kGStageOut - 8 * 2048 - 2048)
-    return launch_gemm_ss<MODE, MODE == 0>(mA, mB0, mB1, mOut, a, st);
+  const size_t room = MODE == 0 ? (size_t)kGStageOut - 8 * 2048 - 2048 : (size_t)kGStage;
+  if (KB % 4 == 0 && KB <= 64 && need <= room) return launch_gemm_ss<MODE, true>(mA, mB0, mB1, mOut, a, st);
   return launch_gemm_ss<MODE, false>(mA, mB0, mB1, mOut, a, st);
 }
 
