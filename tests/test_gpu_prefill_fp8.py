@@ -97,6 +97,23 @@ def test_expert_parallel_and_no_shared(orc):
         _check(orc, shp, layer, x, idx, w, yr, ys, out, shared=shared, e_lo=e_lo, e_hi=e_hi)
 
 
+@pytest.mark.parametrize("H,I", [(4096, 2048), (1280, 768)])
+def test_scale_staging_widths(orc, H, I):
+    """The grouped GEMM brings a tile's scales into shared memory when K is a multiple of 512 and they fit (hidden 4096:
+    32 k-blocks a row in the gate/up launch, 16 in the down launch), and fetches them from global memory block by block
+    otherwise (hidden 1280, intermediate 768: 10 and 6 k-blocks): sampled rows of both against the oracle, segments of
+    several tiles."""
+    from dsgx10_b200 import moe
+    T, E, topk = 700, 4, 2
+    shp, layer, x, wr, bias, idx, w = _setup(H, I, E, topk, T, seed=295 + I)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    yr, ys, out = pl.run(x, idx, w)
+    torch.cuda.synchronize()
+    assert moe.ws_status(pl.ws) == 0
+    rows = np.random.default_rng(1).choice(T, 6, replace=False)
+    _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=rows)
+
+
 def test_rounded_rows_only_and_gemm_hooks(orc):
     """Without the f32 outputs the rounded rows are the same; the bench hooks that launch one grouped GEMM alone over
     the workspace of a whole pass change nothing."""
