@@ -138,36 +138,54 @@ __global__ void __launch_bounds__(256) k_retile_fp8(const uint8_t* __restrict__ 
   *reinterpret_cast<uint4*>(out + (size_t)(8 * n8 + g) * K + 128 * j + 64 * q + 16 * t) = v;
 }
 
-// One warp a (token, 128-k block): the block quantised once (e4m3 + its f32 scale) and written to the token's row (the
-// shared expert's operand) and to the row of each of the token's picks in the (expert id, token) order of the sort
-// (pos_of), together with the picks' scales and routing weights: the routed GEMM's operand without a second pass over
-// the quantised rows.
+// A quarter warp a (token, 128-k block), a warp four blocks of one token: the block quantised once (e4m3 + its f32
+// scale; 16 values a lane) and written to the token's row (the shared expert's operand) and to the row of each of the
+// token's picks in the (expert id, token) order of the sort (pos_of), together with the picks' scales and routing
+// weights: the routed GEMM's operand without a second pass over the quantised rows.  16-byte loads and stores.
 __global__ void __launch_bounds__(256) k_quant_scatter(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                                        const int* __restrict__ pos_of, int T, int K, int topk,
                                                        uint8_t* __restrict__ q, float* __restrict__ s,
                                                        uint8_t* __restrict__ qs, float* __restrict__ ss, float* __restrict__ ws) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, l8 = lane & 7;
   const size_t gw = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int KB = K / 128;
-  if (gw >= (size_t)T * KB) return;
-  const size_t r = gw / KB;
-  const int j = (int)(gw % KB);
+  const int KB = K / 128, groups = (KB + 3) / 4;
+  if (gw >= (size_t)T * groups) return;
+  const size_t r = gw / groups;
+  const int j = 4 * (int)(gw % groups) + (lane >> 3);
+  const bool on = j < KB;
   const int mypos = lane < topk ? __ldg(pos_of + r * topk + lane) : -1;  // (-1: a pick the sort refused)
-  const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + r * K + 128 * j + 4 * lane));
-  const float v0 = bf16_bits_to_f(xv.x & 0xffffu), v1 = bf16_bits_to_f(xv.x >> 16);
-  const float v2 = bf16_bits_to_f(xv.y & 0xffffu), v3 = bf16_bits_to_f(xv.y >> 16);
-  const float sc = act_scale(warp_max(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)))));
-  const uint32_t word = quant_e4m3(v0, sc) | quant_e4m3(v1, sc) << 8 | quant_e4m3(v2, sc) << 16 | quant_e4m3(v3, sc) << 24;
-  *reinterpret_cast<uint32_t*>(q + r * K + 128 * j + 4 * lane) = word;
-  if (lane == 0) s[r * KB + j] = sc;
+  uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+  if (on) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + r * K + 128 * j + 16 * l8);
+    xa = __ldg(src), xb = __ldg(src + 1);
+  }
+  const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+  float v[16];
+  float am = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = bf16_bits_to_f(xw[i] & 0xffffu), v[2 * i + 1] = bf16_bits_to_f(xw[i] >> 16);
+    am = fmaxf(am, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  const float sc = act_scale(am);
+  uint32_t wd[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    wd[i] = quant_e4m3(v[4 * i], sc) | quant_e4m3(v[4 * i + 1], sc) << 8 | quant_e4m3(v[4 * i + 2], sc) << 16 |
+            quant_e4m3(v[4 * i + 3], sc) << 24;
+  const uint4 word = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+  if (on) {
+    *reinterpret_cast<uint4*>(q + r * K + 128 * j + 16 * l8) = word;
+    if (l8 == 0) s[r * KB + j] = sc;
+  }
   for (int jj = 0; jj < topk; ++jj) {
     const int pos = __shfl_sync(0xffffffffu, mypos, jj);
-    if (pos >= 0) *reinterpret_cast<uint32_t*>(qs + (size_t)pos * K + 128 * j + 4 * lane) = word;
+    if (on && pos >= 0) *reinterpret_cast<uint4*>(qs + (size_t)pos * K + 128 * j + 16 * l8) = word;
+    if (on && pos >= 0 && l8 == (jj & 7)) ss[(size_t)pos * KB + j] = sc;
   }
-  if (lane < topk && mypos >= 0) {
-    ss[(size_t)mypos * KB + j] = sc;
-    if (j == 0) ws[mypos] = __ldg(w + r * topk + lane);
-  }
+  if (lane < topk && mypos >= 0 && gw % groups == 0) ws[mypos] = __ldg(w + r * topk + lane);
 }
 
 // The 256-row tiles (128 rows for each CTA of a pair) of the ragged segments: tile_off [E + 1] the prefix of the tiles per
@@ -890,7 +908,7 @@ cudaError_t launch_prefill_fp8(const PrefillParams& q, cudaStream_t st) {
   if (e != cudaSuccess) return e;
   k_tile_offsets<<<1, 512, 0, st>>>(w.counts, w.offsets, E, q.e_lo, q.e_hi, w.tile_off, w.tile_info);
   {
-    const size_t warps = (size_t)T * (H / 128);
+    const size_t warps = (size_t)T * ((H / 128 + 3) / 4);
     k_quant_scatter<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(q.x, q.w, w.pos_of, T, H, topk, w.xq, w.xs, w.xq_s,
                                                                           w.xs_s, w.w_s);
   }
