@@ -16,8 +16,10 @@
  *
  * Pins: oracle/ref_shim.cu compiles the reference's own host functions (route_ref, the packers and readers, the
  * dequant contract) into oracle/_ref/, and tests/golden/ holds outputs of the reference's Python modules; the tests
- * check this file against both.  Two rules have no reference test and are "parity unpinned": group-limited expert
- * selection (restated from the published DeepSeek-V3 rule) and the softmax score's summation order.
+ * check this file against both.  Group-limited expert selection, which neither engine runs, is checked against the
+ * function altar1 docs/model.md:337-347 names as its definition (transformers' GlmMoeDsa route_tokens_to_experts; its
+ * outputs on seeded logits are in tests/golden/group_route.npz).  Two rules have no reference test and are "parity
+ * unpinned": ties between groups in that selection and the softmax score's summation order.
  */
 #include <math.h>
 #include <stdint.h>
@@ -281,8 +283,9 @@ static void row_scores(const float* l, int E, int score_fn, float* s) {
 
 /* idx [R][topk] (descending key, ties to the lower id), w [R][topk].
  * key = score + bias (bias may be NULL); with n_group > 1 only the topk_group groups with the largest
- * (sum of the group's two largest keys) stay eligible (ties to the lower group id): the DeepSeek-V3 rule, which the
- * reference implements nowhere (parity unpinned).  w = score / (sum + 1e-20) * route_scale when norm, else
+ * (sum of the group's two largest keys) stay eligible (ties to the lower group id): the rule of transformers' GlmMoeDsa
+ * router, which altar1 docs/model.md:337-347 names as the definition (the engines run it with one group; the golden
+ * fixture group_route.npz holds that function's outputs; the tie rule between groups is this file's own).  w = score / (sum + 1e-20) * route_scale when norm, else
  * score * route_scale (model.py:823-826). */
 ORC_API int orc_route(const float* logits, const float* bias, int R, int E, int topk, int score_fn, int n_group,
                       int topk_group, int norm, float route_scale, int32_t* idx, float* w) {

@@ -7,6 +7,7 @@ script is how they were made.  Nothing of the reference is copied: its modules a
   FP8:  ds41f ref/inference/model.py (Gate, Expert, MoE) over ref/torchref/kernel.py, switched to the "g128" recipe the
         benchmark configurations name: fp8_block_size 128, f32 scales (scale_fmt None), default dtype bf16.
   INT4: altar1 ref/glmref.py (int4_dequant, moe) with its module constants set to the small shape.
+  group-limited routing: transformers' GlmMoeDsa routing function, which altar1 docs/model.md names as the definition.
 
 Weights are not stored: the tests rebuild them from the same seeds (dsgx10_b200.synth, CPU generator) and check a
 checksum kept in the fixture, so a fixture only holds activations, routing and outputs (a few KB).
@@ -173,7 +174,47 @@ def norm_case(name, T, H, seed):
     print(name, "ok", y_model.shape)
 
 
+# ------------------------------------------------------------------------------------------- group-limited routing
+
+def group_route_case(name, cases):
+    """The group-limited selection (config 2's router: 8 groups, the best 4 kept).  Neither engine of the reference runs it
+    (altar-1's n_group = topk_group = 1, ds41f has no groups); altar1 docs/model.md:337-347 names the function that defines
+    it: transformers' modeling code of GlmMoeDsa, `route_tokens_to_experts` (group score = the sum of a group's two largest
+    sigmoid + bias scores, the best topk_group groups kept, top-k of the kept scores, weights from the sigmoid without the
+    bias, normalised with + 1e-20, times the scaling factor).  That function is third-party code present in this
+    container (transformers, version recorded in the fixture); its own body is run here on seeded logits, through a
+    stand-in object that carries the attributes it reads."""
+    import types
+    import transformers
+    from transformers.models.glm_moe_dsa import modeling_glm_moe_dsa as M
+    out = {"transformers_version": np.array(transformers.__version__)}
+    for ci, (E, ng, tg, topk, scale, T, seed) in enumerate(cases):
+        g = torch.Generator().manual_seed(seed)
+        logits = torch.randn(T, E, generator=g) * 1.5
+        bias = torch.randn(E, generator=g) * 0.05
+        stub = types.SimpleNamespace(n_group=ng, topk_group=tg, n_routed_experts=E, top_k=topk, norm_topk_prob=True,
+                                     routed_scaling_factor=scale, gate=types.SimpleNamespace(e_score_correction_bias=bias))
+        with torch.no_grad():
+            idx, w = M.GlmMoeDsaMoE.route_tokens_to_experts(stub, logits.clone())
+        order = idx.argsort(dim=-1)
+        idx, w = idx.gather(1, order), w.gather(1, order)
+        # how far every decision is from a tie: the kept groups against the dropped ones, the picks against the rest
+        sel = logits.sigmoid() + bias
+        gs = sel.view(T, ng, E // ng).topk(2, dim=-1)[0].sum(-1)
+        gsort = gs.sort(dim=-1, descending=True).values
+        gmargin = (gsort[:, tg - 1] - gsort[:, tg]) if tg < ng else torch.full((T,), 1.0)
+        keep = torch.zeros(T, ng).scatter_(1, gs.topk(tg, dim=-1)[1], 1.0).bool().repeat_interleave(E // ng, dim=1)
+        ssort = sel.masked_fill(~keep, 0.0).sort(dim=-1, descending=True).values
+        margin = torch.minimum(gmargin, ssort[:, topk - 1] - ssort[:, topk])
+        out.update({f"meta{ci}": np.array([E, ng, tg, topk, T], np.int64), f"scale{ci}": np.float32(scale),
+                    f"logits{ci}": logits.numpy(), f"bias{ci}": bias.numpy(), f"idx{ci}": idx.numpy().astype(np.int32),
+                    f"w{ci}": w.numpy(), f"margin{ci}": margin.numpy()})
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), n_cases=np.int64(len(cases)), **out)
+    print(name, "ok", len(cases), "cases")
+
+
 if __name__ == "__main__":
+    group_route_case("group_route", [(256, 8, 4, 8, 2.5, 64, 3401), (64, 4, 2, 6, 1.0, 48, 3402), (32, 8, 3, 4, 1.5, 40, 3403)])
     norm_case("rmsnorm", 6, 4096, 3301)
     fp8_case("fp8_sigmoid_small", 512, 256, 8, 2, 6, "sigmoid", 3101)
     fp8_case("fp8_sigmoid_top6", 1024, 512, 32, 6, 5, "sigmoid", 3102, route_scale=1.5)

@@ -109,3 +109,22 @@ def test_finalize_both_modes():
     assert torch.equal(out1, (R.to(torch.bfloat16).float() + S.to(torch.bfloat16).float()).to(torch.bfloat16))
     assert torch.equal(out_r, R.to(torch.bfloat16))
     assert not torch.equal(out0, out1)   # (the two orders do differ on some elements of this input)
+
+
+def test_group_limited_routing_against_the_golden_fixture():
+    """The CUDA router on the fixture's logits (tests/golden/group_route.npz: transformers' GlmMoeDsa routing function, the
+    definition altar1 docs/model.md names): the same experts as sets and the same weights, without the oracle in between."""
+    import os
+    _lib, moe, synth = _mods()
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "group_route.npz"))
+    for ci in range(int(g["n_cases"])):
+        E, ng, tg, topk, T = (int(v) for v in g[f"meta{ci}"])
+        scale = float(g[f"scale{ci}"])
+        shp = moe.shape(1024, 256, E, topk, n_group=ng, topk_group=tg, score_fn=0, route_scale=scale)
+        idx, w = moe.route(shp, torch.from_numpy(g[f"logits{ci}"]).cuda(), torch.from_numpy(g[f"bias{ci}"]).cuda())
+        torch.cuda.synchronize()
+        idx, w = idx.cpu().numpy(), w.cpu().numpy()
+        order = np.argsort(idx, axis=1)
+        idx, w = np.take_along_axis(idx, order, 1), np.take_along_axis(w, order, 1)
+        assert (idx == g[f"idx{ci}"]).all(), ci
+        assert np.abs(w - g[f"w{ci}"]).max() <= 4e-7 * scale, ci

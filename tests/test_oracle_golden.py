@@ -1,5 +1,6 @@
 """Pins the CPU oracle against outputs of the reference's own Python CPU modules (tests/golden/*.npz, made by
-tests/golden/make_golden.py from ds41f ref/inference/model.py + ref/torchref/kernel.py and altar1 ref/glmref.py)."""
+tests/golden/make_golden.py from ds41f ref/inference/model.py + ref/torchref/kernel.py and altar1 ref/glmref.py) and, for
+the group-limited selection that neither engine runs, against the function altar1 docs/model.md names as its definition."""
 import os
 import zlib
 
@@ -102,3 +103,21 @@ def test_rmsnorm_matches_both_references(orc):
     out, h, normed = orc.add_norm(orc.bf16_to_f32(g["x"]), g["res"], g["w"], 1e-6, 0)
     assert (out == g["x"]).all() and (h == g["h"]).all()
     close(normed, g["y_model_h"])
+
+
+def test_group_limited_routing_matches_the_named_definition(orc):
+    """Config 2's router (8 groups, the best 4 kept; and two smaller shapes).  The fixture holds the outputs of
+    transformers' GlmMoeDsa `route_tokens_to_experts` (altar1 docs/model.md:337-347 gives that function as the router's
+    definition; the engines themselves run it with one group) on seeded logits: the same experts for every row, as sets
+    (that function's top-k is unsorted), and the same weights."""
+    g = np.load(os.path.join(GOLD, "group_route.npz"))
+    for ci in range(int(g["n_cases"])):
+        E, ng, tg, topk, T = (int(v) for v in g[f"meta{ci}"])
+        scale = float(g[f"scale{ci}"])
+        idx, w = orc.route(g[f"logits{ci}"], g[f"bias{ci}"], topk, orc.SCORE_SIGMOID, n_group=ng, topk_group=tg, norm=True,
+                           route_scale=scale)
+        order = np.argsort(idx, axis=1)
+        idx, w = np.take_along_axis(idx, order, 1), np.take_along_axis(w, order, 1)
+        assert float(g[f"margin{ci}"].min()) > 1e-5          # no decision of the fixture is a near-tie
+        assert (idx == g[f"idx{ci}"]).all(), ci
+        assert np.abs(w - g[f"w{ci}"]).max() <= 4e-7 * scale, ci
