@@ -114,6 +114,34 @@ def test_scale_staging_widths(orc, H, I):
     _check(orc, shp, layer, x, idx, w, yr, ys, out, rows=rows)
 
 
+def test_pass_in_a_cuda_graph():
+    """The whole pass (cluster launches chained as programmatic dependents) captured into a CUDA graph and replayed on new
+    inputs gives the bits of the plain launches."""
+    from dsgx10_b200 import moe
+    T = 700
+    shp, layer, x, wr, bias, idx, w = _setup(1024, 512, 16, 4, T, seed=287)
+    shp2, _, x2, _, _, idx2, w2 = _setup(1024, 512, 16, 4, T, seed=288)
+    pl = moe.PrefillLayer(shp, layer.layer_w(), T)
+    out = torch.empty(T, 1024, dtype=torch.bfloat16, device="cuda")
+    want1 = pl.run(x, idx, w, yr=False, ys=False)[2].clone()
+    want2 = pl.run(x2, idx2, w2, yr=False, ys=False)[2].clone()
+    xs, ids, ws_ = x.clone(), idx.clone(), w.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        pl.run(xs, ids, ws_, yr=False, ys=False, out=out)      # (first calls of a stream: nothing lazy left for the capture)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pl.run(xs, ids, ws_, yr=False, ys=False, out=out)
+    for xi, ii, wi, want in ((x, idx, w, want1), (x2, idx2, w2, want2), (x, idx, w, want1)):
+        xs.copy_(xi), ids.copy_(ii), ws_.copy_(wi)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert moe.ws_status(pl.ws) == 0
+        assert torch.equal(out, want)
+
+
 def test_rounded_rows_only_and_gemm_hooks(orc):
     """Without the f32 outputs the rounded rows are the same; the bench hooks that launch one grouped GEMM alone over
     the workspace of a whole pass change nothing."""
