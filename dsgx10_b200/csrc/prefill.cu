@@ -5,12 +5,14 @@
 //                    and to its picks' rows in the (expert id, token) order of the sort, with the routing weights
 //   k_tile_offsets prefix of the 128-row tiles per expert segment
 //   k_gemm_fp8     C = A B^T per 256-row tile on a pair of CTAs (a cluster of two, tcgen05 cta_group::2): each CTA stages its
-//                  128 rows of A and half of B by TMA (128-byte swizzle) through a 6-stage ring, so every byte of B
+//                  128 rows of A and half of B by TMA (128-byte swizzle) through a 5-stage ring, so every byte of B
 //                  crosses into shared memory once for 256 rows; tcgen05.mma kind::f8f6f4 M 256 x N 256 x K 32 issued
 //                  by one thread of the pair's first CTA, accumulators in both CTAs' TMEM (two buffers of 256 columns);
 //                  after every 128-k block each CTA's eight epilogue warps read the block's partial sums of their 128
 //                  rows with tcgen05.ld and promote them into f32 registers with the product of the row's activation
-//                  scale and the weight block's scale, while the next block's MMAs fill the other TMEM buffer.
+//                  scale and the weight block's scale, while the next block's MMAs fill the other TMEM buffer.  The
+//                  scales of a tile are copied into shared memory a tile ahead (template parameter kSS); the launches
+//                  of a pass are programmatic dependents of one another.
 //                  UP:   B = 128 gate + 128 up channels; epilogue: bf16 rounding, SwiGLU, routing weight, bf16 h,
 //                        quantisation of the 128 channels (one scale group) to e4m3.
 //                  DOWN: B = 256 output channels; epilogue: every pick's output rounded to bf16.
