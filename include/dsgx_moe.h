@@ -324,7 +324,9 @@ int dsgx_moe_layer_decode_host(const dsgx_moe_shape* shape, const dsgx_layer_w* 
  * ysum: as dsgx_decode_cfg.ysum.
  * dsgx_prefill_prepare allocates host memory (and, for MXFP4 layers, one device word), reads the descriptors back and
  * synchronises: a load-time call.  The other calls of this header allocate nothing and do not synchronise (dsgx_ws_status and dsgx_sort_static_status copy one word
- * back and so wait for the stream's work). */
+ * back and so wait for the stream's work).  The first dsgx_moe_prefill of a process sets the grouped GEMM kernels'
+ * attributes and asks for their occupancy: make it before any stream capture; later calls only launch (clusters of two
+ * CTAs, chained as programmatic dependents) and can be captured into a CUDA graph. */
 size_t dsgx_prefill_weights_bytes(const dsgx_moe_shape* shape);
 int dsgx_prefill_prepare(const dsgx_moe_shape* shape, const dsgx_layer_w* L, void* wbuf, void* stream);
 size_t dsgx_prefill_ws_bytes(const dsgx_moe_shape* shape, int T);
